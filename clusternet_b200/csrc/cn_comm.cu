@@ -1,0 +1,246 @@
+// Communicator and the sharded product.  One process per GPU; NCCL (over NVLink / NVSwitch) takes the place of
+// the reference's CUDA-aware MPI: ClusterNet::init_MPI / shutdown_MPI (source/clusterNet.cpp:148-183,223-228)
+// and the barrier + ring all-gather + hStackN tail of dotMPI (source/clusterNet.cpp:663-694).
+//
+// NCCL is loaded at run time (dlopen of libnccl.so.2) so that the library has no link-time dependency on it and
+// single-GPU users never touch it; if the host program has already loaded an NCCL (torch does), that copy is used.
+//
+// Data placement of a column-sharded matrix is the reference's (source/clusterNet.cpp:515-516,926-931): rank r owns
+// columns [r*floor(N/G), (r+1)*floor(N/G)), the last rank also the remainder.  In the column-major layout each
+// shard is one contiguous block of the full matrix, so the local GEMM writes its slice in place and the all-gather
+// needs no packing or concatenation kernel (the reference's slice_cols / hStackN copies disappear).
+#include <dlfcn.h>
+#include <nccl.h>
+#include <string.h>
+#include "cn_gemm.h"
+
+struct NcclApi {
+    void *handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*Broadcast)(const void *, void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*GroupStart)() = nullptr;
+    ncclResult_t (*GroupEnd)() = nullptr;
+    const char *(*GetErrorString)(ncclResult_t) = nullptr;
+};
+
+static NcclApi g_nccl;
+
+static int nccl_load()
+{
+    if (g_nccl.handle) return CN_OK;
+    void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    CN_REQUIRE(h, CN_ERR_NCCL, "cannot load libnccl.so.2: %s", dlerror());
+#define CN_SYM(field, name)                                                          \
+    *(void **)(&g_nccl.field) = dlsym(h, name);                                      \
+    CN_REQUIRE(g_nccl.field, CN_ERR_NCCL, "libnccl.so.2 has no symbol %s", name)
+    CN_SYM(GetUniqueId, "ncclGetUniqueId");
+    CN_SYM(CommInitRank, "ncclCommInitRank");
+    CN_SYM(CommDestroy, "ncclCommDestroy");
+    CN_SYM(Broadcast, "ncclBroadcast");
+    CN_SYM(AllGather, "ncclAllGather");
+    CN_SYM(AllReduce, "ncclAllReduce");
+    CN_SYM(GroupStart, "ncclGroupStart");
+    CN_SYM(GroupEnd, "ncclGroupEnd");
+    CN_SYM(GetErrorString, "ncclGetErrorString");
+#undef CN_SYM
+    g_nccl.handle = h;
+    return CN_OK;
+}
+
+#define CN_NCCL(call)                                                                              \
+    do {                                                                                           \
+        ncclResult_t r__ = (call);                                                                 \
+        if (r__ != ncclSuccess) {                                                                  \
+            cn_set_error("NCCL error %d (%s) in %s", (int)r__, g_nccl.GetErrorString(r__), #call); \
+            return CN_ERR_NCCL;                                                                    \
+        }                                                                                          \
+    } while (0)
+
+struct cn_comm_state {
+    ncclComm_t comm = nullptr;
+    int rank = 0, nranks = 1;
+    float *d_scales = nullptr;   // one codec scale per rank
+};
+
+void cn_comm_state_free(cn_context *ctx)
+{
+    if (!ctx->comm) return;
+    if (ctx->comm->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(ctx->comm->comm);
+    cudaFree(ctx->comm->d_scales);
+    delete ctx->comm;
+    ctx->comm = nullptr;
+}
+
+extern "C" int cn_comm_get_unique_id(void *id128)
+{
+    CN_REQUIRE(id128, CN_ERR_ARG, "cn_comm_get_unique_id: null buffer");
+    int st = nccl_load();
+    if (st != CN_OK) return st;
+    static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId is expected to be 128 bytes");
+    ncclUniqueId id;
+    CN_NCCL(g_nccl.GetUniqueId(&id));
+    memcpy(id128, &id, sizeof(id));
+    return CN_OK;
+}
+
+extern "C" int cn_comm_init_rank(cn_context *ctx, const void *id128, int rank, int nranks)
+{
+    CN_REQUIRE(ctx && id128, CN_ERR_ARG, "cn_comm_init_rank: null argument");
+    CN_REQUIRE(nranks >= 1 && rank >= 0 && rank < nranks, CN_ERR_ARG, "cn_comm_init_rank: rank %d of %d", rank, nranks);
+    CN_REQUIRE(!ctx->comm, CN_ERR_ARG, "cn_comm_init_rank: communicator already initialised");
+    int st = nccl_load();
+    if (st != CN_OK) return st;
+    CN_CUDA(cudaSetDevice(ctx->device));
+    cn_comm_state *c = new cn_comm_state();
+    c->rank = rank;
+    c->nranks = nranks;
+    ncclUniqueId id;
+    memcpy(&id, id128, sizeof(id));
+    ncclResult_t r = g_nccl.CommInitRank(&c->comm, nranks, id, rank);
+    if (r != ncclSuccess) {
+        cn_set_error("NCCL error %d (%s) in ncclCommInitRank", (int)r, g_nccl.GetErrorString(r));
+        delete c;
+        return CN_ERR_NCCL;
+    }
+    cudaError_t e = cudaMalloc(&c->d_scales, sizeof(float) * (size_t)nranks);
+    if (e != cudaSuccess) {
+        g_nccl.CommDestroy(c->comm);
+        delete c;
+        return cn_cuda_fail(e, "cn_comm_init_rank");
+    }
+    ctx->comm = c;
+    return CN_OK;
+}
+
+extern "C" int cn_comm_destroy(cn_context *ctx)
+{
+    CN_REQUIRE(ctx, CN_ERR_ARG, "cn_comm_destroy: null context");
+    cn_comm_state_free(ctx);
+    return CN_OK;
+}
+
+extern "C" int cn_comm_rank(const cn_context *ctx) { return (ctx && ctx->comm) ? ctx->comm->rank : 0; }
+extern "C" int cn_comm_size(const cn_context *ctx) { return (ctx && ctx->comm) ? ctx->comm->nranks : 1; }
+
+extern "C" int cn_shard_cols(int64_t n_total, int rank, int nranks, int64_t *col_start, int64_t *col_count)
+{
+    CN_REQUIRE(n_total >= 0 && nranks >= 1 && rank >= 0 && rank < nranks, CN_ERR_ARG, "cn_shard_cols: bad argument");
+    const int64_t split = n_total / nranks;
+    if (col_start) *col_start = split * rank;
+    if (col_count) *col_count = (rank == nranks - 1) ? n_total - split * (nranks - 1) : split;
+    return CN_OK;
+}
+
+extern "C" int cn_bcast_f32(cn_context *ctx, float *d_buf, int64_t n, int root, void *stream)
+{
+    CN_REQUIRE(ctx && n >= 0 && (n == 0 || d_buf), CN_ERR_ARG, "cn_bcast_f32: bad argument");
+    if (!ctx->comm || ctx->comm->nranks == 1 || n == 0) return CN_OK;
+    CN_REQUIRE(root >= 0 && root < ctx->comm->nranks, CN_ERR_ARG, "cn_bcast_f32: root %d", root);
+    CN_NCCL(g_nccl.Broadcast(d_buf, d_buf, (size_t)n, ncclFloat, root, ctx->comm->comm, cn_stream(stream)));
+    return CN_OK;
+}
+
+// All-gather of contiguous per-rank blocks of `elem_size`-byte elements; blocks are equal except possibly the last.
+static int allgather_blocks(cn_context *ctx, void *base, int64_t M, int64_t n_total, ncclDataType_t dt, size_t elem_size, cudaStream_t s)
+{
+    cn_comm_state *c = ctx->comm;
+    if (!c || c->nranks == 1) return CN_OK;
+    const int G = c->nranks;
+    const int64_t split = n_total / G;
+    if (n_total % G == 0) {
+        const size_t count = (size_t)M * split;
+        if (count == 0) return CN_OK;
+        CN_NCCL(g_nccl.AllGather((const uint8_t *)base + (size_t)c->rank * count * elem_size, base, count, dt, c->comm, s));
+        return CN_OK;
+    }
+    // uneven shards: one broadcast per owner, fused into a single NCCL group
+    CN_NCCL(g_nccl.GroupStart());
+    for (int r = 0; r < G; ++r) {
+        int64_t start, cnt;
+        cn_shard_cols(n_total, r, G, &start, &cnt);
+        if (cnt == 0) continue;
+        void *blk = (uint8_t *)base + (size_t)M * start * elem_size;
+        ncclResult_t res = g_nccl.Broadcast(blk, blk, (size_t)M * cnt, dt, r, c->comm, s);
+        if (res != ncclSuccess) {
+            g_nccl.GroupEnd();
+            cn_set_error("NCCL error %d (%s) in ncclBroadcast", (int)res, g_nccl.GetErrorString(res));
+            return CN_ERR_NCCL;
+        }
+    }
+    CN_NCCL(g_nccl.GroupEnd());
+    return CN_OK;
+}
+
+extern "C" int cn_allgather_cols_f32(cn_context *ctx, float *d_C, int64_t M, int64_t n_total, void *stream)
+{
+    CN_REQUIRE(ctx && M >= 0 && n_total >= 0 && (M * n_total == 0 || d_C), CN_ERR_ARG, "cn_allgather_cols_f32: bad argument");
+    return allgather_blocks(ctx, d_C, M, n_total, ncclFloat, sizeof(float), cn_stream(stream));
+}
+
+extern "C" int cn_allgather_cols_u8(cn_context *ctx, uint8_t *d_codes, int64_t M, int64_t n_total, void *stream)
+{
+    CN_REQUIRE(ctx && M >= 0 && n_total >= 0 && (M * n_total == 0 || d_codes), CN_ERR_ARG, "cn_allgather_cols_u8: bad argument");
+    return allgather_blocks(ctx, d_codes, M, n_total, ncclUint8, 1, cn_stream(stream));
+}
+
+extern "C" int cn_allgather_scalar_f32(cn_context *ctx, float *d_vals, void *stream)
+{
+    CN_REQUIRE(ctx && d_vals, CN_ERR_ARG, "cn_allgather_scalar_f32: bad argument");
+    if (!ctx->comm || ctx->comm->nranks == 1) return CN_OK;
+    CN_NCCL(g_nccl.AllGather(d_vals + ctx->comm->rank, d_vals, 1, ncclFloat, ctx->comm->comm, cn_stream(stream)));
+    return CN_OK;
+}
+
+extern "C" int cn_allreduce_sum_f32(cn_context *ctx, float *d_buf, int64_t n, void *stream)
+{
+    CN_REQUIRE(ctx && n >= 0 && (n == 0 || d_buf), CN_ERR_ARG, "cn_allreduce_sum_f32: bad argument");
+    if (!ctx->comm || ctx->comm->nranks == 1 || n == 0) return CN_OK;
+    CN_NCCL(g_nccl.AllReduce(d_buf, d_buf, (size_t)n, ncclFloat, ncclSum, ctx->comm->comm, cn_stream(stream)));
+    return CN_OK;
+}
+
+extern "C" int cn_dotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_total, const float *d_A, const float *d_Wshard,
+                             float *d_C, const cn_epilogue *epi, int mode, int exchange, void *stream)
+{
+    CN_REQUIRE(ctx, CN_ERR_ARG, "cn_dotmpi_f32: null context");
+    CN_REQUIRE(M >= 0 && K >= 0 && n_total >= 0, CN_ERR_SHAPE, "cn_dotmpi_f32: negative dimension");
+    CN_REQUIRE(exchange == 0 || exchange == 1, CN_ERR_ARG, "cn_dotmpi_f32: exchange must be 0 (fp32) or 1 (8-bit)");
+    CN_REQUIRE(!epi || epi->maxout_level <= 1, CN_ERR_UNSUPPORTED, "cn_dotmpi_f32: maxout is not available on the sharded product");
+    const int G = ctx->comm ? ctx->comm->nranks : 1, rank = ctx->comm ? ctx->comm->rank : 0;
+    int64_t start, cnt;
+    cn_shard_cols(n_total, rank, G, &start, &cnt);
+    // local product straight into this rank's window of the full C
+    cn_epilogue local;
+    local.bias = (epi && epi->bias) ? epi->bias + start : nullptr;
+    local.activation = epi ? epi->activation : CN_ACT_LINEAR;
+    local.maxout_level = 0;
+    local.argmax_out = nullptr;
+    float *slice = d_C + (size_t)M * start;
+    int st = cn_gemm_f32(ctx, 0, 0, M, cnt, K, d_A, M, d_Wshard, K, slice, M, &local, mode, stream);
+    if (st != CN_OK || G == 1) return st;
+    if (exchange == 0) return cn_allgather_cols_f32(ctx, d_C, M, n_total, stream);
+
+    // 8-bit exchange: scale = absmax of the own slice, codes gathered next to the per-rank scales, peers' slices
+    // decoded on arrival; the own slice keeps its fp32 values (as the reference's cache[MYRANK] does).
+    void *buf = nullptr;
+    st = cn_gemm_scratch(ctx, CN_GEMM_SLOT_EXCHANGE, (size_t)M * n_total, &buf);
+    if (st != CN_OK) return st;
+    uint8_t *codes = (uint8_t *)buf;
+    float *scales = ctx->comm->d_scales;
+    if ((st = cn_absmax_f32(ctx, slice, M * cnt, scales + rank, stream)) != CN_OK) return st;
+    if ((st = cn_compress_8bit_dp(ctx, slice, scales + rank, M * cnt, codes + (size_t)M * start, stream)) != CN_OK) return st;
+    if ((st = cn_allgather_scalar_f32(ctx, scales, stream)) != CN_OK) return st;
+    if ((st = cn_allgather_cols_u8(ctx, codes, M, n_total, stream)) != CN_OK) return st;
+    for (int r = 0; r < G; ++r) {
+        if (r == rank) continue;
+        int64_t s0, c0;
+        cn_shard_cols(n_total, r, G, &s0, &c0);
+        if ((st = cn_decompress_8bit_dp(ctx, codes + (size_t)M * s0, scales + r, M * c0, d_C + (size_t)M * s0, stream)) != CN_OK) return st;
+    }
+    return CN_OK;
+}

@@ -1,0 +1,662 @@
+// Tensor-core GEMM for sm_100a: TMA -> shared memory -> (converter warps) -> TMEM -> tcgen05.mma -> TMEM
+// accumulators -> tcgen05.ld -> fused bias / activation / maxout -> global stores.
+//
+// Problem: C (M x N) = A (M x K) . W (K x N), everything fp32 column-major (the reference's device layout),
+// which is the product ClusterNet::dot hands to cublasSgemm (source/clusterNet.cpp:459-461).
+//
+// Mapping.  A column-major W has its K index contiguous for a fixed column n, i.e. it is a K-major operand with
+// N "rows".  The kernel therefore computes the transposed tile D[n, m] = sum_k W[k, n] * A[m, k]:
+//   * the tcgen05 "A" operand (128 rows = 128 columns n of W) is read from TENSOR MEMORY.  W is streamed from
+//     HBM exactly once as raw fp32 by TMA; four converter warps read each 128 x 32 tile from shared memory,
+//     split every value into TF32 hi = rna(x) and lo = rna(x - hi) in registers and write both planes to TMEM
+//     with tcgen05.st.  No shared-memory traffic is spent on the split and the raw weights never need a
+//     second copy in HBM;
+//   * the tcgen05 "B" operand (UMMA N = 128 rows m of the activations) is read from shared memory.  The
+//     activations are small next to W (M = 128 in the reference's layers), so a pre-pass re-lays them K-major
+//     and pre-split into hi / lo planes once per call; every CTA then pulls 128 x 32 tiles of both planes by TMA;
+//   * three products per k-step give fp32-level accuracy: D += Whi.Ahi + Wlo.Ahi + Whi.Alo ("3xTF32").
+//     CN_GEMM_TF32 issues only the first.
+//   * the accumulator tile lives in TMEM with lane = n and column = m, so in the epilogue one thread owns one
+//     output column n and 32 consecutive rows m: the bias is a per-thread scalar, the stores are contiguous
+//     128-byte runs of the column-major C, and maxout over L consecutive columns is a shuffle across L lanes.
+//
+// Work decomposition.  One CTA per (m tile of 128, group of NT n tiles of 128, K split).  Skinny products have
+// few tiles, so K is split across CTAs; each split leaves its partial tile in scratch, and the CTA that draws
+// the last ticket of a tile adds the partials in split order (a fixed order, so results are reproducible) and
+// runs the epilogue.  Launch order is split-major, which makes the CTAs resident at one time walk the same K
+// range of the activations and share it through L2.
+//
+// Every wait on an mbarrier is bounded by a clock limit; a wait that runs out sets a status word that the host
+// reads back as CN_ERR_TIMEOUT, lets the other roles drain, frees the tensor memory and returns.
+#include <cuda.h>
+#include <stdlib.h>
+#include "cn_epilogue.cuh"
+#include "cn_gemm.h"
+
+#define TC_THREADS 192
+#define TC_BM 128          // activation rows per CTA = UMMA N
+#define TC_BN 128          // W columns per tile       = UMMA M
+#define TC_BK 32           // fp32 per 128-byte swizzle row
+#define TC_TILE_BYTES (128 * 128)
+#define TC_WAIT_LIMIT (6000000000LL)   // clock cycles (~3 s)
+
+template <int NT>
+struct TcCfg {
+    static constexpr int SMEM_STAGES = NT == 1 ? 4 : 3;
+    static constexpr int TMEM_STAGES = NT == 1 ? 4 : 2;
+    static constexpr int STAGE_BYTES = (NT + 2) * TC_TILE_BYTES;
+    static constexpr int ACC_COL = 0;                 // NT accumulators of 128 columns
+    static constexpr int A_COL = NT * TC_BM;          // then TMEM_STAGES x NT x (32 hi + 32 lo) columns
+    static constexpr int A_STAGE_COLS = NT * 64;
+    static constexpr int SMEM_BYTES = SMEM_STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct TcParams {
+    int64_t M, N, K;
+    float *C;
+    int64_t ldc;
+    const float *bias;
+    int act;
+    int maxout_level;
+    float *argmax;
+    int64_t tiles_n;        // groups of NT*128 columns
+    int64_t tiles_m;
+    int splits;
+    int kb_per_split;       // K blocks (of 32) per split
+    int kb_total;
+    float *partials;        // [tile][split][NT][128 m][128 n]
+    unsigned int *tickets;  // one per tile, self-resetting
+    unsigned int *status;
+};
+
+// ---------------------------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done;
+}
+// Bounded wait.  Returns false when the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned int *status, unsigned int code)
+{
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try(bar, parity)) return true;
+        if ((it & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > TC_WAIT_LIMIT) {
+                *abort_flag = 1;
+                atomicMax(status, code);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t x, int32_t y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// D[tmem] (+)= A[tmem] * B[smem desc]; A: 128 lanes x 8 columns of TF32, B: 128 x 8 K-major TF32 tile
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+#define TC_R32(a) \
+    a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], a[8], a[9], a[10], a[11], a[12], a[13], a[14], a[15], a[16], a[17], \
+    a[18], a[19], a[20], a[21], a[22], a[23], a[24], a[25], a[26], a[27], a[28], a[29], a[30], a[31]
+
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, "
+        "%24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, "
+        "%25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t to_tf32(float x)
+{
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (32 fp32) with the 128-byte
+// swizzle TMA applies: 8-row groups are 1024 bytes apart (stride byte offset), the leading byte offset is
+// unused for swizzled K-major layouts, version field 1 (sm_100), layout type 2 (128-byte swizzle).
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// kind::tf32 instruction descriptor: D fp32 (bits 4-5 = 1), A and B TF32 (format 2 at bits 7-9 and 10-12),
+// both operands K-major (bits 15, 16 = 0), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+__host__ __device__ constexpr uint32_t make_idesc_tf32(int m, int n)
+{
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// ------------------------------------------------------------------------------------------ activation pre-pass
+// A (M x K, column-major, lda) -> planes hi, lo : [M][Kpad] with k contiguous; k in [K, Kpad) is zero.
+__global__ void __launch_bounds__(256)
+cn_act_split_kernel(const float *__restrict__ A, int64_t lda, int64_t M, int64_t K, int64_t Kpad,
+                    float *__restrict__ hi, float *__restrict__ lo, int64_t tiles_k)
+{
+    __shared__ float tile[32][33];
+    const int64_t tm = blockIdx.x / tiles_k, tk = blockIdx.x % tiles_k;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int64_t m_in = tm * 32 + tx;
+#pragma unroll
+    for (int j = ty; j < 32; j += 8) {
+        const int64_t k = tk * 32 + j;
+        tile[j][tx] = (m_in < M && k < K) ? A[m_in + k * lda] : 0.0f;
+    }
+    __syncthreads();
+    const int64_t k_out = tk * 32 + tx;
+#pragma unroll
+    for (int j = ty; j < 32; j += 8) {
+        const int64_t m = tm * 32 + j;
+        if (m < M && k_out < Kpad) {
+            const float x = tile[tx][j];
+            const uint32_t h = to_tf32(x);
+            hi[m * Kpad + k_out] = __uint_as_float(h);
+            if (lo) lo[m * Kpad + k_out] = __uint_as_float(to_tf32(x - __uint_as_float(h)));
+        }
+    }
+}
+
+// -------------------------------------------------------------------------------------------------- main kernel
+template <int NT, bool MODE3X>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_ahi,
+                  const __grid_constant__ CUtensorMap tm_alo, const TcParams p)
+{
+    using Cfg = TcCfg<NT>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    // barriers and small words sit after the stage buffers
+    const uint32_t bar_base = smem_base + Cfg::SMEM_STAGES * Cfg::STAGE_BYTES;
+    uint8_t *bar_gen = smem_gen + Cfg::SMEM_STAGES * Cfg::STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::SMEM_STAGES + s); };
+    auto tfull_bar = [&](int t) { return bar_base + 8u * (2 * Cfg::SMEM_STAGES + t); };
+    auto tempty_bar = [&](int t) { return bar_base + 8u * (2 * Cfg::SMEM_STAGES + Cfg::TMEM_STAGES + t); };
+    const uint32_t acc_bar = bar_base + 8u * (2 * Cfg::SMEM_STAGES + 2 * Cfg::TMEM_STAGES);
+    volatile uint32_t *tmem_holder = reinterpret_cast<volatile uint32_t *>(bar_gen + 192);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(bar_gen + 196);
+    volatile int *last_flag = reinterpret_cast<volatile int *>(bar_gen + 200);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // unit decode: split-major launch order
+    const int64_t tiles = p.tiles_n * p.tiles_m;
+    const int split = (int)(blockIdx.x / tiles);
+    const int64_t tile_id = blockIdx.x % tiles;
+    const int64_t tile_n = tile_id % p.tiles_n, tile_m = tile_id / p.tiles_n;
+    const int64_t n0 = tile_n * (NT * TC_BN), m0 = tile_m * TC_BM;
+    const int kb_begin = split * p.kb_per_split;
+    int kb_end = kb_begin + p.kb_per_split;
+    if (kb_end > p.kb_total) kb_end = p.kb_total;
+    const int num_kb = kb_end - kb_begin;   // >= 1 by construction on the host
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::SMEM_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int t = 0; t < Cfg::TMEM_STAGES; ++t) { mbar_init(tfull_bar(t), 128); mbar_init(tempty_bar(t), 1); }
+        mbar_init(acc_bar, 1);
+        *abort_flag = 0;
+        *last_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {   // this warp owns the tensor-memory allocation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)tmem_holder)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < num_kb; ++i) {
+                const int s = i % Cfg::SMEM_STAGES;
+                const uint32_t ph = (uint32_t)(i / Cfg::SMEM_STAGES) & 1u;
+                if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, 1u)) break;
+                const uint32_t stage = smem_base + s * Cfg::STAGE_BYTES;
+                mbar_expect_tx(full_bar(s), (uint32_t)((NT + (MODE3X ? 2 : 1)) * TC_TILE_BYTES));
+                const int32_t kx = (kb_begin + i) * TC_BK;
+#pragma unroll
+                for (int t = 0; t < NT; ++t)
+                    tma_load_2d(stage + t * TC_TILE_BYTES, &tm_w, full_bar(s), kx, (int32_t)(n0 + t * TC_BN));
+                tma_load_2d(stage + NT * TC_TILE_BYTES, &tm_ahi, full_bar(s), kx, (int32_t)m0);
+                if (MODE3X) tma_load_2d(stage + (NT + 1) * TC_TILE_BYTES, &tm_alo, full_bar(s), kx, (int32_t)m0);
+                issued = i + 1;
+            }
+            if (*abort_flag) {
+                // give copies that are still in flight a bounded chance to land before the CTA exits
+                for (int i = issued > Cfg::SMEM_STAGES ? issued - Cfg::SMEM_STAGES : 0; i < issued; ++i) {
+                    const int s = i % Cfg::SMEM_STAGES;
+                    const uint32_t ph = (uint32_t)(i / Cfg::SMEM_STAGES) & 1u;
+                    const long long t0 = clock64();
+                    while (!mbar_try(full_bar(s), ph) && clock64() - t0 < 20000000LL) {}
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_tf32(TC_BN, TC_BM);
+            bool ok = true;
+            for (int i = 0; i < num_kb && ok; ++i) {
+                const int s = i % Cfg::SMEM_STAGES, t = i % Cfg::TMEM_STAGES;
+                const uint32_t ph = (uint32_t)(i / Cfg::SMEM_STAGES) & 1u, tph = (uint32_t)(i / Cfg::TMEM_STAGES) & 1u;
+                ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 2u) && mbar_wait(tfull_bar(t), tph, abort_flag, p.status, 3u);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t stage = smem_base + s * Cfg::STAGE_BYTES;
+                const uint64_t bhi = make_kmajor_sw128_desc(stage + NT * TC_TILE_BYTES);
+                const uint64_t blo = make_kmajor_sw128_desc(stage + (NT + 1) * TC_TILE_BYTES);
+#pragma unroll
+                for (int w = 0; w < NT; ++w) {
+                    const uint32_t acc = tmem_base + Cfg::ACC_COL + w * TC_BM;
+                    const uint32_t a_hi = tmem_base + Cfg::A_COL + t * Cfg::A_STAGE_COLS + w * 64;
+                    const uint32_t a_lo = a_hi + 32;
+#pragma unroll
+                    for (int j = 0; j < TC_BK / 8; ++j) {
+                        // 8 TF32 per k-step: 8 TMEM columns of A, 32 bytes (descriptor units of 16 B) of B
+                        tc_mma_ts(acc, a_hi + j * 8, bhi + (uint64_t)(j * 2), idesc, (i > 0 || j > 0) ? 1u : 0u);
+                        if (MODE3X) {
+                            tc_mma_ts(acc, a_lo + j * 8, bhi + (uint64_t)(j * 2), idesc, 1u);
+                            tc_mma_ts(acc, a_hi + j * 8, blo + (uint64_t)(j * 2), idesc, 1u);
+                        }
+                    }
+                }
+                tc_commit(empty_bar(s));    // shared-memory stage may be refilled once these MMAs retire
+                tc_commit(tempty_bar(t));   // and the TMEM operand stage rewritten
+            }
+            if (ok) tc_commit(acc_bar);
+        }
+        __syncwarp();
+    } else {
+        // ---------------------------------------------------------------- converter warps (2..5), then epilogue
+        const int q = warp & 3;                       // TMEM lane quarter this warp may touch
+        const int row = q * 32 + lane;                // row of the W tile = TMEM lane
+        const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+        bool ok = true;
+        for (int i = 0; i < num_kb && ok; ++i) {
+            const int s = i % Cfg::SMEM_STAGES, t = i % Cfg::TMEM_STAGES;
+            const uint32_t ph = (uint32_t)(i / Cfg::SMEM_STAGES) & 1u, tph = (uint32_t)(i / Cfg::TMEM_STAGES) & 1u;
+            ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 4u) && mbar_wait(tempty_bar(t), tph ^ 1u, abort_flag, p.status, 5u);
+            ok = __all_sync(0xffffffffu, ok);   // the tcgen05 stores below need the whole warp
+            if (!ok) break;
+            tc_fence_after();
+            const uint8_t *stage = smem_gen + s * Cfg::STAGE_BYTES;
+#pragma unroll
+            for (int w = 0; w < NT; ++w) {
+                const uint8_t *rowp = stage + w * TC_TILE_BYTES + row * 128;
+                uint32_t hi[32], lo[32];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    // 16-byte chunk c of row r sits at chunk position c ^ (r & 7) under the 128-byte swizzle
+                    const float4 v = *reinterpret_cast<const float4 *>(rowp + ((c ^ (row & 7)) << 4));
+                    const float x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const uint32_t h = to_tf32(x[e]);
+                        hi[c * 4 + e] = h;
+                        if (MODE3X) lo[c * 4 + e] = to_tf32(x[e] - __uint_as_float(h));
+                    }
+                }
+                const uint32_t a_hi = tmem_base + lane_addr + Cfg::A_COL + t * Cfg::A_STAGE_COLS + w * 64;
+                tc_st32(a_hi, hi);
+                if (MODE3X) tc_st32(a_hi + 32, lo);
+            }
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(tfull_bar(t));
+        }
+
+        // ------------------------------------------------------------ epilogue (same 128 threads)
+        if (ok) ok = mbar_wait(acc_bar, 0u, abort_flag, p.status, 6u);
+        {   // all 128 epilogue threads go on together or not at all
+            uint32_t all_ok;
+            asm volatile(
+                "{\n\t.reg .pred pi, po;\n\t"
+                "setp.ne.u32 pi, %1, 0;\n\t"
+                "bar.red.and.pred po, 1, 128, pi;\n\t"
+                "selp.u32 %0, 1, 0, po;\n\t}"
+                : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
+            ok = all_ok != 0;
+        }
+        if (ok) {
+            tc_fence_after();
+            const int et = threadIdx.x - 64;           // 0..127
+            const int64_t tile_lin = tile_id;
+            const size_t tile_elems = (size_t)NT * TC_BM * TC_BN;
+            bool do_final = true;
+            if (p.splits > 1) {
+                float *P = p.partials + ((size_t)tile_lin * p.splits + split) * tile_elems;
+#pragma unroll 1
+                for (int w = 0; w < NT; ++w) {
+#pragma unroll 1
+                    for (int c = 0; c < TC_BM / 32; ++c) {
+                        uint32_t r[32];
+                        tc_ld32(tmem_base + lane_addr + Cfg::ACC_COL + w * TC_BM + c * 32, r);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            P[((size_t)w * TC_BM + c * 32 + i) * TC_BN + row] = __uint_as_float(r[i]);
+                    }
+                }
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (et == 0) {
+                    const unsigned int prev = atomicAdd(p.tickets + tile_lin, 1u);
+                    const int last = prev == (unsigned int)(p.splits - 1);
+                    if (last) p.tickets[tile_lin] = 0u;   // ready for the next launch
+                    *last_flag = last;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                do_final = *last_flag != 0;
+                if (do_final) __threadfence();
+            }
+            if (do_final) {
+                const int L = p.maxout_level;
+#pragma unroll 1
+                for (int w = 0; w < NT; ++w) {
+                    const int64_t n = n0 + w * TC_BN + row;
+                    const float bias = (p.bias && n < p.N) ? p.bias[n] : 0.0f;
+#pragma unroll 1
+                    for (int c = 0; c < TC_BM / 32; ++c) {
+                        float v[32];
+                        if (p.splits > 1) {
+                            // fixed summation order over the splits: reproducible whichever CTA comes last
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+                            for (int sp = 0; sp < p.splits; ++sp) {
+                                const float *P = p.partials + ((size_t)tile_lin * p.splits + sp) * tile_elems;
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) v[i] += __ldcg(P + ((size_t)w * TC_BM + c * 32 + i) * TC_BN + row);
+                            }
+                        } else {
+                            uint32_t r[32];
+                            tc_ld32(tmem_base + lane_addr + Cfg::ACC_COL + w * TC_BM + c * 32, r);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = cn_apply_activation(p.bias ? v[i] + bias : v[i], p.act);
+                        const int64_t mbase = m0 + c * 32;
+                        if (L <= 1) {
+                            if (n < p.N) {
+                                float *dst = p.C + n * p.ldc + mbase;
+                                if (mbase + 32 <= p.M && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+#pragma unroll
+                                    for (int i = 0; i < 32; i += 4)
+                                        *reinterpret_cast<float4 *>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                                } else {
+#pragma unroll
+                                    for (int i = 0; i < 32; ++i)
+                                        if (mbase + i < p.M) dst[i] = v[i];
+                                }
+                            }
+                        } else {
+                            // maxout over L consecutive columns = L adjacent lanes (L is a power of two <= 32).
+                            // Same comparison tree as the reference's 32-slot reduction: at offsets L/2 .. 1 slot t
+                            // takes slot t+offset when strictly smaller; larger offsets only meet -FLT_MAX padding.
+                            const int tl = lane & (L - 1);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                float val = v[i], idx = (float)n;
+                                for (int off = L >> 1; off > 0; off >>= 1) {
+                                    const float ov = __shfl_down_sync(0xffffffffu, val, off, L);
+                                    const float oi = __shfl_down_sync(0xffffffffu, idx, off, L);
+                                    if (tl < off && val < ov) { val = ov; idx = oi; }
+                                }
+                                if (tl == 0 && n < p.N && mbase + i < p.M) {
+                                    const int64_t g = n / L;
+                                    p.C[g * p.ldc + mbase + i] = val;
+                                    if (p.argmax) p.argmax[g * p.ldc + mbase + i] = idx;
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int get_encode_fn(cn_context *ctx, EncodeTiledFn *out)
+{
+    if (!ctx->gemm) ctx->gemm = new cn_gemm_workspace();
+    if (!ctx->gemm->encode_fn) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        CN_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        CN_REQUIRE(fn && qres == cudaDriverEntryPointSuccess, CN_ERR_CUDA, "cuTensorMapEncodeTiled is not available in this driver");
+        ctx->gemm->encode_fn = fn;
+    }
+    *out = (EncodeTiledFn)ctx->gemm->encode_fn;
+    return CN_OK;
+}
+
+// 2-D fp32 map over a K-major array: inner extent `inner` (k), outer extent `outer` (rows), row pitch in elements.
+static int make_map(EncodeTiledFn enc, CUtensorMap *map, const float *base, int64_t inner, int64_t outer, int64_t pitch)
+{
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[1] = {(cuuint64_t)pitch * sizeof(float)};
+    cuuint32_t box[2] = {TC_BK, 128};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CN_REQUIRE(r == CUDA_SUCCESS, CN_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (inner %lld outer %lld pitch %lld)", (int)r,
+               (long long)inner, (long long)outer, (long long)pitch);
+    return CN_OK;
+}
+
+bool cn_gemm_tc_can_fuse_maxout(int L) { return L == 2 || L == 4 || L == 8 || L == 16 || L == 32; }
+
+bool cn_gemm_tc_supported(cn_context *, int transA, int transB, int64_t M, int64_t N, int64_t K, const float *,
+                          int64_t, const float *B, int64_t ldb, const float *, int64_t)
+{
+    if (transA || transB) return false;
+    if (M < 1 || N < 16 || K < 32) return false;
+    if ((ldb & 3) != 0 || (reinterpret_cast<uintptr_t>(B) & 15u) != 0) return false;   // TMA: 16-byte pitch and base
+    if (K >= (1LL << 31) - 64 || N >= (1LL << 31) - 256 || M >= (1LL << 31) - 256) return false;   // TMA coordinates are 32-bit
+    return true;
+}
+
+static int pick_splits(int64_t tiles, int kb_total, int sm_count)
+{
+    if (tiles >= 2 * (int64_t)sm_count) return 1;
+    int best = 1;
+    double best_score = -1.0;
+    for (int s = 1; s <= 32; ++s) {
+        if (kb_total / s < 8) break;   // keep at least 8 K blocks (256 k) per split
+        const int64_t units = tiles * s;
+        const int64_t waves = (units + sm_count - 1) / sm_count;
+        const double eff = (double)units / (double)(waves * sm_count);
+        const double score = eff - 0.004 * s;   // prefer fewer splits when the fill is about equal
+        if (score > best_score) { best_score = score; best = s; }
+    }
+    return best;
+}
+
+template <int NT, bool MODE3X>
+static int launch_cfg(const CUtensorMap &mw, const CUtensorMap &mhi, const CUtensorMap &mlo, const TcParams &prm, int64_t grid, cudaStream_t s)
+{
+    CN_CUDA(cudaFuncSetAttribute(cn_gemm_tc_kernel<NT, MODE3X>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<NT>::SMEM_BYTES));
+    cn_gemm_tc_kernel<NT, MODE3X><<<(unsigned)grid, TC_THREADS, TcCfg<NT>::SMEM_BYTES, s>>>(mw, mhi, mlo, prm);
+    CN_CUDA(cudaGetLastError());
+    return CN_OK;
+}
+
+int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const float *A, int64_t lda, const float *B,
+                      int64_t ldb, float *C, int64_t ldc, const cn_epilogue *epi, int mode, cudaStream_t s)
+{
+    EncodeTiledFn enc = nullptr;
+    int st = get_encode_fn(ctx, &enc);
+    if (st != CN_OK) return st;
+    cn_gemm_workspace *ws = ctx->gemm;
+    if (!ws->d_status) {
+        // status word + ticket counters; the kernels leave every ticket at zero again
+        CN_CUDA(cudaMalloc(&ws->d_status, 64 + CN_GEMM_MAX_TICKETS * sizeof(unsigned int)));
+        CN_CUDA(cudaMemset(ws->d_status, 0, 64 + CN_GEMM_MAX_TICKETS * sizeof(unsigned int)));
+    }
+    const bool mode3x = mode == CN_GEMM_3XTF32;
+    const int64_t Kpad = (K + TC_BK - 1) / TC_BK * TC_BK;
+
+    // 1. activations -> K-major hi / lo planes
+    void *planes = nullptr;
+    const size_t plane_elems = (size_t)M * Kpad;
+    st = cn_gemm_scratch(ctx, CN_GEMM_SLOT_ASPLIT, plane_elems * sizeof(float) * (mode3x ? 2 : 1), &planes);
+    if (st != CN_OK) return st;
+    float *hi = (float *)planes, *lo = mode3x ? hi + plane_elems : nullptr;
+    {
+        const int64_t tiles_k = Kpad / 32, tiles_mm = (M + 31) / 32;
+        CN_REQUIRE(tiles_k * tiles_mm < (1LL << 31), CN_ERR_UNSUPPORTED, "cn_gemm_f32: activation matrix too large for the split pre-pass");
+        cn_act_split_kernel<<<(unsigned)(tiles_k * tiles_mm), 256, 0, s>>>(A, lda, M, K, Kpad, hi, lo, tiles_k);
+        CN_CUDA(cudaGetLastError());
+    }
+
+    // 2. tiling
+    int nt = (N >= 2048) ? 2 : 1;
+    if (const char *e = getenv("CN_GEMM_NT")) { int v = atoi(e); if (v == 1 || v == 2) nt = v; }
+    const int64_t tiles_n = (N + nt * TC_BN - 1) / (nt * TC_BN), tiles_m = (M + TC_BM - 1) / TC_BM;
+    const int64_t tiles = tiles_n * tiles_m;
+    const int kb_total = (int)(Kpad / TC_BK);
+    int splits = pick_splits(tiles, kb_total, ctx->sm_count);
+    if (const char *e = getenv("CN_GEMM_SPLITS")) { int v = atoi(e); if (v >= 1 && v <= kb_total) splits = v; }
+    if (tiles > CN_GEMM_MAX_TICKETS) splits = 1;
+    int kb_per_split = (kb_total + splits - 1) / splits;
+    splits = (kb_total + kb_per_split - 1) / kb_per_split;   // no empty split
+    CN_REQUIRE(tiles * splits < (1LL << 31), CN_ERR_UNSUPPORTED, "cn_gemm_f32: too many work units");
+
+    TcParams prm;
+    prm.M = M; prm.N = N; prm.K = K;
+    prm.C = C; prm.ldc = ldc;
+    prm.bias = epi ? epi->bias : nullptr;
+    prm.act = epi ? epi->activation : CN_ACT_LINEAR;
+    prm.maxout_level = epi ? epi->maxout_level : 1;
+    prm.argmax = epi ? epi->argmax_out : nullptr;
+    prm.tiles_n = tiles_n; prm.tiles_m = tiles_m;
+    prm.splits = splits; prm.kb_per_split = kb_per_split; prm.kb_total = kb_total;
+    prm.partials = nullptr; prm.tickets = nullptr;
+    prm.status = ws->d_status;
+    if (splits > 1) {
+        const size_t part_bytes = (size_t)tiles * splits * nt * TC_BM * TC_BN * sizeof(float);
+        void *buf = nullptr;
+        st = cn_gemm_scratch(ctx, CN_GEMM_SLOT_SPLITK, part_bytes, &buf);
+        if (st != CN_OK) return st;
+        prm.tickets = ws->d_status + 16;
+        prm.partials = (float *)buf;
+    }
+
+    // 3. tensor maps
+    CUtensorMap mw, mhi, mlo;
+    if ((st = make_map(enc, &mw, B, K, N, ldb)) != CN_OK) return st;
+    if ((st = make_map(enc, &mhi, hi, Kpad, M, Kpad)) != CN_OK) return st;
+    if ((st = make_map(enc, &mlo, mode3x ? lo : hi, Kpad, M, Kpad)) != CN_OK) return st;
+
+    const int64_t grid = tiles * splits;
+    if (nt == 1) st = mode3x ? launch_cfg<1, true>(mw, mhi, mlo, prm, grid, s) : launch_cfg<1, false>(mw, mhi, mlo, prm, grid, s);
+    else         st = mode3x ? launch_cfg<2, true>(mw, mhi, mlo, prm, grid, s) : launch_cfg<2, false>(mw, mhi, mlo, prm, grid, s);
+    if (st != CN_OK) return st;
+    ctx->gemm_last_path = mode3x ? "tcgen05_3xtf32" : "tcgen05_tf32";
+    return CN_OK;
+}
+
+// Reads the status word that a kernel sets when one of its bounded waits ran out (0 = clean).
+extern "C" int cn_gemm_check_status(cn_context *ctx, void *stream)
+{
+    CN_REQUIRE(ctx, CN_ERR_ARG, "cn_gemm_check_status: null context");
+    cudaStream_t s = cn_stream(stream);
+    if (!ctx->gemm || !ctx->gemm->d_status) return CN_OK;
+    unsigned int h = 0;
+    CN_CUDA(cudaMemcpyAsync(&h, ctx->gemm->d_status, sizeof(h), cudaMemcpyDeviceToHost, s));
+    CN_CUDA(cudaStreamSynchronize(s));
+    if (h != 0) {
+        cudaMemsetAsync(ctx->gemm->d_status, 0, sizeof(h), s);
+        cn_set_error("cn_gemm_f32: a pipeline wait ran out in the tensor-core kernel (role code %u)", h);
+        return CN_ERR_TIMEOUT;
+    }
+    return CN_OK;
+}

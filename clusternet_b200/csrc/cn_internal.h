@@ -1,0 +1,67 @@
+// Shared declarations of the library's translation units (not part of the public C ABI).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <map>
+#include <string>
+#include <vector>
+#include "../../include/clusternet_b200.h"
+
+#define CN_CODEBOOK_N 126
+#define CN_NUM_THR 127      // decision thresholds of the compressor
+#define CN_NUM_LEVELS 128   // levels they separate: 254, 0..125, 127
+#define CN_MAX_PARTIALS 4096
+
+void cn_set_error(const char *fmt, ...);
+int cn_cuda_fail(cudaError_t e, const char *what);
+
+#define CN_CUDA(call)                                         \
+    do {                                                      \
+        cudaError_t e__ = (call);                             \
+        if (e__ != cudaSuccess) return cn_cuda_fail(e__, #call); \
+    } while (0)
+
+#define CN_REQUIRE(cond, status, ...)      \
+    do {                                   \
+        if (!(cond)) {                     \
+            cn_set_error(__VA_ARGS__);     \
+            return (status);               \
+        }                                  \
+    } while (0)
+
+struct cn_timer_slot {
+    cudaEvent_t start = nullptr, stop = nullptr;
+    float cumulative_ms = 0.f;
+};
+
+struct cn_gemm_workspace;  // owned by cn_gemm.cu
+struct cn_comm_state;      // owned by cn_comm.cu
+
+struct cn_context {
+    int device = 0;
+    int sm_count = 0;
+    // codec tables (device)
+    float *d_tbl = nullptr;            // 128 floats: codebook[0..125], +inf, +inf
+    uint32_t *d_thr = nullptr;         // 128 words: 127 thresholds (fp32 bit patterns of |x/precision|) + 0xffffffff pad
+    uint8_t *d_level_codes = nullptr;  // 128 bytes
+    float h_tbl[128];
+    uint32_t h_thr[128];
+    uint8_t h_level_codes[128];
+    // reduction scratch: per-CTA partial maxima + a ticket counter that the last CTA resets
+    float *d_partials = nullptr;
+    unsigned int *d_ticket = nullptr;
+    // GEMM
+    cn_gemm_workspace *gemm = nullptr;
+    const char *gemm_last_path = "";
+    // communicator
+    cn_comm_state *comm = nullptr;
+    // timers
+    std::map<std::string, cn_timer_slot> timers;
+};
+
+// cn_gemm.cu
+void cn_gemm_workspace_free(cn_context *ctx);
+// cn_comm.cu
+void cn_comm_state_free(cn_context *ctx);
+
+static inline cudaStream_t cn_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }

@@ -1,0 +1,229 @@
+/*
+ * clusternet_b200 — C ABI of the B200-native dot / dotMPI / 8-bit codec / batch path.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and 64-bit sizes, and returns a cn_status.
+ * Device pointers are ordinary CUDA device addresses; `stream` is a cudaStream_t passed as void*
+ * (NULL = the legacy default stream, which is what the reference uses everywhere).
+ * All matrices on the device are dense fp32, COLUMN-major with leading dimension = rows, exactly as
+ * the reference keeps them (source/basicOps.cu:14-33: to_gpu transposes on upload).
+ *
+ * Each declaration cites the reference interface (file:line, relative to the reference tree) whose
+ * job it takes over.
+ */
+#ifndef CLUSTERNET_B200_H
+#define CLUSTERNET_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct cn_context cn_context;
+
+typedef enum cn_status {
+    CN_OK = 0,
+    CN_ERR_ARG = 1,         /* null pointer, negative size, misaligned buffer */
+    CN_ERR_SHAPE = 2,       /* operand shapes do not match (the reference throws "Matrix *size* error") */
+    CN_ERR_CUDA = 3,        /* a CUDA runtime/driver call failed; cn_last_error() has the text */
+    CN_ERR_NCCL = 4,
+    CN_ERR_TIMEOUT = 5,     /* a bounded device-side or host-side wait ran out */
+    CN_ERR_UNSUPPORTED = 6, /* valid request that this build has no kernel for */
+    CN_ERR_NOMEM = 7
+} cn_status;
+
+/* Text of the last error raised on the calling thread ("" when none). */
+const char *cn_last_error(void);
+const char *cn_status_string(int status);
+/* Library version, and the compute capability it was compiled for (100 for sm_100a). */
+int cn_version(void);
+int cn_compiled_arch(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Context.  Replaces ClusterNet::init (source/clusterNet.cpp:40-146): binds a device, uploads the
+ * 126-entry codebook (source/clusterNet.cpp:73, file source/8bit_floats.hdf5), derives the codec's
+ * decision thresholds from it and allocates the small scratch buffers the kernels need.
+ * codebook126 is a HOST pointer to 126 strictly increasing floats in (0,1).
+ * ------------------------------------------------------------------------------------------- */
+int cn_context_create(int device, const float *codebook126, cn_context **out);
+int cn_context_destroy(cn_context *ctx);
+int cn_context_device(const cn_context *ctx);
+
+/* Host-only helper (no GPU needed): reads the codebook from the reference's HDF5 file or from a raw
+ * 504-byte dump (replaces read_hdf5 of "/Default", source/util.cu:100-131). */
+int cn_codebook_load(const char *path, float *codebook126);
+
+/* Host-only helper (no GPU needed): derives, from the codebook, the 127 ascending magnitude
+ * thresholds (fp32 bit patterns) at which kCompression_8bit's answer changes, and the 128 codes of
+ * the levels they separate (254, 0..125, 127).  code(|a|) = level_codes[#{j : thr[j] <= bits(|a|)}].
+ * This is an exact re-expression of the search-and-pick of source/clusterKernels.cu:1193-1229. */
+int cn_codec_build_thresholds(const float *codebook126, uint32_t *thr127, uint8_t *level_codes128);
+
+/* ---------------------------------------------------------------------------------------------
+ * 8-bit dynamic-float codec.
+ * ------------------------------------------------------------------------------------------- */
+
+/* absmax: replaces abs() + max() (source/basicOps.cu:810-822,1076-1081; kAbs
+ * source/clusterKernels.cu:429-436).  Writes max_i |A[i]| (or -1.0f when n == 0, the reference's
+ * reduce seed) to the DEVICE scalar d_out.  One pass, no temporary matrix. */
+int cn_absmax_f32(cn_context *ctx, const float *d_A, int64_t n, float *d_out, void *stream);
+
+/* compression_8bit: replaces ::compression_8bit (source/basicOps.cu:1163-1168) and kCompression_8bit
+ * (source/clusterKernels.cu:1163-1232).  codes[i] is bit-identical to the reference kernel's output
+ * for every input for which the reference's answer is defined. */
+int cn_compress_8bit(cn_context *ctx, const float *d_A, float precision, int64_t n, uint8_t *d_codes, void *stream);
+/* Same, with `precision` read from a device scalar (e.g. the output of cn_absmax_f32) so that the
+ * absmax -> compress chain needs no host synchronisation. */
+int cn_compress_8bit_dp(cn_context *ctx, const float *d_A, const float *d_precision, int64_t n, uint8_t *d_codes, void *stream);
+
+/* decompression_8bit: replaces ::decompression_8bit (source/basicOps.cu:1172-1176) and
+ * kDecompression_8bit (source/clusterKernels.cu:1135-1160), including its committed decoding of the
+ * special codes (126, 127, 254 -> +precision; 255 -> -precision). */
+int cn_decompress_8bit(cn_context *ctx, const uint8_t *d_codes, float precision, int64_t n, float *d_out, void *stream);
+int cn_decompress_8bit_dp(cn_context *ctx, const uint8_t *d_codes, const float *d_precision, int64_t n, float *d_out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Layout boundary: host row-major <-> device column-major.
+ * Replaces to_gpu / to_host / to_col_major / to_row_major / kTranspose
+ * (source/basicOps.cu:14-33,35-88,108-127; source/clusterKernels.cu:457-482).
+ * ------------------------------------------------------------------------------------------- */
+/* d_dst (col-major rows x cols) <- d_src (row-major rows x cols); both on the device. */
+int cn_to_col_major(cn_context *ctx, const float *d_src, float *d_dst, int64_t rows, int64_t cols, void *stream);
+/* d_dst (row-major rows x cols) <- d_src (col-major rows x cols). */
+int cn_to_row_major(cn_context *ctx, const float *d_src, float *d_dst, int64_t rows, int64_t cols, void *stream);
+/* Upload: h_src is a HOST row-major rows x cols buffer (pinned for an asynchronous copy), d_stage a
+ * device staging buffer of the same size, d_dst the col-major result. */
+int cn_upload_row_major(cn_context *ctx, const float *h_src, float *d_stage, float *d_dst, int64_t rows, int64_t cols, void *stream);
+/* Download: the inverse; h_dst receives row-major data once the stream has drained. */
+int cn_download_row_major(cn_context *ctx, const float *d_src, float *d_stage, float *h_dst, int64_t rows, int64_t cols, void *stream);
+int cn_fill_f32(cn_context *ctx, float *d_A, int64_t n, float value, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * GEMM.  Replaces the cublasSgemm call of ClusterNet::dot (source/clusterNet.cpp:404-487) and the
+ * elementwise passes that follow it in the reference's layers (addMatrixVector, rectified_linear,
+ * logistic, doubleRectifiedLinear, LinearUnit, maxout: source/basicOps.cu:966-974,1212-1216,672-676,
+ * 728-732,742-746,1287-1299), which are fused into the tile store.
+ *
+ * C(M x N) = act(op(A)(M x K) . op(B)(K x N) + bias), all column-major.  lda/ldb/ldc are leading
+ * dimensions of the stored (untransposed) arrays, as in the reference's call
+ * (lda = A->rows, ldb = B->rows, ldc = out->rows).
+ * ------------------------------------------------------------------------------------------- */
+typedef enum cn_gemm_mode {
+    CN_GEMM_3XTF32 = 0,  /* fp32-accurate: hi/lo TF32 split, three tensor-core products per tile */
+    CN_GEMM_TF32 = 1,    /* single TF32 product (10-bit mantissa operands), reported separately */
+    CN_GEMM_FP32_SIMT = 2 /* plain fp32 FMA kernel; also chosen automatically for shapes the tensor path cannot take */
+} cn_gemm_mode;
+
+typedef enum cn_activation {
+    CN_ACT_LINEAR = 0,          /* LinearUnit: copy */
+    CN_ACT_RELU = 1,            /* rectified_linear: x > 0 ? x : 0 */
+    CN_ACT_LOGISTIC = 2,        /* logistic: 1/(1+expf(-x)) */
+    CN_ACT_DOUBLE_RELU = 3      /* doubleRectifiedLinear: clamp to [0,1] */
+} cn_activation;
+
+typedef struct cn_epilogue {
+    const float *bias;     /* device, N floats, added to every row (kAddMatrixVector: v[i / rows]); NULL = none */
+    int activation;        /* cn_activation */
+    int maxout_level;      /* 0/1 = off; L>1: C becomes M x N/L, each entry the max over L consecutive columns (kMaxout) */
+    float *argmax_out;     /* device, M x N/L col-major, absolute column of the max as float; NULL = not wanted */
+} cn_epilogue;
+
+int cn_gemm_f32(cn_context *ctx, int transA, int transB, int64_t M, int64_t N, int64_t K,
+                const float *d_A, int64_t lda, const float *d_B, int64_t ldb, float *d_C, int64_t ldc,
+                const cn_epilogue *epi, int mode, void *stream);
+/* Name of the kernel family the last cn_gemm_f32 call on this context dispatched to
+ * ("tcgen05_3xtf32", "tcgen05_tf32", "simt_fp32"); for tests and reports. */
+const char *cn_gemm_last_path(const cn_context *ctx);
+/* The tensor-core kernel bounds every wait of its internal pipeline; a wait that runs out makes the kernel
+ * return early and set a device status word.  This call drains `stream`, reads the word and returns
+ * CN_ERR_TIMEOUT if any launch since the last check gave up (the output of that launch is then undefined),
+ * CN_OK otherwise.  No counterpart in the reference (cublasSgemm reports nothing). */
+int cn_gemm_check_status(cn_context *ctx, void *stream);
+
+/* The same elementwise ops as stand-alone kernels over an existing col-major matrix (the reference's
+ * un-fused call sites, e.g. source/Layer.cpp:257-259). */
+int cn_bias_activation(cn_context *ctx, const float *d_A, const float *d_bias, int activation,
+                       float *d_out, int64_t rows, int64_t cols, void *stream);
+int cn_maxout(cn_context *ctx, const float *d_A, float *d_out, float *d_argmax, int64_t rows, int64_t cols,
+              int maxout_level, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Random numbers and weight creation.  Replaces ClusterNet::rand / uniformSqrtWeight /
+ * distributed_uniformSqrtWeight (source/clusterNet.cpp:746-769,874-894,916-938) and
+ * kCreateRdmSqrtWeight_Logistic (source/clusterKernels.cu:126-138).  The generator is a counter-based
+ * Philox-4x32-10 written here, not cuRAND's XORWOW, so streams differ from the reference's; ranges
+ * and statistics are the same (uniform in (0,1]; weights in +-4*sqrtf(6/(in+out_total))).
+ * ------------------------------------------------------------------------------------------- */
+int cn_rand_uniform(cn_context *ctx, float *d_A, int64_t n, uint64_t seed, uint64_t offset, void *stream);
+int cn_rand_normal(cn_context *ctx, float *d_A, int64_t n, float mean, float std, uint64_t seed, uint64_t offset, void *stream);
+int cn_uniform_sqrt_weight(cn_context *ctx, float *d_A, int64_t n, int64_t fan_in, int64_t fan_out_total,
+                           uint64_t seed, uint64_t offset, void *stream);
+/* dropout (source/clusterNet.cpp:842-872, kDropout source/clusterKernels.cu:939-947):
+ * out[i] = u[i] > rate ? A[i] : 0, u uniform in (0,1]; no rescale. */
+int cn_dropout(cn_context *ctx, const float *d_A, float *d_out, int64_t n, float rate, uint64_t seed, uint64_t offset, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Communicator (one process per GPU).  Replaces ClusterNet::init_MPI / shutdown_MPI
+ * (source/clusterNet.cpp:148-183,223-228) with NCCL over NVLink.  The 128-byte id is produced on one
+ * rank and handed to the others by the host program (torch.distributed store, a file, ...).
+ * ------------------------------------------------------------------------------------------- */
+int cn_comm_get_unique_id(void *id128);
+int cn_comm_init_rank(cn_context *ctx, const void *id128, int rank, int nranks);
+int cn_comm_destroy(cn_context *ctx);
+int cn_comm_rank(const cn_context *ctx);
+int cn_comm_size(const cn_context *ctx);
+/* Shard of an N-column matrix owned by `rank`: floor(N/G) columns, the last rank also takes the
+ * remainder (source/clusterNet.cpp:515-516,926-931). Host-only. */
+int cn_shard_cols(int64_t n_total, int rank, int nranks, int64_t *col_start, int64_t *col_count);
+/* Broadcast of the activations ("A is broadcast"): n floats from root to every rank, in place. */
+int cn_bcast_f32(cn_context *ctx, float *d_buf, int64_t n, int root, void *stream);
+/* In-place all-gather of column shards of a col-major M x N_total matrix: rank r has already written
+ * its own columns; on return every rank holds all of C.  Replaces the MPI ring + hStackN
+ * (source/clusterNet.cpp:663-694; source/clusterKernels.cu:225-238). */
+int cn_allgather_cols_f32(cn_context *ctx, float *d_C, int64_t M, int64_t n_total, void *stream);
+int cn_allgather_cols_u8(cn_context *ctx, uint8_t *d_codes, int64_t M, int64_t n_total, void *stream);
+/* All-gather of one float per rank (the per-rank codec scales; the commented intent of
+ * source/Layer.cpp:354-358). d_vals holds nranks floats; entry [rank] is this rank's input. */
+int cn_allgather_scalar_f32(cn_context *ctx, float *d_vals, void *stream);
+int cn_allreduce_sum_f32(cn_context *ctx, float *d_buf, int64_t n, void *stream);
+
+/* dotMPI: replaces ClusterNet::dotMPI (source/clusterNet.cpp:512-697) for a column-sharded B.
+ * A is M x K and already resident on every rank; Wshard is this rank's K x cols_local block of the
+ * K x n_total weight; C is the full M x n_total col-major output on every rank.
+ * exchange = 0: fp32 all-gather; 1: the slice is absmax-scaled, 8-bit compressed, gathered as codes
+ * and decoded on arrival (the reference's commented 8-bit ring, source/clusterNet.cpp:670-677). */
+int cn_dotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_total, const float *d_A,
+                  const float *d_Wshard, float *d_C, const cn_epilogue *epi, int mode, int exchange, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Batch allocator (dense path).  Replaces BatchAllocator::init / init_batch_buffer /
+ * broadcast_batch_to_processes / allocate_next_batch_async / replace_current_batch_with_next
+ * (source/batchAllocator.cpp:101-251,253-338,399-425,759-864,977-1053).
+ * The full data set stays in host memory (row-major); each step stages the next batch's rows in a
+ * pinned buffer, copies them on side streams, and the swap transposes them to col-major into the
+ * current-batch matrices on the compute stream, ordered by events instead of stream synchronisation.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct cn_batch cn_batch;
+int cn_batch_create(cn_context *ctx, const float *h_X, const float *h_y, int64_t rows, int64_t cols_X, int64_t cols_y,
+                    int64_t batch_size, int skip_last_batch, cn_batch **out);
+int cn_batch_destroy(cn_batch *b);
+int64_t cn_batch_total_batches(const cn_batch *b);
+/* The batch that is current now (after cn_batch_create: the first batch, as BatchAllocator::init leaves it). */
+int cn_batch_current(const cn_batch *b, float **d_X, float **d_y, int64_t *batch_rows);
+/* Stage + asynchronous copy of the next batch (allocate_next_batch_async). */
+int cn_batch_copy_next_async(cn_batch *b);
+/* Make the next batch current (replace_current_batch_with_next): waits (on the device, through an
+ * event) for the copies, transposes into the current-batch buffers on `stream`, advances the counter
+ * with wrap-around.  Returns the device pointers and the row count of the batch (the last batch of an
+ * epoch may be short). */
+int cn_batch_swap(cn_batch *b, void *stream, float **d_X, float **d_y, int64_t *batch_rows);
+
+/* Named cumulative timers: ClusterNet::tick / tock (source/clusterNet.cpp:798-840). */
+int cn_tick(cn_context *ctx, const char *name, void *stream);
+int cn_tock(cn_context *ctx, const char *name, void *stream, float *cumulative_ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CLUSTERNET_B200_H */

@@ -1,0 +1,129 @@
+"""GEMM parity: the reference's known-answer tests, an fp64 host GEMM as accuracy yardstick, fused epilogues."""
+import numpy as np
+import pytest
+import torch
+
+from clusternet_b200 import _lib
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL_3XTF32 = 1e-5      # max |C - C64| / max |C64|, the bound the 3xTF32 mode has to meet
+TOL_TF32 = 2e-3        # looser bound of the single-pass TF32 mode (10-bit mantissa operands)
+
+
+def normwise(got, ref):
+    return float(np.abs(got.astype(np.float64) - ref).max() / max(np.abs(ref).max(), 1e-300))
+
+
+def test_dot_known_answers(ctx):
+    """The reference's own known-answer vectors (tests/clusterNet_test.cu:16-36,67-84,106-129,158-165), which it
+    checks with float equality."""
+    import json
+    import os
+    kat = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "gemm_kat.json")))
+    mats = {k: np.array(kat[k]["data"], np.float32).reshape(kat[k]["rows"], kat[k]["cols"]) for k in ("m1", "m2")}
+    for case in kat["cases"]:
+        A, B = ctx.colmajor(mats[case["a"]]), ctx.colmajor(mats[case["b"]])
+        C = ctx.to_numpy(ctx.gemm(A, B, transA=case["op"] == "Tdot", transB=case["op"] == "dotT"))
+        assert ctx.gemm_last_path() == "simt_fp32"
+        want = np.array(case["expect"], np.float32).reshape(case["rows"], case["cols"])
+        assert C.shape == want.shape
+        assert np.array_equal(C, want), (case["op"], C, want)
+
+
+def test_shape_mismatch_is_an_error(ctx):
+    from clusternet_b200 import CnError
+    A = ctx.colmajor(np.ones((4, 5), np.float32))
+    B = ctx.colmajor(np.ones((6, 3), np.float32))
+    with pytest.raises(CnError) as e:
+        ctx.gemm(A, B)
+    assert e.value.status == _lib.CN_ERR_SHAPE
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 32, 128), (128, 64, 128), (128, 256, 128), (128, 784, 1024), (64, 128, 256),
+                                   (1, 64, 16), (130, 100, 200), (256, 512, 384), (300, 1000, 520), (128, 4096, 2304)])
+@pytest.mark.parametrize("mode", [_lib.GEMM_3XTF32, _lib.GEMM_TF32])
+def test_tensor_core_gemm_vs_fp64(ctx, M, K, N, mode):
+    rng = np.random.default_rng(M * 7 + K * 3 + N)
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    C = ctx.gemm(ctx.colmajor(A), ctx.colmajor(B), mode=mode)
+    ctx.gemm_check()
+    assert ctx.gemm_last_path() == ("tcgen05_3xtf32" if mode == _lib.GEMM_3XTF32 else "tcgen05_tf32")
+    err = normwise(ctx.to_numpy(C), oracle.gemm_f64(A, B))
+    assert err < (TOL_3XTF32 if mode == _lib.GEMM_3XTF32 else TOL_TF32), err
+
+
+def test_config1_dot_bias_relu(ctx):
+    """Single-layer dot: A 128x784, B 784x1024 uniform(-1,1) seed 0, + bias + ReLU, vs fp64."""
+    rng = np.random.default_rng(0)
+    A = rng.uniform(-1, 1, (128, 784)).astype(np.float32)
+    B = rng.uniform(-1, 1, (784, 1024)).astype(np.float32)
+    bias = rng.uniform(-1, 1, 1024).astype(np.float32)
+    dbias = torch.from_numpy(bias).cuda()
+    ref = np.maximum(oracle.gemm_f64(A, B) + bias, 0)
+    for mode, tol, path in [(_lib.GEMM_3XTF32, TOL_3XTF32, "tcgen05_3xtf32"), (_lib.GEMM_TF32, TOL_TF32, "tcgen05_tf32"),
+                            (_lib.GEMM_FP32_SIMT, 1e-6, "simt_fp32")]:
+        C = ctx.gemm(ctx.colmajor(A), ctx.colmajor(B), bias=dbias, activation=_lib.ACT_RELU, mode=mode)
+        ctx.gemm_check()
+        assert ctx.gemm_last_path() == path
+        err = normwise(ctx.to_numpy(C), ref)
+        assert err < tol, (mode, err)
+
+
+@pytest.mark.parametrize("splits,nt", [(1, 1), (3, 1), (7, 1), (1, 2), (4, 2)])
+def test_split_k_and_tile_variants(ctx, splits, nt, monkeypatch):
+    monkeypatch.setenv("CN_GEMM_SPLITS", str(splits))
+    monkeypatch.setenv("CN_GEMM_NT", str(nt))
+    rng = np.random.default_rng(splits * 10 + nt)
+    M, K, N = 128, 2048, 640
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    bias = rng.uniform(-1, 1, N).astype(np.float32)
+    dA, dB, db = ctx.colmajor(A), ctx.colmajor(B), torch.from_numpy(bias).cuda()
+    C1 = ctx.gemm(dA, dB, bias=db, activation=_lib.ACT_RELU)
+    C2 = ctx.gemm(dA, dB, bias=db, activation=_lib.ACT_RELU)
+    ctx.gemm_check()
+    assert torch.equal(C1, C2), "split-K reduction must be reproducible"
+    ref = np.maximum(oracle.gemm_f64(A, B) + bias, 0)
+    assert normwise(ctx.to_numpy(C1), ref) < TOL_3XTF32
+
+
+@pytest.mark.parametrize("act", [_lib.ACT_LINEAR, _lib.ACT_RELU, _lib.ACT_LOGISTIC, _lib.ACT_DOUBLE_RELU])
+def test_fused_epilogue_matches_unfused(ctx, act):
+    rng = np.random.default_rng(act)
+    A = rng.uniform(-1, 1, (128, 160)).astype(np.float32)
+    B = rng.uniform(-1, 1, (160, 256)).astype(np.float32)
+    bias = rng.uniform(-1, 1, 256).astype(np.float32)
+    dA, dB, db = ctx.colmajor(A), ctx.colmajor(B), torch.from_numpy(bias).cuda()
+    plain = ctx.gemm(dA, dB)
+    fused = ctx.gemm(dA, dB, bias=db, activation=act)
+    unfused = ctx.bias_activation(plain, db, act)
+    ctx.gemm_check()
+    assert torch.equal(fused, unfused)
+    want = oracle.bias_activation(ctx.to_numpy(plain), bias, act)
+    got = ctx.to_numpy(fused)
+    if act == _lib.ACT_LOGISTIC:
+        assert np.abs(got - want).max() <= 2.4e-7   # expf differs by an ulp or two between libm and CUDA
+    else:
+        assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("level", [2, 4, 8, 32, 3, 5])
+def test_maxout_fused_and_standalone(ctx, level):
+    rng = np.random.default_rng(level)
+    N = 480 if level in (3, 5, 2, 4, 8, 32) else 256
+    N = {2: 256, 4: 256, 8: 256, 32: 256, 3: 240, 5: 160}[level]
+    A = rng.uniform(-1, 1, (128, 96)).astype(np.float32)
+    B = rng.uniform(-1, 1, (96, N)).astype(np.float32)
+    dA, dB = ctx.colmajor(A), ctx.colmajor(B)
+    plain = ctx.gemm(dA, dB)
+    arg = ctx.empty(128, N // level)
+    out = ctx.gemm(dA, dB, maxout_level=level, argmax_out=arg)
+    ctx.gemm_check()
+    wv, wi = oracle.maxout(ctx.to_numpy(plain), level)
+    assert np.array_equal(ctx.to_numpy(out), wv)
+    assert np.array_equal(ctx.to_numpy(arg), wi)
+    sv, si = ctx.maxout(plain, level)
+    assert np.array_equal(ctx.to_numpy(sv), wv) and np.array_equal(ctx.to_numpy(si), wi)
