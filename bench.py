@@ -1,0 +1,351 @@
+#!/usr/bin/env python
+"""Benchmark of the dot / dotMPI hot path: the README two-layer skinny product
+(128 x 100000) . (100000 x 40000) . (40000 x 20000), fp32, W column-sharded over the ranks.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--mode 3xtf32|tf32] [--exchange fp32|8bit]
+
+One process per GPU (torchrun sets RANK / LOCAL_RANK / WORLD_SIZE for N > 1).  Rank 0 prints one JSON line.
+
+  value     whole-job TFLOP/s of the two dotMPI calls with the batch and the weights resident in HBM
+            (2*M*N*K flops, the three TF32 products of the 3xTF32 mode counted once), CUDA events, max over ranks
+  e2e       the same two calls through the C ABI starting from a pinned HOST batch (row-major) and ending with the
+            row-major result in pinned host memory: upload + transpose, broadcast, two dotMPI, transpose + download
+  roofline  the tensor-core kernel of layer 1 alone, timed by events around its launches inside the timed region
+  codec     8-bit compress / decompress / absmax GB/s on config 2 (4096 x 4096, rotating buffers) and on 1 GiB
+  cpu_baseline  multithreaded fp32 sgemm (numpy / OpenBLAS) of a column sample of the same product on the host cores
+
+--impl reference times the CPU stand-in of the reference path (clusterNet itself is CUDA + MPI only and cannot be
+built here): the same sgemm on a bounded column sample per step.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M, K1, N1, N2 = 128, 100000, 40000, 20000
+FLOPS_L1 = 2.0 * M * K1 * N1
+FLOPS_L2 = 2.0 * M * N1 * N2
+FLOPS_STEP = FLOPS_L1 + FLOPS_L2          # 1.2288e12
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [l.split(", ") for (t, l) in self.lines if t0 - 0.05 <= t <= t1 + 0.15] or [l.split(", ") for (_, l) in self.lines[-3:]]
+        sm, reasons, smax = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                smax = float(r[2])
+            except ValueError:
+                continue
+            for name, v in zip(names, r[5:9]):
+                if v.strip().lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_sgemm_sample(seconds_target=12.0, threads=None):
+    """Multithreaded fp32 sgemm of column samples of both layers; returns TFLOP/s and a description."""
+    cores = len(os.sched_getaffinity(0))
+    rng = np.random.default_rng(0)
+    batch = rng.random((M, K1), dtype=np.float32)
+    lim1 = 4.0 * np.sqrt(6.0 / (K1 + N1))
+    probe_cols = 256
+    W = rng.uniform(-lim1, lim1, (K1, probe_cols)).astype(np.float32)
+    t = time.perf_counter(); batch @ W; dt = time.perf_counter() - t
+    t = time.perf_counter(); batch @ W; dt = min(dt, time.perf_counter() - t)
+    rate = 2.0 * M * K1 * probe_cols / dt
+    cols1 = int(min(N1, max(probe_cols, seconds_target * 0.8 * rate / (2.0 * M * K1) / 3)))
+    cols1 = max(256, cols1 // 256 * 256)
+    W1 = rng.uniform(-lim1, lim1, (K1, cols1)).astype(np.float32)
+    lim2 = 4.0 * np.sqrt(6.0 / (N1 + N2))
+    cols2 = max(128, cols1 // 2)
+    W2 = rng.uniform(-lim2, lim2, (N1, cols2)).astype(np.float32)
+    act = rng.random((M, N1), dtype=np.float32)
+    best = None
+    for _ in range(3):
+        t = time.perf_counter()
+        batch @ W1
+        act @ W2
+        d = time.perf_counter() - t
+        best = d if best is None else min(best, d)
+    flops = 2.0 * M * K1 * cols1 + 2.0 * M * N1 * cols2
+    return flops / best / 1e12, cores, f"numpy float32 @ (OpenBLAS): 128x{K1} . {K1}x{cols1} + 128x{N1} . {N1}x{cols2} column sample, best of 3"
+
+
+def run_reference(args, rank):
+    """CPU stand-in of the reference path: rank 0 alone, bounded column sample per step."""
+    if rank != 0:
+        return
+    cores = len(os.sched_getaffinity(0))
+    rng = np.random.default_rng(0)
+    batch = rng.random((M, K1), dtype=np.float32)
+    lim1, lim2 = 4.0 * np.sqrt(6.0 / (K1 + N1)), 4.0 * np.sqrt(6.0 / (N1 + N2))
+    cols1, cols2 = 1024, 512
+    W1 = rng.uniform(-lim1, lim1, (K1, cols1)).astype(np.float32)
+    W2 = rng.uniform(-lim2, lim2, (N1, cols2)).astype(np.float32)
+    act = rng.random((M, N1), dtype=np.float32)
+    for _ in range(args.warmup):
+        batch @ W1; act @ W2
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        batch @ W1; act @ W2
+    dt = time.perf_counter() - t0
+    flops = (2.0 * M * K1 * cols1 + 2.0 * M * N1 * cols2) * args.steps
+    v = flops / dt / 1e12
+    sample = f"per step 128x{K1} . {K1}x{cols1} and 128x{N1} . {N1}x{cols2} (column sample of both layers), numpy float32 @ on the host"
+    print(json.dumps({
+        "impl": "reference", "metric": "dotMPI TFLOP/s", "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": {"workload": "README dotMPI two-layer skinny GEMM 128x100000 . 100000x40000 . 40000x20000"},
+        "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+
+
+def codec_bench(ctx, torch, peaks):
+    """compress / decompress / absmax GB/s: config 2 (4096^2, five rotating buffer sets so that no launch finds its
+    input in L2) and a 1 GiB tensor."""
+    out = {}
+    for label, n, sets, iters in (("config2_4096x4096", 4096 * 4096, 6, 30), ("1GiB", 1 << 28, 2, 6)):
+        xs = [torch.randn(n, device="cuda") * 0.1 for _ in range(sets)]
+        codes = [torch.empty(n, dtype=torch.uint8, device="cuda") for _ in range(sets)]
+        outs = [torch.empty(n, device="cuda") for _ in range(sets)]
+        pm = ctx.absmax(xs[0])
+        p = float(pm.item())
+        res = {}
+        for name, fn, bytes_per in (("compress", lambda i: ctx.compress(xs[i], p, out=codes[i]), 5),
+                                    ("decompress", lambda i: ctx.decompress(codes[i], p, out=outs[i]), 5),
+                                    ("absmax", lambda i: ctx.absmax(xs[i], out=pm), 4)):
+            for i in range(sets):
+                fn(i)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for it in range(iters):
+                fn(it % sets)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            gbs = n * bytes_per / ms / 1e6
+            res[name] = {"GB/s": round(gbs, 1), "us": round(ms * 1e3, 2), "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4)}
+        out[label] = res
+        del xs, codes, outs
+        torch.cuda.empty_cache()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--mode", default="3xtf32", choices=["3xtf32", "tf32"])
+    ap.add_argument("--exchange", default="fp32", choices=["fp32", "8bit"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-codec", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+    import clusternet_b200 as cn
+    from clusternet_b200 import _lib
+
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torchrun (--nproc-per-node N) for --gpus N > 1")
+    torch.cuda.set_device(local_rank)
+    ctx = cn.Context(local_rank)
+    lib = ctx.lib
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        ids = [ctx.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        ctx.comm_init(ids[0], rank, world)
+    peaks = measured_peaks()
+    mode = _lib.GEMM_3XTF32 if args.mode == "3xtf32" else _lib.GEMM_TF32
+    exchange = 1 if args.exchange == "8bit" else 0
+
+    # ---- workload: weights sharded by columns, created on the owning rank (distributed_uniformSqrtWeight)
+    s1, c1 = ctx.shard_cols(N1, rank, world)
+    s2, c2 = ctx.shard_cols(N2, rank, world)
+    seed = 0 + 10000 * rank + 12345
+    W1 = ctx.empty(K1, c1)
+    cn.check(lib.cn_uniform_sqrt_weight(ctx.h, W1.data_ptr(), W1.numel(), K1, N1, seed, 0, ctx.stream_ptr()))
+    W2 = ctx.empty(N1, c2)
+    cn.check(lib.cn_uniform_sqrt_weight(ctx.h, W2.data_ptr(), W2.numel(), N1, N2, seed + 1, 0, ctx.stream_ptr()))
+    # batch: uniform [0,1) seed 0 on the host (row-major, pinned), as a user of the reference would hold it
+    h_batch = torch.from_numpy(np.random.default_rng(0).random((M, K1), dtype=np.float32)).pin_memory()
+    h_out = torch.empty((M, N2), dtype=torch.float32).pin_memory()
+    d_stage_in = torch.empty((M, K1), dtype=torch.float32, device="cuda")
+    d_stage_out = torch.empty((M, N2), dtype=torch.float32, device="cuda")
+    batch = ctx.empty(M, K1)
+    out1 = ctx.empty(M, N1)
+    out2 = ctx.empty(M, N2)
+    sp = ctx.stream_ptr()
+
+    def upload():
+        if rank == 0:
+            cn.check(lib.cn_upload_row_major(ctx.h, h_batch.data_ptr(), d_stage_in.data_ptr(), batch.data_ptr(), M, K1, sp))
+        if world > 1:
+            ctx.bcast(batch, 0)
+
+    def two_layers():
+        ctx.dotmpi(batch, W1, N1, out=out1, mode=mode, exchange=exchange)
+        ctx.dotmpi(out1, W2, N2, out=out2, mode=mode, exchange=exchange)
+
+    def download():
+        if rank == 0:
+            cn.check(lib.cn_download_row_major(ctx.h, out2.data_ptr(), d_stage_out.data_ptr(), h_out.data_ptr(), M, N2, sp))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    upload()
+    for _ in range(args.warmup):
+        two_layers()
+    ctx.gemm_check()
+
+    # ---- timed region 1: resident inputs
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    cn.check(lib.cn_gemm_profile_enable(ctx.h, 1))
+    launches0 = lib.cn_kernel_launches()
+    barrier()
+    t_wall0 = time.time()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        two_layers()
+    e1.record()
+    barrier()
+    t_wall1 = time.time()
+    launches = lib.cn_kernel_launches() - launches0
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    buf = (ctypes.c_float * (4 * args.steps + 8))()
+    cnt = ctypes.c_int()
+    cn.check(lib.cn_gemm_profile_read(ctx.h, buf, len(buf), ctypes.byref(cnt)))
+    cn.check(lib.cn_gemm_profile_enable(ctx.h, 0))
+    kern_ms = [buf[i] for i in range(min(cnt.value, len(buf)))]
+    l1_ms = max_over_ranks(float(np.mean(kern_ms[0::2]))) if kern_ms else None
+    l2_ms = max_over_ranks(float(np.mean(kern_ms[1::2]))) if kern_ms else None
+    ctx.gemm_check()
+    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+
+    # ---- timed region 2: end to end from host memory through the C ABI
+    for _ in range(2):
+        upload(); two_layers(); download()
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for _ in range(args.steps):
+        upload(); two_layers(); download()
+    e3.record()
+    barrier()
+    ms_e2e = max_over_ranks(e2.elapsed_time(e3))
+    checksum = float(h_out.double().abs().mean())
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    value = FLOPS_STEP * args.steps / (ms_total * 1e-3) / 1e12
+    e2e_value = FLOPS_STEP * args.steps / (ms_e2e * 1e-3) / 1e12
+    tf32_peak = peaks["bf16_tflops"] / 2.0
+    peak = tf32_peak / 3.0 if args.mode == "3xtf32" else tf32_peak
+    l1_flops_rank = 2.0 * M * K1 * (N1 // world if world > 1 else N1)
+    achieved = l1_flops_rank / (l1_ms * 1e-3) / 1e12 if l1_ms else None
+    line = {
+        "metric": "dotMPI TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "README dotMPI two-layer skinny GEMM: 128x100000 . 100000x40000 . 40000x20000, W column-sharded",
+                   "gemm_mode": args.mode, "exchange": args.exchange, "parallelism": f"tp{world} (columns of W)",
+                   "l2": "inputs larger than L2 (19 GB of weights stream once per step)", "flops_per_step": FLOPS_STEP},
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": M * K1 * 4,
+                "d2h_bytes_per_step": M * N2 * 4, "result_checksum": checksum},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": {"kernel": "cn_gemm_tc_kernel (layer 1, per rank)", "bound": "tensor", "achieved": achieved, "peak": peak,
+                     "unit": "TFLOP/s", "frac": (achieved / peak) if achieved else None, "traffic": None,
+                     "ms_per_launch": l1_ms, "layer2_ms_per_launch": l2_ms,
+                     "peak_source": f"{peaks['source']}: bf16_tflops {peaks['bf16_tflops']} / 2 (TF32 rate)" + (" / 3 (three TF32 products per tile)" if args.mode == "3xtf32" else ""),
+                     "hbm_frac_layer1": (4.0 * K1 * (N1 / world) / (l1_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]) if l1_ms else None},
+    }
+    if not args.no_codec and world == 1:
+        line["codec"] = codec_bench(ctx, torch, peaks)
+    if not args.no_cpu_baseline and world == 1:
+        v, cores, sample = cpu_sgemm_sample()
+        line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -28,6 +28,9 @@ _SIGNATURES = {
     "cn_status_string": (c_char_p, [c_int]),
     "cn_version": (c_int, []),
     "cn_compiled_arch": (c_int, []),
+    "cn_kernel_launches": (c_uint64, []),
+    "cn_gemm_profile_enable": (c_int, [c_void_p, c_int]),
+    "cn_gemm_profile_read": (c_int, [c_void_p, c_void_p, c_int, ctypes.POINTER(c_int)]),
     "cn_context_create": (c_int, [c_int, c_void_p, ctypes.POINTER(c_void_p)]),
     "cn_context_destroy": (c_int, [c_void_p]),
     "cn_context_device": (c_int, [c_void_p]),

@@ -322,6 +322,7 @@ static int compress_impl(cn_context *ctx, const float *d_A, float precision, con
     else
         cn_compress_kernel<false><<<grid, CODEC_THREADS, 0, cn_stream(stream)>>>(d_A, precision, nullptr, n, d_codes, ctx->d_thr, ctx->d_level_codes, vector_ok);
     CN_CUDA(cudaGetLastError());
+    cn_count_launch();
     return CN_OK;
 }
 
@@ -350,6 +351,7 @@ static int decompress_impl(cn_context *ctx, const uint8_t *d_codes, float precis
     else
         cn_decompress_kernel<false><<<grid, CODEC_THREADS, 0, cn_stream(stream)>>>(d_codes, precision, nullptr, n, d_out, ctx->d_tbl, vector_ok);
     CN_CUDA(cudaGetLastError());
+    cn_count_launch();
     return CN_OK;
 }
 
@@ -373,5 +375,6 @@ extern "C" int cn_absmax_f32(cn_context *ctx, const float *d_A, int64_t n, float
     if (grid > CN_MAX_PARTIALS) grid = CN_MAX_PARTIALS;
     cn_absmax_kernel<<<grid, ABSMAX_THREADS, 0, cn_stream(stream)>>>(d_A, n, d_out, ctx->d_partials, ctx->d_ticket, vector_ok);
     CN_CUDA(cudaGetLastError());
+    cn_count_launch();
     return CN_OK;
 }

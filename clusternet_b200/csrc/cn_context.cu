@@ -5,7 +5,12 @@
 #include <string.h>
 #include "cn_internal.h"
 
+#include <atomic>
 static thread_local char g_err[512] = "";
+static std::atomic<unsigned long long> g_launches{0};
+
+void cn_count_launch(void) { g_launches.fetch_add(1, std::memory_order_relaxed); }
+extern "C" uint64_t cn_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
 
 void cn_set_error(const char *fmt, ...)
 {

@@ -56,6 +56,7 @@ extern "C" int cn_bias_activation(cn_context *ctx, const float *d_A, const float
     int64_t blocks = (n + 255) / 256, cap = (int64_t)ctx->sm_count * 8;
     cn_bias_act_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, cn_stream(stream)>>>(d_A, d_bias, activation, d_out, rows, n);
     CN_CUDA(cudaGetLastError());
+    cn_count_launch();
     return CN_OK;
 }
 
@@ -72,5 +73,6 @@ extern "C" int cn_maxout(cn_context *ctx, const float *d_A, float *d_out, float 
     int64_t blocks = (total + 7) / 8, cap = (int64_t)ctx->sm_count * 8;
     cn_maxout_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, cn_stream(stream)>>>(d_A, d_out, d_argmax, rows, out_cols, maxout_level);
     CN_CUDA(cudaGetLastError());
+    cn_count_launch();
     return CN_OK;
 }

@@ -90,6 +90,7 @@ static int simt_launch(cn_context *ctx, int transA, int transB, int64_t M, int64
     CN_REQUIRE(tiles_m * tiles_n < (1LL << 31), CN_ERR_UNSUPPORTED, "cn_gemm_f32: too many tiles for the fp32 FMA kernel");
     cn_sgemm_simt_kernel<<<(unsigned)(tiles_m * tiles_n), SG_THREADS, 0, s>>>(transA, transB, M, N, K, A, lda, B, ldb, C, ldc, bias, act, tiles_m);
     CN_CUDA(cudaGetLastError());
+    cn_count_launch();
     ctx->gemm_last_path = "simt_fp32";
     return CN_OK;
 }
@@ -124,6 +125,7 @@ void cn_gemm_workspace_free(cn_context *ctx)
     if (!ctx->gemm) return;
     for (int i = 0; i < CN_GEMM_SLOTS; ++i) cudaFree(ctx->gemm->ptr[i]);
     cudaFree(ctx->gemm->d_status);
+    for (cudaEvent_t e : ctx->gemm->prof_events) cudaEventDestroy(e);
     delete ctx->gemm;
     ctx->gemm = nullptr;
 }

@@ -17,6 +17,9 @@ struct cn_gemm_workspace {
     size_t bytes[CN_GEMM_SLOTS] = {0, 0, 0, 0};
     unsigned int *d_status = nullptr;   // word 0: set by a kernel whose bounded wait ran out; words 16..: split-K tickets
     void *encode_fn = nullptr;          // cuTensorMapEncodeTiled, resolved once
+    bool profile = false;               // bracket main-kernel launches with events
+    std::vector<cudaEvent_t> prof_events;   // start, stop, start, stop, ...
+    size_t prof_used = 0;
 };
 
 // Grow-only scratch buffers owned by the context.

@@ -566,6 +566,7 @@ static int launch_cfg(const CUtensorMap &mw, const CUtensorMap &mhi, const CUten
     CN_CUDA(cudaFuncSetAttribute(cn_gemm_tc_kernel<NT, MODE3X>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<NT>::SMEM_BYTES));
     cn_gemm_tc_kernel<NT, MODE3X><<<(unsigned)grid, TC_THREADS, TcCfg<NT>::SMEM_BYTES, s>>>(mw, mhi, mlo, prm);
     CN_CUDA(cudaGetLastError());
+    cn_count_launch();
     return CN_OK;
 }
 
@@ -595,6 +596,7 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
         CN_REQUIRE(tiles_k * tiles_mm < (1LL << 31), CN_ERR_UNSUPPORTED, "cn_gemm_f32: activation matrix too large for the split pre-pass");
         cn_act_split_kernel<<<(unsigned)(tiles_k * tiles_mm), 256, 0, s>>>(A, lda, M, K, Kpad, hi, lo, tiles_k);
         CN_CUDA(cudaGetLastError());
+        cn_count_launch();
     }
 
     // 2. tiling
@@ -637,9 +639,21 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
     if ((st = make_map(enc, &mlo, mode3x ? lo : hi, Kpad, M, Kpad)) != CN_OK) return st;
 
     const int64_t grid = tiles * splits;
+    cudaEvent_t ev_stop = nullptr;
+    if (ws->profile) {
+        while (ws->prof_events.size() < ws->prof_used + 2) {
+            cudaEvent_t e;
+            CN_CUDA(cudaEventCreate(&e));
+            ws->prof_events.push_back(e);
+        }
+        CN_CUDA(cudaEventRecord(ws->prof_events[ws->prof_used], s));
+        ev_stop = ws->prof_events[ws->prof_used + 1];
+        ws->prof_used += 2;
+    }
     if (nt == 1) st = mode3x ? launch_cfg<1, true>(mw, mhi, mlo, prm, grid, s) : launch_cfg<1, false>(mw, mhi, mlo, prm, grid, s);
     else         st = mode3x ? launch_cfg<2, true>(mw, mhi, mlo, prm, grid, s) : launch_cfg<2, false>(mw, mhi, mlo, prm, grid, s);
     if (st != CN_OK) return st;
+    if (ev_stop) CN_CUDA(cudaEventRecord(ev_stop, s));
     ctx->gemm_last_path = mode3x ? "tcgen05_3xtf32" : "tcgen05_tf32";
     return CN_OK;
 }
@@ -658,5 +672,31 @@ extern "C" int cn_gemm_check_status(cn_context *ctx, void *stream)
         cn_set_error("cn_gemm_f32: a pipeline wait ran out in the tensor-core kernel (role code %u)", h);
         return CN_ERR_TIMEOUT;
     }
+    return CN_OK;
+}
+
+extern "C" int cn_gemm_profile_enable(cn_context *ctx, int enable)
+{
+    CN_REQUIRE(ctx, CN_ERR_ARG, "cn_gemm_profile_enable: null context");
+    if (!ctx->gemm) ctx->gemm = new cn_gemm_workspace();
+    ctx->gemm->profile = enable != 0;
+    return CN_OK;
+}
+
+extern "C" int cn_gemm_profile_read(cn_context *ctx, float *ms_out, int max, int *count)
+{
+    CN_REQUIRE(ctx && count, CN_ERR_ARG, "cn_gemm_profile_read: null argument");
+    *count = 0;
+    if (!ctx->gemm) return CN_OK;
+    cn_gemm_workspace *ws = ctx->gemm;
+    const size_t pairs = ws->prof_used / 2;
+    for (size_t i = 0; i < pairs; ++i) {
+        CN_CUDA(cudaEventSynchronize(ws->prof_events[2 * i + 1]));
+        float ms = 0.f;
+        CN_CUDA(cudaEventElapsedTime(&ms, ws->prof_events[2 * i], ws->prof_events[2 * i + 1]));
+        if ((int)i < max && ms_out) ms_out[i] = ms;
+    }
+    *count = (int)pairs;
+    ws->prof_used = 0;
     return CN_OK;
 }

@@ -13,6 +13,8 @@
 #define CN_MAX_PARTIALS 4096
 
 void cn_set_error(const char *fmt, ...);
+// every kernel launch of the library is counted (cn_kernel_launches), so that callers can tell library work from fallbacks
+void cn_count_launch(void);
 int cn_cuda_fail(cudaError_t e, const char *what);
 
 #define CN_CUDA(call)                                         \

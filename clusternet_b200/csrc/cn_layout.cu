@@ -44,6 +44,7 @@ static int transpose_launch(const float *in, float *out, int64_t R, int64_t C, c
     CN_REQUIRE(tiles < (1LL << 31), CN_ERR_UNSUPPORTED, "transpose: %lld tiles exceed the grid limit", (long long)tiles);
     cn_transpose_kernel<<<(unsigned)tiles, TP_TILE * TP_ROWS, 0, s>>>(in, out, R, C, tiles_c);
     CN_CUDA(cudaGetLastError());
+    cn_count_launch();
     return CN_OK;
 }
 
@@ -86,5 +87,6 @@ extern "C" int cn_fill_f32(cn_context *ctx, float *d_A, int64_t n, float value, 
     int64_t cap = (int64_t)ctx->sm_count * 8;
     cn_fill_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, cn_stream(stream)>>>(d_A, n, value);
     CN_CUDA(cudaGetLastError());
+    cn_count_launch();
     return CN_OK;
 }

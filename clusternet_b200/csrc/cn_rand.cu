@@ -70,6 +70,7 @@ static int rand_launch(cn_context *ctx, const float *A, float *out, int64_t n, u
     int64_t cap = (int64_t)ctx->sm_count * 8;
     cn_rand_kernel<KIND><<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, cn_stream(stream)>>>(A, out, n, seed, offset, p0, p1);
     CN_CUDA(cudaGetLastError());
+    cn_count_launch();
     return CN_OK;
 }
 

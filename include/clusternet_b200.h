@@ -38,6 +38,8 @@ const char *cn_last_error(void);
 const char *cn_status_string(int status);
 /* Library version, and the compute capability it was compiled for (100 for sm_100a). */
 int cn_version(void);
+/* Number of CUDA kernels this library has launched in the calling process so far (all contexts). */
+uint64_t cn_kernel_launches(void);
 int cn_compiled_arch(void);
 
 /* ---------------------------------------------------------------------------------------------
@@ -140,6 +142,12 @@ const char *cn_gemm_last_path(const cn_context *ctx);
  * CN_ERR_TIMEOUT if any launch since the last check gave up (the output of that launch is then undefined),
  * CN_OK otherwise.  No counterpart in the reference (cublasSgemm reports nothing). */
 int cn_gemm_check_status(cn_context *ctx, void *stream);
+/* Timing of the tensor-core kernel alone: while enabled, every launch of the main GEMM kernel (not its activation
+ * pre-pass) is bracketed by CUDA events on the launching stream.  cn_gemm_profile_read waits for the recorded
+ * launches, writes up to `max` durations in milliseconds, in launch order, and clears the record.
+ * Takes the place of the reference's tick/tock around a dot call (source/clusterNet.cpp:798-840). */
+int cn_gemm_profile_enable(cn_context *ctx, int enable);
+int cn_gemm_profile_read(cn_context *ctx, float *ms_out, int max, int *count);
 
 /* The same elementwise ops as stand-alone kernels over an existing col-major matrix (the reference's
  * un-fused call sites, e.g. source/Layer.cpp:257-259). */

