@@ -307,6 +307,21 @@ def main():
     ms_e2e = max_over_ranks(e2.elapsed_time(e3))
     checksum = float(h_out.double().abs().mean())
 
+    # ---- accuracy on sampled columns against an fp64 host product (rank 0's shard edges + random columns)
+    def sampled_error(act_dev, W_dev, out_dev, col0, ncols_local, kdim):
+        rng_s = np.random.default_rng(7)
+        cols = np.unique(np.concatenate([[0, 1, 127, 128, 129, ncols_local - 1], rng_s.integers(0, ncols_local, 58)]))
+        cols = cols[(cols >= 0) & (cols < ncols_local)]
+        a64 = act_dev.T.double().cpu().numpy()                      # (M, kdim)
+        w64 = W_dev[torch.from_numpy(cols).cuda()].double().cpu().numpy().T   # (kdim, ncols)
+        ref = a64 @ w64
+        got = out_dev[torch.from_numpy(cols + col0).cuda()].double().cpu().numpy().T
+        scale = float(out_dev.abs().max().item())
+        return float(np.abs(got - ref).max() / scale)
+
+    err1 = sampled_error(batch, W1, out1, s1, c1, K1)
+    err2 = sampled_error(out1, W2, out2, s2, c2, N1)
+
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -328,6 +343,8 @@ def main():
                    "l2": "inputs larger than L2 (19 GB of weights stream once per step)", "flops_per_step": FLOPS_STEP},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": M * K1 * 4,
                 "d2h_bytes_per_step": M * N2 * 4, "result_checksum": checksum},
+        "accuracy": {"metric": "max |C - C64| / max |C| over 64 sampled columns of rank 0's shard, fp64 host product of the same inputs",
+                     "layer1": err1, "layer2": err2},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": {"kernel": "cn_gemm_tc_kernel (layer 1, per rank)", "bound": "tensor", "achieved": achieved, "peak": peak,

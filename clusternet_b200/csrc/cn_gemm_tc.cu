@@ -33,22 +33,28 @@
 #include "cn_epilogue.cuh"
 #include "cn_gemm.h"
 
-#define TC_THREADS 192
 #define TC_BM 128          // activation rows per CTA = UMMA N
 #define TC_BN 128          // W columns per tile       = UMMA M
 #define TC_BK 32           // fp32 per 128-byte swizzle row
 #define TC_TILE_BYTES (128 * 128)
+#define TC_CHAIN 8         // K blocks (of 32) accumulated in TMEM before the sum is drained to registers
 #define TC_WAIT_LIMIT (6000000000LL)   // clock cycles (~3 s)
 
 template <int NT>
 struct TcCfg {
+    static constexpr int THREADS = 256 + 128 * NT;    // WG0 (producer, MMA), WG1 (converters), NT drain warpgroups
     static constexpr int SMEM_STAGES = NT == 1 ? 4 : 3;
     static constexpr int TMEM_STAGES = NT == 1 ? 4 : 2;
+    static constexpr int ACC_BUFS = NT == 1 ? 2 : 1;  // accumulators per W tile
     static constexpr int STAGE_BYTES = (NT + 2) * TC_TILE_BYTES;
-    static constexpr int ACC_COL = 0;                 // NT accumulators of 128 columns
-    static constexpr int A_COL = NT * TC_BM;          // then TMEM_STAGES x NT x (32 hi + 32 lo) columns
+    static constexpr int ACC_COL = 0;                 // NT * ACC_BUFS accumulators of 128 columns
+    static constexpr int A_COL = NT * ACC_BUFS * TC_BM;   // then TMEM_STAGES x NT x (32 hi + 32 lo) columns
     static constexpr int A_STAGE_COLS = NT * 64;
     static constexpr int SMEM_BYTES = SMEM_STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    // register budgets after the warpgroups re-balance (multiples of 8); launch value is 65536 / THREADS
+    static constexpr int REGS_WG0 = 56;
+    static constexpr int REGS_CONV = 72;
+    static constexpr int REGS_DRAIN = NT == 1 ? 232 : 192;
 };
 
 struct TcParams {
@@ -167,6 +173,14 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
           "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t to_tf32(float x)
@@ -227,8 +241,20 @@ cn_act_split_kernel(const float *__restrict__ A, int64_t lda, int64_t M, int64_t
 }
 
 // -------------------------------------------------------------------------------------------------- main kernel
+// Warp roles (warpgroups of 4 warps so that register budgets can be moved between them):
+//   WG0  warp 0: TMA producer, warp 1: MMA issuer + TMEM owner, warps 2-3 idle
+//   WG1  warps 4-7:  converters (raw W tile in shared memory -> TF32 hi / lo planes in TMEM)
+//   WG2  warps 8-11: accumulator drain + epilogue of W tile 0
+//   WG3  warps 12-15 (NT == 2 only): the same for W tile 1
+//
+// Accumulation chains.  The tensor core adds into its fp32 accumulator with truncation, so a long chain of
+// accumulating MMAs drifts (about 6e-8 of the running sum per step, all in one direction).  The K loop is therefore
+// cut into chains of TC_CHAIN K blocks: each chain starts a fresh TMEM accumulator, and when it ends the drain warps
+// read it with tcgen05.ld and add it, in round-to-nearest fp32, to running sums that they keep in registers
+// (one thread = one output column n, 128 sums = 128 rows m).  With two W tiles per CTA the drain of one tile runs
+// while the MMAs of the other tile execute; with one tile the accumulator is double-buffered in TMEM instead.
 template <int NT, bool MODE3X>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TcCfg<NT>::THREADS, 1)
 cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_ahi,
                   const __grid_constant__ CUtensorMap tm_alo, const TcParams p)
 {
@@ -243,10 +269,11 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::SMEM_STAGES + s); };
     auto tfull_bar = [&](int t) { return bar_base + 8u * (2 * Cfg::SMEM_STAGES + t); };
     auto tempty_bar = [&](int t) { return bar_base + 8u * (2 * Cfg::SMEM_STAGES + Cfg::TMEM_STAGES + t); };
-    const uint32_t acc_bar = bar_base + 8u * (2 * Cfg::SMEM_STAGES + 2 * Cfg::TMEM_STAGES);
-    volatile uint32_t *tmem_holder = reinterpret_cast<volatile uint32_t *>(bar_gen + 192);
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(bar_gen + 196);
-    volatile int *last_flag = reinterpret_cast<volatile int *>(bar_gen + 200);
+    auto accfull_bar = [&](int w, int b) { return bar_base + 8u * (2 * Cfg::SMEM_STAGES + 2 * Cfg::TMEM_STAGES + w * Cfg::ACC_BUFS + b); };
+    auto accempty_bar = [&](int w, int b) { return bar_base + 8u * (2 * Cfg::SMEM_STAGES + 2 * Cfg::TMEM_STAGES + NT * Cfg::ACC_BUFS + w * Cfg::ACC_BUFS + b); };
+    volatile uint32_t *tmem_holder = reinterpret_cast<volatile uint32_t *>(bar_gen + 224);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(bar_gen + 228);
+    volatile int *last_flag = reinterpret_cast<volatile int *>(bar_gen + 232);   // one word per W tile
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -260,13 +287,16 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     int kb_end = kb_begin + p.kb_per_split;
     if (kb_end > p.kb_total) kb_end = p.kb_total;
     const int num_kb = kb_end - kb_begin;   // >= 1 by construction on the host
+    const int num_chains = (num_kb + TC_CHAIN - 1) / TC_CHAIN;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::SMEM_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int t = 0; t < Cfg::TMEM_STAGES; ++t) { mbar_init(tfull_bar(t), 128); mbar_init(tempty_bar(t), 1); }
-        mbar_init(acc_bar, 1);
+        for (int w = 0; w < NT; ++w)
+            for (int b = 0; b < Cfg::ACC_BUFS; ++b) { mbar_init(accfull_bar(w, b), 1); mbar_init(accempty_bar(w, b), 128); }
         *abort_flag = 0;
-        *last_flag = 0;
+        last_flag[0] = 0;
+        last_flag[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {   // this warp owns the tensor-memory allocation
@@ -278,72 +308,87 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
 
-    if (warp == 0) {
-        // ---------------------------------------------------------------- TMA producer
-        if (lane == 0) {
-            int issued = 0;
-            for (int i = 0; i < num_kb; ++i) {
-                const int s = i % Cfg::SMEM_STAGES;
-                const uint32_t ph = (uint32_t)(i / Cfg::SMEM_STAGES) & 1u;
-                if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, 1u)) break;
-                const uint32_t stage = smem_base + s * Cfg::STAGE_BYTES;
-                mbar_expect_tx(full_bar(s), (uint32_t)((NT + (MODE3X ? 2 : 1)) * TC_TILE_BYTES));
-                const int32_t kx = (kb_begin + i) * TC_BK;
-#pragma unroll
-                for (int t = 0; t < NT; ++t)
-                    tma_load_2d(stage + t * TC_TILE_BYTES, &tm_w, full_bar(s), kx, (int32_t)(n0 + t * TC_BN));
-                tma_load_2d(stage + NT * TC_TILE_BYTES, &tm_ahi, full_bar(s), kx, (int32_t)m0);
-                if (MODE3X) tma_load_2d(stage + (NT + 1) * TC_TILE_BYTES, &tm_alo, full_bar(s), kx, (int32_t)m0);
-                issued = i + 1;
-            }
-            if (*abort_flag) {
-                // give copies that are still in flight a bounded chance to land before the CTA exits
-                for (int i = issued > Cfg::SMEM_STAGES ? issued - Cfg::SMEM_STAGES : 0; i < issued; ++i) {
+    if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_WG0));
+        if (warp == 0) {
+            // ------------------------------------------------------------ TMA producer
+            if (lane == 0) {
+                int issued = 0;
+                for (int i = 0; i < num_kb; ++i) {
                     const int s = i % Cfg::SMEM_STAGES;
                     const uint32_t ph = (uint32_t)(i / Cfg::SMEM_STAGES) & 1u;
-                    const long long t0 = clock64();
-                    while (!mbar_try(full_bar(s), ph) && clock64() - t0 < 20000000LL) {}
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, 1u)) break;
+                    const uint32_t stage = smem_base + s * Cfg::STAGE_BYTES;
+                    mbar_expect_tx(full_bar(s), (uint32_t)((NT + (MODE3X ? 2 : 1)) * TC_TILE_BYTES));
+                    const int32_t kx = (kb_begin + i) * TC_BK;
+#pragma unroll
+                    for (int t = 0; t < NT; ++t)
+                        tma_load_2d(stage + t * TC_TILE_BYTES, &tm_w, full_bar(s), kx, (int32_t)(n0 + t * TC_BN));
+                    tma_load_2d(stage + NT * TC_TILE_BYTES, &tm_ahi, full_bar(s), kx, (int32_t)m0);
+                    if (MODE3X) tma_load_2d(stage + (NT + 1) * TC_TILE_BYTES, &tm_alo, full_bar(s), kx, (int32_t)m0);
+                    issued = i + 1;
                 }
-            }
-        }
-        __syncwarp();
-    } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_tf32(TC_BN, TC_BM);
-            bool ok = true;
-            for (int i = 0; i < num_kb && ok; ++i) {
-                const int s = i % Cfg::SMEM_STAGES, t = i % Cfg::TMEM_STAGES;
-                const uint32_t ph = (uint32_t)(i / Cfg::SMEM_STAGES) & 1u, tph = (uint32_t)(i / Cfg::TMEM_STAGES) & 1u;
-                ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 2u) && mbar_wait(tfull_bar(t), tph, abort_flag, p.status, 3u);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t stage = smem_base + s * Cfg::STAGE_BYTES;
-                const uint64_t bhi = make_kmajor_sw128_desc(stage + NT * TC_TILE_BYTES);
-                const uint64_t blo = make_kmajor_sw128_desc(stage + (NT + 1) * TC_TILE_BYTES);
-#pragma unroll
-                for (int w = 0; w < NT; ++w) {
-                    const uint32_t acc = tmem_base + Cfg::ACC_COL + w * TC_BM;
-                    const uint32_t a_hi = tmem_base + Cfg::A_COL + t * Cfg::A_STAGE_COLS + w * 64;
-                    const uint32_t a_lo = a_hi + 32;
-#pragma unroll
-                    for (int j = 0; j < TC_BK / 8; ++j) {
-                        // 8 TF32 per k-step: 8 TMEM columns of A, 32 bytes (descriptor units of 16 B) of B
-                        tc_mma_ts(acc, a_hi + j * 8, bhi + (uint64_t)(j * 2), idesc, (i > 0 || j > 0) ? 1u : 0u);
-                        if (MODE3X) {
-                            tc_mma_ts(acc, a_lo + j * 8, bhi + (uint64_t)(j * 2), idesc, 1u);
-                            tc_mma_ts(acc, a_hi + j * 8, blo + (uint64_t)(j * 2), idesc, 1u);
-                        }
+                if (*abort_flag) {
+                    // give copies that are still in flight a bounded chance to land before the CTA exits
+                    for (int i = issued > Cfg::SMEM_STAGES ? issued - Cfg::SMEM_STAGES : 0; i < issued; ++i) {
+                        const int s = i % Cfg::SMEM_STAGES;
+                        const uint32_t ph = (uint32_t)(i / Cfg::SMEM_STAGES) & 1u;
+                        const long long t0 = clock64();
+                        while (!mbar_try(full_bar(s), ph) && clock64() - t0 < 20000000LL) {}
                     }
                 }
-                tc_commit(empty_bar(s));    // shared-memory stage may be refilled once these MMAs retire
-                tc_commit(tempty_bar(t));   // and the TMEM operand stage rewritten
             }
-            if (ok) tc_commit(acc_bar);
+            __syncwarp();
+        } else if (warp == 1) {
+            // ------------------------------------------------------------ MMA issuer
+            if (lane == 0) {
+                constexpr uint32_t idesc = make_idesc_tf32(TC_BN, TC_BM);
+                bool ok = true;
+                for (int i = 0; i < num_kb && ok; ++i) {
+                    const int s = i % Cfg::SMEM_STAGES, t = i % Cfg::TMEM_STAGES;
+                    const uint32_t ph = (uint32_t)(i / Cfg::SMEM_STAGES) & 1u, tph = (uint32_t)(i / Cfg::TMEM_STAGES) & 1u;
+                    const int chain = i / TC_CHAIN;
+                    const bool chain_first = (i % TC_CHAIN) == 0;
+                    const bool chain_last = (i % TC_CHAIN) == TC_CHAIN - 1 || i == num_kb - 1;
+                    const int ab = chain % Cfg::ACC_BUFS;
+                    const uint32_t aph = (uint32_t)(chain / Cfg::ACC_BUFS) & 1u;
+                    ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 2u) && mbar_wait(tfull_bar(t), tph, abort_flag, p.status, 3u);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t stage = smem_base + s * Cfg::STAGE_BYTES;
+                    const uint64_t bhi = make_kmajor_sw128_desc(stage + NT * TC_TILE_BYTES);
+                    const uint64_t blo = make_kmajor_sw128_desc(stage + (NT + 1) * TC_TILE_BYTES);
+#pragma unroll
+                    for (int w = 0; w < NT; ++w) {
+                        if (chain_first) {   // the drain warps must have emptied this accumulator
+                            ok = mbar_wait(accempty_bar(w, ab), aph ^ 1u, abort_flag, p.status, 7u);
+                            if (!ok) break;
+                            tc_fence_after();
+                        }
+                        const uint32_t acc = tmem_base + Cfg::ACC_COL + (w * Cfg::ACC_BUFS + ab) * TC_BM;
+                        const uint32_t a_hi = tmem_base + Cfg::A_COL + t * Cfg::A_STAGE_COLS + w * 64;
+                        const uint32_t a_lo = a_hi + 32;
+#pragma unroll
+                        for (int j = 0; j < TC_BK / 8; ++j) {
+                            // 8 TF32 per k-step: 8 TMEM columns of A, 32 bytes (descriptor units of 16 B) of B
+                            tc_mma_ts(acc, a_hi + j * 8, bhi + (uint64_t)(j * 2), idesc, (!chain_first || j > 0) ? 1u : 0u);
+                            if (MODE3X) {
+                                tc_mma_ts(acc, a_lo + j * 8, bhi + (uint64_t)(j * 2), idesc, 1u);
+                                tc_mma_ts(acc, a_hi + j * 8, blo + (uint64_t)(j * 2), idesc, 1u);
+                            }
+                        }
+                        if (chain_last) tc_commit(accfull_bar(w, ab));
+                    }
+                    if (!ok) break;
+                    tc_commit(empty_bar(s));    // shared-memory stage may be refilled once these MMAs retire
+                    tc_commit(tempty_bar(t));   // and the TMEM operand stage rewritten
+                }
+            }
+            __syncwarp();
         }
-        __syncwarp();
-    } else {
-        // ---------------------------------------------------------------- converter warps (2..5), then epilogue
+    } else if (warp < 8) {
+        // ---------------------------------------------------------------- converter warps
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_CONV));
         const int q = warp & 3;                       // TMEM lane quarter this warp may touch
         const int row = q * 32 + lane;                // row of the W tile = TMEM lane
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
@@ -356,133 +401,139 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             if (!ok) break;
             tc_fence_after();
             const uint8_t *stage = smem_gen + s * Cfg::STAGE_BYTES;
-#pragma unroll
+#pragma unroll 1
             for (int w = 0; w < NT; ++w) {
                 const uint8_t *rowp = stage + w * TC_TILE_BYTES + row * 128;
-                uint32_t hi[32], lo[32];
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    // 16-byte chunk c of row r sits at chunk position c ^ (r & 7) under the 128-byte swizzle
-                    const float4 v = *reinterpret_cast<const float4 *>(rowp + ((c ^ (row & 7)) << 4));
-                    const float x[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const uint32_t h = to_tf32(x[e]);
-                        hi[c * 4 + e] = h;
-                        if (MODE3X) lo[c * 4 + e] = to_tf32(x[e] - __uint_as_float(h));
-                    }
-                }
                 const uint32_t a_hi = tmem_base + lane_addr + Cfg::A_COL + t * Cfg::A_STAGE_COLS + w * 64;
-                tc_st32(a_hi, hi);
-                if (MODE3X) tc_st32(a_hi + 32, lo);
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t hi[16], lo[16];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        // 16-byte chunk c of row r sits at chunk position c ^ (r & 7) under the 128-byte swizzle
+                        const float4 v = *reinterpret_cast<const float4 *>(rowp + (((half * 4 + c) ^ (row & 7)) << 4));
+                        const float x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const uint32_t h = to_tf32(x[e]);
+                            hi[c * 4 + e] = h;
+                            if (MODE3X) lo[c * 4 + e] = to_tf32(x[e] - __uint_as_float(h));
+                        }
+                    }
+                    tc_st16(a_hi + half * 16, hi);
+                    if (MODE3X) tc_st16(a_hi + 32 + half * 16, lo);
+                }
             }
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(tfull_bar(t));
         }
-
-        // ------------------------------------------------------------ epilogue (same 128 threads)
-        if (ok) ok = mbar_wait(acc_bar, 0u, abort_flag, p.status, 6u);
-        {   // all 128 epilogue threads go on together or not at all
+    } else {
+        // ---------------------------------------------------------------- drain + epilogue warps, one warpgroup per W tile
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_DRAIN));
+        const int w = (warp - 8) >> 2;                // W tile of this warpgroup
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+        const int et = threadIdx.x & 127;
+        float acc[TC_BM];
+#pragma unroll
+        for (int i = 0; i < TC_BM; ++i) acc[i] = 0.0f;
+        bool ok = true;
+        for (int c = 0; c < num_chains && ok; ++c) {
+            const int ab = c % Cfg::ACC_BUFS;
+            const uint32_t aph = (uint32_t)(c / Cfg::ACC_BUFS) & 1u;
+            ok = mbar_wait(accfull_bar(w, ab), aph, abort_flag, p.status, 6u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t src = tmem_base + lane_addr + Cfg::ACC_COL + (w * Cfg::ACC_BUFS + ab) * TC_BM;
+#pragma unroll
+            for (int cc = 0; cc < TC_BM / 32; ++cc) {
+                uint32_t r[32];
+                tc_ld32(src + cc * 32, r);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[cc * 32 + i] += __uint_as_float(r[i]);
+            }
+            tc_fence_before();
+            mbar_arrive(accempty_bar(w, ab));
+        }
+        {   // all 128 threads of the warpgroup go on together or not at all
             uint32_t all_ok;
             asm volatile(
                 "{\n\t.reg .pred pi, po;\n\t"
                 "setp.ne.u32 pi, %1, 0;\n\t"
-                "bar.red.and.pred po, 1, 128, pi;\n\t"
+                "bar.red.and.pred po, %2, 128, pi;\n\t"
                 "selp.u32 %0, 1, 0, po;\n\t}"
-                : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
+                : "=r"(all_ok) : "r"((uint32_t)ok), "r"(1 + w) : "memory");
             ok = all_ok != 0;
         }
         if (ok) {
-            tc_fence_after();
-            const int et = threadIdx.x - 64;           // 0..127
-            const int64_t tile_lin = tile_id;
-            const size_t tile_elems = (size_t)NT * TC_BM * TC_BN;
+            const int64_t ticket_id = tile_id * NT + w;
+            const size_t tile_elems = (size_t)TC_BM * TC_BN;
             bool do_final = true;
             if (p.splits > 1) {
-                float *P = p.partials + ((size_t)tile_lin * p.splits + split) * tile_elems;
-#pragma unroll 1
-                for (int w = 0; w < NT; ++w) {
-#pragma unroll 1
-                    for (int c = 0; c < TC_BM / 32; ++c) {
-                        uint32_t r[32];
-                        tc_ld32(tmem_base + lane_addr + Cfg::ACC_COL + w * TC_BM + c * 32, r);
+                float *P = p.partials + ((size_t)ticket_id * p.splits + split) * tile_elems;
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            P[((size_t)w * TC_BM + c * 32 + i) * TC_BN + row] = __uint_as_float(r[i]);
+                for (int i = 0; i < TC_BM; ++i) P[(size_t)i * TC_BN + row] = acc[i];
+                __threadfence();
+                asm volatile("bar.sync %0, 128;" ::"r"(1 + w) : "memory");
+                if (et == 0) {
+                    const unsigned int prev = atomicAdd(p.tickets + ticket_id, 1u);
+                    const int last = prev == (unsigned int)(p.splits - 1);
+                    if (last) p.tickets[ticket_id] = 0u;   // ready for the next launch
+                    last_flag[w] = last;
+                }
+                asm volatile("bar.sync %0, 128;" ::"r"(1 + w) : "memory");
+                do_final = last_flag[w] != 0;
+                if (do_final) {
+                    __threadfence();
+                    // fixed summation order over the splits: reproducible whichever CTA comes last
+#pragma unroll
+                    for (int i = 0; i < TC_BM; ++i) acc[i] = 0.0f;
+                    for (int sp = 0; sp < p.splits; ++sp) {
+                        const float *Q = p.partials + ((size_t)ticket_id * p.splits + sp) * tile_elems;
+#pragma unroll
+                        for (int i = 0; i < TC_BM; ++i) acc[i] += __ldcg(Q + (size_t)i * TC_BN + row);
                     }
                 }
-                __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (et == 0) {
-                    const unsigned int prev = atomicAdd(p.tickets + tile_lin, 1u);
-                    const int last = prev == (unsigned int)(p.splits - 1);
-                    if (last) p.tickets[tile_lin] = 0u;   // ready for the next launch
-                    *last_flag = last;
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                do_final = *last_flag != 0;
-                if (do_final) __threadfence();
             }
             if (do_final) {
                 const int L = p.maxout_level;
-#pragma unroll 1
-                for (int w = 0; w < NT; ++w) {
-                    const int64_t n = n0 + w * TC_BN + row;
-                    const float bias = (p.bias && n < p.N) ? p.bias[n] : 0.0f;
-#pragma unroll 1
-                    for (int c = 0; c < TC_BM / 32; ++c) {
-                        float v[32];
-                        if (p.splits > 1) {
-                            // fixed summation order over the splits: reproducible whichever CTA comes last
+                const int64_t n = n0 + w * TC_BN + row;
+                const float bias = (p.bias && n < p.N) ? p.bias[n] : 0.0f;
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = 0.0f;
-                            for (int sp = 0; sp < p.splits; ++sp) {
-                                const float *P = p.partials + ((size_t)tile_lin * p.splits + sp) * tile_elems;
+                for (int i = 0; i < TC_BM; ++i) acc[i] = cn_apply_activation(p.bias ? acc[i] + bias : acc[i], p.act);
+                if (L <= 1) {
+                    if (n < p.N) {
+                        float *dst = p.C + n * p.ldc + m0;
+                        if (m0 + TC_BM <= p.M && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
 #pragma unroll
-                                for (int i = 0; i < 32; ++i) v[i] += __ldcg(P + ((size_t)w * TC_BM + c * 32 + i) * TC_BN + row);
-                            }
+                            for (int i = 0; i < TC_BM; i += 4)
+                                *reinterpret_cast<float4 *>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
                         } else {
-                            uint32_t r[32];
-                            tc_ld32(tmem_base + lane_addr + Cfg::ACC_COL + w * TC_BM + c * 32, r);
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                            for (int i = 0; i < TC_BM; ++i)
+                                if (m0 + i < p.M) dst[i] = acc[i];
                         }
+                    }
+                } else {
+                    // maxout over L consecutive columns = L adjacent lanes (L is a power of two <= 32).
+                    // Same comparison tree as the reference's 32-slot reduction: at offsets L/2 .. 1 slot t
+                    // takes slot t+offset when strictly smaller; larger offsets only meet -FLT_MAX padding.
+                    const int tl = lane & (L - 1);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = cn_apply_activation(p.bias ? v[i] + bias : v[i], p.act);
-                        const int64_t mbase = m0 + c * 32;
-                        if (L <= 1) {
-                            if (n < p.N) {
-                                float *dst = p.C + n * p.ldc + mbase;
-                                if (mbase + 32 <= p.M && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
-#pragma unroll
-                                    for (int i = 0; i < 32; i += 4)
-                                        *reinterpret_cast<float4 *>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                                } else {
-#pragma unroll
-                                    for (int i = 0; i < 32; ++i)
-                                        if (mbase + i < p.M) dst[i] = v[i];
-                                }
-                            }
-                        } else {
-                            // maxout over L consecutive columns = L adjacent lanes (L is a power of two <= 32).
-                            // Same comparison tree as the reference's 32-slot reduction: at offsets L/2 .. 1 slot t
-                            // takes slot t+offset when strictly smaller; larger offsets only meet -FLT_MAX padding.
-                            const int tl = lane & (L - 1);
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                float val = v[i], idx = (float)n;
-                                for (int off = L >> 1; off > 0; off >>= 1) {
-                                    const float ov = __shfl_down_sync(0xffffffffu, val, off, L);
-                                    const float oi = __shfl_down_sync(0xffffffffu, idx, off, L);
-                                    if (tl < off && val < ov) { val = ov; idx = oi; }
-                                }
-                                if (tl == 0 && n < p.N && mbase + i < p.M) {
-                                    const int64_t g = n / L;
-                                    p.C[g * p.ldc + mbase + i] = val;
-                                    if (p.argmax) p.argmax[g * p.ldc + mbase + i] = idx;
-                                }
-                            }
+                    for (int i = 0; i < TC_BM; ++i) {
+                        float val = acc[i], idx = (float)n;
+                        for (int off = L >> 1; off > 0; off >>= 1) {
+                            const float ov = __shfl_down_sync(0xffffffffu, val, off, L);
+                            const float oi = __shfl_down_sync(0xffffffffu, idx, off, L);
+                            if (tl < off && val < ov) { val = ov; idx = oi; }
+                        }
+                        if (tl == 0 && n < p.N && m0 + i < p.M) {
+                            const int64_t g = n / L;
+                            p.C[g * p.ldc + m0 + i] = val;
+                            if (p.argmax) p.argmax[g * p.ldc + m0 + i] = idx;
                         }
                     }
                 }
@@ -564,7 +615,7 @@ template <int NT, bool MODE3X>
 static int launch_cfg(const CUtensorMap &mw, const CUtensorMap &mhi, const CUtensorMap &mlo, const TcParams &prm, int64_t grid, cudaStream_t s)
 {
     CN_CUDA(cudaFuncSetAttribute(cn_gemm_tc_kernel<NT, MODE3X>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<NT>::SMEM_BYTES));
-    cn_gemm_tc_kernel<NT, MODE3X><<<(unsigned)grid, TC_THREADS, TcCfg<NT>::SMEM_BYTES, s>>>(mw, mhi, mlo, prm);
+    cn_gemm_tc_kernel<NT, MODE3X><<<(unsigned)grid, TcCfg<NT>::THREADS, TcCfg<NT>::SMEM_BYTES, s>>>(mw, mhi, mlo, prm);
     CN_CUDA(cudaGetLastError());
     cn_count_launch();
     return CN_OK;
@@ -607,7 +658,7 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
     const int kb_total = (int)(Kpad / TC_BK);
     int splits = pick_splits(tiles, kb_total, ctx->sm_count);
     if (const char *e = getenv("CN_GEMM_SPLITS")) { int v = atoi(e); if (v >= 1 && v <= kb_total) splits = v; }
-    if (tiles > CN_GEMM_MAX_TICKETS) splits = 1;
+    if (tiles * nt > CN_GEMM_MAX_TICKETS) splits = 1;
     int kb_per_split = (kb_total + splits - 1) / splits;
     splits = (kb_total + kb_per_split - 1) / kb_per_split;   // no empty split
     CN_REQUIRE(tiles * splits < (1LL << 31), CN_ERR_UNSUPPORTED, "cn_gemm_f32: too many work units");
