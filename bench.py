@@ -32,9 +32,18 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 M, K1, N1, N2 = 128, 100000, 40000, 20000
-FLOPS_L1 = 2.0 * M * K1 * N1
-FLOPS_L2 = 2.0 * M * N1 * N2
-FLOPS_STEP = FLOPS_L1 + FLOPS_L2          # 1.2288e12
+
+
+def set_sizes(k1, n1, n2):
+    """The headline workload is fixed; smaller N1 / N2 exist only so that a profiler capture stays small."""
+    global K1, N1, N2, FLOPS_L1, FLOPS_L2, FLOPS_STEP
+    K1, N1, N2 = k1, n1, n2
+    FLOPS_L1 = 2.0 * M * K1 * N1
+    FLOPS_L2 = 2.0 * M * N1 * N2
+    FLOPS_STEP = FLOPS_L1 + FLOPS_L2          # 1.2288e12 at the headline sizes
+
+
+set_sizes(K1, N1, N2)
 
 
 def measured_peaks():
@@ -188,6 +197,10 @@ def main():
     ap.add_argument("--exchange", default="fp32", choices=["fp32", "8bit"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-codec", action="store_true")
+    ap.add_argument("--only-codec", action="store_true", help="run the codec measurements alone (small profiler captures)")
+    ap.add_argument("--k1", type=int, default=K1, help="profiling aid: inner dimension of layer 1")
+    ap.add_argument("--n1", type=int, default=N1, help="profiling aid: columns of W1 (headline: 40000)")
+    ap.add_argument("--n2", type=int, default=N2, help="profiling aid: columns of W2 (headline: 20000)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -195,6 +208,8 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank)
         return
+    headline = (args.k1, args.n1, args.n2) == (K1, N1, N2)
+    set_sizes(args.k1, args.n1, args.n2)
     args.warmup = max(args.warmup, 3)
 
     import torch
@@ -214,6 +229,10 @@ def main():
         dist.broadcast_object_list(ids, src=0)
         ctx.comm_init(ids[0], rank, world)
     peaks = measured_peaks()
+    if args.only_codec:
+        if rank == 0:
+            print(json.dumps({"codec": codec_bench(ctx, torch, peaks)}), flush=True)
+        return
     mode = _lib.GEMM_3XTF32 if args.mode == "3xtf32" else _lib.GEMM_TF32
     exchange = 1 if args.exchange == "8bit" else 0
 
@@ -338,9 +357,10 @@ def main():
         "metric": "dotMPI TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "README dotMPI two-layer skinny GEMM: 128x100000 . 100000x40000 . 40000x20000, W column-sharded",
+        "config": {"workload": ("README dotMPI two-layer skinny GEMM: " if headline else "REDUCED (profiling) two-layer skinny GEMM: ") +
+                               f"128x{K1} . {K1}x{N1} . {N1}x{N2}, W column-sharded",
                    "gemm_mode": args.mode, "exchange": args.exchange, "parallelism": f"tp{world} (columns of W)",
-                   "l2": "inputs larger than L2 (19 GB of weights stream once per step)", "flops_per_step": FLOPS_STEP},
+                   "l2": f"inputs larger than L2 ({4e-9 * (K1 * N1 + N1 * N2):.1f} GB of weights stream once per step)", "flops_per_step": FLOPS_STEP},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": M * K1 * 4,
                 "d2h_bytes_per_step": M * N2 * 4, "result_checksum": checksum},
         "accuracy": {"metric": "max |C - C64| / max |C| over 64 sampled columns of rank 0's shard, fp64 host product of the same inputs",

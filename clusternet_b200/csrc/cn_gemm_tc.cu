@@ -37,24 +37,32 @@
 #define TC_BN 128          // W columns per tile       = UMMA M
 #define TC_BK 32           // fp32 per 128-byte swizzle row
 #define TC_TILE_BYTES (128 * 128)
-#define TC_CHAIN 8         // K blocks (of 32) accumulated in TMEM before the sum is drained to registers
+#define TC_CHAIN_DEFAULT 16   // K blocks (of 32) accumulated in TMEM before the sum is drained to registers
+#define TC_DRAIN_SLEEP_NS 200   // poll interval of the drain warps while a chain accumulates
 #define TC_WAIT_LIMIT (6000000000LL)   // clock cycles (~3 s)
 
 template <int NT>
 struct TcCfg {
-    static constexpr int THREADS = 256 + 128 * NT;    // WG0 (producer, MMA), WG1 (converters), NT drain warpgroups
-    static constexpr int SMEM_STAGES = NT == 1 ? 4 : 3;
+    static constexpr int THREADS = 256 + 128 * NT;    // WG0 (producers, MMA), WG1 (converters), NT drain warpgroups
+    // Two shared-memory rings with their own depth: raw W tiles (released by the converters as soon as they have
+    // been read) and activation hi / lo tiles (released when the MMAs that read them retire).
+    static constexpr int W_STAGES = NT == 1 ? 4 : 3;
+    static constexpr int A_STAGES = NT == 1 ? 4 : 3;
+    static constexpr int W_STAGE_BYTES = NT * TC_TILE_BYTES;
+    static constexpr int A_STAGE_BYTES = 2 * TC_TILE_BYTES;
+    static constexpr int W_RING = 0;
+    static constexpr int A_RING = W_STAGES * W_STAGE_BYTES;
+    static constexpr int RING_BYTES = A_RING + A_STAGES * A_STAGE_BYTES;
     static constexpr int TMEM_STAGES = NT == 1 ? 4 : 2;
     static constexpr int ACC_BUFS = NT == 1 ? 2 : 1;  // accumulators per W tile
-    static constexpr int STAGE_BYTES = (NT + 2) * TC_TILE_BYTES;
     static constexpr int ACC_COL = 0;                 // NT * ACC_BUFS accumulators of 128 columns
     static constexpr int A_COL = NT * ACC_BUFS * TC_BM;   // then TMEM_STAGES x NT x (32 hi + 32 lo) columns
     static constexpr int A_STAGE_COLS = NT * 64;
-    static constexpr int SMEM_BYTES = SMEM_STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int SMEM_BYTES = RING_BYTES + 1024 /*align*/ + 512 /*barriers*/;
     // register budgets after the warpgroups re-balance (multiples of 8); launch value is 65536 / THREADS
-    static constexpr int REGS_WG0 = 56;
+    static constexpr int REGS_WG0 = 88;
     static constexpr int REGS_CONV = 72;
-    static constexpr int REGS_DRAIN = NT == 1 ? 232 : 192;
+    static constexpr int REGS_DRAIN = NT == 1 ? 232 : 176;
 };
 
 struct TcParams {
@@ -70,6 +78,7 @@ struct TcParams {
     int splits;
     int kb_per_split;       // K blocks (of 32) per split
     int kb_total;
+    int chain_kb;           // K blocks accumulated in TMEM before the sum is drained to registers
     float *partials;        // [tile][split][NT][128 m][128 n]
     unsigned int *tickets;  // one per tile, self-resetting
     unsigned int *status;
@@ -101,11 +110,15 @@ __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity)
     return done;
 }
 // Bounded wait.  Returns false when the limit ran out or another role already gave up.
+// SLEEP_NS > 0 parks the warp between polls: used by roles that wait for a long time (the drain warps sit out a
+// whole accumulation chain) so that their polling does not take issue slots from the converter and MMA warps.
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned int *status, unsigned int code)
 {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t it = 1;; ++it) {
+        if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if (mbar_try(bar, parity)) return true;
         if ((it & 63u) == 0u) {
             if (*abort_flag) return false;
@@ -133,14 +146,16 @@ __device__ __forceinline__ void tc_commit(uint32_t bar)
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// D[tmem] (+)= A[tmem] * B[smem desc]; A: 128 lanes x 8 columns of TF32, B: 128 x 8 K-major TF32 tile
-__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+// D[tmem] (+)= A[tmem] * B[smem desc]; A: 128 lanes x 8 columns of TF32, B: 128 x 8 K-major TF32 tile.
+// The descriptor travels as two 32-bit halves so that stepping along K is a 32-bit add on the low half.
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_desc_lo, uint32_t b_desc_hi, uint32_t idesc, uint32_t accumulate)
 {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+        "{\n\t.reg .pred p;\n\t.reg .b64 bd;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 bd, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], bd, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_desc_lo), "r"(b_desc_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
 
 #define TC_R32(a) \
@@ -183,11 +198,12 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16])
 }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// fp32 -> TF32 (10 mantissa bits kept, low 13 bits zero), round to nearest with ties away from zero: add half a
+// TF32 ulp to the magnitude bits and truncate.  Same result as cvt.rna.tf32.f32 for finite inputs, but two full-rate
+// integer operations; the cvt form issues at a fraction of that rate and made the converter warps the bottleneck.
 __device__ __forceinline__ uint32_t to_tf32(float x)
 {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return r;
+    return (__float_as_uint(x) + 0x1000u) & 0xffffe000u;
 }
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (32 fp32) with the 128-byte
@@ -242,14 +258,15 @@ cn_act_split_kernel(const float *__restrict__ A, int64_t lda, int64_t M, int64_t
 
 // -------------------------------------------------------------------------------------------------- main kernel
 // Warp roles (warpgroups of 4 warps so that register budgets can be moved between them):
-//   WG0  warp 0: TMA producer, warp 1: MMA issuer + TMEM owner, warps 2-3 idle
+//   WG0  warp 0: TMA producer for W, warp 1: MMA issuer of W tile 0 + TMEM owner, warp 2: TMA producer for the
+//        activations, warp 3: MMA issuer of W tile 1 (NT == 2)
 //   WG1  warps 4-7:  converters (raw W tile in shared memory -> TF32 hi / lo planes in TMEM)
 //   WG2  warps 8-11: accumulator drain + epilogue of W tile 0
 //   WG3  warps 12-15 (NT == 2 only): the same for W tile 1
 //
 // Accumulation chains.  The tensor core adds into its fp32 accumulator with truncation, so a long chain of
 // accumulating MMAs drifts (about 6e-8 of the running sum per step, all in one direction).  The K loop is therefore
-// cut into chains of TC_CHAIN K blocks: each chain starts a fresh TMEM accumulator, and when it ends the drain warps
+// cut into chains of a few hundred k (TC_CHAIN_DEFAULT K blocks): each chain starts a fresh TMEM accumulator, and when it ends the drain warps
 // read it with tcgen05.ld and add it, in round-to-nearest fp32, to running sums that they keep in registers
 // (one thread = one output column n, 128 sums = 128 rows m).  With two W tiles per CTA the drain of one tile runs
 // while the MMAs of the other tile execute; with one tile the accumulator is double-buffered in TMEM instead.
@@ -262,18 +279,26 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-    // barriers and small words sit after the stage buffers
-    const uint32_t bar_base = smem_base + Cfg::SMEM_STAGES * Cfg::STAGE_BYTES;
-    uint8_t *bar_gen = smem_gen + Cfg::SMEM_STAGES * Cfg::STAGE_BYTES;
-    auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::SMEM_STAGES + s); };
-    auto tfull_bar = [&](int t) { return bar_base + 8u * (2 * Cfg::SMEM_STAGES + t); };
-    auto tempty_bar = [&](int t) { return bar_base + 8u * (2 * Cfg::SMEM_STAGES + Cfg::TMEM_STAGES + t); };
-    auto accfull_bar = [&](int w, int b) { return bar_base + 8u * (2 * Cfg::SMEM_STAGES + 2 * Cfg::TMEM_STAGES + w * Cfg::ACC_BUFS + b); };
-    auto accempty_bar = [&](int w, int b) { return bar_base + 8u * (2 * Cfg::SMEM_STAGES + 2 * Cfg::TMEM_STAGES + NT * Cfg::ACC_BUFS + w * Cfg::ACC_BUFS + b); };
-    volatile uint32_t *tmem_holder = reinterpret_cast<volatile uint32_t *>(bar_gen + 224);
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(bar_gen + 228);
-    volatile int *last_flag = reinterpret_cast<volatile int *>(bar_gen + 232);   // one word per W tile
+    // barriers and small words sit after the rings
+    const uint32_t bar_base = smem_base + Cfg::RING_BYTES;
+    uint8_t *bar_gen = smem_gen + Cfg::RING_BYTES;
+    constexpr int B_WFULL = 0, B_WEMPTY = B_WFULL + Cfg::W_STAGES, B_AFULL = B_WEMPTY + Cfg::W_STAGES,
+                  B_AEMPTY = B_AFULL + Cfg::A_STAGES, B_TFULL = B_AEMPTY + Cfg::A_STAGES, B_TEMPTY = B_TFULL + Cfg::TMEM_STAGES,
+                  B_ACCFULL = B_TEMPTY + Cfg::TMEM_STAGES, B_ACCEMPTY = B_ACCFULL + NT * Cfg::ACC_BUFS,
+                  B_COUNT = B_ACCEMPTY + NT * Cfg::ACC_BUFS;
+    static_assert(B_COUNT * 8 <= 448, "barrier area");
+    auto bar = [&](int idx) { return bar_base + 8u * idx; };
+    auto wfull_bar = [&](int s) { return bar(B_WFULL + s); };
+    auto wempty_bar = [&](int s) { return bar(B_WEMPTY + s); };
+    auto afull_bar = [&](int s) { return bar(B_AFULL + s); };
+    auto aempty_bar = [&](int s) { return bar(B_AEMPTY + s); };
+    auto tfull_bar = [&](int t) { return bar(B_TFULL + t); };
+    auto tempty_bar = [&](int t) { return bar(B_TEMPTY + t); };
+    auto accfull_bar = [&](int w, int b) { return bar(B_ACCFULL + w * Cfg::ACC_BUFS + b); };
+    auto accempty_bar = [&](int w, int b) { return bar(B_ACCEMPTY + w * Cfg::ACC_BUFS + b); };
+    volatile uint32_t *tmem_holder = reinterpret_cast<volatile uint32_t *>(bar_gen + 448);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(bar_gen + 452);
+    volatile int *last_flag = reinterpret_cast<volatile int *>(bar_gen + 456);   // one word per W tile
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -287,11 +312,13 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     int kb_end = kb_begin + p.kb_per_split;
     if (kb_end > p.kb_total) kb_end = p.kb_total;
     const int num_kb = kb_end - kb_begin;   // >= 1 by construction on the host
-    const int num_chains = (num_kb + TC_CHAIN - 1) / TC_CHAIN;
+    const int chain_kb = p.chain_kb;
+    const int num_chains = (num_kb + chain_kb - 1) / chain_kb;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < Cfg::SMEM_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int t = 0; t < Cfg::TMEM_STAGES; ++t) { mbar_init(tfull_bar(t), 128); mbar_init(tempty_bar(t), 1); }
+        for (int s = 0; s < Cfg::W_STAGES; ++s) { mbar_init(wfull_bar(s), 1); mbar_init(wempty_bar(s), 128); }
+        for (int s = 0; s < Cfg::A_STAGES; ++s) { mbar_init(afull_bar(s), 1); mbar_init(aempty_bar(s), NT); }
+        for (int t = 0; t < Cfg::TMEM_STAGES; ++t) { mbar_init(tfull_bar(t), 128); mbar_init(tempty_bar(t), NT); }
         for (int w = 0; w < NT; ++w)
             for (int b = 0; b < Cfg::ACC_BUFS; ++b) { mbar_init(accfull_bar(w, b), 1); mbar_init(accempty_bar(w, b), 128); }
         *abort_flag = 0;
@@ -310,77 +337,97 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
 
     if (warp < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_WG0));
-        if (warp == 0) {
-            // ------------------------------------------------------------ TMA producer
+        if (warp == 0 || warp == 2) {
+            // ------------------------------------------------------------ TMA producers: warp 0 streams W, warp 2 the activations
             if (lane == 0) {
+                const bool is_w = warp == 0;
+                const int depth = is_w ? Cfg::W_STAGES : Cfg::A_STAGES;
                 int issued = 0;
                 for (int i = 0; i < num_kb; ++i) {
-                    const int s = i % Cfg::SMEM_STAGES;
-                    const uint32_t ph = (uint32_t)(i / Cfg::SMEM_STAGES) & 1u;
-                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, 1u)) break;
-                    const uint32_t stage = smem_base + s * Cfg::STAGE_BYTES;
-                    mbar_expect_tx(full_bar(s), (uint32_t)((NT + (MODE3X ? 2 : 1)) * TC_TILE_BYTES));
+                    const int s = i % depth;
+                    const uint32_t ph = (uint32_t)(i / depth) & 1u;
                     const int32_t kx = (kb_begin + i) * TC_BK;
+                    if (is_w) {
+                        if (!mbar_wait(wempty_bar(s), ph ^ 1u, abort_flag, p.status, 1u)) break;
+                        const uint32_t stage = smem_base + Cfg::W_RING + s * Cfg::W_STAGE_BYTES;
+                        mbar_expect_tx(wfull_bar(s), (uint32_t)Cfg::W_STAGE_BYTES);
 #pragma unroll
-                    for (int t = 0; t < NT; ++t)
-                        tma_load_2d(stage + t * TC_TILE_BYTES, &tm_w, full_bar(s), kx, (int32_t)(n0 + t * TC_BN));
-                    tma_load_2d(stage + NT * TC_TILE_BYTES, &tm_ahi, full_bar(s), kx, (int32_t)m0);
-                    if (MODE3X) tma_load_2d(stage + (NT + 1) * TC_TILE_BYTES, &tm_alo, full_bar(s), kx, (int32_t)m0);
+                        for (int t = 0; t < NT; ++t)
+                            tma_load_2d(stage + t * TC_TILE_BYTES, &tm_w, wfull_bar(s), kx, (int32_t)(n0 + t * TC_BN));
+                    } else {
+                        if (!mbar_wait(aempty_bar(s), ph ^ 1u, abort_flag, p.status, 8u)) break;
+                        const uint32_t stage = smem_base + Cfg::A_RING + s * Cfg::A_STAGE_BYTES;
+                        mbar_expect_tx(afull_bar(s), (uint32_t)((MODE3X ? 2 : 1) * TC_TILE_BYTES));
+                        tma_load_2d(stage, &tm_ahi, afull_bar(s), kx, (int32_t)m0);
+                        if (MODE3X) tma_load_2d(stage + TC_TILE_BYTES, &tm_alo, afull_bar(s), kx, (int32_t)m0);
+                    }
                     issued = i + 1;
                 }
                 if (*abort_flag) {
                     // give copies that are still in flight a bounded chance to land before the CTA exits
-                    for (int i = issued > Cfg::SMEM_STAGES ? issued - Cfg::SMEM_STAGES : 0; i < issued; ++i) {
-                        const int s = i % Cfg::SMEM_STAGES;
-                        const uint32_t ph = (uint32_t)(i / Cfg::SMEM_STAGES) & 1u;
+                    for (int i = issued > depth ? issued - depth : 0; i < issued; ++i) {
+                        const int s = i % depth;
+                        const uint32_t ph = (uint32_t)(i / depth) & 1u;
                         const long long t0 = clock64();
-                        while (!mbar_try(full_bar(s), ph) && clock64() - t0 < 20000000LL) {}
+                        while (!mbar_try(is_w ? wfull_bar(s) : afull_bar(s), ph) && clock64() - t0 < 20000000LL) {}
                     }
                 }
             }
             __syncwarp();
-        } else if (warp == 1) {
-            // ------------------------------------------------------------ MMA issuer
+        } else if (warp == 1 || (NT == 2 && warp == 3)) {
+            // ------------------------------------------------------------ MMA issuers: one thread per W tile (a single thread
+            // cannot issue the 64-cycle TF32 MMAs of two tiles fast enough to keep the tensor pipe busy)
             if (lane == 0) {
+                const int w = warp == 1 ? 0 : 1;
                 constexpr uint32_t idesc = make_idesc_tf32(TC_BN, TC_BM);
                 bool ok = true;
+                // chain bookkeeping without divisions: position inside the chain, accumulator buffer and its phase
+                int chain_pos = 0, ab = 0;
+                uint32_t aph = 0;
+                // operands of the first K block
+                ok = mbar_wait(afull_bar(0), 0u, abort_flag, p.status, 2u) && mbar_wait(tfull_bar(0), 0u, abort_flag, p.status, 3u);
                 for (int i = 0; i < num_kb && ok; ++i) {
-                    const int s = i % Cfg::SMEM_STAGES, t = i % Cfg::TMEM_STAGES;
-                    const uint32_t ph = (uint32_t)(i / Cfg::SMEM_STAGES) & 1u, tph = (uint32_t)(i / Cfg::TMEM_STAGES) & 1u;
-                    const int chain = i / TC_CHAIN;
-                    const bool chain_first = (i % TC_CHAIN) == 0;
-                    const bool chain_last = (i % TC_CHAIN) == TC_CHAIN - 1 || i == num_kb - 1;
-                    const int ab = chain % Cfg::ACC_BUFS;
-                    const uint32_t aph = (uint32_t)(chain / Cfg::ACC_BUFS) & 1u;
-                    ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 2u) && mbar_wait(tfull_bar(t), tph, abort_flag, p.status, 3u);
-                    if (!ok) break;
+                    const int s = i % Cfg::A_STAGES, t = i % Cfg::TMEM_STAGES;
+                    const bool chain_first = chain_pos == 0;
+                    const bool chain_last = chain_pos == chain_kb - 1 || i == num_kb - 1;
                     tc_fence_after();
-                    const uint32_t stage = smem_base + s * Cfg::STAGE_BYTES;
-                    const uint64_t bhi = make_kmajor_sw128_desc(stage + NT * TC_TILE_BYTES);
-                    const uint64_t blo = make_kmajor_sw128_desc(stage + (NT + 1) * TC_TILE_BYTES);
-#pragma unroll
-                    for (int w = 0; w < NT; ++w) {
-                        if (chain_first) {   // the drain warps must have emptied this accumulator
-                            ok = mbar_wait(accempty_bar(w, ab), aph ^ 1u, abort_flag, p.status, 7u);
-                            if (!ok) break;
-                            tc_fence_after();
-                        }
-                        const uint32_t acc = tmem_base + Cfg::ACC_COL + (w * Cfg::ACC_BUFS + ab) * TC_BM;
-                        const uint32_t a_hi = tmem_base + Cfg::A_COL + t * Cfg::A_STAGE_COLS + w * 64;
-                        const uint32_t a_lo = a_hi + 32;
-#pragma unroll
-                        for (int j = 0; j < TC_BK / 8; ++j) {
-                            // 8 TF32 per k-step: 8 TMEM columns of A, 32 bytes (descriptor units of 16 B) of B
-                            tc_mma_ts(acc, a_hi + j * 8, bhi + (uint64_t)(j * 2), idesc, (!chain_first || j > 0) ? 1u : 0u);
-                            if (MODE3X) {
-                                tc_mma_ts(acc, a_lo + j * 8, bhi + (uint64_t)(j * 2), idesc, 1u);
-                                tc_mma_ts(acc, a_hi + j * 8, blo + (uint64_t)(j * 2), idesc, 1u);
-                            }
-                        }
-                        if (chain_last) tc_commit(accfull_bar(w, ab));
+                    const uint32_t stage = smem_base + Cfg::A_RING + s * Cfg::A_STAGE_BYTES;
+                    const uint64_t bhi = make_kmajor_sw128_desc(stage);
+                    const uint64_t blo = make_kmajor_sw128_desc(stage + TC_TILE_BYTES);
+                    const uint32_t bhi_lo = (uint32_t)bhi, bhi_hi = (uint32_t)(bhi >> 32), blo_lo = (uint32_t)blo, blo_hi = (uint32_t)(blo >> 32);
+                    if (chain_first) {   // the drain warps must have emptied this accumulator
+                        ok = mbar_wait(accempty_bar(w, ab), aph ^ 1u, abort_flag, p.status, 7u);
+                        if (!ok) break;
+                        tc_fence_after();
                     }
-                    if (!ok) break;
-                    tc_commit(empty_bar(s));    // shared-memory stage may be refilled once these MMAs retire
+                    const uint32_t acc = tmem_base + Cfg::ACC_COL + (w * Cfg::ACC_BUFS + ab) * TC_BM;
+                    const uint32_t a_hi = tmem_base + Cfg::A_COL + t * Cfg::A_STAGE_COLS + w * 64;
+                    const uint32_t a_lo = a_hi + 32;
+#pragma unroll
+                    for (int j = 0; j < TC_BK / 8; ++j) {
+                        if (j == TC_BK / 8 - 1 && i + 1 < num_kb) {
+                            // Look ahead: make sure the operands of the next K block are there BEFORE the last MMAs of
+                            // this one are issued.  Issue is back-pressured by the tensor pipe, so once those are in,
+                            // only the commits stand between them and the next block's first MMA.
+                            const int s1 = (i + 1) % Cfg::A_STAGES, t1 = (i + 1) % Cfg::TMEM_STAGES;
+                            const uint32_t ph1 = (uint32_t)((i + 1) / Cfg::A_STAGES) & 1u, tph1 = (uint32_t)((i + 1) / Cfg::TMEM_STAGES) & 1u;
+                            ok = mbar_wait(afull_bar(s1), ph1, abort_flag, p.status, 2u) && mbar_wait(tfull_bar(t1), tph1, abort_flag, p.status, 3u);
+                        }
+                        // 8 TF32 per k-step: 8 TMEM columns of A, 32 bytes (descriptor units of 16 B) of B
+                        tc_mma_ts(acc, a_hi + j * 8, bhi_lo + j * 2, bhi_hi, idesc, (!chain_first || j > 0) ? 1u : 0u);
+                        if (MODE3X) {
+                            tc_mma_ts(acc, a_lo + j * 8, bhi_lo + j * 2, bhi_hi, idesc, 1u);
+                            tc_mma_ts(acc, a_hi + j * 8, blo_lo + j * 2, blo_hi, idesc, 1u);
+                        }
+                    }
+                    if (chain_last) {
+                        tc_commit(accfull_bar(w, ab));
+                        chain_pos = 0;
+                        if (++ab == Cfg::ACC_BUFS) { ab = 0; aph ^= 1u; }
+                    } else {
+                        ++chain_pos;
+                    }
+                    tc_commit(aempty_bar(s));   // activation stage may be refilled once these MMAs retire
                     tc_commit(tempty_bar(t));   // and the TMEM operand stage rewritten
                 }
             }
@@ -394,36 +441,34 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
         bool ok = true;
         for (int i = 0; i < num_kb && ok; ++i) {
-            const int s = i % Cfg::SMEM_STAGES, t = i % Cfg::TMEM_STAGES;
-            const uint32_t ph = (uint32_t)(i / Cfg::SMEM_STAGES) & 1u, tph = (uint32_t)(i / Cfg::TMEM_STAGES) & 1u;
-            ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 4u) && mbar_wait(tempty_bar(t), tph ^ 1u, abort_flag, p.status, 5u);
+            const int s = i % Cfg::W_STAGES, t = i % Cfg::TMEM_STAGES;
+            const uint32_t ph = (uint32_t)(i / Cfg::W_STAGES) & 1u, tph = (uint32_t)(i / Cfg::TMEM_STAGES) & 1u;
+            ok = mbar_wait(wfull_bar(s), ph, abort_flag, p.status, 4u) && mbar_wait(tempty_bar(t), tph ^ 1u, abort_flag, p.status, 5u);
             ok = __all_sync(0xffffffffu, ok);   // the tcgen05 stores below need the whole warp
             if (!ok) break;
             tc_fence_after();
-            const uint8_t *stage = smem_gen + s * Cfg::STAGE_BYTES;
+            const uint8_t *stage = smem_gen + Cfg::W_RING + s * Cfg::W_STAGE_BYTES;
 #pragma unroll 1
             for (int w = 0; w < NT; ++w) {
                 const uint8_t *rowp = stage + w * TC_TILE_BYTES + row * 128;
                 const uint32_t a_hi = tmem_base + lane_addr + Cfg::A_COL + t * Cfg::A_STAGE_COLS + w * 64;
+                uint32_t hi[32], lo[32];
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t hi[16], lo[16];
+                for (int c = 0; c < 8; ++c) {
+                    // 16-byte chunk c of row r sits at chunk position c ^ (r & 7) under the 128-byte swizzle
+                    const float4 v = *reinterpret_cast<const float4 *>(rowp + ((c ^ (row & 7)) << 4));
+                    const float x[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        // 16-byte chunk c of row r sits at chunk position c ^ (r & 7) under the 128-byte swizzle
-                        const float4 v = *reinterpret_cast<const float4 *>(rowp + (((half * 4 + c) ^ (row & 7)) << 4));
-                        const float x[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const uint32_t h = to_tf32(x[e]);
-                            hi[c * 4 + e] = h;
-                            if (MODE3X) lo[c * 4 + e] = to_tf32(x[e] - __uint_as_float(h));
-                        }
+                    for (int e = 0; e < 4; ++e) {
+                        const uint32_t h = to_tf32(x[e]);
+                        hi[c * 4 + e] = h;
+                        if (MODE3X) lo[c * 4 + e] = to_tf32(x[e] - __uint_as_float(h));
                     }
-                    tc_st16(a_hi + half * 16, hi);
-                    if (MODE3X) tc_st16(a_hi + 32 + half * 16, lo);
                 }
+                tc_st32(a_hi, hi);
+                if (MODE3X) tc_st32(a_hi + 32, lo);
             }
+            mbar_arrive(wempty_bar(s));   // the raw tile now lives in registers / TMEM: its ring slot may be refilled
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(tfull_bar(t));
@@ -443,7 +488,7 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         for (int c = 0; c < num_chains && ok; ++c) {
             const int ab = c % Cfg::ACC_BUFS;
             const uint32_t aph = (uint32_t)(c / Cfg::ACC_BUFS) & 1u;
-            ok = mbar_wait(accfull_bar(w, ab), aph, abort_flag, p.status, 6u);
+            ok = mbar_wait<TC_DRAIN_SLEEP_NS>(accfull_bar(w, ab), aph, abort_flag, p.status, 6u);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -672,6 +717,8 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
     prm.argmax = epi ? epi->argmax_out : nullptr;
     prm.tiles_n = tiles_n; prm.tiles_m = tiles_m;
     prm.splits = splits; prm.kb_per_split = kb_per_split; prm.kb_total = kb_total;
+    prm.chain_kb = TC_CHAIN_DEFAULT;
+    if (const char *e = getenv("CN_GEMM_CHAIN")) { int v = atoi(e); if (v >= 1) prm.chain_kb = v; }
     prm.partials = nullptr; prm.tickets = nullptr;
     prm.status = ws->d_status;
     if (splits > 1) {

@@ -1,0 +1,95 @@
+"""CPU-only checks of the C ABI: the library loads, exports every symbol the header declares, and its host-only
+entry points (codebook loader, threshold builder, shard arithmetic, error reporting) behave."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+
+import clusternet_b200
+from clusternet_b200 import _lib
+from oracle import oracle
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    names = _lib.declared_symbols()
+    assert len(names) >= 40
+    missing = [n for n in names if not hasattr(built_lib, n)]
+    assert not missing, missing
+    unbound = [n for n in names if n not in _lib._SIGNATURES]
+    assert not unbound, f"declared but not bound in _lib.py: {unbound}"
+    assert built_lib.cn_compiled_arch() == 100
+    assert built_lib.cn_status_string(5).decode() == "CN_ERR_TIMEOUT"
+
+
+def test_codebook_loader_reads_raw_and_hdf5_container(built_lib, codebook, tmp_path):
+    tbl = np.zeros(126, np.float32)
+    raw = os.path.join(ROOT, "tests", "golden", "codebook_126.f32")
+    assert built_lib.cn_codebook_load(raw.encode(), tbl.ctypes.data) == 0
+    assert np.array_equal(tbl, codebook)
+    # a container with the HDF5 signature and the table as its last 504 bytes (the reference file's layout)
+    fake = tmp_path / "c.hdf5"
+    fake.write_bytes(b"\x89HDF\r\n\x1a\n" + bytes(2136) + codebook.tobytes())
+    tbl2 = np.zeros(126, np.float32)
+    assert built_lib.cn_codebook_load(str(fake).encode(), tbl2.ctypes.data) == 0
+    assert np.array_equal(tbl2, codebook)
+    assert np.array_equal(oracle.load_codebook(str(fake)), codebook)
+    bad = tmp_path / "bad.bin"
+    bad.write_bytes(bytes(777))
+    assert built_lib.cn_codebook_load(str(bad).encode(), tbl2.ctypes.data) == _lib.CN_ERR_ARG
+    assert b"neither" in built_lib.cn_last_error()
+    # the packaged copy is the same table
+    assert np.array_equal(clusternet_b200.load_codebook(), codebook)
+
+
+def test_codebook_matches_reference_file_when_mounted(codebook):
+    ref = "/root/reference/source/8bit_floats.hdf5"
+    if not os.path.exists(ref):
+        pytest.skip("reference tree not mounted")
+    import hashlib
+    blob = open(ref, "rb").read()
+    assert hashlib.sha256(blob).hexdigest() == "d584e1a65e8d1f0b48e53dcf814ea2d3bd43982b6088c7c1159e616e4418ae7b"
+    assert np.array_equal(oracle.load_codebook(ref), codebook)
+
+
+def test_threshold_table_equals_the_restated_kernel_for_every_float(built_lib, codebook):
+    """The product derives 127 thresholds from the codebook; 'number of thresholds <= |a|' must reproduce the restated
+    kCompression_8bit decision for EVERY non-negative fp32 (0 .. +inf: 2 139 095 041 bit patterns)."""
+    thr = np.zeros(127, np.uint32)
+    lc = np.zeros(128, np.uint8)
+    assert built_lib.cn_codec_build_thresholds(codebook.ctypes.data, thr.ctypes.data, lc.ctypes.data) == 0
+    assert np.all(np.diff(thr.astype(np.int64)) > 0)
+    assert list(lc) == [254] + list(range(126)) + [127]
+    bad, first = oracle.sweep_thresholds(codebook, thr, lc)
+    assert bad == 0, hex(first)
+
+
+def test_threshold_builder_rejects_a_broken_codebook(built_lib, codebook):
+    thr = np.zeros(127, np.uint32)
+    lc = np.zeros(128, np.uint8)
+    broken = codebook.copy()
+    broken[10] = broken[9]
+    assert built_lib.cn_codec_build_thresholds(broken.ctypes.data, thr.ctypes.data, lc.ctypes.data) == _lib.CN_ERR_ARG
+
+
+@pytest.mark.parametrize("n,g", [(40000, 8), (20000, 8), (1024, 3), (10, 4), (7, 7), (5, 8), (0, 2)])
+def test_shard_cols_matches_reference_split(built_lib, n, g):
+    """split = N / G, remainder to the last rank (source/clusterNet.cpp:515-516,926-931)."""
+    total = 0
+    for r in range(g):
+        a, b = ctypes.c_int64(), ctypes.c_int64()
+        assert built_lib.cn_shard_cols(n, r, g, ctypes.byref(a), ctypes.byref(b)) == 0
+        assert (a.value, b.value) == oracle.shard_cols(n, r, g)
+        assert a.value == total
+        total += b.value
+    assert total == n
+    assert built_lib.cn_shard_cols(10, 4, 4, None, None) == _lib.CN_ERR_ARG
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _lib.load()

@@ -1,0 +1,140 @@
+"""Layout boundary, random numbers / weight creation, batch allocator, timers — on the GPU through the C ABI."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import clusternet_b200 as cn
+from clusternet_b200 import _lib
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1), (2, 3), (31, 33), (128, 784), (1000, 17), (5, 4099)])
+def test_layout_round_trip(ctx, rows, cols):
+    """tests/basicOps_test.cu:20-57: to_gpu (row-major -> col-major) and to_host are inverse; device order is col-major."""
+    a = np.arange(rows * cols, dtype=np.float32).reshape(rows, cols)
+    d = ctx.colmajor(a)
+    assert np.array_equal(d.cpu().numpy().ravel(), a.T.ravel())      # memory = column-major
+    assert np.array_equal(ctx.to_numpy(d), a)
+
+
+def test_fill(ctx):
+    t = torch.empty(100003, device="cuda")
+    cn.check(ctx.lib.cn_fill_f32(ctx.h, t.data_ptr(), t.numel(), 1.7, ctx.stream_ptr()))
+    assert float(t.min()) == float(t.max()) == np.float32(1.7)
+
+
+def test_rand_is_deterministic_and_in_range(ctx):
+    """tests/clusterNet_test.cu:177-255: same seed -> same numbers, values in (0,1], mean 0.5, different seeds differ."""
+    a = ctx.rand(100, 1000, seed=42)
+    b = ctx.rand(100, 1000, seed=42)
+    c = ctx.rand(100, 1000, seed=43)
+    assert torch.equal(a, b) and not torch.equal(a, c)
+    assert float(a.min()) > 0.0 and float(a.max()) <= 1.0
+    assert abs(float(a.mean()) - 0.5) < 0.01
+    # a stream does not depend on how it is cut: the second half equals a separate launch with an offset
+    whole = ctx.rand(1, 4096, seed=7)
+    part = ctx.rand(1, 2048, seed=7, offset=512)      # offset counts groups of four values
+    assert torch.equal(whole.flatten()[2048:], part.flatten())
+    n = ctx.randn(200, 1000, seed=1, mean=1.0, std=2.0)
+    assert abs(float(n.mean()) - 1.0) < 0.02 and abs(float(n.std()) - 2.0) < 0.02
+
+
+@pytest.mark.parametrize("rows,cols,total", [(784, 1200, 1200), (100, 40, 320), (5, 5, 5)])
+def test_uniform_sqrt_weight_range(ctx, rows, cols, total):
+    """tests/clusterNet_test.cu:279-314,499-577: weights lie within +-4*sqrt(6/(in+out)) and fill that range."""
+    w = ctx.uniform_sqrt_weight(rows, cols, seed=3, fan_out_total=total)
+    lim = float(oracle.sqrt_weight_limit(rows, total))
+    assert float(w.max()) <= lim and float(w.min()) >= -lim
+    if rows * cols > 10000:
+        assert float(w.max()) > 0.99 * lim and float(w.min()) < -0.99 * lim and abs(float(w.mean())) < 0.02 * lim
+
+
+def test_dropout_rate_and_values(ctx):
+    """tests/clusterNet_test.cu:467-495: about `rate` of the entries become zero, the rest are unchanged (no rescale)."""
+    a = ctx.rand(500, 1000, seed=9) + 1.0
+    for rate in (0.2, 0.5, 0.8):
+        d = ctx.dropout(a, rate, seed=11)
+        zero = (d == 0)
+        assert abs(float(zero.float().mean()) - rate) < 0.01
+        assert torch.equal(d[~zero], a[~zero])
+
+
+def _batch_epochs(ctx, rows, cols_x, cols_y, B, skip_last=False, epochs=2):
+    X = np.arange(rows * cols_x, dtype=np.float32).reshape(rows, cols_x)
+    y = np.arange(rows * cols_y, dtype=np.float32).reshape(rows, cols_y) + 0.5
+    hX, hy = torch.from_numpy(X), torch.from_numpy(y)
+    h = ctypes.c_void_p()
+    cn.check(ctx.lib.cn_batch_create(ctx.h, hX.data_ptr(), hy.data_ptr(), rows, cols_x, cols_y, B, int(skip_last), ctypes.byref(h)))
+    ora = oracle.BatchOracle(rows, B, skip_last)
+    assert ctx.lib.cn_batch_total_batches(h) == ora.total
+    px, py, n = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_int64()
+    cn.check(ctx.lib.cn_batch_current(h, ctypes.byref(px), ctypes.byref(py), ctypes.byref(n)))
+    start, cnt = ora.current
+    total = 0.0
+    for step in range(epochs * ora.total + 3):
+        assert n.value == cnt
+        # current batch on the device is column-major n x cols
+        bx = torch.empty((cols_x, n.value), dtype=torch.float32, device="cuda")
+        cn.check(0 if torch.cuda.current_stream().synchronize() is None else 0)
+        ctypes.cdll.LoadLibrary("libcudart.so.12").cudaMemcpy(ctypes.c_void_p(bx.data_ptr()), px, ctypes.c_size_t(bx.numel() * 4), 3)
+        by = torch.empty((cols_y, n.value), dtype=torch.float32, device="cuda")
+        ctypes.cdll.LoadLibrary("libcudart.so.12").cudaMemcpy(ctypes.c_void_p(by.data_ptr()), py, ctypes.c_size_t(by.numel() * 4), 3)
+        assert np.array_equal(bx.cpu().numpy().T, X[start:start + cnt])
+        assert np.array_equal(by.cpu().numpy().T, y[start:start + cnt])
+        total += float(bx.double().sum())
+        cn.check(ctx.lib.cn_batch_copy_next_async(h))
+        cn.check(ctx.lib.cn_batch_swap(h, ctx.stream_ptr(), ctypes.byref(px), ctypes.byref(py), ctypes.byref(n)))
+        start, cnt = ora.advance()
+    ctx.lib.cn_batch_destroy(h)
+
+
+def test_batch_allocator_epochs_with_partial_last_batch(ctx):
+    """tests/batchAllocator_test.cu:40-114: arange data, every element of every batch equals a running counter, the last
+    batch of an epoch is short, the counter wraps around."""
+    _batch_epochs(ctx, rows=1000, cols_x=17, cols_y=1, B=128)
+
+
+def test_batch_allocator_exact_multiple_and_skip_last(ctx):
+    _batch_epochs(ctx, rows=512, cols_x=8, cols_y=2, B=128)
+    _batch_epochs(ctx, rows=1000, cols_x=5, cols_y=1, B=128, skip_last=True)
+
+
+def test_batch_size_larger_than_data_is_rejected(ctx):
+    x = torch.zeros(10, 4)
+    h = ctypes.c_void_p()
+    st = ctx.lib.cn_batch_create(ctx.h, x.data_ptr(), x.data_ptr(), 10, 4, 4, 128, 0, ctypes.byref(h))
+    assert st == _lib.CN_ERR_SHAPE and b"Batch size must be smaller" in ctx.lib.cn_last_error()
+
+
+def test_tick_tock_accumulates(ctx):
+    ctx.tick("t")
+    a = ctx.rand(1000, 1000, seed=1)
+    first = ctx.tock("t")
+    ctx.tick("t")
+    a = ctx.rand(1000, 1000, seed=2)
+    second = ctx.tock("t")
+    assert first > 0 and second > first
+    with pytest.raises(cn.CnError):
+        ctx.tock("never-ticked")
+
+
+def test_kernel_launch_counter_moves(ctx):
+    n0 = ctx.lib.cn_kernel_launches()
+    ctx.rand(10, 10, seed=1)
+    assert ctx.lib.cn_kernel_launches() == n0 + 1
+
+
+def test_single_rank_dotmpi_equals_dot(ctx):
+    """tests/clusterNet_test.cu:257-276 at one rank: dotMPI == dot on 0.3*ones(200x400) . 1.1748345*ones(400x800)."""
+    A = ctx.colmajor(np.full((200, 400), 0.3, np.float32))
+    W = ctx.colmajor(np.full((400, 800), 1.1748345, np.float32))
+    C1 = ctx.gemm(A, W)
+    C2 = ctx.dotmpi(A, W, 800)
+    ctx.gemm_check()
+    assert torch.equal(C1, C2)
+    want = np.float64(np.float32(0.3)) * np.float64(np.float32(1.1748345)) * 400
+    assert np.abs(ctx.to_numpy(C2) - want).max() / want < 1e-6
