@@ -1,0 +1,112 @@
+"""Worker of the multi-rank tests (launched by torchrun from tests/test_dist*.py).
+
+    backend nccl: one rank per GPU, sharded product through cn_dotmpi_f32, checked against the single-GPU product
+    backend gloo: CPU ranks; the same sharding arithmetic (cn_shard_cols) and gather order with numpy products
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import ctypes  # noqa: E402
+
+import clusternet_b200 as cn  # noqa: E402
+from clusternet_b200 import _lib  # noqa: E402
+from oracle import oracle  # noqa: E402
+
+
+def shard(lib, n, r, g):
+    a, b = ctypes.c_int64(), ctypes.c_int64()
+    cn.check(lib.cn_shard_cols(n, r, g, ctypes.byref(a), ctypes.byref(b)))
+    return a.value, b.value
+
+
+def run_gloo():
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    lib = cn.load()
+    rng = np.random.default_rng(0)
+    for (M, K, N) in [(8, 16, 10), (4, 7, 2 * world), (3, 5, world + 1), (16, 32, 101)]:
+        A = rng.standard_normal((M, K))
+        W = rng.standard_normal((K, N))
+        s0, c0 = shard(lib, N, rank, world)
+        local = A @ W[:, s0:s0 + c0]
+        # column-major full C: shard r is the contiguous block [M*start_r, M*(start_r+count_r))
+        full = np.zeros(M * N)
+        full[M * s0:M * (s0 + c0)] = local.T.ravel()
+        t = torch.from_numpy(full)
+        for r in range(world):                      # grouped broadcasts, the uneven-shard form of the gather
+            sr, cr = shard(lib, N, r, world)
+            blk = t[M * sr:M * (sr + cr)]
+            if cr:
+                dist.broadcast(blk, src=r)
+        got = t.numpy().reshape(N, M).T
+        assert np.allclose(got, A @ W), (M, K, N)
+        assert sum(shard(lib, N, r, world)[1] for r in range(world)) == N
+    dist.barrier()
+    if rank == 0:
+        print("GLOO-OK")
+
+
+def run_nccl():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ctx = cn.Context(local)
+    ids = [ctx.unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(ids, src=0)
+    ctx.comm_init(ids[0], rank, world)
+    assert ctx.lib.cn_comm_rank(ctx.h) == rank and ctx.lib.cn_comm_size(ctx.h) == world
+    rng = np.random.default_rng(5)
+    for (M, K, N) in [(128, 512, 1024), (128, 256, 1000 + world + 1), (64, 384, 272)]:
+        A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+        W = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+        bias = rng.uniform(-1, 1, N).astype(np.float32)
+        dA = ctx.colmajor(A if rank == 0 else np.zeros_like(A))
+        ctx.bcast(dA, 0)                                        # "A is broadcast"
+        s0, c0 = ctx.shard_cols(N, rank, world)
+        dW = ctx.colmajor(np.ascontiguousarray(W[:, s0:s0 + c0]))
+        db = torch.from_numpy(bias).cuda()
+        full = ctx.gemm(dA, ctx.colmajor(W), bias=db, activation=_lib.ACT_RELU)
+        C = ctx.dotmpi(dA, dW, N, bias=db, activation=_lib.ACT_RELU)
+        ctx.gemm_check()
+        ref = np.maximum(oracle.gemm_f64(A, W) + bias, 0)
+        got = ctx.to_numpy(C)
+        assert np.abs(got - ref).max() / np.abs(ref).max() < 1e-5, (M, K, N)
+        # sharded == unsharded up to the different split-K schedules of the two launches
+        assert np.abs(got - ctx.to_numpy(full)).max() / np.abs(ref).max() < 2e-6
+        # 8-bit exchange: own slice exact, peers' slices = decode(encode(slice, absmax of that slice))
+        C8 = ctx.dotmpi(dA, dW, N, bias=db, activation=_lib.ACT_RELU, exchange=1)
+        ctx.gemm_check()
+        got8 = ctx.to_numpy(C8)
+        for r in range(world):
+            sr, cr = ctx.shard_cols(N, r, world)
+            sl = np.ascontiguousarray(got[:, sr:sr + cr].T)       # column-major element order of the slice
+            if r == rank:
+                assert np.array_equal(got8[:, sr:sr + cr], got[:, sr:sr + cr])
+            else:
+                p = oracle.absmax(sl)
+                want = oracle.decompress(ctx.codebook, oracle.compress(ctx.codebook, sl, p), p)
+                assert np.array_equal(got8[:, sr:sr + cr], want.reshape(cr, M).T), (M, K, N, r)
+    # scalar gather and all-reduce
+    v = torch.zeros(world, device="cuda")
+    v[rank] = rank + 1.5
+    cn.check(ctx.lib.cn_allgather_scalar_f32(ctx.h, v.data_ptr(), ctx.stream_ptr()))
+    t = torch.full((1000,), float(rank + 1), device="cuda")
+    cn.check(ctx.lib.cn_allreduce_sum_f32(ctx.h, t.data_ptr(), t.numel(), ctx.stream_ptr()))
+    torch.cuda.synchronize()
+    assert v.tolist() == [r + 1.5 for r in range(world)]
+    assert float(t[0]) == world * (world + 1) / 2
+    dist.barrier()
+    cn.check(ctx.lib.cn_comm_destroy(ctx.h))
+    if rank == 0:
+        print("NCCL-OK")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    run_gloo() if sys.argv[1] == "gloo" else run_nccl()
