@@ -73,6 +73,7 @@ _SIGNATURES = {
     "cn_batch_destroy": (c_int, [c_void_p]),
     "cn_batch_total_batches": (c_int64, [c_void_p]),
     "cn_batch_current": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64)]),
+    "cn_batch_set_skip_last": (c_int, [c_void_p, c_int]),
     "cn_batch_copy_next_async": (c_int, [c_void_p]),
     "cn_batch_swap": (c_int, [c_void_p, c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64)]),
     "cn_tick": (c_int, [c_void_p, c_char_p, c_void_p]),

@@ -90,6 +90,13 @@ extern "C" int cn_batch_create(cn_context *ctx, const float *h_X, const float *h
     return CN_OK;
 }
 
+extern "C" int cn_batch_set_skip_last(cn_batch *b, int skip)
+{
+    CN_REQUIRE(b, CN_ERR_ARG, "cn_batch_set_skip_last: null handle");
+    b->skip_last = skip ? 1 : 0;
+    return CN_OK;
+}
+
 extern "C" int64_t cn_batch_total_batches(const cn_batch *b) { return b ? b->total_batches : 0; }
 
 extern "C" int cn_batch_current(const cn_batch *b, float **d_X, float **d_y, int64_t *batch_rows)

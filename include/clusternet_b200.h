@@ -219,6 +219,8 @@ int cn_batch_destroy(cn_batch *b);
 int64_t cn_batch_total_batches(const cn_batch *b);
 /* The batch that is current now (after cn_batch_create: the first batch, as BatchAllocator::init leaves it). */
 int cn_batch_current(const cn_batch *b, float **d_X, float **d_y, int64_t *batch_rows);
+/* BatchAllocator::SKIP_LAST_BATCH is a public field that callers flip after init (source/batchAllocator.h:37). */
+int cn_batch_set_skip_last(cn_batch *b, int skip_last_batch);
 /* Stage + asynchronous copy of the next batch (allocate_next_batch_async). */
 int cn_batch_copy_next_async(cn_batch *b);
 /* Make the next batch current (replace_current_batch_with_next): waits (on the device, through an
