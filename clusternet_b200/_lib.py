@@ -37,6 +37,7 @@ _SIGNATURES = {
     "cn_codebook_load": (c_int, [c_char_p, c_void_p]),
     "cn_codec_build_thresholds": (c_int, [c_void_p, c_void_p, c_void_p]),
     "cn_absmax_f32": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "cn_absmax_f32_noalloc": (c_int, [c_void_p, c_int64, c_void_p, c_void_p]),
     "cn_compress_8bit": (c_int, [c_void_p, c_void_p, c_float, c_int64, c_void_p, c_void_p]),
     "cn_compress_8bit_dp": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "cn_decompress_8bit": (c_int, [c_void_p, c_void_p, c_float, c_int64, c_void_p, c_void_p]),

@@ -378,3 +378,73 @@ extern "C" int cn_absmax_f32(cn_context *ctx, const float *d_A, int64_t n, float
     cn_count_launch();
     return CN_OK;
 }
+
+// ------------------------------------------------------------------------------------------------
+// cn_absmax_f32_noalloc: absmax for callers that must not allocate.
+//
+// Some hosts cannot call cudaMalloc on the path where they need the scale of a tensor: real-time or plugin
+// callbacks that are forbidden to take the allocator's lock (cudaMalloc may block and synchronise the device),
+// processes that handed their whole device memory to another allocator at start-up, and recovery paths that run
+// when device memory is already exhausted.
+// cn_absmax_f32 needs a cn_context, whose creation allocates the scratch for the per-CTA partial maxima.  This entry
+// point takes no context: the same kernel runs with its scratch in the fixed array below, which is part of the
+// library image (every GPU that loads the library holds these 4352 bytes until the process exits).
+//
+// Consequences of the shared, fixed scratch:
+//   * at most CN_ABSMAX_NOALLOC_MAX_CTAS partial maxima, and inputs of at most CN_ABSMAX_NOALLOC_MAX_N elements;
+//     larger inputs are refused with CN_ERR_ARG;
+//   * every call on a device uses the same array, so two calls that overlap on the GPU (different streams, or
+//     different host threads) race; serialise them on one stream;
+//   * the ticket word must be zero when a launch starts.  The array is zero when the module is loaded and the
+//     kernel puts the ticket back to zero before it ends, so no clearing launch is needed between calls.
+//
+// In host code `g_absmax_noalloc_scratch` is only a handle of the device symbol, not an address the GPU can use:
+// the set-up below asks the runtime for the device address with cudaGetSymbolAddress, once per device, with that
+// device current, and the kernel receives that pointer.  The set-up happens inside the first call on a device;
+// make that first call before starting any stream capture.
+// ------------------------------------------------------------------------------------------------
+#define CN_ABSMAX_NOALLOC_MAX_CTAS 1024
+#define CN_ABSMAX_NOALLOC_MAX_N (1LL << 32)
+#define CN_ABSMAX_NOALLOC_MAX_DEVICES 64
+
+// [0, 1024): partial maxima (float bits); [1024]: ticket; rest: padding to a 256-byte multiple
+static __device__ __align__(256) unsigned int g_absmax_noalloc_scratch[CN_ABSMAX_NOALLOC_MAX_CTAS + 64];
+
+struct NoallocDevice {
+    unsigned int *scratch = nullptr;   // device address of the array on this device
+    int sm_count = 0;
+};
+static NoallocDevice g_noalloc_dev[CN_ABSMAX_NOALLOC_MAX_DEVICES];
+
+extern "C" int cn_absmax_f32_noalloc(const float *d_A, int64_t n, float *d_out, void *stream)
+{
+    CN_REQUIRE(d_out, CN_ERR_ARG, "cn_absmax_f32_noalloc: null output pointer");
+    CN_REQUIRE(n >= 0 && (n == 0 || d_A), CN_ERR_ARG, "cn_absmax_f32_noalloc: bad input");
+    CN_REQUIRE(n <= CN_ABSMAX_NOALLOC_MAX_N, CN_ERR_ARG,
+               "cn_absmax_f32_noalloc: %lld elements exceed the limit of %lld of the fixed scratch variant; use cn_absmax_f32",
+               (long long)n, (long long)CN_ABSMAX_NOALLOC_MAX_N);
+    int dev = -1;
+    CN_CUDA(cudaGetDevice(&dev));
+    CN_REQUIRE(dev >= 0 && dev < CN_ABSMAX_NOALLOC_MAX_DEVICES, CN_ERR_UNSUPPORTED, "cn_absmax_f32_noalloc: device index %d", dev);
+    NoallocDevice &nd = g_noalloc_dev[dev];
+    if (!nd.scratch) {
+        // once per device, with that device current: device address of the symbol, and the SM count for the grid
+        void *p = nullptr;
+        CN_CUDA(cudaGetSymbolAddress(&p, g_absmax_noalloc_scratch));
+        int sms = 0;
+        CN_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        nd.sm_count = sms;
+        nd.scratch = static_cast<unsigned int *>(p);
+    }
+    int64_t need = (n + (int64_t)ABSMAX_THREADS * 16 - 1) / ((int64_t)ABSMAX_THREADS * 16);
+    int64_t cap = (int64_t)nd.sm_count * 4;
+    if (cap > CN_ABSMAX_NOALLOC_MAX_CTAS) cap = CN_ABSMAX_NOALLOC_MAX_CTAS;
+    if (need < 1) need = 1;
+    const int grid = (int)(need < cap ? need : cap);
+    const int vector_ok = ((uintptr_t)d_A % 16 == 0);
+    cn_absmax_kernel<<<grid, ABSMAX_THREADS, 0, cn_stream(stream)>>>(d_A, n, d_out, reinterpret_cast<float *>(nd.scratch),
+                                                                     nd.scratch + CN_ABSMAX_NOALLOC_MAX_CTAS, vector_ok);
+    CN_CUDA(cudaGetLastError());
+    cn_count_launch();
+    return CN_OK;
+}

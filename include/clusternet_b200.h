@@ -71,6 +71,17 @@ int cn_codec_build_thresholds(const float *codebook126, uint32_t *thr127, uint8_
  * reduce seed) to the DEVICE scalar d_out.  One pass, no temporary matrix. */
 int cn_absmax_f32(cn_context *ctx, const float *d_A, int64_t n, float *d_out, void *stream);
 
+/* absmax without any allocation and without a context, for callers that cannot call cudaMalloc where they need the
+ * scale: callbacks that must not take the allocator's lock (cudaMalloc may block and synchronise the device),
+ * processes whose device memory is already owned by another allocator, recovery paths that run when device memory is
+ * exhausted.  Same kernel and same result as
+ * cn_absmax_f32; the per-CTA partial maxima live in a fixed 4352-byte array inside the library image instead of in
+ * context scratch.  Limits: n <= 2^32 elements (larger inputs return CN_ERR_ARG); all calls on a device share the
+ * array, so calls that overlap on the GPU race — keep them on one stream; the first call on a device looks the
+ * array's device address up and should be made before any stream capture starts.  Uses the current device.
+ * This entry point has no counterpart in the reference. */
+int cn_absmax_f32_noalloc(const float *d_A, int64_t n, float *d_out, void *stream);
+
 /* compression_8bit: replaces ::compression_8bit (source/basicOps.cu:1163-1168) and kCompression_8bit
  * (source/clusterKernels.cu:1163-1232).  codes[i] is bit-identical to the reference kernel's output
  * for every input for which the reference's answer is defined. */
