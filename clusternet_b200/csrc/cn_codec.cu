@@ -73,6 +73,30 @@ __device__ __forceinline__ uint32_t pack4(uint32_t c0, uint32_t c1, uint32_t c2,
     return __byte_perm(__byte_perm(c0, c1, 0x0040), __byte_perm(c2, c3, 0x0040), 0x5410);
 }
 
+// Four codes of the fast path for one 16-byte group.  The sign bits are taken from the top bytes of the four inputs in
+// one go; a NaN anywhere in the group (rare) sends the group through the per-element form.
+__device__ __forceinline__ uint32_t fast_code4(const float4 q, uint32_t pb, uint32_t psign4, const CodecTables &t, int base, int nbm1, uint32_t xtop)
+{
+    const uint32_t x0 = __float_as_uint(q.x), x1 = __float_as_uint(q.y), x2 = __float_as_uint(q.z), x3 = __float_as_uint(q.w);
+    const uint32_t a0 = x0 & 0x7fffffffu, a1 = x1 & 0x7fffffffu, a2 = x2 & 0x7fffffffu, a3 = x3 & 0x7fffffffu;
+    if (max(max(a0, a1), max(a2, a3)) > 0x7f800000u)
+        return pack4(fast_code(x0, pb, t, base, nbm1, xtop), fast_code(x1, pb, t, base, nbm1, xtop),
+                     fast_code(x2, pb, t, base, nbm1, xtop), fast_code(x3, pb, t, base, nbm1, xtop));
+    uint32_t c[4];
+    const uint32_t a[4] = {a0, a1, a2, a3};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int key = (int)(a[i] >> LUT_SHIFT) - base;
+        key = min(max(key, 0), nbm1);
+        const uint2 e = t.lut[key];
+        c[i] = (a[i] >= e.x) ? (e.y >> 16) : e.y;
+        if (a[i] >= xtop) c[i] = 127u;
+    }
+    // top bytes of x0..x3 -> one word; flip by the sign of precision; keep bit 7 of each byte
+    const uint32_t tops = __byte_perm(__byte_perm(x0, x1, 0x0073), __byte_perm(x2, x3, 0x0073), 0x5410);
+    return pack4(c[0], c[1], c[2], c[3]) | ((tops ^ psign4) & 0x80808080u);
+}
+
 template <bool PRECISION_ON_DEVICE>
 __global__ void __launch_bounds__(CODEC_THREADS, 1)
 cn_compress_kernel(const float *__restrict__ A, float precision_arg, const float *__restrict__ d_precision,
@@ -83,21 +107,25 @@ cn_compress_kernel(const float *__restrict__ A, float precision_arg, const float
     const int tid = threadIdx.x;
     const float p = PRECISION_ON_DEVICE ? *d_precision : precision_arg;
     const uint32_t pb = __float_as_uint(p);
+    const uint32_t psign4 = (pb >> 31) * 0x80808080u;
     const float ap = fabsf(p);
     // 2^-100 <= |p| <= 2^100 keeps every boundary T*|p| a normal number; NaN fails both tests
     const bool p_ok = (ap >= 7.8886090522101181e-31f) && (ap <= 1.2676506002282294e30f);
 
     const int64_t nvec = vector_ok ? (n >> 2) : 0;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t step = 4 * stride;
     int64_t v = (int64_t)blockIdx.x * blockDim.x + tid;
     const float4 *A4 = reinterpret_cast<const float4 *>(A);
     uint32_t *out4 = reinterpret_cast<uint32_t *>(out);
 
-    // first loads are issued before the table build so that their latency overlaps it
-    float4 pre0 = make_float4(0.f, 0.f, 0.f, 0.f), pre1 = pre0;
-    const bool has0 = v < nvec, has1 = v + stride < nvec;
-    if (has0) pre0 = __ldcs(A4 + v);
-    if (has1) pre1 = __ldcs(A4 + v + stride);
+    // the first group of loads is issued before the table build so that its latency overlaps it
+    float4 cur[4];
+    const bool have_group = v + 3 * stride < nvec;
+    if (have_group) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) cur[u] = __ldcs(A4 + v + u * stride);
+    }
 
     if (tid < 128) {
         t.T[tid] = g_thr[tid];
@@ -107,15 +135,20 @@ cn_compress_kernel(const float *__restrict__ A, float precision_arg, const float
         if (tid < CN_NUM_THR && p_ok) {
             const float T = __uint_as_float(g_thr[tid]);
             xb = __float_as_uint(__fmul_rn(T, ap));
-            // smallest |x| with fl(|x|/|p|) >= T: the product is within a few ulps of it
-            for (int it = 0; it < 6; ++it) {
+            // smallest |x| with fl(|x|/|p|) >= T.  The product is within a few ulps of it: walk down while the lower
+            // neighbour still reaches T, and up only if nothing was found below (then xb itself may fall short).
+            int down = 0;
+            for (; down < 6; ++down) {
                 if (xb > 0u && __fdiv_rn(__uint_as_float(xb - 1u), ap) >= T) --xb; else break;
             }
-            for (int it = 0; it < 6; ++it) {
-                if (__fdiv_rn(__uint_as_float(xb), ap) < T) ++xb; else break;
+            good = down < 6;
+            if (down == 0) {
+                int up = 0;
+                for (; up < 6; ++up) {
+                    if (__fdiv_rn(__uint_as_float(xb), ap) < T) ++xb; else break;
+                }
+                good = up < 6;
             }
-            good = (__fdiv_rn(__uint_as_float(xb), ap) >= T) &&
-                   (xb == 0u || __fdiv_rn(__uint_as_float(xb - 1u), ap) < T);
         }
         t.X[tid] = good ? xb : 0xfffffffeu;   // 0xfffffffe marks a boundary that could not be pinned
     }
@@ -145,8 +178,8 @@ cn_compress_kernel(const float *__restrict__ A, float precision_arg, const float
             const uint32_t kbv = (uint32_t)(b + base);
             int lo = 0;
 #pragma unroll
-            for (int step = 64; step > 0; step >>= 1)
-                if ((t.X[lo + step - 1] >> LUT_SHIFT) < kbv) lo += step;
+            for (int step2 = 64; step2 > 0; step2 >>= 1)
+                if ((t.X[lo + step2 - 1] >> LUT_SHIFT) < kbv) lo += step2;
             uint2 e;
             if (lo < CN_NUM_THR - 1 && (t.X[lo] >> LUT_SHIFT) == kbv) {
                 e.x = t.X[lo];
@@ -164,26 +197,30 @@ cn_compress_kernel(const float *__restrict__ A, float precision_arg, const float
     const int base = t.base, nbm1 = t.nb - 1;
     const uint32_t xtop = t.xtop;
 
-#define CN_CODE4(q)                                                                                         \
-    (fast ? pack4(fast_code(__float_as_uint((q).x), pb, t, base, nbm1, xtop), fast_code(__float_as_uint((q).y), pb, t, base, nbm1, xtop), \
-                  fast_code(__float_as_uint((q).z), pb, t, base, nbm1, xtop), fast_code(__float_as_uint((q).w), pb, t, base, nbm1, xtop)) \
+#define CN_CODE4(q)                                                                                             \
+    (fast ? fast_code4((q), pb, psign4, t, base, nbm1, xtop)                                                    \
           : pack4(generic_code((q).x, p, t), generic_code((q).y, p, t), generic_code((q).z, p, t), generic_code((q).w, p, t)))
 
-    if (has0) __stcs(out4 + v, CN_CODE4(pre0));
-    if (has1) __stcs(out4 + v + stride, CN_CODE4(pre1));
-    v += 2 * stride;
-    for (; v + 3 * stride < nvec; v += 4 * stride) {
-        float4 q0 = __ldcs(A4 + v);
-        float4 q1 = __ldcs(A4 + v + stride);
-        float4 q2 = __ldcs(A4 + v + 2 * stride);
-        float4 q3 = __ldcs(A4 + v + 3 * stride);
-        __stcs(out4 + v, CN_CODE4(q0));
-        __stcs(out4 + v + stride, CN_CODE4(q1));
-        __stcs(out4 + v + 2 * stride, CN_CODE4(q2));
-        __stcs(out4 + v + 3 * stride, CN_CODE4(q3));
+    // whole groups of four 16-byte loads per thread; the next group is in flight while the current one is coded
+    if (have_group) {
+        while (true) {
+            const int64_t vn = v + step;
+            const bool more = vn + 3 * stride < nvec;
+            float4 nxt[4];
+            if (more) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) nxt[u] = __ldcs(A4 + vn + u * stride);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) __stcs(out4 + v + u * stride, CN_CODE4(cur[u]));
+            v = vn;
+            if (!more) break;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) cur[u] = nxt[u];
+        }
     }
     for (; v < nvec; v += stride) {
-        float4 q0 = __ldcs(A4 + v);
+        const float4 q0 = __ldcs(A4 + v);
         __stcs(out4 + v, CN_CODE4(q0));
     }
 #undef CN_CODE4
@@ -223,15 +260,26 @@ cn_decompress_kernel(const uint8_t *__restrict__ codes, float precision_arg, con
     const uint32_t *in4 = reinterpret_cast<const uint32_t *>(codes);
     float4 *out4 = reinterpret_cast<float4 *>(out);
 #define CN_DEC4(w) make_float4(lut[(w) & 0xffu], lut[((w) >> 8) & 0xffu], lut[((w) >> 16) & 0xffu], lut[(w) >> 24])
-    for (; v + 3 * stride < nvec; v += 4 * stride) {
-        uint32_t w0 = __ldcs(in4 + v);
-        uint32_t w1 = __ldcs(in4 + v + stride);
-        uint32_t w2 = __ldcs(in4 + v + 2 * stride);
-        uint32_t w3 = __ldcs(in4 + v + 3 * stride);
-        __stcs(out4 + v, CN_DEC4(w0));
-        __stcs(out4 + v + stride, CN_DEC4(w1));
-        __stcs(out4 + v + 2 * stride, CN_DEC4(w2));
-        __stcs(out4 + v + 3 * stride, CN_DEC4(w3));
+    if (v + 3 * stride < nvec) {
+        const int64_t step = 4 * stride;
+        uint32_t cur[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) cur[u] = __ldcs(in4 + v + u * stride);
+        while (true) {
+            const int64_t vn = v + step;
+            const bool more = vn + 3 * stride < nvec;
+            uint32_t nxt[4];
+            if (more) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) nxt[u] = __ldcs(in4 + vn + u * stride);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) __stcs(out4 + v + u * stride, CN_DEC4(cur[u]));
+            v = vn;
+            if (!more) break;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) cur[u] = nxt[u];
+        }
     }
     for (; v < nvec; v += stride) {
         uint32_t w0 = __ldcs(in4 + v);
