@@ -368,7 +368,11 @@ def main():
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": {"kernel": "cn_gemm_tc_kernel (layer 1, per rank)", "bound": "tensor", "achieved": achieved, "peak": peak,
-                     "unit": "TFLOP/s", "frac": (achieved / peak) if achieved else None, "traffic": None,
+                     "unit": "TFLOP/s", "frac": (achieved / peak) if achieved else None,
+                     # DRAM bytes per launch: ncu capture of 128x100000x4096 (profiles/gemm_tc_kernel_128x100000x4096.md:
+                     # 1.772 GB for 1.6384 GB of W), scaled by the W bytes of this rank's layer-1 launch
+                     "traffic": 1.772e9 / 1.6384e9 * 4.0 * K1 * (N1 // world if world > 1 else N1),
+                     "traffic_source": "ncu dram__bytes_read+write of a 4096-column case, scaled by W bytes",
                      "ms_per_launch": l1_ms, "layer2_ms_per_launch": l2_ms,
                      "peak_source": f"{peaks['source']}: bf16_tflops {peaks['bf16_tflops']} / 2 (TF32 rate)" + (" / 3 (three TF32 products per tile)" if args.mode == "3xtf32" else ""),
                      "hbm_frac_layer1": (4.0 * K1 * (N1 / world) / (l1_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]) if l1_ms else None},

@@ -393,7 +393,7 @@ static int decompress_impl(cn_context *ctx, const uint8_t *d_codes, float precis
     if (n == 0) return CN_OK;
     CN_REQUIRE(d_out && d_codes, CN_ERR_ARG, "cn_decompress_8bit: null buffer");
     int vector_ok = ((uintptr_t)d_out % 16 == 0) && ((uintptr_t)d_codes % 4 == 0);
-    int grid = codec_grid(ctx, n, CODEC_THREADS, 4, 2);
+    int grid = codec_grid(ctx, n, CODEC_THREADS, 4, 1);   // 1024 threads x 64 registers fill an SM: one resident CTA
     if (d_precision)
         cn_decompress_kernel<true><<<grid, CODEC_THREADS, 0, cn_stream(stream)>>>(d_codes, 0.f, d_precision, n, d_out, ctx->d_tbl, vector_ok);
     else
