@@ -195,6 +195,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default="3xtf32", choices=["3xtf32", "tf32"])
     ap.add_argument("--exchange", default="fp32", choices=["fp32", "8bit"])
+    ap.add_argument("--nccl-gather", action="store_true", help="gather C with ncclAllGather instead of the fused peer stores")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-codec", action="store_true")
     ap.add_argument("--only-codec", action="store_true", help="run the codec measurements alone (small profiler captures)")
@@ -250,8 +251,10 @@ def main():
     d_stage_in = torch.empty((M, K1), dtype=torch.float32, device="cuda")
     d_stage_out = torch.empty((M, N2), dtype=torch.float32, device="cuda")
     batch = ctx.empty(M, K1)
-    out1 = ctx.empty(M, N1)
-    out2 = ctx.empty(M, N2)
+    # outputs in symmetric buffers: the all-gather of each layer is fused into the GEMM epilogue (stores to peer memory)
+    fused = world > 1 and exchange == 0 and not args.nccl_gather
+    out1 = ctx.sym_empty(M, N1) if fused else ctx.empty(M, N1)
+    out2 = ctx.sym_empty(M, N2) if fused else ctx.empty(M, N2)
     sp = ctx.stream_ptr()
 
     def upload():
@@ -359,7 +362,7 @@ def main():
         "data": "synthetic",
         "config": {"workload": ("README dotMPI two-layer skinny GEMM: " if headline else "REDUCED (profiling) two-layer skinny GEMM: ") +
                                f"128x{K1} . {K1}x{N1} . {N1}x{N2}, W column-sharded",
-                   "gemm_mode": args.mode, "exchange": args.exchange, "parallelism": f"tp{world} (columns of W)",
+                   "gemm_mode": args.mode, "exchange": args.exchange, "gather": ("fused peer stores" if fused else ("nccl" if world > 1 else "none")), "parallelism": f"tp{world} (columns of W)",
                    "l2": f"inputs larger than L2 ({4e-9 * (K1 * N1 + N1 * N2):.1f} GB of weights stream once per step)", "flops_per_step": FLOPS_STEP},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": M * K1 * 4,
                 "d2h_bytes_per_step": M * N2 * 4, "result_checksum": checksum},

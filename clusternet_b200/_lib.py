@@ -68,6 +68,8 @@ _SIGNATURES = {
     "cn_allgather_cols_u8": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "cn_allgather_scalar_f32": (c_int, [c_void_p, c_void_p, c_void_p]),
     "cn_allreduce_sum_f32": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
+    "cn_sym_alloc": (c_int, [c_void_p, ctypes.c_size_t, ctypes.POINTER(c_void_p)]),
+    "cn_sym_free": (c_int, [c_void_p, c_void_p]),
     "cn_dotmpi_f32": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, ctypes.POINTER(Epilogue),
                               c_int, c_int, c_void_p]),
     "cn_batch_create": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, ctypes.POINTER(c_void_p)]),

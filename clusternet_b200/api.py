@@ -190,6 +190,24 @@ class Context:
         check(self.lib.cn_shard_cols(n_total, rank, nranks, ctypes.byref(a), ctypes.byref(b)))
         return a.value, b.value
 
+    def sym_empty(self, rows, cols):
+        """Column-major rows x cols matrix in a symmetric buffer (collective call; see cn_sym_alloc)."""
+        p = ctypes.c_void_p()
+        nbytes = rows * cols * 4
+        check(self.lib.cn_sym_alloc(self.h, nbytes, ctypes.byref(p)))
+
+        class _Raw:
+            __cuda_array_interface__ = {"shape": (cols, rows), "typestr": "<f4", "data": (p.value, False), "version": 2, "strides": None}
+        t = torch.as_tensor(_Raw(), device=self.device)
+        self._sym = getattr(self, "_sym", [])
+        self._sym.append(p)
+        return t
+
+    def sym_free_all(self):
+        for p in getattr(self, "_sym", []):
+            self.lib.cn_sym_free(self.h, p)
+        self._sym = []
+
     def bcast(self, t, root=0):
         check(self.lib.cn_bcast_f32(self.h, _ptr(t), t.numel(), root, self.stream_ptr()))
         return t

@@ -12,6 +12,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 #include <string.h>
+#include <vector>
 #include "cn_gemm.h"
 
 struct NcclApi {
@@ -61,15 +62,41 @@ static int nccl_load()
         }                                                                                          \
     } while (0)
 
+// A buffer that exists with the same size on every rank and that every rank has mapped from every peer
+// (cudaIpc handles exchanged once through the communicator).
+struct cn_sym_buf {
+    void *base = nullptr;
+    size_t bytes = 0;
+    std::vector<void *> peer;   // [nranks]; peer[rank] == base
+};
+
 struct cn_comm_state {
     ncclComm_t comm = nullptr;
     int rank = 0, nranks = 1;
     float *d_scales = nullptr;   // one codec scale per rank
+    std::vector<cn_sym_buf> sym;
+    // cross-GPU flags (a symmetric buffer of its own): slot 0 = "my copy may be written", slot 1 = "my stores are done";
+    // entry [slot * nranks + r] on a GPU is written by rank r
+    unsigned int *flags = nullptr;
+    std::vector<unsigned int *> peer_flags;
+    unsigned int **d_peer_flags = nullptr;   // device copy of peer_flags
+    unsigned int epoch = 0;
 };
+
+static void sym_release(cn_comm_state *c, cn_sym_buf &b)
+{
+    for (int r = 0; r < (int)b.peer.size(); ++r)
+        if (r != c->rank && b.peer[r]) cudaIpcCloseMemHandle(b.peer[r]);
+    cudaFree(b.base);
+    b.base = nullptr;
+}
 
 void cn_comm_state_free(cn_context *ctx)
 {
     if (!ctx->comm) return;
+    cudaDeviceSynchronize();
+    for (auto &b : ctx->comm->sym) sym_release(ctx->comm, b);
+    cudaFree(ctx->comm->d_peer_flags);
     if (ctx->comm->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(ctx->comm->comm);
     cudaFree(ctx->comm->d_scales);
     delete ctx->comm;
@@ -204,6 +231,148 @@ extern "C" int cn_allreduce_sum_f32(cn_context *ctx, float *d_buf, int64_t n, vo
     return CN_OK;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Symmetric buffers and the flag barrier used by the fused GEMM -> all-gather path.
+// ------------------------------------------------------------------------------------------------
+static int sym_alloc_impl(cn_context *ctx, size_t bytes, cn_sym_buf *out)
+{
+    cn_comm_state *c = ctx->comm;
+    const int G = c->nranks;
+    cn_sym_buf b;
+    b.bytes = bytes;
+    CN_CUDA(cudaMalloc(&b.base, bytes ? bytes : 256));
+    b.peer.assign(G, nullptr);
+    b.peer[c->rank] = b.base;
+    // exchange the IPC handles: every rank contributes 64 bytes
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "cudaIpcMemHandle_t is expected to be 64 bytes");
+    cudaIpcMemHandle_t mine;
+    CN_CUDA(cudaIpcGetMemHandle(&mine, b.base));
+    unsigned char *d_h = nullptr;
+    CN_CUDA(cudaMalloc(&d_h, 64 * (size_t)G));
+    CN_CUDA(cudaMemcpy(d_h + 64 * c->rank, &mine, 64, cudaMemcpyHostToDevice));
+    ncclResult_t r = g_nccl.AllGather(d_h + 64 * c->rank, d_h, 64, ncclUint8, c->comm, nullptr);
+    std::vector<cudaIpcMemHandle_t> all(G);
+    cudaError_t e = cudaMemcpy(all.data(), d_h, 64 * (size_t)G, cudaMemcpyDeviceToHost);   // synchronises the default stream
+    cudaFree(d_h);
+    if (r != ncclSuccess || e != cudaSuccess) {
+        cudaFree(b.base);
+        cn_set_error("cn_sym_alloc: exchange of the memory handles failed (nccl %d, cuda %d)", (int)r, (int)e);
+        return CN_ERR_NCCL;
+    }
+    for (int p = 0; p < G; ++p) {
+        if (p == c->rank) continue;
+        e = cudaIpcOpenMemHandle(&b.peer[p], all[p], cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            sym_release(c, b);
+            return cn_cuda_fail(e, "cudaIpcOpenMemHandle");
+        }
+    }
+    *out = b;
+    return CN_OK;
+}
+
+extern "C" int cn_sym_alloc(cn_context *ctx, size_t bytes, void **ptr)
+{
+    CN_REQUIRE(ctx && ptr, CN_ERR_ARG, "cn_sym_alloc: null argument");
+    *ptr = nullptr;
+    CN_CUDA(cudaSetDevice(ctx->device));
+    if (!ctx->comm || ctx->comm->nranks == 1) {   // nothing to map: an ordinary allocation
+        CN_CUDA(cudaMalloc(ptr, bytes ? bytes : 256));
+        return CN_OK;
+    }
+    cn_comm_state *c = ctx->comm;
+    CN_REQUIRE(c->nranks - 1 <= CN_MAX_PEERS, CN_ERR_UNSUPPORTED, "cn_sym_alloc: at most %d ranks", CN_MAX_PEERS + 1);
+    int st;
+    if (!c->flags) {   // first use: the flag words, zeroed, and the device table of their peer addresses
+        cn_sym_buf f;
+        if ((st = sym_alloc_impl(ctx, 4096, &f)) != CN_OK) return st;
+        CN_CUDA(cudaMemset(f.base, 0, 4096));
+        c->flags = (unsigned int *)f.base;
+        for (void *q : f.peer) c->peer_flags.push_back((unsigned int *)q);
+        CN_CUDA(cudaMalloc(&c->d_peer_flags, sizeof(unsigned int *) * c->nranks));
+        CN_CUDA(cudaMemcpy(c->d_peer_flags, c->peer_flags.data(), sizeof(unsigned int *) * c->nranks, cudaMemcpyHostToDevice));
+        c->sym.push_back(f);
+        // nobody may signal into flags that a slower rank has not zeroed yet
+        float *d_tmp = nullptr;
+        CN_CUDA(cudaMalloc(&d_tmp, 4));
+        CN_CUDA(cudaMemset(d_tmp, 0, 4));
+        ncclResult_t r = g_nccl.AllReduce(d_tmp, d_tmp, 1, ncclFloat, ncclSum, c->comm, nullptr);
+        cudaError_t e = cudaDeviceSynchronize();
+        cudaFree(d_tmp);
+        CN_REQUIRE(r == ncclSuccess && e == cudaSuccess, CN_ERR_NCCL, "cn_sym_alloc: barrier after flag set-up failed");
+    }
+    cn_sym_buf b;
+    if ((st = sym_alloc_impl(ctx, bytes, &b)) != CN_OK) return st;
+    c->sym.push_back(b);
+    *ptr = b.base;
+    return CN_OK;
+}
+
+extern "C" int cn_sym_free(cn_context *ctx, void *ptr)
+{
+    CN_REQUIRE(ctx, CN_ERR_ARG, "cn_sym_free: null context");
+    if (!ptr) return CN_OK;
+    if (ctx->comm) {
+        auto &v = ctx->comm->sym;
+        for (size_t i = 0; i < v.size(); ++i) {
+            if (v[i].base == ptr) {
+                CN_CUDA(cudaDeviceSynchronize());
+                sym_release(ctx->comm, v[i]);
+                v.erase(v.begin() + i);
+                return CN_OK;
+            }
+        }
+    }
+    CN_CUDA(cudaFree(ptr));
+    return CN_OK;
+}
+
+// Raise this rank's flag in `slot` on every peer (after making this GPU's earlier writes visible system-wide).
+__global__ void cn_flag_signal_kernel(unsigned int *const *peer_flags, int nranks, int my_rank, int slot, unsigned int epoch)
+{
+    const int r = threadIdx.x;
+    if (r < nranks && r != my_rank) {
+        __threadfence_system();
+        volatile unsigned int *f = peer_flags[r] + slot * nranks + my_rank;
+        *f = epoch;
+    }
+}
+
+// Raise the flag, then wait (bounded) until every peer has raised its own for this epoch.
+__global__ void cn_flag_barrier_kernel(unsigned int *const *peer_flags, const unsigned int *local_flags, int nranks, int my_rank,
+                                       int slot, unsigned int epoch, unsigned int *status)
+{
+    const int r = threadIdx.x;
+    if (r < nranks && r != my_rank) {
+        __threadfence_system();
+        volatile unsigned int *f = peer_flags[r] + slot * nranks + my_rank;
+        *f = epoch;
+        const volatile unsigned int *mine = local_flags + slot * nranks + r;
+        const long long t0 = clock64();
+        while ((int)(*mine - epoch) < 0) {
+            if (clock64() - t0 > 6000000000LL) { atomicMax(status, 10u); break; }
+            __nanosleep(200);
+        }
+        __threadfence_system();
+    }
+}
+
+// Is [p, p + bytes) inside a symmetric buffer?  Fills the peer addresses of p.
+static bool sym_lookup(cn_comm_state *c, const void *p, size_t bytes, float **peers_out)
+{
+    for (auto &b : c->sym) {
+        const char *lo = (const char *)b.base;
+        if ((const char *)p >= lo && (const char *)p + bytes <= lo + b.bytes) {
+            const size_t off = (const char *)p - lo;
+            int k = 0;
+            for (int r = 0; r < c->nranks; ++r)
+                if (r != c->rank) peers_out[k++] = (float *)((char *)b.peer[r] + off);
+            return true;
+        }
+    }
+    return false;
+}
+
 extern "C" int cn_dotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_total, const float *d_A, const float *d_Wshard,
                              float *d_C, const cn_epilogue *epi, int mode, int exchange, void *stream)
 {
@@ -221,7 +390,45 @@ extern "C" int cn_dotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_to
     local.maxout_level = 0;
     local.argmax_out = nullptr;
     float *slice = d_C + (size_t)M * start;
-    int st = cn_gemm_f32(ctx, 0, 0, M, cnt, K, d_A, M, d_Wshard, K, slice, M, &local, mode, stream);
+    int st;
+    // Fused form: when C lives in a symmetric buffer, the GEMM's epilogue stores every finished tile into all peers'
+    // copies of C as well (stores over NVLink), framed by two flag exchanges: "my copy may be written" before the
+    // kernel and "my stores are complete" after it.  No separate gather kernel runs.
+    cn_peer_out po;
+    // Whether to push is decided from values that are equal on every rank (shapes, mode), so that all ranks take the
+    // same branch: the narrowest shard must still be a shape the tensor-core kernel takes.
+    const bool shape_ok = mode != CN_GEMM_FP32_SIMT && (n_total / G) >= 16 && K >= 32 && (K & 3) == 0 && M >= 1;
+    if (G > 1 && exchange == 0 && shape_ok && ctx->comm->flags &&
+        sym_lookup(ctx->comm, d_C, (size_t)M * n_total * sizeof(float), po.C)) {
+        cn_comm_state *c = ctx->comm;
+        cudaStream_t s = cn_stream(stream);
+        const unsigned int epoch = ++c->epoch;
+        for (int i = 0; i < G - 1; ++i) po.C[i] += (size_t)M * start;   // the window this rank writes
+        po.npeers = G - 1;
+        po.ready = c->flags;   // slot 0
+        po.nranks = G;
+        po.my_rank = rank;
+        po.epoch = epoch;
+        cn_flag_signal_kernel<<<1, 32, 0, s>>>(c->d_peer_flags, G, rank, 0, epoch);
+        CN_CUDA(cudaGetLastError());
+        cn_count_launch();
+        bool pushed = false;
+        st = cn_gemm_dispatch(ctx, 0, 0, M, cnt, K, d_A, M, d_Wshard, K, slice, M, &local, mode, stream, &po, &pushed);
+        if (st != CN_OK) return st;
+        if (!ctx->gemm) ctx->gemm = new cn_gemm_workspace();
+        if (!ctx->gemm->d_status) {
+            CN_CUDA(cudaMalloc(&ctx->gemm->d_status, 64 + CN_GEMM_MAX_TICKETS * sizeof(unsigned int)));
+            CN_CUDA(cudaMemset(ctx->gemm->d_status, 0, 64 + CN_GEMM_MAX_TICKETS * sizeof(unsigned int)));
+        }
+        // a rank whose operands the tensor-core kernel refused (a misaligned shard pointer) cannot fall back on its own:
+        // the peers are already past the point of calling a collective
+        CN_REQUIRE(pushed, CN_ERR_UNSUPPORTED, "cn_dotmpi_f32: this rank's shard cannot take the fused path (16-byte alignment of W)");
+        cn_flag_barrier_kernel<<<1, 32, 0, s>>>(c->d_peer_flags, c->flags, G, rank, 1, epoch, ctx->gemm->d_status);
+        CN_CUDA(cudaGetLastError());
+        cn_count_launch();
+        return CN_OK;
+    }
+    st = cn_gemm_f32(ctx, 0, 0, M, cnt, K, d_A, M, d_Wshard, K, slice, M, &local, mode, stream);
     if (st != CN_OK || G == 1) return st;
     if (exchange == 0) return cn_allgather_cols_f32(ctx, d_C, M, n_total, stream);
 

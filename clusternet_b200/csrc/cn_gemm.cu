@@ -136,6 +136,14 @@ extern "C" int cn_gemm_f32(cn_context *ctx, int transA, int transB, int64_t M, i
                            const float *d_A, int64_t lda, const float *d_B, int64_t ldb, float *d_C, int64_t ldc,
                            const cn_epilogue *epi, int mode, void *stream)
 {
+    return cn_gemm_dispatch(ctx, transA, transB, M, N, K, d_A, lda, d_B, ldb, d_C, ldc, epi, mode, stream, nullptr, nullptr);
+}
+
+int cn_gemm_dispatch(cn_context *ctx, int transA, int transB, int64_t M, int64_t N, int64_t K, const float *d_A, int64_t lda,
+                     const float *d_B, int64_t ldb, float *d_C, int64_t ldc, const cn_epilogue *epi, int mode, void *stream,
+                     const cn_peer_out *peers, bool *used_peers)
+{
+    if (used_peers) *used_peers = false;
     CN_REQUIRE(ctx, CN_ERR_ARG, "cn_gemm_f32: null context");
     CN_REQUIRE(M >= 0 && N >= 0 && K >= 0, CN_ERR_SHAPE, "cn_gemm_f32: negative dimension");
     CN_REQUIRE(mode >= CN_GEMM_3XTF32 && mode <= CN_GEMM_FP32_SIMT, CN_ERR_ARG, "cn_gemm_f32: unknown mode %d", mode);
@@ -173,7 +181,9 @@ extern "C" int cn_gemm_f32(cn_context *ctx, int transA, int transB, int64_t M, i
         e2.activation = act;
         e2.maxout_level = fused_maxout ? L : 1;
         e2.argmax_out = fused_maxout ? argmax : nullptr;
-        st = cn_gemm_tc_launch(ctx, M, N, K, d_A, lda, d_B, ldb, target, target_ld, &e2, mode, s);
+        const bool push = peers && peers->npeers > 0 && L == 1;
+        st = cn_gemm_tc_launch(ctx, M, N, K, d_A, lda, d_B, ldb, target, target_ld, &e2, mode, s, push ? peers : nullptr);
+        if (push && used_peers) *used_peers = true;
     } else {
         st = simt_launch(ctx, transA, transB, M, N, K, d_A, lda, d_B, ldb, target, target_ld, bias, act, s);
     }

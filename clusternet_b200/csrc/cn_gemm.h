@@ -25,8 +25,25 @@ struct cn_gemm_workspace {
 // Grow-only scratch buffers owned by the context.
 int cn_gemm_scratch(cn_context *ctx, int slot, size_t bytes, void **out);
 
+// Peer windows of the output for the fused all-gather: the tensor-core kernel's epilogue stores each finished tile into
+// the same window of every peer's C (plain stores to peer memory over NVLink) in addition to the local C.
+#define CN_MAX_PEERS 7
+struct cn_peer_out {
+    int npeers = 0;
+    float *C[CN_MAX_PEERS] = {};          // peer addresses of the window that d_C points to locally
+    const unsigned int *ready = nullptr;  // local flags, one per rank, raised by the peers when they may be written to
+    int nranks = 0;
+    int my_rank = 0;
+    unsigned int epoch = 0;
+};
+
 bool cn_gemm_tc_supported(cn_context *ctx, int transA, int transB, int64_t M, int64_t N, int64_t K,
                           const float *A, int64_t lda, const float *B, int64_t ldb, const float *C, int64_t ldc);
 bool cn_gemm_tc_can_fuse_maxout(int level);
 int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const float *A, int64_t lda,
-                      const float *B, int64_t ldb, float *C, int64_t ldc, const cn_epilogue *epi, int mode, cudaStream_t s);
+                      const float *B, int64_t ldb, float *C, int64_t ldc, const cn_epilogue *epi, int mode, cudaStream_t s,
+                      const cn_peer_out *peers = nullptr);
+// cn_gemm_f32 with optional peer windows; *used_peers tells whether the launch took them (tensor-core path only).
+int cn_gemm_dispatch(cn_context *ctx, int transA, int transB, int64_t M, int64_t N, int64_t K, const float *d_A, int64_t lda,
+                     const float *d_B, int64_t ldb, float *d_C, int64_t ldc, const cn_epilogue *epi, int mode, void *stream,
+                     const cn_peer_out *peers, bool *used_peers);

@@ -82,6 +82,13 @@ struct TcParams {
     float *partials;        // [tile][split][NT][128 m][128 n]
     unsigned int *tickets;  // one per tile, self-resetting
     unsigned int *status;
+    // fused all-gather: peer copies of the C window (same leading dimension), flags the peers raise when ready
+    int npeers;
+    float *peerC[CN_MAX_PEERS];
+    const unsigned int *ready;
+    int nranks;
+    int my_rank;
+    unsigned int epoch;
 };
 
 // ---------------------------------------------------------------------------------------------- PTX wrappers
@@ -550,16 +557,44 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
 #pragma unroll
                 for (int i = 0; i < TC_BM; ++i) acc[i] = cn_apply_activation(p.bias ? acc[i] + bias : acc[i], p.act);
                 if (L <= 1) {
+                    if (p.npeers > 0) {
+                        // the peers must have announced that their copy of C may be overwritten (bounded wait)
+                        if (et == 0) {
+                            const long long t0 = clock64();
+                            for (int r = 0; r < p.nranks; ++r) {
+                                if (r == p.my_rank) continue;
+                                const volatile unsigned int *f = p.ready + r;
+                                while ((int)(*f - p.epoch) < 0) {
+                                    if (clock64() - t0 > TC_WAIT_LIMIT) { atomicMax(p.status, 9u); break; }
+                                    __nanosleep(100);
+                                }
+                            }
+                        }
+                        asm volatile("bar.sync %0, 128;" ::"r"(1 + w) : "memory");
+                    }
                     if (n < p.N) {
-                        float *dst = p.C + n * p.ldc + m0;
+                        const int64_t off = n * p.ldc + m0;
+                        float *dst = p.C + off;
                         if (m0 + TC_BM <= p.M && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
 #pragma unroll
                             for (int i = 0; i < TC_BM; i += 4)
                                 *reinterpret_cast<float4 *>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+                            for (int pr = 0; pr < p.npeers; ++pr) {
+                                float *pd = p.peerC[pr] + off;   // peer allocations are 256-byte aligned like the local one
+#pragma unroll
+                                for (int i = 0; i < TC_BM; i += 4)
+                                    *reinterpret_cast<float4 *>(pd + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+                            }
                         } else {
 #pragma unroll
                             for (int i = 0; i < TC_BM; ++i)
                                 if (m0 + i < p.M) dst[i] = acc[i];
+                            for (int pr = 0; pr < p.npeers; ++pr) {
+                                float *pd = p.peerC[pr] + off;
+#pragma unroll
+                                for (int i = 0; i < TC_BM; ++i)
+                                    if (m0 + i < p.M) pd[i] = acc[i];
+                            }
                         }
                     }
                 } else {
@@ -659,7 +694,13 @@ static int pick_splits(int64_t tiles, int kb_total, int sm_count)
 template <int NT, bool MODE3X>
 static int launch_cfg(const CUtensorMap &mw, const CUtensorMap &mhi, const CUtensorMap &mlo, const TcParams &prm, int64_t grid, cudaStream_t s)
 {
-    CN_CUDA(cudaFuncSetAttribute(cn_gemm_tc_kernel<NT, MODE3X>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<NT>::SMEM_BYTES));
+    static bool attr_set[64] = {};   // per device: the attribute belongs to the device's copy of the function
+    int dev = 0;
+    CN_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        CN_CUDA(cudaFuncSetAttribute(cn_gemm_tc_kernel<NT, MODE3X>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<NT>::SMEM_BYTES));
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
     cn_gemm_tc_kernel<NT, MODE3X><<<(unsigned)grid, TcCfg<NT>::THREADS, TcCfg<NT>::SMEM_BYTES, s>>>(mw, mhi, mlo, prm);
     CN_CUDA(cudaGetLastError());
     cn_count_launch();
@@ -667,7 +708,7 @@ static int launch_cfg(const CUtensorMap &mw, const CUtensorMap &mhi, const CUten
 }
 
 int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const float *A, int64_t lda, const float *B,
-                      int64_t ldb, float *C, int64_t ldc, const cn_epilogue *epi, int mode, cudaStream_t s)
+                      int64_t ldb, float *C, int64_t ldc, const cn_epilogue *epi, int mode, cudaStream_t s, const cn_peer_out *peers)
 {
     EncodeTiledFn enc = nullptr;
     int st = get_encode_fn(ctx, &enc);
@@ -721,6 +762,16 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
     if (const char *e = getenv("CN_GEMM_CHAIN")) { int v = atoi(e); if (v >= 1) prm.chain_kb = v; }
     prm.partials = nullptr; prm.tickets = nullptr;
     prm.status = ws->d_status;
+    prm.npeers = 0;
+    prm.ready = nullptr;
+    prm.nranks = 0; prm.my_rank = 0; prm.epoch = 0;
+    for (int i = 0; i < CN_MAX_PEERS; ++i) prm.peerC[i] = nullptr;
+    if (peers && peers->npeers > 0) {
+        prm.npeers = peers->npeers;
+        for (int i = 0; i < peers->npeers; ++i) prm.peerC[i] = peers->C[i];
+        prm.ready = peers->ready;
+        prm.nranks = peers->nranks; prm.my_rank = peers->my_rank; prm.epoch = peers->epoch;
+    }
     if (splits > 1) {
         const size_t part_bytes = (size_t)tiles * splits * nt * TC_BM * TC_BN * sizeof(float);
         void *buf = nullptr;

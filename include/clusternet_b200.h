@@ -207,6 +207,14 @@ int cn_allgather_cols_u8(cn_context *ctx, uint8_t *d_codes, int64_t M, int64_t n
 int cn_allgather_scalar_f32(cn_context *ctx, float *d_vals, void *stream);
 int cn_allreduce_sum_f32(cn_context *ctx, float *d_buf, int64_t n, void *stream);
 
+/* Symmetric buffers.  A collective call: every rank allocates `bytes` and maps the allocation of every peer (CUDA IPC
+ * over NVLink).  When the output of cn_dotmpi_f32 lies in such a buffer, the all-gather is fused into the GEMM: the
+ * kernel's epilogue stores each finished tile straight into every peer's copy of C, framed by two flag exchanges, and
+ * no gather kernel runs.  This takes the place of the per-shape receive slots that dotMPI keeps in m_matrixCache
+ * (source/clusterNet.cpp:523-556).  With one rank the call is an ordinary allocation. */
+int cn_sym_alloc(cn_context *ctx, size_t bytes, void **ptr);
+int cn_sym_free(cn_context *ctx, void *ptr);
+
 /* dotMPI: replaces ClusterNet::dotMPI (source/clusterNet.cpp:512-697) for a column-sharded B.
  * A is M x K and already resident on every rank; Wshard is this rank's K x cols_local block of the
  * K x n_total weight; C is the full M x n_total col-major output on every rank.

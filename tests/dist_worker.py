@@ -79,6 +79,15 @@ def run_nccl():
         assert np.abs(got - ref).max() / np.abs(ref).max() < 1e-5, (M, K, N)
         # sharded == unsharded up to the different split-K schedules of the two launches
         assert np.abs(got - ctx.to_numpy(full)).max() / np.abs(ref).max() < 2e-6
+        # fused GEMM -> all-gather through symmetric buffers: identical to the NCCL gather, twice in a row (epochs)
+        Cs = ctx.sym_empty(M, N)
+        for rep in range(2):
+            Cs.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            ctx.dotmpi(dA, dW, N, out=Cs, bias=db, activation=_lib.ACT_RELU)
+            ctx.gemm_check()
+            assert torch.equal(Cs, C), (M, K, N, rep, float((Cs - C).abs().max()))
         # 8-bit exchange: own slice exact, peers' slices = decode(encode(slice, absmax of that slice))
         C8 = ctx.dotmpi(dA, dW, N, bias=db, activation=_lib.ACT_RELU, exchange=1)
         ctx.gemm_check()
@@ -102,6 +111,7 @@ def run_nccl():
     assert v.tolist() == [r + 1.5 for r in range(world)]
     assert float(t[0]) == world * (world + 1) / 2
     dist.barrier()
+    ctx.sym_free_all()
     cn.check(ctx.lib.cn_comm_destroy(ctx.h))
     if rank == 0:
         print("NCCL-OK")
