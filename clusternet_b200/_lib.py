@@ -72,6 +72,8 @@ _SIGNATURES = {
     "cn_sym_free": (c_int, [c_void_p, c_void_p]),
     "cn_dotmpi_f32": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, ctypes.POINTER(Epilogue),
                               c_int, c_int, c_void_p]),
+    "cn_dottmpi_f32": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "cn_dot_sharded_out_f32": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "cn_batch_create": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, ctypes.POINTER(c_void_p)]),
     "cn_batch_destroy": (c_int, [c_void_p]),
     "cn_batch_total_batches": (c_int64, [c_void_p]),

@@ -220,6 +220,23 @@ class Context:
                                      int(exchange), self.stream_ptr()))
         return out
 
+    def dottmpi(self, A, Bshard, out=None, mode=_lib.GEMM_3XTF32):
+        """out (M x R) = A (M x n_total) . B^T with B column-sharded (this rank: R x cols_local)."""
+        n_total, M = A.shape
+        _, R = Bshard.shape
+        out = out if out is not None else self.empty(M, R)
+        check(self.lib.cn_dottmpi_f32(self.h, M, n_total, R, _ptr(A), _ptr(Bshard), _ptr(out), int(mode), self.stream_ptr()))
+        return out
+
+    def dot_sharded_out(self, A, B, out_shard, transA=False, mode=_lib.GEMM_3XTF32):
+        """out_shard (M x cols_local) = op(A) . B[:, shard]."""
+        a_cols, a_rows = A.shape
+        M, K = (a_cols, a_rows) if transA else (a_rows, a_cols)
+        n_total = B.shape[0]
+        check(self.lib.cn_dot_sharded_out_f32(self.h, int(transA), M, K, n_total, _ptr(A), _ptr(B), _ptr(out_shard), int(mode),
+                                              self.stream_ptr()))
+        return out_shard
+
     # ------------------------------------------------------------------ timers
     def tick(self, name="default"):
         check(self.lib.cn_tick(self.h, name.encode(), self.stream_ptr()))

@@ -147,6 +147,21 @@ public:
         if (B->isDistributed == 1 || out->isDistributed == 1) { dotMPI(A, B, out); return; }
         gemm(A, B, out, 0, 0, nullptr);
     }
+    // backward through a sharded weight: out = A . B^T summed over the ranks (source/clusterNet.cpp:511)
+    Matrix *dotTMPI(Matrix *A, Matrix *B) { Matrix *out = empty(A->rows, B->rows); dotTMPI(A, B, out); return out; }
+    void dotTMPI(Matrix *A, Matrix *B, Matrix *out)
+    {
+        if (B->isDistributed != 1) throw "dotTMPI: B must be a distributed (column-sharded) matrix";
+        if (A->cols != B->cols_distributed || out->rows != A->rows || out->cols != B->rows) throw "Matrix *size* error";
+        cn_detail::check(cn_dottmpi_f32(ctx_.get(), A->rows, B->cols_distributed, B->rows, A->data, B->data, out->data, GEMM_MODE, nullptr));
+    }
+    // gradient of a sharded weight: out_shard = A^T . B[:, shard] (source/clusterNet.cpp:510)
+    void TdotMPI(Matrix *A, Matrix *B, Matrix *out)
+    {
+        if (out->isDistributed != 1) throw "TdotMPI: out must be a distributed (column-sharded) matrix";
+        if (A->rows != B->rows || out->rows != A->cols || out->cols_distributed != B->cols) throw "Matrix *size* error";
+        cn_detail::check(cn_dot_sharded_out_f32(ctx_.get(), 1, A->cols, A->rows, B->cols, A->data, B->data, out->data, GEMM_MODE, nullptr));
+    }
     void Tdot(Matrix *A, Matrix *B, Matrix *out) { gemm(A, B, out, 1, 0, nullptr); }
     void dotT(Matrix *A, Matrix *B, Matrix *out) { gemm(A, B, out, 0, 1, nullptr); }
     // fused form: out = act(A.B + bias), optional maxout
@@ -155,6 +170,11 @@ public:
     Matrix *dotMPI(Matrix *A, Matrix *B) { Matrix *out = empty(A->rows, B->cols_distributed); dotMPI(A, B, out); return out; }
     void dotMPI(Matrix *A, Matrix *B, Matrix *out, int exchange_8bit = 0)
     {
+        if (out->isDistributed == 1 && B->isDistributed != 1) {   // full B, sharded out: local product, no exchange
+            if (A->cols != B->rows || out->rows != A->rows || out->cols_distributed != B->cols) throw "Matrix *size* error";
+            cn_detail::check(cn_dot_sharded_out_f32(ctx_.get(), 0, A->rows, A->cols, B->cols, A->data, B->data, out->data, GEMM_MODE, nullptr));
+            return;
+        }
         if (B->isDistributed != 1) throw "dotMPI: B must be a distributed (column-sharded) matrix";
         if (A->cols != B->rows || out->rows != A->rows || out->cols != B->cols_distributed) throw "Matrix *size* error";
         cn_detail::check(cn_dotmpi_f32(ctx_.get(), A->rows, A->cols, B->cols_distributed, A->data, B->data, out->data, nullptr,

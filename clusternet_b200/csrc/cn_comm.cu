@@ -451,3 +451,36 @@ extern "C" int cn_dotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_to
     }
     return CN_OK;
 }
+
+extern "C" int cn_dottmpi_f32(cn_context *ctx, int64_t M, int64_t n_total, int64_t R, const float *d_A, const float *d_Bshard,
+                              float *d_out, int mode, void *stream)
+{
+    CN_REQUIRE(ctx, CN_ERR_ARG, "cn_dottmpi_f32: null context");
+    CN_REQUIRE(M >= 0 && n_total >= 0 && R >= 0, CN_ERR_SHAPE, "cn_dottmpi_f32: negative dimension");
+    const int G = ctx->comm ? ctx->comm->nranks : 1, rank = ctx->comm ? ctx->comm->rank : 0;
+    int64_t start, cnt;
+    cn_shard_cols(n_total, rank, G, &start, &cnt);
+    // A1 = columns [start, start + cnt) of A: a contiguous block in column-major, no slice copy
+    const float *A1 = d_A + (size_t)M * start;
+    int st;
+    if (cnt > 0) {
+        st = cn_gemm_f32(ctx, 0, 1, M, R, cnt, A1, M, d_Bshard, R, d_out, M, nullptr, mode, stream);
+    } else {
+        st = cn_fill_f32(ctx, d_out, M * R, 0.0f, stream);
+    }
+    if (st != CN_OK || G == 1) return st;
+    return cn_allreduce_sum_f32(ctx, d_out, M * R, stream);
+}
+
+extern "C" int cn_dot_sharded_out_f32(cn_context *ctx, int transA, int64_t M, int64_t K, int64_t n_total, const float *d_A,
+                                      const float *d_B, float *d_out_shard, int mode, void *stream)
+{
+    CN_REQUIRE(ctx, CN_ERR_ARG, "cn_dot_sharded_out_f32: null context");
+    CN_REQUIRE(M >= 0 && K >= 0 && n_total >= 0, CN_ERR_SHAPE, "cn_dot_sharded_out_f32: negative dimension");
+    const int G = ctx->comm ? ctx->comm->nranks : 1, rank = ctx->comm ? ctx->comm->rank : 0;
+    int64_t start, cnt;
+    cn_shard_cols(n_total, rank, G, &start, &cnt);
+    if (cnt == 0) return CN_OK;
+    const float *B1 = d_B + (size_t)K * start;   // columns of B owned by this rank
+    return cn_gemm_f32(ctx, transA, 0, M, cnt, K, d_A, transA ? K : M, B1, K, d_out_shard, M, nullptr, mode, stream);
+}

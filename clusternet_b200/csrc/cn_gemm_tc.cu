@@ -572,29 +572,62 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                         }
                         asm volatile("bar.sync %0, 128;" ::"r"(1 + w) : "memory");
                     }
-                    if (n < p.N) {
+                    const int64_t rows_valid = (p.M - m0) < TC_BM ? (p.M - m0) : TC_BM;
+                    if (p.npeers > 0 && (rows_valid & 3) == 0 && (p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15u) == 0) {
+                        // Fused all-gather.  Scattered 16-byte stores from registers are a poor fit for NVLink, so the tile is
+                        // first laid out in shared memory exactly as it lies in C (column n = 512 contiguous bytes; the rings
+                        // are idle by now: tile 0 borrows the W ring, tile 1 the activation ring) and then written to the
+                        // local C and to every peer's C with bulk asynchronous copies.
+                        float *stg = reinterpret_cast<float *>(smem_gen + (w == 0 ? Cfg::W_RING : Cfg::A_RING));
+#pragma unroll
+                        for (int i = 0; i < TC_BM; i += 4)
+                            *reinterpret_cast<float4 *>(stg + row * TC_BM + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        asm volatile("bar.sync %0, 128;" ::"r"(1 + w) : "memory");
+                        const int64_t col0 = n0 + w * TC_BN;
+                        const int64_t cols_valid = (p.N - col0) < TC_BN ? (p.N - col0) : TC_BN;
+                        if (rows_valid == TC_BM && p.ldc == TC_BM) {
+                            // the tile is one contiguous block of C: one copy per destination
+                            if (et == 0 && cols_valid > 0) {
+                                const uint32_t bytes = (uint32_t)(cols_valid * TC_BM * sizeof(float));
+                                const int64_t off = col0 * p.ldc + m0;
+                                for (int d = 0; d <= p.npeers; ++d) {
+                                    float *dst = (d == 0 ? p.C : p.peerC[d - 1]) + off;
+                                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                                                 ::"l"(dst), "r"(smem_u32(stg)), "r"(bytes) : "memory");
+                                }
+                                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                                asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                            }
+                        } else if (n < p.N) {
+                            // one copy per column and destination
+                            const uint32_t bytes = (uint32_t)(rows_valid * sizeof(float));
+                            const int64_t off = n * p.ldc + m0;
+                            for (int d = 0; d <= p.npeers; ++d) {
+                                float *dst = (d == 0 ? p.C : p.peerC[d - 1]) + off;
+                                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                                             ::"l"(dst), "r"(smem_u32(stg + row * TC_BM)), "r"(bytes) : "memory");
+                            }
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                        }
+                    } else if (n < p.N) {
                         const int64_t off = n * p.ldc + m0;
                         float *dst = p.C + off;
                         if (m0 + TC_BM <= p.M && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
 #pragma unroll
                             for (int i = 0; i < TC_BM; i += 4)
                                 *reinterpret_cast<float4 *>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
-                            for (int pr = 0; pr < p.npeers; ++pr) {
-                                float *pd = p.peerC[pr] + off;   // peer allocations are 256-byte aligned like the local one
-#pragma unroll
-                                for (int i = 0; i < TC_BM; i += 4)
-                                    *reinterpret_cast<float4 *>(pd + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
-                            }
                         } else {
 #pragma unroll
                             for (int i = 0; i < TC_BM; ++i)
                                 if (m0 + i < p.M) dst[i] = acc[i];
-                            for (int pr = 0; pr < p.npeers; ++pr) {
-                                float *pd = p.peerC[pr] + off;
+                        }
+                        for (int pr = 0; pr < p.npeers; ++pr) {   // rare shapes only: rows not a multiple of four
+                            float *pd = p.peerC[pr] + off;
 #pragma unroll
-                                for (int i = 0; i < TC_BM; ++i)
-                                    if (m0 + i < p.M) pd[i] = acc[i];
-                            }
+                            for (int i = 0; i < TC_BM; ++i)
+                                if (m0 + i < p.M) pd[i] = acc[i];
                         }
                     }
                 } else {

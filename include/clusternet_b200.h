@@ -223,6 +223,18 @@ int cn_sym_free(cn_context *ctx, void *ptr);
 int cn_dotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_total, const float *d_A,
                   const float *d_Wshard, float *d_C, const cn_epilogue *epi, int mode, int exchange, void *stream);
 
+/* dotTMPI: replaces ClusterNet::dotTMPI (source/clusterNet.cpp:511,628-642,698-727), the backward product through a
+ * column-sharded weight: out (M x R) = A (M x n_total) . B^T, where this rank holds the R x cols_local block of the
+ * R x n_total matrix B.  Each rank multiplies its column slice of A with its shard (transposed) and the full-size
+ * partial products are summed over the ranks (all-reduce in place of the reference's ring of partials + add loop). */
+int cn_dottmpi_f32(cn_context *ctx, int64_t M, int64_t n_total, int64_t R, const float *d_A, const float *d_Bshard,
+                   float *d_out, int mode, void *stream);
+/* dot / TdotMPI into a column-sharded output (source/clusterNet.cpp:510,612-625,729-730): out_shard (M x cols_local)
+ * = op(A) . B[:, shard], B being a full K x n_total matrix on every rank; no communication.  transA = 1 gives
+ * TdotMPI (A stored K x M). */
+int cn_dot_sharded_out_f32(cn_context *ctx, int transA, int64_t M, int64_t K, int64_t n_total, const float *d_A,
+                           const float *d_B, float *d_out_shard, int mode, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Batch allocator (dense path).  Replaces BatchAllocator::init / init_batch_buffer /
  * broadcast_batch_to_processes / allocate_next_batch_async / replace_current_batch_with_next

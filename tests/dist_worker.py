@@ -101,6 +101,34 @@ def run_nccl():
                 p = oracle.absmax(sl)
                 want = oracle.decompress(ctx.codebook, oracle.compress(ctx.codebook, sl, p), p)
                 assert np.array_equal(got8[:, sr:sr + cr], want.reshape(cr, M).T), (M, K, N, r)
+    # tests/clusterNet_test.cu:338-394: sharded all-ones weight 8783 x 317; dot -> 8783, dotTMPI -> 317, dot into the
+    # sharded matrix -> 17, exactly, over several epochs
+    s0, c0 = ctx.shard_cols(317, rank, world)
+    m1 = torch.ones((c0, 8783), device="cuda")                   # local shard 8783 x c0 (column-major)
+    m2, m3, m4 = torch.ones((8783, 111), device="cuda"), torch.ones((317, 17), device="cuda"), torch.ones((17, 8783), device="cuda")
+    for epoch in range(2):
+        d = ctx.dotmpi(m2, m1, 317)
+        assert d.shape == (317, 111) and bool((d == 8783.0).all())
+        t = ctx.dottmpi(m3, m1)
+        assert t.shape == (8783, 17) and bool((t == 317.0).all())
+        ctx.dot_sharded_out(m4, m3, m1)
+        assert bool((m1 == 17.0).all())
+        m1.fill_(1.0)
+    # random data: dotTMPI and TdotMPI against fp64
+    A = rng.uniform(-1, 1, (64, 400)).astype(np.float32)
+    Bf = rng.uniform(-1, 1, (96, 400)).astype(np.float32)       # full B: R x n_total
+    s0, c0 = ctx.shard_cols(400, rank, world)
+    got = ctx.to_numpy(ctx.dottmpi(ctx.colmajor(A), ctx.colmajor(np.ascontiguousarray(Bf[:, s0:s0 + c0]))))
+    ref = oracle.gemm_f64(A, Bf, transB=True)
+    assert np.abs(got - ref).max() / np.abs(ref).max() < 1e-5
+    At = rng.uniform(-1, 1, (128, 200)).astype(np.float32)      # stored K x M
+    Bn = rng.uniform(-1, 1, (128, 300)).astype(np.float32)
+    s0, c0 = ctx.shard_cols(300, rank, world)
+    osh = ctx.empty(200, c0)
+    ctx.dot_sharded_out(ctx.colmajor(At), ctx.colmajor(Bn), osh, transA=True)
+    ref = oracle.gemm_f64(At, Bn, transA=True)[:, s0:s0 + c0]
+    assert np.abs(ctx.to_numpy(osh) - ref).max() / np.abs(ref).max() < 1e-5
+    ctx.gemm_check()
     # scalar gather and all-reduce
     v = torch.zeros(world, device="cuda")
     v[rank] = rank + 1.5
