@@ -74,6 +74,15 @@ _SIGNATURES = {
                               c_int, c_int, c_void_p]),
     "cn_dottmpi_f32": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "cn_dot_sharded_out_f32": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "cn_softmax": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "cn_create_t_matrix": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "cn_add": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "cn_sub": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "cn_mul": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "cn_scalar_mul": (c_int, [c_void_p, c_void_p, c_float, c_void_p, c_int64, c_void_p]),
+    "cn_activation_gradient": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p]),
+    "cn_rmsprop_update": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_int64, c_void_p]),
+    "cn_grad_sync_8bit": (c_int, [c_void_p, c_void_p, c_int64, c_float, c_void_p]),
     "cn_batch_create": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, ctypes.POINTER(c_void_p)]),
     "cn_batch_destroy": (c_int, [c_void_p]),
     "cn_batch_total_batches": (c_int64, [c_void_p]),

@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libclusternet_b200.so")
 SOURCES = ["cn_context.cu", "cn_codec.cu", "cn_layout.cu", "cn_rand.cu", "cn_elementwise.cu", "cn_gemm.cu",
-           "cn_gemm_tc.cu", "cn_comm.cu", "cn_batch.cu"]
+           "cn_gemm_tc.cu", "cn_comm.cu", "cn_batch.cu", "cn_train.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fno-fast-math", "-Xcompiler", "-ffp-contract=off"]

@@ -360,3 +360,157 @@ private:
         publish(X, Y, dx, dy, n);
     }
 };
+
+
+// ------------------------------------------------------------------------------------------------------------
+// Layer: the reference's data-parallel MLP layer (source/Layer.h, source/Layer.cpp), dense path.
+//   forward           source/Layer.cpp:250-261 (+ unit_activation :147-178)   dot + bias + activation fused in one GEMM
+//   backward_errors   :314-330      softmax output: out - onehot(target); hidden: dotT(next->error, w) * f'(activation)
+//   backward_grads    :332-339      Tdot(activation, next->error), then the gradient exchange
+//   MPI_synchronization_async + wait_for_synchronization :341-437   -> cn_grad_sync_8bit (compress, gather, decode-sum)
+//   weight_update     :439-471      RMSprop_with_weight_update on the summed gradient
+// As in the reference the bias is never updated (its update is commented out there), the gradient is summed over the
+// ranks and not averaged, and with useDropout == false the activation is scaled by (1 - DROPOUT) instead.
+// ------------------------------------------------------------------------------------------------------------
+typedef enum Unittype_t { Logistic = 0, Rectified_Linear = 1, Softmax = 2, Linear = 4, Double_Rectified_Linear = 8, Input = 16 } Unittype_t;
+typedef enum ParallelismType_t { None = 0, DataParallelism = 1, ModelParallelism = 2 } ParallelismType_t;
+typedef enum Compression_t { bits_32 = 0, bits_8 = 1 } Compression_t;
+
+class Layer {
+public:
+    Matrix *out = nullptr, *activation = nullptr, *error = nullptr, *target = nullptr, *target_matrix = nullptr;
+    Matrix *w_next = nullptr, *b_next = nullptr, *w_rms_next = nullptr, *w_grad_next = nullptr;
+    Layer *next = nullptr, *prev = nullptr;
+    float LEARNING_RATE = 0.006f, RMSPROP_MOMENTUM = 0.9f, DROPOUT = 0.5f, MAX_GRAD_VALUE = 1.0f;
+    float RUNNING_ERROR = 0.0f, RUNNING_SAMPLE_SIZE = 0.0f;
+    int64_t UNITCOUNT = 0, BATCH_SIZE = 0;
+    Unittype_t UNIT_TYPE = Rectified_Linear;
+    ParallelismType_t PARALLELISM = None;
+    Compression_t compression = bits_8;
+    bool GATHER_SCALES = false;   // false: the reference's fixed MAX_GRAD_VALUE; true: per-rank absmax, gathered with the codes
+    ClusterNet *GPU = nullptr;
+
+    Layer(int64_t unitcount, int64_t start_batch_size, Unittype_t unit, ClusterNet *gpu) { init(unitcount, start_batch_size, unit, gpu); }
+    Layer(int64_t unitcount, Unittype_t unit) { init(unitcount, 0, unit, nullptr); }
+
+    void link_with_next_layer(Layer *next_layer)
+    {
+        next = next_layer;
+        if (next->BATCH_SIZE == 0) next->BATCH_SIZE = BATCH_SIZE;
+        if (!next->GPU) next->GPU = GPU;
+        next->PARALLELISM = PARALLELISM;
+        w_next = GPU->uniformSqrtWeight(UNITCOUNT, next->UNITCOUNT);
+        w_rms_next = GPU->zeros(UNITCOUNT, next->UNITCOUNT);
+        w_grad_next = GPU->zeros(UNITCOUNT, next->UNITCOUNT);
+        b_next = GPU->zeros(1, next->UNITCOUNT);
+        next->out = GPU->zeros(BATCH_SIZE, next->UNITCOUNT);
+        next->activation = GPU->zeros(BATCH_SIZE, next->UNITCOUNT);
+        next->error = GPU->zeros(BATCH_SIZE, next->UNITCOUNT);
+        next->prev = this;
+    }
+
+    void forward(bool useDropout = true)
+    {
+        if (!prev) {   // input layer: `activation` holds the batch
+            unit_activation(useDropout);
+            next->forward(useDropout);
+            return;
+        }
+        if (PARALLELISM == DataParallelism && useDropout) { prev->wait_for_synchronization(); prev->weight_update(); }
+        // dot + addMatrixVector + activation: one fused GEMM; softmax and dropout follow as in unit_activation
+        cn_epilogue epi;
+        epi.bias = prev->b_next->data;
+        epi.activation = UNIT_TYPE == Rectified_Linear ? CN_ACT_RELU : UNIT_TYPE == Logistic ? CN_ACT_LOGISTIC
+                         : UNIT_TYPE == Double_Rectified_Linear ? CN_ACT_DOUBLE_RELU : CN_ACT_LINEAR;
+        epi.maxout_level = 0;
+        epi.argmax_out = nullptr;
+        GPU->dot(prev->out, prev->w_next, UNIT_TYPE == Softmax ? out : activation, epi);
+        unit_activation(useDropout);
+        if (next) next->forward(useDropout);
+    }
+
+    void backward_errors()
+    {
+        if (!target) next->backward_errors();
+        if (target) {
+            if (out->cols != target->cols) {
+                if (!target_matrix) target_matrix = GPU->zeros(BATCH_SIZE, out->cols);
+                cn_detail::check(cn_create_t_matrix(GPU->context(), target->data, target_matrix->data, out->rows, out->cols, nullptr));
+                cn_detail::check(cn_sub(GPU->context(), out->data, target_matrix->data, error->data, out->size, nullptr));
+            } else {
+                cn_detail::check(cn_sub(GPU->context(), activation->data, target->data, error->data, out->size, nullptr));
+            }
+            return;
+        }
+        if (UNIT_TYPE == Input) { backward_grads(); return; }
+        int act = UNIT_TYPE == Rectified_Linear ? CN_ACT_RELU : UNIT_TYPE == Logistic ? CN_ACT_LOGISTIC
+                  : UNIT_TYPE == Double_Rectified_Linear ? CN_ACT_DOUBLE_RELU : -1;
+        if (act < 0) throw "Unknown unit";
+        cn_detail::check(cn_activation_gradient(GPU->context(), activation->data, act, out->data, out->size, nullptr));
+        GPU->dotT(next->error, w_next, error);
+        cn_detail::check(cn_mul(GPU->context(), error->data, out->data, error->data, out->size, nullptr));
+    }
+
+    void backward_grads()
+    {
+        GPU->Tdot(activation, next->error, w_grad_next);
+        MPI_synchronization_async();
+        if (!next->target) next->backward_grads();
+    }
+
+    void MPI_synchronization_async()
+    {
+        if (PARALLELISM != DataParallelism) return;
+        isSynchronizing = true;   // the exchange itself is queued in wait_for_synchronization, stream-ordered
+    }
+
+    void wait_for_synchronization()
+    {
+        if (target || !isSynchronizing || PARALLELISM != DataParallelism) return;
+        if (compression == bits_8)
+            cn_detail::check(cn_grad_sync_8bit(GPU->context(), w_grad_next->data, w_grad_next->size, GATHER_SCALES ? 0.0f : MAX_GRAD_VALUE, nullptr));
+        else
+            cn_detail::check(cn_allreduce_sum_f32(GPU->context(), w_grad_next->data, w_grad_next->size, nullptr));
+        isSynchronizing = false;
+    }
+
+    void weight_update()
+    {
+        if (target) return;
+        if (PARALLELISM != DataParallelism && next) next->weight_update();
+        cn_detail::check(cn_rmsprop_update(GPU->context(), w_rms_next->data, w_grad_next->data, w_next->data, RMSPROP_MOMENTUM, LEARNING_RATE,
+                                          w_next->size, nullptr));
+    }
+
+private:
+    bool isSynchronizing = false;
+
+    void init(int64_t unitcount, int64_t start_batch_size, Unittype_t unit, ClusterNet *gpu)
+    {
+        UNITCOUNT = unitcount;
+        BATCH_SIZE = start_batch_size;
+        UNIT_TYPE = unit;
+        GPU = gpu;
+        if (BATCH_SIZE > 0 && gpu) {
+            out = gpu->zeros(BATCH_SIZE, UNITCOUNT);
+            activation = gpu->zeros(BATCH_SIZE, UNITCOUNT);
+        }
+    }
+
+    void unit_activation(bool useDropout)
+    {
+        if (UNIT_TYPE == Softmax) {
+            cn_detail::check(cn_softmax(GPU->context(), out->data, out->data, out->rows, out->cols, nullptr));
+            return;
+        }
+        if (useDropout) {
+            Matrix *d = GPU->dropout(activation, DROPOUT);
+            cn_detail::cuda(cudaMemcpyAsync(out->data, d->data, out->bytes, cudaMemcpyDeviceToDevice, nullptr));
+            cn_detail::cuda(cudaStreamSynchronize(nullptr));
+            cudaFree(d->data);
+            free(d);
+        } else {
+            cn_detail::check(cn_scalar_mul(GPU->context(), activation->data, 1.0f - DROPOUT, out->data, out->size, nullptr));
+        }
+    }
+};

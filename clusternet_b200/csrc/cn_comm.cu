@@ -327,17 +327,6 @@ extern "C" int cn_sym_free(cn_context *ctx, void *ptr)
     return CN_OK;
 }
 
-// Raise this rank's flag in `slot` on every peer (after making this GPU's earlier writes visible system-wide).
-__global__ void cn_flag_signal_kernel(unsigned int *const *peer_flags, int nranks, int my_rank, int slot, unsigned int epoch)
-{
-    const int r = threadIdx.x;
-    if (r < nranks && r != my_rank) {
-        __threadfence_system();
-        volatile unsigned int *f = peer_flags[r] + slot * nranks + my_rank;
-        *f = epoch;
-    }
-}
-
 // Raise the flag, then wait (bounded) until every peer has raised its own for this epoch.
 __global__ void cn_flag_barrier_kernel(unsigned int *const *peer_flags, const unsigned int *local_flags, int nranks, int my_rank,
                                        int slot, unsigned int epoch, unsigned int *status)
@@ -392,8 +381,8 @@ extern "C" int cn_dotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_to
     float *slice = d_C + (size_t)M * start;
     int st;
     // Fused form: when C lives in a symmetric buffer, the GEMM's epilogue stores every finished tile into all peers'
-    // copies of C as well (stores over NVLink), framed by two flag exchanges: "my copy may be written" before the
-    // kernel and "my stores are complete" after it.  No separate gather kernel runs.
+    // copies of C as well (bulk copies over NVLink), framed by two flag exchanges: "my copy may be written", raised by
+    // the GEMM kernel when it starts, and "my stores are complete", a one-block kernel after it.  No gather kernel runs.
     cn_peer_out po;
     // Whether to push is decided from values that are equal on every rank (shapes, mode), so that all ranks take the
     // same branch: the narrowest shard must still be a shape the tensor-core kernel takes.
@@ -409,9 +398,7 @@ extern "C" int cn_dotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_to
         po.nranks = G;
         po.my_rank = rank;
         po.epoch = epoch;
-        cn_flag_signal_kernel<<<1, 32, 0, s>>>(c->d_peer_flags, G, rank, 0, epoch);
-        CN_CUDA(cudaGetLastError());
-        cn_count_launch();
+        po.peer_flags = c->d_peer_flags;   // the GEMM kernel raises this rank's "ready" flag itself when it starts
         bool pushed = false;
         st = cn_gemm_dispatch(ctx, 0, 0, M, cnt, K, d_A, M, d_Wshard, K, slice, M, &local, mode, stream, &po, &pushed);
         if (st != CN_OK) return st;
@@ -483,4 +470,26 @@ extern "C" int cn_dot_sharded_out_f32(cn_context *ctx, int transA, int64_t M, in
     if (cnt == 0) return CN_OK;
     const float *B1 = d_B + (size_t)K * start;   // columns of B owned by this rank
     return cn_gemm_f32(ctx, transA, 0, M, cnt, K, d_A, transA ? K : M, B1, K, d_out_shard, M, nullptr, mode, stream);
+}
+
+// ---- helpers for the gradient exchange in cn_train.cu
+int cn_comm_info(cn_context *ctx, int *rank, int *nranks, float **d_scales)
+{
+    *rank = ctx->comm ? ctx->comm->rank : 0;
+    *nranks = ctx->comm ? ctx->comm->nranks : 1;
+    *d_scales = ctx->comm ? ctx->comm->d_scales : nullptr;
+    return CN_OK;
+}
+
+// codes_all: nranks blocks of n bytes, block [rank] filled; scales (optional): nranks floats, entry [rank] filled
+int cn_comm_gather_codes(cn_context *ctx, uint8_t *d_codes_all, int64_t n, float *d_scales, void *stream)
+{
+    cn_comm_state *c = ctx->comm;
+    if (!c || c->nranks == 1) return CN_OK;
+    CN_NCCL(g_nccl.GroupStart());
+    ncclResult_t r1 = g_nccl.AllGather(d_codes_all + (size_t)c->rank * n, d_codes_all, (size_t)n, ncclUint8, c->comm, cn_stream(stream));
+    ncclResult_t r2 = d_scales ? g_nccl.AllGather(d_scales + c->rank, d_scales, 1, ncclFloat, c->comm, cn_stream(stream)) : ncclSuccess;
+    ncclResult_t r3 = g_nccl.GroupEnd();
+    CN_REQUIRE(r1 == ncclSuccess && r2 == ncclSuccess && r3 == ncclSuccess, CN_ERR_NCCL, "cn_grad_sync_8bit: all-gather failed");
+    return CN_OK;
 }

@@ -32,6 +32,7 @@ struct cn_peer_out {
     int npeers = 0;
     float *C[CN_MAX_PEERS] = {};          // peer addresses of the window that d_C points to locally
     const unsigned int *ready = nullptr;  // local flags, one per rank, raised by the peers when they may be written to
+    unsigned int *const *peer_flags = nullptr;   // device table: flag block of every rank (this kernel raises its own "ready")
     int nranks = 0;
     int my_rank = 0;
     unsigned int epoch = 0;

@@ -86,6 +86,7 @@ struct TcParams {
     int npeers;
     float *peerC[CN_MAX_PEERS];
     const unsigned int *ready;
+    unsigned int *const *peer_flags;
     int nranks;
     int my_rank;
     unsigned int epoch;
@@ -308,6 +309,14 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     volatile int *last_flag = reinterpret_cast<volatile int *>(bar_gen + 456);   // one word per W tile
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // Fused all-gather: the start of this kernel means everything queued earlier on this GPU's stream has finished, so
+    // this rank's copy of C may now be overwritten by its peers: tell them (slot 0 of their flag block).
+    if (p.npeers > 0 && blockIdx.x == 0 && threadIdx.x < p.nranks && (int)threadIdx.x != p.my_rank) {
+        __threadfence_system();
+        volatile unsigned int *f = p.peer_flags[threadIdx.x] + p.my_rank;
+        *f = p.epoch;
+    }
 
     // unit decode: split-major launch order
     const int64_t tiles = p.tiles_n * p.tiles_m;
@@ -797,12 +806,14 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
     prm.status = ws->d_status;
     prm.npeers = 0;
     prm.ready = nullptr;
+    prm.peer_flags = nullptr;
     prm.nranks = 0; prm.my_rank = 0; prm.epoch = 0;
     for (int i = 0; i < CN_MAX_PEERS; ++i) prm.peerC[i] = nullptr;
     if (peers && peers->npeers > 0) {
         prm.npeers = peers->npeers;
         for (int i = 0; i < peers->npeers; ++i) prm.peerC[i] = peers->C[i];
         prm.ready = peers->ready;
+        prm.peer_flags = peers->peer_flags;
         prm.nranks = peers->nranks; prm.my_rank = peers->my_rank; prm.epoch = peers->epoch;
     }
     if (splits > 1) {

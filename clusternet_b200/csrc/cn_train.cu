@@ -1,0 +1,195 @@
+// Elementwise kernels of the data-parallel training step and the 8-bit gradient exchange.
+// They take the place of the kernels the reference's Layer class strings together per step
+// (source/Layer.cpp:147-178,180-200,314-339,341-437,439-471):
+//   kSoftMax source/clusterKernels.cu:651-688, kCreate_t_matrix :775-790, kSub :332-339, kMul :323-330, kAdd :313-320,
+//   kScalarMul, kRectifiedLinear_Derivative :813-821, kLogisticGrad, kDoubleRectifiedLinear_Derivative,
+//   kRMSprop_with_weight_update :1306-1325,
+// and fuse the per-peer decompression_8bit + add loop of Layer::wait_for_synchronization into one pass.
+#include <float.h>
+#include "cn_gemm.h"
+
+// ---- softmax over the columns of a column-major rows x cols matrix: one thread per row, the row's maximum, sum and
+// quotient taken in the reference's order with the same fast exponential, so results match it bit for bit.
+__global__ void cn_softmax_kernel(const float *__restrict__ A, float *__restrict__ out, int64_t rows, int64_t cols)
+{
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; row < rows; row += stride) {
+        float mx = -FLT_MAX;
+        for (int64_t i = 0; i < cols; ++i) {
+            const float v = A[i * rows + row];
+            if (v > mx) mx = v;
+        }
+        float sum = 0.0f;
+        for (int64_t i = 0; i < cols; ++i) sum += __expf(A[i * rows + row] - mx);
+        for (int64_t i = 0; i < cols; ++i) out[i * rows + row] = __expf(A[i * rows + row] - mx) / sum;
+    }
+}
+
+// out = one-hot(labels): zero fill and scatter in one pass over the output
+__global__ void cn_t_matrix_kernel(const float *__restrict__ labels, float *__restrict__ out, int64_t rows, int64_t n)
+{
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const int64_t row = i % rows, col = i / rows;
+        out[i] = ((int64_t)(int)labels[row] == col) ? 1.0f : 0.0f;
+    }
+}
+
+enum { EW_ADD = 0, EW_SUB = 1, EW_MUL = 2, EW_SCALAR_MUL = 3, EW_GRAD_RELU = 4, EW_GRAD_LOGISTIC = 5, EW_GRAD_DOUBLE_RELU = 6 };
+
+template <int OP>
+__global__ void cn_ew_kernel(const float *__restrict__ A, const float *__restrict__ B, float s, float *__restrict__ out, int64_t n)
+{
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float a = A[i];
+        float r;
+        if (OP == EW_ADD) r = a + B[i];
+        else if (OP == EW_SUB) r = a - B[i];
+        else if (OP == EW_MUL) r = a * B[i];
+        else if (OP == EW_SCALAR_MUL) r = a * s;
+        else if (OP == EW_GRAD_RELU) r = a > 0.0f ? 1.0f : 0.0f;
+        else if (OP == EW_GRAD_LOGISTIC) r = a * (1.0f - a);
+        else r = (a > 0.0f && a < 1.0f) ? 1.0f : 0.0f;
+        out[i] = r;
+    }
+}
+
+// kRMSprop_with_weight_update: RMS = m*RMS + (1-m)*g^2 ; w -= lr * g / (sqrt(RMS) + 1e-8).  The reference divides with
+// fdividef and squares with powf(g, 2); both are reproduced (powf(x, 2.0f) equals x*x in CUDA's implementation).
+__global__ void cn_rmsprop_kernel(float *__restrict__ RMS, const float *__restrict__ grad, float *__restrict__ w, float rms_mult, float lr, int64_t n)
+{
+    const float rec = 1.0f - rms_mult;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float g = grad[i];
+        const float r = (rms_mult * RMS[i]) + (powf(g, 2.0f) * rec);
+        RMS[i] = r;
+        w[i] -= lr * fdividef(g, sqrtf(r) + 1.0e-08f);
+    }
+}
+
+// grad[i] += sum over peers r != me of decode_r(codes_r[i]); decode tables as kDecompression_8bit builds them, one per
+// rank with that rank's scale; peers are added in rank order (the order of the reference's loop).
+__global__ void __launch_bounds__(512)
+cn_decode_sum_kernel(float *__restrict__ grad, const uint8_t *__restrict__ codes, const float *__restrict__ scales,
+                     const float *__restrict__ g_tbl, int64_t n, int nranks, int my_rank)
+{
+    extern __shared__ float lut[];   // nranks x 256
+    for (int e = threadIdx.x; e < nranks * 256; e += blockDim.x) {
+        const int r = e >> 8, c = e & 255, i = c & 127;
+        const float p = scales[r];
+        float v;
+        if (i < CN_CODEBOOK_N) {
+            v = __fmul_rn(g_tbl[i], p);
+            if (c >= 128) v = -v;
+        } else {
+            v = (c == 255) ? -p : p;
+        }
+        lut[e] = v;
+    }
+    __syncthreads();
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float g = grad[i];
+        for (int r = 0; r < nranks; ++r)
+            if (r != my_rank) g += lut[(r << 8) + codes[(size_t)r * n + i]];
+        grad[i] = g;
+    }
+}
+
+static int ew_grid(const cn_context *ctx, int64_t n)
+{
+    int64_t blocks = (n + 255) / 256, cap = (int64_t)ctx->sm_count * 8;
+    if (blocks < 1) blocks = 1;
+    return (int)(blocks < cap ? blocks : cap);
+}
+
+extern "C" int cn_softmax(cn_context *ctx, const float *d_A, float *d_out, int64_t rows, int64_t cols, void *stream)
+{
+    CN_REQUIRE(ctx && rows >= 0 && cols >= 0 && (rows * cols == 0 || (d_A && d_out)), CN_ERR_ARG, "cn_softmax: bad argument");
+    if (rows * cols == 0) return CN_OK;
+    cn_softmax_kernel<<<(unsigned)((rows + 127) / 128 < 1024 ? (rows + 127) / 128 : 1024), 128, 0, cn_stream(stream)>>>(d_A, d_out, rows, cols);
+    CN_CUDA(cudaGetLastError());
+    cn_count_launch();
+    return CN_OK;
+}
+
+extern "C" int cn_create_t_matrix(cn_context *ctx, const float *d_labels, float *d_out, int64_t rows, int64_t cols, void *stream)
+{
+    CN_REQUIRE(ctx && rows >= 0 && cols >= 0 && (rows * cols == 0 || (d_labels && d_out)), CN_ERR_ARG, "cn_create_t_matrix: bad argument");
+    if (rows * cols == 0) return CN_OK;
+    cn_t_matrix_kernel<<<ew_grid(ctx, rows * cols), 256, 0, cn_stream(stream)>>>(d_labels, d_out, rows, rows * cols);
+    CN_CUDA(cudaGetLastError());
+    cn_count_launch();
+    return CN_OK;
+}
+
+template <int OP>
+static int ew_launch(cn_context *ctx, const float *A, const float *B, float s, float *out, int64_t n, void *stream, bool needs_b)
+{
+    CN_REQUIRE(ctx && n >= 0 && (n == 0 || (A && out && (!needs_b || B))), CN_ERR_ARG, "elementwise op: bad argument");
+    if (n == 0) return CN_OK;
+    cn_ew_kernel<OP><<<ew_grid(ctx, n), 256, 0, cn_stream(stream)>>>(A, B, s, out, n);
+    CN_CUDA(cudaGetLastError());
+    cn_count_launch();
+    return CN_OK;
+}
+
+extern "C" int cn_add(cn_context *ctx, const float *a, const float *b, float *out, int64_t n, void *stream) { return ew_launch<EW_ADD>(ctx, a, b, 0.f, out, n, stream, true); }
+extern "C" int cn_sub(cn_context *ctx, const float *a, const float *b, float *out, int64_t n, void *stream) { return ew_launch<EW_SUB>(ctx, a, b, 0.f, out, n, stream, true); }
+extern "C" int cn_mul(cn_context *ctx, const float *a, const float *b, float *out, int64_t n, void *stream) { return ew_launch<EW_MUL>(ctx, a, b, 0.f, out, n, stream, true); }
+extern "C" int cn_scalar_mul(cn_context *ctx, const float *a, float s, float *out, int64_t n, void *stream) { return ew_launch<EW_SCALAR_MUL>(ctx, a, nullptr, s, out, n, stream, false); }
+
+extern "C" int cn_activation_gradient(cn_context *ctx, const float *d_activation, int activation, float *d_out, int64_t n, void *stream)
+{
+    switch (activation) {
+        case CN_ACT_RELU: return ew_launch<EW_GRAD_RELU>(ctx, d_activation, nullptr, 0.f, d_out, n, stream, false);
+        case CN_ACT_LOGISTIC: return ew_launch<EW_GRAD_LOGISTIC>(ctx, d_activation, nullptr, 0.f, d_out, n, stream, false);
+        case CN_ACT_DOUBLE_RELU: return ew_launch<EW_GRAD_DOUBLE_RELU>(ctx, d_activation, nullptr, 0.f, d_out, n, stream, false);
+    }
+    cn_set_error("cn_activation_gradient: no derivative for activation %d (the reference throws 'Unknown unit')", activation);
+    return CN_ERR_ARG;
+}
+
+extern "C" int cn_rmsprop_update(cn_context *ctx, float *d_rms, const float *d_grad, float *d_w, float rms_multiplier, float learning_rate,
+                                 int64_t n, void *stream)
+{
+    CN_REQUIRE(ctx && n >= 0 && (n == 0 || (d_rms && d_grad && d_w)), CN_ERR_ARG, "cn_rmsprop_update: bad argument");
+    if (n == 0) return CN_OK;
+    cn_rmsprop_kernel<<<ew_grid(ctx, n), 256, 0, cn_stream(stream)>>>(d_rms, d_grad, d_w, rms_multiplier, learning_rate, n);
+    CN_CUDA(cudaGetLastError());
+    cn_count_launch();
+    return CN_OK;
+}
+
+// comm-side pieces live in cn_comm.cu
+int cn_comm_gather_codes(cn_context *ctx, uint8_t *d_codes_all, int64_t n, float *d_scales, void *stream);
+int cn_comm_info(cn_context *ctx, int *rank, int *nranks, float **d_scales);
+
+extern "C" int cn_grad_sync_8bit(cn_context *ctx, float *d_grad, int64_t n, float fixed_precision, void *stream)
+{
+    CN_REQUIRE(ctx && n >= 0 && (n == 0 || d_grad), CN_ERR_ARG, "cn_grad_sync_8bit: bad argument");
+    int rank = 0, G = 1;
+    float *scales = nullptr;
+    cn_comm_info(ctx, &rank, &G, &scales);
+    if (G == 1 || n == 0) return CN_OK;
+    void *buf = nullptr;
+    int st = cn_gemm_scratch(ctx, CN_GEMM_SLOT_EXCHANGE, (size_t)G * n, &buf);
+    if (st != CN_OK) return st;
+    uint8_t *codes = (uint8_t *)buf;
+    // scale: this rank's absmax (gathered with the codes), or the caller's fixed value on every rank
+    if (fixed_precision > 0.0f) {
+        if ((st = cn_fill_f32(ctx, scales, G, fixed_precision, stream)) != CN_OK) return st;
+    } else {
+        if ((st = cn_absmax_f32(ctx, d_grad, n, scales + rank, stream)) != CN_OK) return st;
+    }
+    if ((st = cn_compress_8bit_dp(ctx, d_grad, scales + rank, n, codes + (size_t)rank * n, stream)) != CN_OK) return st;
+    if ((st = cn_comm_gather_codes(ctx, codes, n, fixed_precision > 0.0f ? nullptr : scales, stream)) != CN_OK) return st;
+    int64_t blocks = (n + 511) / 512, cap = (int64_t)ctx->sm_count * 4;
+    cn_decode_sum_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 512, (size_t)G * 256 * sizeof(float), cn_stream(stream)>>>(
+        d_grad, codes, scales, ctx->d_tbl, n, G, rank);
+    CN_CUDA(cudaGetLastError());
+    cn_count_launch();
+    return CN_OK;
+}

@@ -236,6 +236,33 @@ int cn_dot_sharded_out_f32(cn_context *ctx, int transA, int64_t M, int64_t K, in
                            const float *d_B, float *d_out_shard, int mode, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Data-parallel training step (the reference's Layer class, source/Layer.cpp): elementwise pieces and the 8-bit
+ * gradient exchange.
+ * ------------------------------------------------------------------------------------------- */
+/* softmax over the columns of each row (kSoftMax, source/clusterKernels.cu:651-688; same order, same __expf). */
+int cn_softmax(cn_context *ctx, const float *d_A, float *d_out, int64_t rows, int64_t cols, void *stream);
+/* one-hot target matrix from a rows x 1 label vector stored as floats (kCreate_t_matrix, :775-790; zero fill included). */
+int cn_create_t_matrix(cn_context *ctx, const float *d_labels, float *d_out, int64_t rows, int64_t cols, void *stream);
+/* add / sub / mul / scalarMul (kAdd :313-320, kSub :332-339, kMul :323-330). */
+int cn_add(cn_context *ctx, const float *d_a, const float *d_b, float *d_out, int64_t n, void *stream);
+int cn_sub(cn_context *ctx, const float *d_a, const float *d_b, float *d_out, int64_t n, void *stream);
+int cn_mul(cn_context *ctx, const float *d_a, const float *d_b, float *d_out, int64_t n, void *stream);
+int cn_scalar_mul(cn_context *ctx, const float *d_a, float s, float *d_out, int64_t n, void *stream);
+/* derivative of the unit from its activation (Layer::activation_gradient, source/Layer.cpp:180-200): ReLU x>0?1:0
+ * (kRectifiedLinear_Derivative :813-821), logistic a(1-a), double ReLU 0<a<1?1:0. */
+int cn_activation_gradient(cn_context *ctx, const float *d_activation, int activation, float *d_out, int64_t n, void *stream);
+/* RMSprop_with_weight_update (kRMSprop_with_weight_update, :1306-1325): RMS = m RMS + (1-m) g^2; w -= lr g / (sqrt(RMS)+1e-8). */
+int cn_rmsprop_update(cn_context *ctx, float *d_rms, const float *d_grad, float *d_w, float rms_multiplier, float learning_rate,
+                      int64_t n, void *stream);
+/* Layer::MPI_synchronization_async + wait_for_synchronization (source/Layer.cpp:341-437) in one call: the rank's
+ * gradient is 8-bit compressed, codes (and scales) are all-gathered, and the peers' decoded gradients are added to
+ * d_grad in rank order — one fused decode-and-sum pass instead of a decompression_8bit + add pair per peer.
+ * fixed_precision > 0 uses that scale on every rank (the reference's MAX_GRAD_VALUE = 1.0f); fixed_precision <= 0 uses
+ * each rank's absmax and gathers the scales (what the reference's commented-out code intended; as committed it decodes
+ * with an uninitialised array). */
+int cn_grad_sync_8bit(cn_context *ctx, float *d_grad, int64_t n, float fixed_precision, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Batch allocator (dense path).  Replaces BatchAllocator::init / init_batch_buffer /
  * broadcast_batch_to_processes / allocate_next_batch_async / replace_current_batch_with_next
  * (source/batchAllocator.cpp:101-251,253-338,399-425,759-864,977-1053).

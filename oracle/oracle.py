@@ -156,3 +156,44 @@ class BatchOracle:
         if self.next >= self.total:
             self.next = 0
         return self.current
+
+
+# ---------------------------------------------------------------------------------------------- training step
+def softmax_rows(A):
+    """kSoftMax (source/clusterKernels.cu:651-688): per row, subtract the maximum, exponentiate, divide by the sum."""
+    a = A.astype(np.float32)
+    e = np.exp((a - a.max(axis=1, keepdims=True)).astype(np.float32)).astype(np.float32)
+    return (e / e.sum(axis=1, keepdims=True, dtype=np.float32)).astype(np.float32)
+
+
+def t_matrix(labels, classes):
+    """kCreate_t_matrix (source/clusterKernels.cu:775-790): one-hot rows from float labels."""
+    out = np.zeros((labels.size, classes), np.float32)
+    out[np.arange(labels.size), labels.astype(np.int64).ravel()] = 1.0
+    return out
+
+
+def rmsprop_update(rms, grad, w, rms_mult, lr):
+    """kRMSprop_with_weight_update (source/clusterKernels.cu:1306-1325) in fp32."""
+    rms, grad, w = rms.astype(np.float32), grad.astype(np.float32), w.astype(np.float32)
+    r = (np.float32(rms_mult) * rms + (grad * grad) * np.float32(1.0 - rms_mult)).astype(np.float32)
+    return r, (w - np.float32(lr) * (grad / (np.sqrt(r) + np.float32(1.0e-08)))).astype(np.float32)
+
+
+def mlp_step_gradients(X, y, weights, dropout=0.0):
+    """Forward / backward of the reference's Layer chain (source/Layer.cpp:250-261,314-339) for ReLU hidden layers and a
+    softmax output, biases zero, dropout rate 0 (activations pass unchanged): returns the softmax output and the weight
+    gradients Tdot(activation_l, error_{l+1}) of every layer, computed in float64."""
+    acts = [X.astype(np.float64)]
+    for W in weights[:-1]:
+        acts.append(np.maximum(acts[-1] @ W.astype(np.float64), 0.0))
+    z = acts[-1] @ weights[-1].astype(np.float64)
+    e = np.exp(z - z.max(axis=1, keepdims=True))
+    probs = e / e.sum(axis=1, keepdims=True)
+    err = probs - t_matrix(y, z.shape[1])
+    grads = [None] * len(weights)
+    for l in range(len(weights) - 1, -1, -1):
+        grads[l] = acts[l].T @ err
+        if l > 0:
+            err = (err @ weights[l].astype(np.float64).T) * (acts[l] > 0)
+    return probs, grads

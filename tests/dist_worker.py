@@ -129,6 +129,20 @@ def run_nccl():
     ref = oracle.gemm_f64(At, Bn, transA=True)[:, s0:s0 + c0]
     assert np.abs(ctx.to_numpy(osh) - ref).max() / np.abs(ref).max() < 1e-5
     ctx.gemm_check()
+    # 8-bit gradient exchange: own gradient + decode(encode(peer gradient)) in rank order, fixed and gathered scales
+    n = 70001
+    grads = [np.random.default_rng(100 + r).standard_normal(n).astype(np.float32) * np.float32(0.01 * (r + 1)) for r in range(world)]
+    for fixed in (1.0, 0.0):
+        g = torch.from_numpy(grads[rank].copy()).cuda()
+        cn.check(ctx.lib.cn_grad_sync_8bit(ctx.h, g.data_ptr(), n, fixed, ctx.stream_ptr()))
+        want = grads[rank].copy()
+        for r in range(world):
+            if r == rank:
+                continue
+            p = fixed if fixed > 0 else oracle.absmax(grads[r])
+            want = (want + oracle.decompress(ctx.codebook, oracle.compress(ctx.codebook, grads[r], p), p)).astype(np.float32)
+        torch.cuda.synchronize()
+        assert np.array_equal(g.cpu().numpy(), want), fixed
     # scalar gather and all-reduce
     v = torch.zeros(world, device="cuda")
     v[rank] = rank + 1.5

@@ -1,0 +1,94 @@
+"""Data-parallel training step: each elementwise kernel against its numpy restatement, the 8-bit gradient sync at one
+rank, and the facade's Layer chain (forward / backward on the config-4 MLP shape) against an fp64 restatement."""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+import torch
+
+import clusternet_b200 as cn
+from clusternet_b200 import _lib
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_softmax_and_t_matrix(ctx):
+    rng = np.random.default_rng(0)
+    for rows, cols in [(128, 10), (1, 3), (1000, 37)]:
+        A = (rng.standard_normal((rows, cols)) * 3).astype(np.float32)
+        d = ctx.colmajor(A)
+        out = ctx.empty(rows, cols)
+        cn.check(ctx.lib.cn_softmax(ctx.h, d.data_ptr(), out.data_ptr(), rows, cols, ctx.stream_ptr()))
+        got = ctx.to_numpy(out)
+        assert np.abs(got - oracle.softmax_rows(A)).max() < 2e-6      # __expf vs libm exp
+        assert np.abs(got.sum(1) - 1).max() < 1e-5
+        labels = rng.integers(0, cols, rows).astype(np.float32)
+        t = ctx.empty(rows, cols)
+        t.fill_(7.0)
+        cn.check(ctx.lib.cn_create_t_matrix(ctx.h, torch.from_numpy(labels).cuda().data_ptr(), t.data_ptr(), rows, cols, ctx.stream_ptr()))
+        assert np.array_equal(ctx.to_numpy(t), oracle.t_matrix(labels, cols))
+
+
+def test_elementwise_and_activation_gradients(ctx):
+    rng = np.random.default_rng(1)
+    a = rng.standard_normal(100003).astype(np.float32)
+    b = rng.standard_normal(100003).astype(np.float32)
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    out = torch.empty_like(da)
+    sp = ctx.stream_ptr()
+    for fn, want in [(ctx.lib.cn_add, a + b), (ctx.lib.cn_sub, a - b), (ctx.lib.cn_mul, a * b)]:
+        cn.check(fn(ctx.h, da.data_ptr(), db.data_ptr(), out.data_ptr(), a.size, sp))
+        assert np.array_equal(out.cpu().numpy(), want)
+    cn.check(ctx.lib.cn_scalar_mul(ctx.h, da.data_ptr(), 0.5, out.data_ptr(), a.size, sp))
+    assert np.array_equal(out.cpu().numpy(), a * np.float32(0.5))
+    for act, want in [(_lib.ACT_RELU, (a > 0).astype(np.float32)), (_lib.ACT_LOGISTIC, a * (np.float32(1) - a)),
+                      (_lib.ACT_DOUBLE_RELU, ((a > 0) & (a < 1)).astype(np.float32))]:
+        cn.check(ctx.lib.cn_activation_gradient(ctx.h, da.data_ptr(), act, out.data_ptr(), a.size, sp))
+        assert np.array_equal(out.cpu().numpy(), want)
+    assert ctx.lib.cn_activation_gradient(ctx.h, da.data_ptr(), _lib.ACT_LINEAR, out.data_ptr(), a.size, sp) == _lib.CN_ERR_ARG
+
+
+def test_rmsprop_update(ctx):
+    rng = np.random.default_rng(2)
+    n = 50001
+    rms = np.abs(rng.standard_normal(n)).astype(np.float32)
+    g = rng.standard_normal(n).astype(np.float32)
+    w = rng.standard_normal(n).astype(np.float32)
+    drms, dg, dw = (torch.from_numpy(x.copy()).cuda() for x in (rms, g, w))
+    cn.check(ctx.lib.cn_rmsprop_update(ctx.h, drms.data_ptr(), dg.data_ptr(), dw.data_ptr(), 0.9, 0.006, n, ctx.stream_ptr()))
+    r_want, w_want = oracle.rmsprop_update(rms, g, w, 0.9, 0.006)
+    assert np.abs(drms.cpu().numpy() - r_want).max() <= 1e-6 * np.abs(r_want).max()
+    assert np.abs(dw.cpu().numpy() - w_want).max() <= 2e-6
+
+
+def test_grad_sync_is_identity_on_one_rank(ctx):
+    g = torch.randn(10000, device="cuda")
+    ref = g.clone()
+    cn.check(ctx.lib.cn_grad_sync_8bit(ctx.h, g.data_ptr(), g.numel(), 1.0, ctx.stream_ptr()))
+    assert torch.equal(g, ref)
+
+
+def test_layer_chain_gradients_and_training(built_lib, tmp_path):
+    """Config-4 MLP shape 784-1200-1200-10, batch 128, through the C++ facade's Layer class: probabilities and the three
+    weight gradients of one step against the fp64 restatement, then 40 RMSprop steps must cut the training error."""
+    exe = str(tmp_path / "layer_test")
+    libdir = os.path.join(ROOT, "clusternet_b200")
+    subprocess.check_call(["/usr/local/cuda/bin/nvcc", "-std=c++17", "-O1", "-gencode", "arch=compute_100a,code=sm_100a",
+                           os.path.join(ROOT, "tests", "layer_test.cu"), "-o", exe, f"-L{libdir}", "-lclusternet_b200",
+                           "-Xlinker", f"-rpath={libdir}"])
+    r = subprocess.run([exe, os.path.join(ROOT, "tests", "golden", "codebook_126.f32"), "784", "1200", "10", "128", "40", str(tmp_path)],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "All tests passed" in r.stdout, r.stdout + r.stderr
+
+    def load(name, rows, cols):
+        return np.fromfile(tmp_path / name, dtype=np.float32).reshape(rows, cols)
+    X, y = load("X.bin", 128, 784), load("y.bin", 128, 1)
+    W = [load("w0.bin", 784, 1200), load("w1.bin", 1200, 1200), load("w2.bin", 1200, 10)]
+    probs, grads = oracle.mlp_step_gradients(X, y, W)
+    assert np.abs(load("probs.bin", 128, 10) - probs).max() < 5e-6
+    for name, g in zip(("g0.bin", "g1.bin", "g2.bin"), grads):
+        got = load(name, *g.shape)
+        assert np.abs(got - g).max() / np.abs(g).max() < 2e-5, name
