@@ -3,7 +3,7 @@
 // cn_gemm_f32 takes over the cublasSgemm call of ClusterNet::dot (source/clusterNet.cpp:404-487): column-
 // major operands, alpha = 1, beta = 0, optional transposes, shape check first.  Shapes the tensor-core
 // kernel can take (see cn_gemm_tc.cu) go there; everything else — tiny matrices such as the reference's
-// 2x3 . 3x2 known-answer tests, K not a multiple of 4, transposed operands — runs on the fp32 FMA kernel
+// 2x3 . 3x2 known-answer tests, a weight pitch that is not a multiple of 4 — runs on the fp32 FMA kernel
 // below, which accumulates along k in order and therefore reproduces plain fp32 dot products exactly.
 #include "cn_epilogue.cuh"
 #include "cn_gemm.h"
@@ -182,7 +182,7 @@ int cn_gemm_dispatch(cn_context *ctx, int transA, int transB, int64_t M, int64_t
         e2.maxout_level = fused_maxout ? L : 1;
         e2.argmax_out = fused_maxout ? argmax : nullptr;
         const bool push = peers && peers->npeers > 0 && L == 1;
-        st = cn_gemm_tc_launch(ctx, M, N, K, d_A, lda, d_B, ldb, target, target_ld, &e2, mode, s, push ? peers : nullptr);
+        st = cn_gemm_tc_launch(ctx, M, N, K, d_A, lda, d_B, ldb, target, target_ld, &e2, mode, s, push ? peers : nullptr, transA, transB);
         if (push && used_peers) *used_peers = true;
     } else {
         st = simt_launch(ctx, transA, transB, M, N, K, d_A, lda, d_B, ldb, target, target_ld, bias, act, s);

@@ -43,7 +43,7 @@ bool cn_gemm_tc_supported(cn_context *ctx, int transA, int transB, int64_t M, in
 bool cn_gemm_tc_can_fuse_maxout(int level);
 int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const float *A, int64_t lda,
                       const float *B, int64_t ldb, float *C, int64_t ldc, const cn_epilogue *epi, int mode, cudaStream_t s,
-                      const cn_peer_out *peers = nullptr);
+                      const cn_peer_out *peers = nullptr, int transA = 0, int transB = 0);
 // cn_gemm_f32 with optional peer windows; *used_peers tells whether the launch took them (tensor-core path only).
 int cn_gemm_dispatch(cn_context *ctx, int transA, int transB, int64_t M, int64_t N, int64_t K, const float *d_A, int64_t lda,
                      const float *d_B, int64_t ldb, float *d_C, int64_t ldc, const cn_epilogue *epi, int mode, void *stream,

@@ -264,6 +264,23 @@ cn_act_split_kernel(const float *__restrict__ A, int64_t lda, int64_t M, int64_t
     }
 }
 
+// Same planes for a transposed activation operand: op(A)(m, k) = A[k + m * lda] is already K-major, so this is a
+// plain copy-and-split.
+__global__ void __launch_bounds__(256)
+cn_act_split_t_kernel(const float *__restrict__ A, int64_t lda, int64_t M, int64_t K, int64_t Kpad,
+                      float *__restrict__ hi, float *__restrict__ lo)
+{
+    const int64_t total = M * Kpad;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t m = i / Kpad, k = i - m * Kpad;
+        const float x = k < K ? A[k + m * lda] : 0.0f;
+        const uint32_t h = to_tf32(x);
+        hi[i] = __uint_as_float(h);
+        if (lo) lo[i] = __uint_as_float(to_tf32(x - __uint_as_float(h)));
+    }
+}
+
 // -------------------------------------------------------------------------------------------------- main kernel
 // Warp roles (warpgroups of 4 warps so that register budgets can be moved between them):
 //   WG0  warp 0: TMA producer for W, warp 1: MMA issuer of W tile 0 + TMEM owner, warp 2: TMA producer for the
@@ -278,7 +295,10 @@ cn_act_split_kernel(const float *__restrict__ A, int64_t lda, int64_t M, int64_t
 // read it with tcgen05.ld and add it, in round-to-nearest fp32, to running sums that they keep in registers
 // (one thread = one output column n, 128 sums = 128 rows m).  With two W tiles per CTA the drain of one tile runs
 // while the MMAs of the other tile execute; with one tile the accumulator is double-buffered in TMEM instead.
-template <int NT, bool MODE3X>
+// TRANSB: the weight operand is stored transposed (N x K column-major, n contiguous).  Its tiles then arrive in shared
+// memory as [32 k][128 n] without swizzle and the converters read them column-wise (conflict-free: consecutive lanes
+// read consecutive n); everything downstream of TMEM is unchanged.
+template <int NT, bool MODE3X, bool TRANSB>
 __global__ void __launch_bounds__(TcCfg<NT>::THREADS, 1)
 cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_ahi,
                   const __grid_constant__ CUtensorMap tm_alo, const TcParams p)
@@ -368,8 +388,10 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                         const uint32_t stage = smem_base + Cfg::W_RING + s * Cfg::W_STAGE_BYTES;
                         mbar_expect_tx(wfull_bar(s), (uint32_t)Cfg::W_STAGE_BYTES);
 #pragma unroll
-                        for (int t = 0; t < NT; ++t)
-                            tma_load_2d(stage + t * TC_TILE_BYTES, &tm_w, wfull_bar(s), kx, (int32_t)(n0 + t * TC_BN));
+                        for (int t = 0; t < NT; ++t) {
+                            if (TRANSB) tma_load_2d(stage + t * TC_TILE_BYTES, &tm_w, wfull_bar(s), (int32_t)(n0 + t * TC_BN), kx);
+                            else        tma_load_2d(stage + t * TC_TILE_BYTES, &tm_w, wfull_bar(s), kx, (int32_t)(n0 + t * TC_BN));
+                        }
                     } else {
                         if (!mbar_wait(aempty_bar(s), ph ^ 1u, abort_flag, p.status, 8u)) break;
                         const uint32_t stage = smem_base + Cfg::A_RING + s * Cfg::A_STAGE_BYTES;
@@ -466,19 +488,30 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             const uint8_t *stage = smem_gen + Cfg::W_RING + s * Cfg::W_STAGE_BYTES;
 #pragma unroll 1
             for (int w = 0; w < NT; ++w) {
-                const uint8_t *rowp = stage + w * TC_TILE_BYTES + row * 128;
+                const uint8_t *tilep = stage + w * TC_TILE_BYTES;
                 const uint32_t a_hi = tmem_base + lane_addr + Cfg::A_COL + t * Cfg::A_STAGE_COLS + w * 64;
                 uint32_t hi[32], lo[32];
+                if (TRANSB) {
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    // 16-byte chunk c of row r sits at chunk position c ^ (r & 7) under the 128-byte swizzle
-                    const float4 v = *reinterpret_cast<const float4 *>(rowp + ((c ^ (row & 7)) << 4));
-                    const float x[4] = {v.x, v.y, v.z, v.w};
+                    for (int k = 0; k < 32; ++k) {
+                        const float x = *reinterpret_cast<const float *>(tilep + k * (TC_BN * 4) + row * 4);
+                        const uint32_t h = to_tf32(x);
+                        hi[k] = h;
+                        if (MODE3X) lo[k] = to_tf32(x - __uint_as_float(h));
+                    }
+                } else {
+                    const uint8_t *rowp = tilep + row * 128;
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const uint32_t h = to_tf32(x[e]);
-                        hi[c * 4 + e] = h;
-                        if (MODE3X) lo[c * 4 + e] = to_tf32(x[e] - __uint_as_float(h));
+                    for (int c = 0; c < 8; ++c) {
+                        // 16-byte chunk c of row r sits at chunk position c ^ (r & 7) under the 128-byte swizzle
+                        const float4 v = *reinterpret_cast<const float4 *>(rowp + ((c ^ (row & 7)) << 4));
+                        const float x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const uint32_t h = to_tf32(x[e]);
+                            hi[c * 4 + e] = h;
+                            if (MODE3X) lo[c * 4 + e] = to_tf32(x[e] - __uint_as_float(h));
+                        }
                     }
                 }
                 tc_st32(a_hi, hi);
@@ -691,15 +724,17 @@ static int get_encode_fn(cn_context *ctx, EncodeTiledFn *out)
 }
 
 // 2-D fp32 map over a K-major array: inner extent `inner` (k), outer extent `outer` (rows), row pitch in elements.
-static int make_map(EncodeTiledFn enc, CUtensorMap *map, const float *base, int64_t inner, int64_t outer, int64_t pitch)
+// transposed = false: box 32 (k, inner) x 128 rows with the 128-byte swizzle; transposed = true (weight stored with n
+// contiguous): box 128 (n, inner) x 32 k-rows, no swizzle.
+static int make_map(EncodeTiledFn enc, CUtensorMap *map, const float *base, int64_t inner, int64_t outer, int64_t pitch, bool transposed = false)
 {
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
     cuuint64_t strides[1] = {(cuuint64_t)pitch * sizeof(float)};
-    cuuint32_t box[2] = {TC_BK, 128};
+    cuuint32_t box[2] = {transposed ? 128u : (cuuint32_t)TC_BK, transposed ? (cuuint32_t)TC_BK : 128u};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, transposed ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     CN_REQUIRE(r == CUDA_SUCCESS, CN_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (inner %lld outer %lld pitch %lld)", (int)r,
                (long long)inner, (long long)outer, (long long)pitch);
     return CN_OK;
@@ -710,7 +745,8 @@ bool cn_gemm_tc_can_fuse_maxout(int L) { return L == 2 || L == 4 || L == 8 || L 
 bool cn_gemm_tc_supported(cn_context *, int transA, int transB, int64_t M, int64_t N, int64_t K, const float *,
                           int64_t, const float *B, int64_t ldb, const float *, int64_t)
 {
-    if (transA || transB) return false;
+    (void)transA;   // a transposed activation operand only changes the pre-pass
+    (void)transB;   // a transposed weight only changes the TMA box and the converter's read pattern
     if (M < 1 || N < 16 || K < 32) return false;
     if ((ldb & 3) != 0 || (reinterpret_cast<uintptr_t>(B) & 15u) != 0) return false;   // TMA: 16-byte pitch and base
     if (K >= (1LL << 31) - 64 || N >= (1LL << 31) - 256 || M >= (1LL << 31) - 256) return false;   // TMA coordinates are 32-bit
@@ -733,24 +769,25 @@ static int pick_splits(int64_t tiles, int kb_total, int sm_count)
     return best;
 }
 
-template <int NT, bool MODE3X>
+template <int NT, bool MODE3X, bool TRANSB>
 static int launch_cfg(const CUtensorMap &mw, const CUtensorMap &mhi, const CUtensorMap &mlo, const TcParams &prm, int64_t grid, cudaStream_t s)
 {
     static bool attr_set[64] = {};   // per device: the attribute belongs to the device's copy of the function
     int dev = 0;
     CN_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        CN_CUDA(cudaFuncSetAttribute(cn_gemm_tc_kernel<NT, MODE3X>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<NT>::SMEM_BYTES));
+        CN_CUDA(cudaFuncSetAttribute(cn_gemm_tc_kernel<NT, MODE3X, TRANSB>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<NT>::SMEM_BYTES));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    cn_gemm_tc_kernel<NT, MODE3X><<<(unsigned)grid, TcCfg<NT>::THREADS, TcCfg<NT>::SMEM_BYTES, s>>>(mw, mhi, mlo, prm);
+    cn_gemm_tc_kernel<NT, MODE3X, TRANSB><<<(unsigned)grid, TcCfg<NT>::THREADS, TcCfg<NT>::SMEM_BYTES, s>>>(mw, mhi, mlo, prm);
     CN_CUDA(cudaGetLastError());
     cn_count_launch();
     return CN_OK;
 }
 
 int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const float *A, int64_t lda, const float *B,
-                      int64_t ldb, float *C, int64_t ldc, const cn_epilogue *epi, int mode, cudaStream_t s, const cn_peer_out *peers)
+                      int64_t ldb, float *C, int64_t ldc, const cn_epilogue *epi, int mode, cudaStream_t s, const cn_peer_out *peers,
+                      int transA, int transB)
 {
     EncodeTiledFn enc = nullptr;
     int st = get_encode_fn(ctx, &enc);
@@ -773,7 +810,12 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
     {
         const int64_t tiles_k = Kpad / 32, tiles_mm = (M + 31) / 32;
         CN_REQUIRE(tiles_k * tiles_mm < (1LL << 31), CN_ERR_UNSUPPORTED, "cn_gemm_f32: activation matrix too large for the split pre-pass");
-        cn_act_split_kernel<<<(unsigned)(tiles_k * tiles_mm), 256, 0, s>>>(A, lda, M, K, Kpad, hi, lo, tiles_k);
+        if (transA) {
+            int64_t blocks = (M * Kpad + 255) / 256, cap = (int64_t)ctx->sm_count * 16;
+            cn_act_split_t_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(A, lda, M, K, Kpad, hi, lo);
+        } else {
+            cn_act_split_kernel<<<(unsigned)(tiles_k * tiles_mm), 256, 0, s>>>(A, lda, M, K, Kpad, hi, lo, tiles_k);
+        }
         CN_CUDA(cudaGetLastError());
         cn_count_launch();
     }
@@ -827,7 +869,9 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
 
     // 3. tensor maps
     CUtensorMap mw, mhi, mlo;
-    if ((st = make_map(enc, &mw, B, K, N, ldb)) != CN_OK) return st;
+    if (transB) st = make_map(enc, &mw, B, N, K, ldb, true);   // stored N x K, n contiguous
+    else        st = make_map(enc, &mw, B, K, N, ldb);
+    if (st != CN_OK) return st;
     if ((st = make_map(enc, &mhi, hi, Kpad, M, Kpad)) != CN_OK) return st;
     if ((st = make_map(enc, &mlo, mode3x ? lo : hi, Kpad, M, Kpad)) != CN_OK) return st;
 
@@ -843,8 +887,15 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
         ev_stop = ws->prof_events[ws->prof_used + 1];
         ws->prof_used += 2;
     }
-    if (nt == 1) st = mode3x ? launch_cfg<1, true>(mw, mhi, mlo, prm, grid, s) : launch_cfg<1, false>(mw, mhi, mlo, prm, grid, s);
-    else         st = mode3x ? launch_cfg<2, true>(mw, mhi, mlo, prm, grid, s) : launch_cfg<2, false>(mw, mhi, mlo, prm, grid, s);
+#define CN_LAUNCH(NTV, M3, TB) launch_cfg<NTV, M3, TB>(mw, mhi, mlo, prm, grid, s)
+    if (nt == 1) {
+        if (transB) st = mode3x ? CN_LAUNCH(1, true, true) : CN_LAUNCH(1, false, true);
+        else        st = mode3x ? CN_LAUNCH(1, true, false) : CN_LAUNCH(1, false, false);
+    } else {
+        if (transB) st = mode3x ? CN_LAUNCH(2, true, true) : CN_LAUNCH(2, false, true);
+        else        st = mode3x ? CN_LAUNCH(2, true, false) : CN_LAUNCH(2, false, false);
+    }
+#undef CN_LAUNCH
     if (st != CN_OK) return st;
     if (ev_stop) CN_CUDA(cudaEventRecord(ev_stop, s));
     ctx->gemm_last_path = mode3x ? "tcgen05_3xtf32" : "tcgen05_tf32";

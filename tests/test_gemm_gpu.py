@@ -55,6 +55,22 @@ def test_tensor_core_gemm_vs_fp64(ctx, M, K, N, mode):
     assert err < (TOL_3XTF32 if mode == _lib.GEMM_3XTF32 else TOL_TF32), err
 
 
+@pytest.mark.parametrize("transA,transB", [(True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("M,K,N", [(128, 1200, 1200), (784, 128, 1200), (200, 96, 333 * 4), (128, 4096, 1024)])
+def test_transposed_operands_on_the_tensor_path(ctx, transA, transB, M, K, N):
+    """Tdot / dotT shapes of the backward pass (source/Layer.cpp:327,334): op(A) M x K, op(B) K x N."""
+    rng = np.random.default_rng(M + K + N + transA * 2 + transB)
+    A = rng.uniform(-1, 1, (K, M) if transA else (M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (N, K) if transB else (K, N)).astype(np.float32)
+    bias = rng.uniform(-1, 1, N).astype(np.float32)
+    C = ctx.gemm(ctx.colmajor(A), ctx.colmajor(B), transA=transA, transB=transB, bias=torch.from_numpy(bias).cuda(),
+                 activation=_lib.ACT_RELU)
+    ctx.gemm_check()
+    assert ctx.gemm_last_path() == "tcgen05_3xtf32"
+    ref = np.maximum(oracle.gemm_f64(A, B, transA, transB) + bias, 0)
+    assert normwise(ctx.to_numpy(C), ref) < TOL_3XTF32
+
+
 def test_config1_dot_bias_relu(ctx):
     """Single-layer dot: A 128x784, B 784x1024 uniform(-1,1) seed 0, + bias + ReLU, vs fp64."""
     rng = np.random.default_rng(0)
