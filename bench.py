@@ -150,7 +150,8 @@ def run_reference(args, rank):
     print(json.dumps({
         "impl": "reference", "metric": "dotMPI TFLOP/s", "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic", "config": {"workload": "README dotMPI two-layer skinny GEMM 128x100000 . 100000x40000 . 40000x20000"},
+        "dtype": "f32", "data": "synthetic", "config": {"workload": "README dotMPI two-layer skinny GEMM: 128x100000 . 100000x40000 . 40000x20000, W column-sharded",
+                   "note": "host CPU stand-in: clusterNet has no CPU path and cannot be built here (MPI, HDF5 absent)"},
         "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
 
@@ -187,6 +188,74 @@ def codec_bench(ctx, torch, peaks):
     return out
 
 
+def train_step_bench(ctx, cn, _lib, torch, dist, world, rank, steps=30):
+    """Config 4: data-parallel MLP 784-1200-1200-10, ReLU, dropout (0.2 input, 0.5 hidden), softmax, batch 128 per GPU,
+    8-bit compressed gradient exchange (per-rank absmax scales gathered with the codes), RMSprop — the call sequence of the
+    reference's Layer class (source/Layer.cpp:250-261,314-339,341-471) through the C ABI.  Returns ms per step."""
+    lib, h, sp = ctx.lib, ctx.h, ctx.stream_ptr()
+    B, sizes, drops = 128, [784, 1200, 1200, 10], [0.2, 0.5, 0.5]
+    X = ctx.randn(B, sizes[0], seed=100 + rank)
+    y = torch.randint(0, 10, (B,), device="cuda").float()
+    W = [ctx.uniform_sqrt_weight(sizes[i], sizes[i + 1], seed=7 + i) for i in range(3)]     # same weights on every rank
+    bias = [torch.zeros(sizes[i + 1], device="cuda") for i in range(3)]
+    rms = [torch.zeros_like(w) for w in W]
+    grad = [torch.zeros_like(w) for w in W]
+    act = [X] + [ctx.empty(B, sizes[i + 1]) for i in range(3)]
+    out = [ctx.empty(B, s) for s in sizes]
+    err = [None] + [ctx.empty(B, sizes[i + 1]) for i in range(3)]
+    tmat = ctx.empty(B, 10)
+    step_no = [0]
+
+    def one_step():
+        step_no[0] += 1
+        seed = 1000 + step_no[0]
+        # forward: (wait for the previous exchange + update), fused dot+bias+activation, dropout
+        cn.check(lib.cn_dropout(h, act[0].data_ptr(), out[0].data_ptr(), act[0].numel(), drops[0], seed, 0, sp))
+        for l in range(3):
+            if step_no[0] > 1:
+                cn.check(lib.cn_grad_sync_8bit(h, grad[l].data_ptr(), grad[l].numel(), 0.0, sp))
+                cn.check(lib.cn_rmsprop_update(h, rms[l].data_ptr(), grad[l].data_ptr(), W[l].data_ptr(), 0.9, 0.006, W[l].numel(), sp))
+            last = l == 2
+            ctx.gemm(out[l], W[l], out=(out[l + 1] if last else act[l + 1]), bias=bias[l],
+                     activation=_lib.ACT_LINEAR if last else _lib.ACT_RELU)
+            if last:
+                cn.check(lib.cn_softmax(h, out[3].data_ptr(), out[3].data_ptr(), B, 10, sp))
+            else:
+                cn.check(lib.cn_dropout(h, act[l + 1].data_ptr(), out[l + 1].data_ptr(), act[l + 1].numel(), drops[l + 1], seed, 100 * (l + 1), sp))
+        # backward errors
+        cn.check(lib.cn_create_t_matrix(h, y.data_ptr(), tmat.data_ptr(), B, 10, sp))
+        cn.check(lib.cn_sub(h, out[3].data_ptr(), tmat.data_ptr(), err[3].data_ptr(), err[3].numel(), sp))
+        for l in (2, 1):
+            cn.check(lib.cn_activation_gradient(h, act[l].data_ptr(), _lib.ACT_RELU, out[l].data_ptr(), out[l].numel(), sp))
+            ctx.gemm(err[l + 1], W[l], out=err[l], transB=True)
+            cn.check(lib.cn_mul(h, err[l].data_ptr(), out[l].data_ptr(), err[l].data_ptr(), err[l].numel(), sp))
+        # gradients
+        for l in range(3):
+            ctx.gemm(act[l], err[l + 1], out=grad[l], transA=True)
+
+    for _ in range(5):
+        one_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    n0 = lib.cn_kernel_launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        one_step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ctx.gemm_check()
+    return {"workload": "config 4: MLP 784-1200-1200-10, batch 128 per GPU, 8-bit gradient exchange, RMSprop", "ms_per_step": ms,
+            "samples_per_s": 128 * world / (ms * 1e-3), "launches_per_step": (lib.cn_kernel_launches() - n0) / steps,
+            "flops_per_step_per_gpu": 6.0 * 128 * (784 * 1200 + 1200 * 1200 + 1200 * 10)}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -198,6 +267,7 @@ def main():
     ap.add_argument("--nccl-gather", action="store_true", help="gather C with ncclAllGather instead of the fused peer stores")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-codec", action="store_true")
+    ap.add_argument("--no-train-step", action="store_true", help="skip the config-4 training-step measurement")
     ap.add_argument("--only-codec", action="store_true", help="run the codec measurements alone (small profiler captures)")
     ap.add_argument("--k1", type=int, default=K1, help="profiling aid: inner dimension of layer 1")
     ap.add_argument("--n1", type=int, default=N1, help="profiling aid: columns of W1 (headline: 40000)")
@@ -344,6 +414,8 @@ def main():
     err1 = sampled_error(batch, W1, out1, s1, c1, K1)
     err2 = sampled_error(out1, W2, out2, s2, c2, N1)
 
+    train = None if (args.no_train_step or not headline) else train_step_bench(ctx, cn, _lib, torch, dist if world > 1 else None, world, rank)
+
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -380,6 +452,8 @@ def main():
                      "peak_source": f"{peaks['source']}: bf16_tflops {peaks['bf16_tflops']} / 2 (TF32 rate)" + (" / 3 (three TF32 products per tile)" if args.mode == "3xtf32" else ""),
                      "hbm_frac_layer1": (4.0 * K1 * (N1 / world) / (l1_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]) if l1_ms else None},
     }
+    if train:
+        line["train_step"] = train
     if not args.no_codec and world == 1:
         line["codec"] = codec_bench(ctx, torch, peaks)
     if not args.no_cpu_baseline and world == 1:
