@@ -219,9 +219,17 @@ cn_compress_kernel(const float *__restrict__ A, float precision_arg, const float
             for (int u = 0; u < 4; ++u) cur[u] = nxt[u];
         }
     }
-    for (; v < nvec; v += stride) {
-        const float4 q0 = __ldcs(A4 + v);
-        __stcs(out4 + v, CN_CODE4(q0));
+    if (v < nvec) {   // last, partial group: all its loads are issued before any is used
+        float4 q[3];
+        bool has[3];
+#pragma unroll
+        for (int u = 0; u < 3; ++u) {
+            has[u] = v + u * stride < nvec;
+            if (has[u]) q[u] = __ldcs(A4 + v + u * stride);
+        }
+#pragma unroll
+        for (int u = 0; u < 3; ++u)
+            if (has[u]) __stcs(out4 + v + u * stride, CN_CODE4(q[u]));
     }
 #undef CN_CODE4
     // elements not covered by whole 16-byte groups (all of them when the buffers are not aligned)
@@ -281,9 +289,17 @@ cn_decompress_kernel(const uint8_t *__restrict__ codes, float precision_arg, con
             for (int u = 0; u < 4; ++u) cur[u] = nxt[u];
         }
     }
-    for (; v < nvec; v += stride) {
-        uint32_t w0 = __ldcs(in4 + v);
-        __stcs(out4 + v, CN_DEC4(w0));
+    if (v < nvec) {   // last, partial group: all its loads are issued before any is used
+        uint32_t q[3];
+        bool has[3];
+#pragma unroll
+        for (int u = 0; u < 3; ++u) {
+            has[u] = v + u * stride < nvec;
+            if (has[u]) q[u] = __ldcs(in4 + v + u * stride);
+        }
+#pragma unroll
+        for (int u = 0; u < 3; ++u)
+            if (has[u]) __stcs(out4 + v + u * stride, CN_DEC4(q[u]));
     }
 #undef CN_DEC4
     for (int64_t i = (nvec << 2) + (int64_t)blockIdx.x * blockDim.x + tid; i < n; i += stride) out[i] = lut[codes[i]];
@@ -310,9 +326,13 @@ cn_absmax_kernel(const float *__restrict__ A, int64_t n, float *__restrict__ out
         m = fmaxf(m, fmaxf(fmaxf(fabsf(q2.x), fabsf(q2.y)), fmaxf(fabsf(q2.z), fabsf(q2.w))));
         m = fmaxf(m, fmaxf(fmaxf(fabsf(q3.x), fabsf(q3.y)), fmaxf(fabsf(q3.z), fabsf(q3.w))));
     }
-    for (; v < nvec; v += stride) {
-        float4 q0 = __ldcs(A4 + v);
-        m = fmaxf(m, fmaxf(fmaxf(fabsf(q0.x), fabsf(q0.y)), fmaxf(fabsf(q0.z), fabsf(q0.w))));
+    if (v < nvec) {   // last, partial group: all its loads are issued before any is used
+        float4 q[3];
+#pragma unroll
+        for (int u = 0; u < 3; ++u) q[u] = (v + u * stride < nvec) ? __ldcs(A4 + v + u * stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < 3; ++u)
+            if (v + u * stride < nvec) m = fmaxf(m, fmaxf(fmaxf(fabsf(q[u].x), fabsf(q[u].y)), fmaxf(fabsf(q[u].z), fabsf(q[u].w))));
     }
     for (int64_t i = (nvec << 2) + (int64_t)blockIdx.x * blockDim.x + tid; i < n; i += stride) m = fmaxf(m, fabsf(A[i]));
 #pragma unroll

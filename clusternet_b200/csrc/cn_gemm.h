@@ -15,7 +15,7 @@ enum {
 struct cn_gemm_workspace {
     void *ptr[CN_GEMM_SLOTS] = {nullptr, nullptr, nullptr, nullptr};
     size_t bytes[CN_GEMM_SLOTS] = {0, 0, 0, 0};
-    unsigned int *d_status = nullptr;   // word 0: set by a kernel whose bounded wait ran out; words 16..: split-K tickets
+    unsigned int *d_status = nullptr;   // word 0: set by a kernel whose bounded wait ran out
     void *encode_fn = nullptr;          // cuTensorMapEncodeTiled, resolved once
     bool profile = false;               // bracket main-kernel launches with events
     std::vector<cudaEvent_t> prof_events;   // start, stop, start, stop, ...

@@ -21,9 +21,8 @@
 //     128-byte runs of the column-major C, and maxout over L consecutive columns is a shuffle across L lanes.
 //
 // Work decomposition.  One CTA per (m tile of 128, group of NT n tiles of 128, K split).  Skinny products have
-// few tiles, so K is split across CTAs; each split leaves its partial tile in scratch, and the CTA that draws
-// the last ticket of a tile adds the partials in split order (a fixed order, so results are reproducible) and
-// runs the epilogue.  Launch order is split-major, which makes the CTAs resident at one time walk the same K
+// few tiles, so K is split across CTAs; each split leaves its partial tile in scratch and a second, grid-wide
+// kernel adds the partials in split order (a fixed order, so results are reproducible) and runs the epilogue.  Launch order is split-major, which makes the CTAs resident at one time walk the same K
 // range of the activations and share it through L2.
 //
 // Every wait on an mbarrier is bounded by a clock limit; a wait that runs out sets a status word that the host
@@ -79,8 +78,7 @@ struct TcParams {
     int kb_per_split;       // K blocks (of 32) per split
     int kb_total;
     int chain_kb;           // K blocks accumulated in TMEM before the sum is drained to registers
-    float *partials;        // [tile][split][NT][128 m][128 n]
-    unsigned int *tickets;  // one per tile, self-resetting
+    float *partials;        // [tile * NT + w][split][128 n][128 m]: every partial tile laid out like C
     unsigned int *status;
     // fused all-gather: peer copies of the C window (same leading dimension), flags the peers raise when ready
     int npeers;
@@ -326,7 +324,6 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     auto accempty_bar = [&](int w, int b) { return bar(B_ACCEMPTY + w * Cfg::ACC_BUFS + b); };
     volatile uint32_t *tmem_holder = reinterpret_cast<volatile uint32_t *>(bar_gen + 448);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(bar_gen + 452);
-    volatile int *last_flag = reinterpret_cast<volatile int *>(bar_gen + 456);   // one word per W tile
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -358,8 +355,6 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         for (int w = 0; w < NT; ++w)
             for (int b = 0; b < Cfg::ACC_BUFS; ++b) { mbar_init(accfull_bar(w, b), 1); mbar_init(accempty_bar(w, b), 128); }
         *abort_flag = 0;
-        last_flag[0] = 0;
-        last_flag[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {   // this warp owns the tensor-memory allocation
@@ -567,30 +562,23 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             const size_t tile_elems = (size_t)TC_BM * TC_BN;
             bool do_final = true;
             if (p.splits > 1) {
-                float *P = p.partials + ((size_t)ticket_id * p.splits + split) * tile_elems;
+                // Split-K: this CTA's partial tile goes to scratch as one contiguous 64 KB block laid out like C (column n =
+                // 512 bytes), staged through the idle rings and written with a single bulk copy; cn_splitk_reduce_kernel adds
+                // the partials of all splits in split order and applies the epilogue, spread over the whole GPU.
+                float *stg = reinterpret_cast<float *>(smem_gen + (w == 0 ? Cfg::W_RING : Cfg::A_RING));
 #pragma unroll
-                for (int i = 0; i < TC_BM; ++i) P[(size_t)i * TC_BN + row] = acc[i];
-                __threadfence();
+                for (int i = 0; i < TC_BM; i += 4)
+                    *reinterpret_cast<float4 *>(stg + row * TC_BM + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("bar.sync %0, 128;" ::"r"(1 + w) : "memory");
                 if (et == 0) {
-                    const unsigned int prev = atomicAdd(p.tickets + ticket_id, 1u);
-                    const int last = prev == (unsigned int)(p.splits - 1);
-                    if (last) p.tickets[ticket_id] = 0u;   // ready for the next launch
-                    last_flag[w] = last;
+                    float *P = p.partials + ((size_t)ticket_id * p.splits + split) * tile_elems;
+                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                                 ::"l"(P), "r"(smem_u32(stg)), "r"((uint32_t)(tile_elems * sizeof(float))) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
                 }
-                asm volatile("bar.sync %0, 128;" ::"r"(1 + w) : "memory");
-                do_final = last_flag[w] != 0;
-                if (do_final) {
-                    __threadfence();
-                    // fixed summation order over the splits: reproducible whichever CTA comes last
-#pragma unroll
-                    for (int i = 0; i < TC_BM; ++i) acc[i] = 0.0f;
-                    for (int sp = 0; sp < p.splits; ++sp) {
-                        const float *Q = p.partials + ((size_t)ticket_id * p.splits + sp) * tile_elems;
-#pragma unroll
-                        for (int i = 0; i < TC_BM; ++i) acc[i] += __ldcg(Q + (size_t)i * TC_BN + row);
-                    }
-                }
+                do_final = false;
             }
             if (do_final) {
                 const int L = p.maxout_level;
@@ -701,6 +689,81 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------- split-K reduction
+// One thread = four consecutive rows m of one output column n: adds the partial tiles of all splits in split order (a
+// fixed order, so the result does not depend on scheduling), applies bias and activation, stores to C and, for the
+// fused all-gather, to every peer's C (a warp writes 512 contiguous bytes of a column: full NVLink packets).
+struct ReduceParams {
+    const float *partials;
+    int splits, nt;
+    int64_t tiles_n, tiles_m, M, N;
+    float *C;
+    int64_t ldc;
+    const float *bias;
+    int act;
+    int npeers;
+    float *peerC[CN_MAX_PEERS];
+    const unsigned int *ready;
+    int nranks, my_rank;
+    unsigned int epoch;
+    unsigned int *status;
+};
+
+__global__ void __launch_bounds__(256)
+cn_splitk_reduce_kernel(const ReduceParams p)
+{
+    if (p.npeers > 0) {   // peers must have announced that their copy of C may be overwritten (bounded wait)
+        if (threadIdx.x == 0) {
+            const long long t0 = clock64();
+            for (int r = 0; r < p.nranks; ++r) {
+                if (r == p.my_rank) continue;
+                const volatile unsigned int *f = p.ready + r;
+                while ((int)(*f - p.epoch) < 0) {
+                    if (clock64() - t0 > TC_WAIT_LIMIT) { atomicMax(p.status, 9u); break; }
+                    __nanosleep(100);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    const size_t tile_elems = (size_t)TC_BM * TC_BN;
+    const int64_t quads_per_tile = tile_elems / 4;
+    const int64_t total = p.tiles_n * p.tiles_m * p.nt * quads_per_tile;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < total; q += stride) {
+        const int64_t ticket = q / quads_per_tile;          // (tile_id * nt + w)
+        const int64_t inner = q - ticket * quads_per_tile;  // n_local * 32 + m4
+        const int n_local = (int)(inner >> 5), m_local = (int)(inner & 31) * 4;
+        const int64_t tile_id = ticket / p.nt;
+        const int w = (int)(ticket - tile_id * p.nt);
+        const int64_t tile_n = tile_id % p.tiles_n, tile_m = tile_id / p.tiles_n;
+        const int64_t n = tile_n * (p.nt * TC_BN) + w * TC_BN + n_local, m = tile_m * TC_BM + m_local;
+        if (n >= p.N || m >= p.M) continue;
+        const float *src = p.partials + (size_t)ticket * p.splits * tile_elems + (size_t)n_local * TC_BM + m_local;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int sp = 0; sp < p.splits; ++sp) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)sp * tile_elems));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        const float b = p.bias ? p.bias[n] : 0.0f;
+        float r[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) r[i] = cn_apply_activation(p.bias ? r[i] + b : r[i], p.act);
+        const int64_t off = n * p.ldc + m;
+        const bool vec = (m + 4 <= p.M) && ((p.ldc & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
+        for (int d = 0; d <= p.npeers; ++d) {
+            float *dst = (d == 0 ? p.C : p.peerC[d - 1]) + off;
+            if (vec) {
+                *reinterpret_cast<float4 *>(dst) = make_float4(r[0], r[1], r[2], r[3]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (m + i < p.M) dst[i] = r[i];
+            }
+        }
     }
 }
 
@@ -821,6 +884,7 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
     }
 
     // 2. tiling
+    const int prm_maxout = epi ? epi->maxout_level : 1;
     int nt = (N >= 2048) ? 2 : 1;
     if (const char *e = getenv("CN_GEMM_NT")) { int v = atoi(e); if (v == 1 || v == 2) nt = v; }
     const int64_t tiles_n = (N + nt * TC_BN - 1) / (nt * TC_BN), tiles_m = (M + TC_BM - 1) / TC_BM;
@@ -828,7 +892,7 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
     const int kb_total = (int)(Kpad / TC_BK);
     int splits = pick_splits(tiles, kb_total, ctx->sm_count);
     if (const char *e = getenv("CN_GEMM_SPLITS")) { int v = atoi(e); if (v >= 1 && v <= kb_total) splits = v; }
-    if (tiles * nt > CN_GEMM_MAX_TICKETS) splits = 1;
+    if (prm_maxout > 1) splits = 1;   // the split-K reduction kernel has no maxout; such layers are small
     int kb_per_split = (kb_total + splits - 1) / splits;
     splits = (kb_total + kb_per_split - 1) / kb_per_split;   // no empty split
     CN_REQUIRE(tiles * splits < (1LL << 31), CN_ERR_UNSUPPORTED, "cn_gemm_f32: too many work units");
@@ -844,7 +908,7 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
     prm.splits = splits; prm.kb_per_split = kb_per_split; prm.kb_total = kb_total;
     prm.chain_kb = TC_CHAIN_DEFAULT;
     if (const char *e = getenv("CN_GEMM_CHAIN")) { int v = atoi(e); if (v >= 1) prm.chain_kb = v; }
-    prm.partials = nullptr; prm.tickets = nullptr;
+    prm.partials = nullptr;
     prm.status = ws->d_status;
     prm.npeers = 0;
     prm.ready = nullptr;
@@ -863,7 +927,6 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
         void *buf = nullptr;
         st = cn_gemm_scratch(ctx, CN_GEMM_SLOT_SPLITK, part_bytes, &buf);
         if (st != CN_OK) return st;
-        prm.tickets = ws->d_status + 16;
         prm.partials = (float *)buf;
     }
 
@@ -897,6 +960,20 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
     }
 #undef CN_LAUNCH
     if (st != CN_OK) return st;
+    if (splits > 1) {
+        ReduceParams rp;
+        rp.partials = prm.partials; rp.splits = splits; rp.nt = nt;
+        rp.tiles_n = tiles_n; rp.tiles_m = tiles_m; rp.M = M; rp.N = N;
+        rp.C = C; rp.ldc = ldc; rp.bias = prm.bias; rp.act = prm.act;
+        rp.npeers = prm.npeers;
+        for (int i = 0; i < CN_MAX_PEERS; ++i) rp.peerC[i] = prm.peerC[i];
+        rp.ready = prm.ready; rp.nranks = prm.nranks; rp.my_rank = prm.my_rank; rp.epoch = prm.epoch; rp.status = prm.status;
+        const int64_t quads = tiles * nt * (TC_BM * TC_BN / 4);
+        int64_t blocks = (quads + 255) / 256, cap = (int64_t)ctx->sm_count * 8;
+        cn_splitk_reduce_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(rp);
+        CN_CUDA(cudaGetLastError());
+        cn_count_launch();
+    }
     if (ev_stop) CN_CUDA(cudaEventRecord(ev_stop, s));
     ctx->gemm_last_path = mode3x ? "tcgen05_3xtf32" : "tcgen05_tf32";
     return CN_OK;
