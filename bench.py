@@ -386,18 +386,43 @@ def main():
     ctx.gemm_check()
     clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
 
-    # ---- timed region 2: end to end from host memory through the C ABI
+    # ---- timed region 2: end to end from host memory through the C ABI.  The host holds a (pinned, row-major) data set
+    # of two batches; every step one batch is copied host->device by the asynchronous batch allocator on its side
+    # stream (the copy of step i+1 runs while step i computes, as allocate_next_batch_async is meant to be used),
+    # transposed into the current batch, broadcast, multiplied twice, and the result is transposed and copied back.
+    h_set = torch.cat([h_batch, h_batch.flip(0)], 0).pin_memory() if rank == 0 else None
+    h_lab = torch.zeros((2 * M, 1), dtype=torch.float32).pin_memory() if rank == 0 else None
+    bh = ctypes.c_void_p()
+    if rank == 0:
+        cn.check(lib.cn_batch_create(ctx.h, h_set.data_ptr(), h_lab.data_ptr(), 2 * M, K1, 1, M, 0, ctypes.byref(bh)))
+    px, py, pn = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_int64()
+
+    def e2e_step():
+        if rank == 0:
+            cn.check(lib.cn_batch_copy_next_async(bh))                     # prefetch of the NEXT batch (side stream)
+            cn.check(lib.cn_batch_current(bh, ctypes.byref(px), ctypes.byref(py), ctypes.byref(pn)))
+            cudart.cudaMemcpyAsync(ctypes.c_void_p(batch.data_ptr()), px, ctypes.c_size_t(M * K1 * 4), 3, sp)   # current batch -> A
+        if world > 1:
+            ctx.bcast(batch, 0)
+        two_layers()
+        download()
+        if rank == 0:
+            cn.check(lib.cn_batch_swap(bh, sp, ctypes.byref(px), ctypes.byref(py), ctypes.byref(pn)))
+
+    cudart = ctypes.CDLL("libcudart.so.12")
     for _ in range(2):
-        upload(); two_layers(); download()
+        e2e_step()
     barrier()
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2.record()
     for _ in range(args.steps):
-        upload(); two_layers(); download()
+        e2e_step()
     e3.record()
     barrier()
     ms_e2e = max_over_ranks(e2.elapsed_time(e3))
     checksum = float(h_out.double().abs().mean())
+    if rank == 0:
+        lib.cn_batch_destroy(bh)
 
     # ---- accuracy on sampled columns against an fp64 host product (rank 0's shard edges + random columns)
     def sampled_error(act_dev, W_dev, out_dev, col0, ncols_local, kdim):

@@ -20,6 +20,7 @@ struct cn_batch {
     int64_t next_rows = 0;       // rows of the batch now in the "next" buffers
     int64_t cur_rows = 0;
     bool copy_pending = false;
+    bool direct = false;         // the data set itself is pinned: copy from it, no staging memcpy
     float *p_X = nullptr, *p_y = nullptr;     // pinned staging
     float *dn_X = nullptr, *dn_y = nullptr;   // device, next batch, row-major
     float *dc_X = nullptr, *dc_y = nullptr;   // device, current batch, column-major
@@ -66,8 +67,16 @@ extern "C" int cn_batch_create(cn_context *ctx, const float *h_X, const float *h
     b->total_batches = (rows + batch_size - 1) / batch_size;
     const size_t bx = (size_t)batch_size * cols_X * sizeof(float), by = (size_t)batch_size * cols_y * sizeof(float);
     cudaError_t e;
-    if ((e = cudaHostAlloc(&b->p_X, bx, cudaHostAllocPortable)) != cudaSuccess ||
-        (e = cudaHostAlloc(&b->p_y, by, cudaHostAllocPortable)) != cudaSuccess ||
+    {   // the reference keeps the whole data set in pinned memory (empty_pinned); if the caller did the same, the
+        // batch rows (contiguous in the row-major set) are copied straight from it
+        cudaPointerAttributes ax, ay;
+        const bool px = cudaPointerGetAttributes(&ax, h_X) == cudaSuccess && ax.type == cudaMemoryTypeHost;
+        const bool py = cudaPointerGetAttributes(&ay, h_y) == cudaSuccess && ay.type == cudaMemoryTypeHost;
+        cudaGetLastError();
+        b->direct = px && py;
+    }
+    if ((!b->direct && (e = cudaHostAlloc(&b->p_X, bx, cudaHostAllocPortable)) != cudaSuccess) ||
+        (!b->direct && (e = cudaHostAlloc(&b->p_y, by, cudaHostAllocPortable)) != cudaSuccess) ||
         (e = cudaMalloc(&b->dn_X, bx)) != cudaSuccess || (e = cudaMalloc(&b->dn_y, by)) != cudaSuccess ||
         (e = cudaMalloc(&b->dc_X, bx)) != cudaSuccess || (e = cudaMalloc(&b->dc_y, by)) != cudaSuccess ||
         (e = cudaStreamCreateWithFlags(&b->s_X, cudaStreamNonBlocking)) != cudaSuccess ||
@@ -112,18 +121,23 @@ extern "C" int cn_batch_copy_next_async(cn_batch *b)
 {
     CN_REQUIRE(b, CN_ERR_ARG, "cn_batch_copy_next_async: null handle");
     const int64_t idx = b->next_batch, r = rows_of_batch(b, idx);
-    // the staging buffers are free once the previous copy out of them has finished
-    if (b->copy_pending) {
-        CN_CUDA(cudaEventSynchronize(b->e_X));
-        CN_CUDA(cudaEventSynchronize(b->e_y));
+    const float *src_X = b->h_X + (size_t)idx * b->batch * b->cols_X, *src_y = b->h_y + (size_t)idx * b->batch * b->cols_y;
+    if (!b->direct) {
+        // the staging buffers are free once the previous copy out of them has finished
+        if (b->copy_pending) {
+            CN_CUDA(cudaEventSynchronize(b->e_X));
+            CN_CUDA(cudaEventSynchronize(b->e_y));
+        }
+        memcpy(b->p_X, src_X, (size_t)r * b->cols_X * sizeof(float));
+        memcpy(b->p_y, src_y, (size_t)r * b->cols_y * sizeof(float));
+        src_X = b->p_X;
+        src_y = b->p_y;
     }
-    memcpy(b->p_X, b->h_X + (size_t)idx * b->batch * b->cols_X, (size_t)r * b->cols_X * sizeof(float));
-    memcpy(b->p_y, b->h_y + (size_t)idx * b->batch * b->cols_y, (size_t)r * b->cols_y * sizeof(float));
     // do not overwrite the device "next" buffers while the last swap's transposes may still read them
     CN_CUDA(cudaStreamWaitEvent(b->s_X, b->e_consumed, 0));
     CN_CUDA(cudaStreamWaitEvent(b->s_y, b->e_consumed, 0));
-    CN_CUDA(cudaMemcpyAsync(b->dn_X, b->p_X, (size_t)r * b->cols_X * sizeof(float), cudaMemcpyHostToDevice, b->s_X));
-    CN_CUDA(cudaMemcpyAsync(b->dn_y, b->p_y, (size_t)r * b->cols_y * sizeof(float), cudaMemcpyHostToDevice, b->s_y));
+    CN_CUDA(cudaMemcpyAsync(b->dn_X, src_X, (size_t)r * b->cols_X * sizeof(float), cudaMemcpyHostToDevice, b->s_X));
+    CN_CUDA(cudaMemcpyAsync(b->dn_y, src_y, (size_t)r * b->cols_y * sizeof(float), cudaMemcpyHostToDevice, b->s_y));
     CN_CUDA(cudaEventRecord(b->e_X, b->s_X));
     CN_CUDA(cudaEventRecord(b->e_y, b->s_y));
     b->next_rows = r;
