@@ -810,7 +810,7 @@ bool cn_gemm_tc_supported(cn_context *, int transA, int transB, int64_t M, int64
 {
     (void)transA;   // a transposed activation operand only changes the pre-pass
     (void)transB;   // a transposed weight only changes the TMA box and the converter's read pattern
-    if (M < 1 || N < 16 || K < 32) return false;
+    if (M < 1 || N < 1 || K < 1) return false;   // short dimensions are zero-filled by TMA up to the tile
     if ((ldb & 3) != 0 || (reinterpret_cast<uintptr_t>(B) & 15u) != 0) return false;   // TMA: 16-byte pitch and base
     if (K >= (1LL << 31) - 64 || N >= (1LL << 31) - 256 || M >= (1LL << 31) - 256) return false;   // TMA coordinates are 32-bit
     return true;

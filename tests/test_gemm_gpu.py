@@ -42,7 +42,7 @@ def test_shape_mismatch_is_an_error(ctx):
 
 
 @pytest.mark.parametrize("M,K,N", [(128, 32, 128), (128, 64, 128), (128, 256, 128), (128, 784, 1024), (64, 128, 256),
-                                   (1, 64, 16), (130, 100, 200), (256, 512, 384), (300, 1000, 520), (128, 4096, 2304)])
+                                   (1, 64, 16), (128, 1200, 10), (128, 12, 1200), (3, 4, 8), (130, 100, 200), (256, 512, 384), (300, 1000, 520), (128, 4096, 2304)])
 @pytest.mark.parametrize("mode", [_lib.GEMM_3XTF32, _lib.GEMM_TF32])
 def test_tensor_core_gemm_vs_fp64(ctx, M, K, N, mode):
     rng = np.random.default_rng(M * 7 + K * 3 + N)
