@@ -182,6 +182,19 @@ def codec_bench(ctx, torch, peaks):
             ms = e0.elapsed_time(e1) / iters
             gbs = n * bytes_per / ms / 1e6
             res[name] = {"GB/s": round(gbs, 1), "us": round(ms * 1e3, 2), "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4)}
+        # yardstick at the same size: a plain device copy (read + write bytes) through torch, same rotation of buffers.
+        # At 64 MiB a launch lasts ~20 us, so launch ramp and tail weigh on every kernel, the copy included.
+        for i in range(sets):
+            outs[i].copy_(xs[i])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for it in range(iters):
+            outs[it % sets].copy_(xs[it % sets])
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        res["torch_copy_same_size"] = {"GB/s": round(n * 8 / ms / 1e6, 1), "us": round(ms * 1e3, 2)}
         out[label] = res
         del xs, codes, outs
         torch.cuda.empty_cache()

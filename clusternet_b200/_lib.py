@@ -55,6 +55,7 @@ _SIGNATURES = {
     "cn_maxout": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "cn_rand_uniform": (c_int, [c_void_p, c_void_p, c_int64, c_uint64, c_uint64, c_void_p]),
     "cn_rand_normal": (c_int, [c_void_p, c_void_p, c_int64, c_float, c_float, c_uint64, c_uint64, c_void_p]),
+    "cn_rand_int": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_uint64, c_uint64, c_void_p]),
     "cn_uniform_sqrt_weight": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_uint64, c_uint64, c_void_p]),
     "cn_dropout": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_float, c_uint64, c_uint64, c_void_p]),
     "cn_comm_get_unique_id": (c_int, [c_void_p]),

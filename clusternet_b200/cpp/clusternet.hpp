@@ -188,6 +188,20 @@ public:
         cn_detail::check(cn_rand_uniform(ctx_.get(), m->data, m->size, seed_, next_offset(m->size), nullptr));
         return m;
     }
+    Matrix *rand_int(int64_t rows, int64_t cols, int low, int high)
+    {
+        Matrix *m = empty(rows, cols);
+        cn_detail::check(cn_rand_int(ctx_.get(), m->data, m->size, low, high, seed_, next_offset(m->size), nullptr));
+        return m;
+    }
+    // same numbers on every rank (the reference's second generator, seeded with 12345 everywhere)
+    Matrix *rand_same_seed_MPI(int64_t rows, int64_t cols)
+    {
+        Matrix *m = empty(rows, cols);
+        cn_detail::check(cn_rand_uniform(ctx_.get(), m->data, m->size, same_seed_, same_offset_, nullptr));
+        same_offset_ += (uint64_t)(m->size + 3) / 4;
+        return m;
+    }
     Matrix *randn(int64_t rows, int64_t cols, float mean = 0.0f, float std = 1.0f)
     {
         Matrix *m = empty(rows, cols);

@@ -29,7 +29,7 @@ __device__ __forceinline__ uint4 philox4x32_10(uint64_t counter, uint64_t seed)
 // uniform in (0, 1], the range of curandGenerateUniform that the reference's kernels assume
 __device__ __forceinline__ float u01(uint32_t x) { return fmaf((float)x, 2.3283064365386963e-10f, 2.3283064365386963e-10f * 0.5f); }
 
-enum { RAND_UNIFORM = 0, RAND_NORMAL = 1, RAND_SQRT_WEIGHT = 2, RAND_DROPOUT = 3 };
+enum { RAND_UNIFORM = 0, RAND_NORMAL = 1, RAND_SQRT_WEIGHT = 2, RAND_DROPOUT = 3, RAND_INT = 4 };
 
 template <int KIND>
 __global__ void cn_rand_kernel(const float *__restrict__ A, float *__restrict__ out, int64_t n, uint64_t seed, uint64_t offset,
@@ -56,6 +56,7 @@ __global__ void cn_rand_kernel(const float *__restrict__ A, float *__restrict__ 
             if (i >= n) break;
             if (KIND == RAND_SQRT_WEIGHT) out[i] = p0 + v[k] * p1;            // lower + u * range, as the reference kernel
             else if (KIND == RAND_DROPOUT) out[i] = v[k] > p0 ? A[i] : 0.0f;  // kDropout: keep where u > rate, no rescale
+            else if (KIND == RAND_INT) out[i] = fminf((float)((int)(v[k] * p1)) + p0, p0 + p1 - 1.0f);   // kRandInt; u == 1 stays in range
             else out[i] = v[k];
         }
     }
@@ -98,4 +99,12 @@ extern "C" int cn_dropout(cn_context *ctx, const float *d_A, float *d_out, int64
 {
     CN_REQUIRE(n == 0 || d_A, CN_ERR_ARG, "cn_dropout: null input");
     return rand_launch<RAND_DROPOUT>(ctx, d_A, d_out, n, seed, offset, rate, 0.f, stream);
+}
+
+// rand_int (source/clusterNet.cpp:790-796, kRandInt source/clusterKernels.cu:159-170): integers low..high as floats,
+// (int)(u * (high - low + 1)) + low.  The reference lets u == 1.0 produce high + 1; here that one value maps to high.
+extern "C" int cn_rand_int(cn_context *ctx, float *d_A, int64_t n, int low, int high, uint64_t seed, uint64_t offset, void *stream)
+{
+    CN_REQUIRE(high >= low, CN_ERR_ARG, "cn_rand_int: high < low");
+    return rand_launch<RAND_INT>(ctx, nullptr, d_A, n, seed, offset, (float)low, (float)(high - low + 1), stream);
 }

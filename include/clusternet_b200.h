@@ -176,6 +176,8 @@ int cn_maxout(cn_context *ctx, const float *d_A, float *d_out, float *d_argmax, 
  * ------------------------------------------------------------------------------------------- */
 int cn_rand_uniform(cn_context *ctx, float *d_A, int64_t n, uint64_t seed, uint64_t offset, void *stream);
 int cn_rand_normal(cn_context *ctx, float *d_A, int64_t n, float mean, float std, uint64_t seed, uint64_t offset, void *stream);
+/* rand_int (source/clusterNet.cpp:790-796; kRandInt source/clusterKernels.cu:159-170): integers low..high stored as floats. */
+int cn_rand_int(cn_context *ctx, float *d_A, int64_t n, int low, int high, uint64_t seed, uint64_t offset, void *stream);
 int cn_uniform_sqrt_weight(cn_context *ctx, float *d_A, int64_t n, int64_t fan_in, int64_t fan_out_total,
                            uint64_t seed, uint64_t offset, void *stream);
 /* dropout (source/clusterNet.cpp:842-872, kDropout source/clusterKernels.cu:939-947):

@@ -43,6 +43,14 @@ def test_rand_is_deterministic_and_in_range(ctx):
     assert abs(float(n.mean()) - 1.0) < 0.02 and abs(float(n.std()) - 2.0) < 0.02
 
 
+def test_rand_int_range(ctx):
+    t = torch.empty(200000, device="cuda")
+    cn.check(ctx.lib.cn_rand_int(ctx.h, t.data_ptr(), t.numel(), 3, 9, 5, 0, ctx.stream_ptr()))
+    assert float(t.min()) == 3.0 and float(t.max()) == 9.0 and bool((t == t.round()).all())
+    counts = torch.bincount(t.long())[3:]
+    assert float(counts.float().std() / counts.float().mean()) < 0.02
+
+
 @pytest.mark.parametrize("rows,cols,total", [(784, 1200, 1200), (100, 40, 320), (5, 5, 5)])
 def test_uniform_sqrt_weight_range(ctx, rows, cols, total):
     """tests/clusterNet_test.cu:279-314,499-577: weights lie within +-4*sqrt(6/(in+out)) and fill that range."""
