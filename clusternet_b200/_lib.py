@@ -19,6 +19,10 @@ GEMM_3XTF32, GEMM_TF32, GEMM_FP32_SIMT = 0, 1, 2
 ACT_LINEAR, ACT_RELU, ACT_LOGISTIC, ACT_DOUBLE_RELU = 0, 1, 2, 3
 
 
+class Coded(ctypes.Structure):
+    _fields_ = [("codes", c_void_p), ("scales", c_void_p), ("own_fp32", c_void_p), ("rows", c_int64), ("cols", c_int64)]
+
+
 class Epilogue(ctypes.Structure):
     _fields_ = [("bias", c_void_p), ("activation", c_int), ("maxout_level", c_int), ("argmax_out", c_void_p)]
 
@@ -73,6 +77,10 @@ _SIGNATURES = {
     "cn_sym_free": (c_int, [c_void_p, c_void_p]),
     "cn_dotmpi_f32": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, ctypes.POINTER(Epilogue),
                               c_int, c_int, c_void_p]),
+    "cn_dotmpi_to_coded_f32": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, ctypes.POINTER(Coded),
+                                       ctypes.POINTER(Epilogue), c_int, c_void_p]),
+    "cn_dotmpi_from_coded_f32": (c_int, [c_void_p, ctypes.POINTER(Coded), c_int64, c_void_p, c_void_p, ctypes.POINTER(Epilogue),
+                                         c_int, c_int, c_void_p]),
     "cn_dottmpi_f32": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "cn_dot_sharded_out_f32": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "cn_softmax": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),

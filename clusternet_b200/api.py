@@ -220,6 +220,26 @@ class Context:
                                      int(exchange), self.stream_ptr()))
         return out
 
+    def dotmpi_to_coded(self, A, Wshard, n_total, bias=None, activation=_lib.ACT_LINEAR, mode=_lib.GEMM_3XTF32, rank=0, nranks=1):
+        """Sharded product whose gathered output stays 8-bit coded; returns (Coded struct, the tensors that back it)."""
+        K, M = A.shape
+        _, cnt = self.shard_cols(n_total, rank, nranks)
+        codes = torch.empty((n_total, M), dtype=torch.uint8, device=self.device)
+        scales = torch.zeros(max(nranks, 1), dtype=torch.float32, device=self.device)
+        own = torch.empty((cnt, M), dtype=torch.float32, device=self.device)
+        c = _lib.Coded(_ptr(codes), _ptr(scales), _ptr(own), M, n_total)
+        epi = Epilogue(_ptr(bias), int(activation), 0, None)
+        check(self.lib.cn_dotmpi_to_coded_f32(self.h, M, K, n_total, _ptr(A), _ptr(Wshard), ctypes.byref(c), ctypes.byref(epi), int(mode),
+                                              self.stream_ptr()))
+        return c, (codes, scales, own)
+
+    def dotmpi_from_coded(self, coded, Wshard, n_total, out=None, bias=None, activation=_lib.ACT_LINEAR, mode=_lib.GEMM_3XTF32, exchange=0):
+        out = out if out is not None else self.empty(coded.rows, n_total)
+        epi = Epilogue(_ptr(bias), int(activation), 0, None)
+        check(self.lib.cn_dotmpi_from_coded_f32(self.h, ctypes.byref(coded), n_total, _ptr(Wshard), _ptr(out), ctypes.byref(epi), int(mode),
+                                                int(exchange), self.stream_ptr()))
+        return out
+
     def dottmpi(self, A, Bshard, out=None, mode=_lib.GEMM_3XTF32):
         """out (M x R) = A (M x n_total) . B^T with B column-sharded (this rank: R x cols_local)."""
         n_total, M = A.shape

@@ -493,3 +493,71 @@ int cn_comm_gather_codes(cn_context *ctx, uint8_t *d_codes_all, int64_t n, float
     CN_REQUIRE(r1 == ncclSuccess && r2 == ncclSuccess && r3 == ncclSuccess, CN_ERR_NCCL, "cn_grad_sync_8bit: all-gather failed");
     return CN_OK;
 }
+
+// ---- 8-bit exchange with the decode inside the consumer GEMM
+extern "C" int cn_dotmpi_to_coded_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_total, const float *d_A, const float *d_Wshard,
+                                      cn_coded *out, const cn_epilogue *epi, int mode, void *stream)
+{
+    CN_REQUIRE(ctx && out && out->codes && out->scales && out->own_fp32, CN_ERR_ARG, "cn_dotmpi_to_coded_f32: null argument");
+    CN_REQUIRE(M >= 0 && K >= 0 && n_total >= 0, CN_ERR_SHAPE, "cn_dotmpi_to_coded_f32: negative dimension");
+    CN_REQUIRE(!epi || epi->maxout_level <= 1, CN_ERR_UNSUPPORTED, "cn_dotmpi_to_coded_f32: maxout is not available on the sharded product");
+    const int G = ctx->comm ? ctx->comm->nranks : 1, rank = ctx->comm ? ctx->comm->rank : 0;
+    int64_t start, cnt;
+    cn_shard_cols(n_total, rank, G, &start, &cnt);
+    cn_epilogue local;
+    local.bias = (epi && epi->bias) ? epi->bias + start : nullptr;
+    local.activation = epi ? epi->activation : CN_ACT_LINEAR;
+    local.maxout_level = 0;
+    local.argmax_out = nullptr;
+    out->rows = M;
+    out->cols = n_total;
+    int st = cn_gemm_f32(ctx, 0, 0, M, cnt, K, d_A, M, d_Wshard, K, out->own_fp32, M, &local, mode, stream);
+    if (st != CN_OK) return st;
+    if ((st = cn_absmax_f32(ctx, out->own_fp32, M * cnt, out->scales + rank, stream)) != CN_OK) return st;
+    if ((st = cn_compress_8bit_dp(ctx, out->own_fp32, out->scales + rank, M * cnt, out->codes + (size_t)M * start, stream)) != CN_OK) return st;
+    if (G == 1) return CN_OK;
+    if ((st = cn_allgather_scalar_f32(ctx, out->scales, stream)) != CN_OK) return st;
+    return cn_allgather_cols_u8(ctx, out->codes, M, n_total, stream);
+}
+
+extern "C" int cn_dotmpi_from_coded_f32(cn_context *ctx, const cn_coded *A, int64_t n_total, const float *d_Wshard, float *d_C,
+                                        const cn_epilogue *epi, int mode, int exchange, void *stream)
+{
+    CN_REQUIRE(ctx && A && A->codes && A->scales && d_Wshard && d_C, CN_ERR_ARG, "cn_dotmpi_from_coded_f32: null argument");
+    const int64_t M = A->rows, K = A->cols;
+    const int G = ctx->comm ? ctx->comm->nranks : 1, rank = ctx->comm ? ctx->comm->rank : 0;
+    int64_t start, cnt;
+    cn_shard_cols(n_total, rank, G, &start, &cnt);
+    if (mode != CN_GEMM_FP32_SIMT && cnt > 0 &&
+        cn_gemm_tc_supported(ctx, 0, 0, M, cnt, K, A->own_fp32, M, d_Wshard, K, d_C, M)) {
+        if (!ctx->gemm) ctx->gemm = new cn_gemm_workspace();
+        cn_coded_src src;
+        src.codes = A->codes;
+        src.scales = A->scales;
+        src.own_fp32 = A->own_fp32;
+        src.nranks = G;
+        src.own_rank = rank;
+        ctx->gemm->coded_src = &src;   // consumed by the launch inside the call below
+        // the fp32 pointer handed down is only a placeholder: the pre-pass reads the codes
+        int st = cn_dotmpi_f32(ctx, M, K, n_total, A->own_fp32 ? A->own_fp32 : reinterpret_cast<const float *>(A->codes), d_Wshard, d_C,
+                               epi, mode, exchange, stream);
+        ctx->gemm->coded_src = nullptr;
+        return st;
+    }
+    // shapes the tensor-core kernel does not take: decode to fp32 scratch first
+    void *buf = nullptr;
+    int st = cn_gemm_scratch(ctx, CN_GEMM_SLOT_MAXOUT, (size_t)M * K * sizeof(float), &buf);
+    if (st != CN_OK) return st;
+    float *Af = (float *)buf;
+    for (int r = 0; r < G; ++r) {
+        int64_t s0, c0;
+        cn_shard_cols(K, r, G, &s0, &c0);
+        if (c0 == 0) continue;
+        if (r == rank && A->own_fp32) {
+            CN_CUDA(cudaMemcpyAsync(Af + (size_t)M * s0, A->own_fp32, (size_t)M * c0 * sizeof(float), cudaMemcpyDeviceToDevice, cn_stream(stream)));
+        } else if ((st = cn_decompress_8bit_dp(ctx, A->codes + (size_t)M * s0, A->scales + r, M * c0, Af + (size_t)M * s0, stream)) != CN_OK) {
+            return st;
+        }
+    }
+    return cn_dotmpi_f32(ctx, M, K, n_total, Af, d_Wshard, d_C, epi, mode, exchange, stream);
+}

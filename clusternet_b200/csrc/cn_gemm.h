@@ -12,11 +12,22 @@ enum {
 
 #define CN_GEMM_MAX_TICKETS 4096
 
+// Activations that exist only as gathered 8-bit codes (plus this rank's own block in fp32): set by
+// cn_dotmpi_from_coded_f32 right before the dispatch, consumed by the tensor-core launch, whose pre-pass then decodes
+// while it transposes and splits.
+struct cn_coded_src {
+    const uint8_t *codes = nullptr;
+    const float *scales = nullptr;
+    const float *own_fp32 = nullptr;
+    int nranks = 1, own_rank = 0;
+};
+
 struct cn_gemm_workspace {
     void *ptr[CN_GEMM_SLOTS] = {nullptr, nullptr, nullptr, nullptr};
     size_t bytes[CN_GEMM_SLOTS] = {0, 0, 0, 0};
     unsigned int *d_status = nullptr;   // word 0: set by a kernel whose bounded wait ran out
     void *encode_fn = nullptr;          // cuTensorMapEncodeTiled, resolved once
+    const cn_coded_src *coded_src = nullptr;   // one-shot: see cn_coded_src
     bool profile = false;               // bracket main-kernel launches with events
     std::vector<cudaEvent_t> prof_events;   // start, stop, start, stop, ...
     size_t prof_used = 0;

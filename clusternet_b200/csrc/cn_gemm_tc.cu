@@ -262,6 +262,60 @@ cn_act_split_kernel(const float *__restrict__ A, int64_t lda, int64_t M, int64_t
     }
 }
 
+// The consumer-side half of the 8-bit exchange: the activations arrive as gathered codes (column-major like the fp32
+// matrix; column block r was coded by rank r with scale scales[r]) and are decoded here, inside the pre-pass of the GEMM
+// that consumes them, instead of being written out as fp32 first.  This rank's own block is taken from its exact fp32
+// values.  Decode table as kDecompression_8bit builds it (source/clusterKernels.cu:1141-1152).
+__global__ void __launch_bounds__(256)
+cn_act_split_coded_kernel(const uint8_t *__restrict__ codes, const float *__restrict__ scales, const float *__restrict__ g_tbl,
+                          const float *__restrict__ own_fp32, int own_rank, int nranks, int64_t M, int64_t K, int64_t Kpad,
+                          float *__restrict__ hi, float *__restrict__ lo, int64_t tiles_k)
+{
+    __shared__ float tile[32][33];
+    extern __shared__ float lut[];   // nranks x 256
+    for (int e = threadIdx.x; e < nranks * 256; e += blockDim.x) {
+        const int r = e >> 8, c = e & 255, i = c & 127;
+        const float p = scales[r];
+        float v;
+        if (i < CN_CODEBOOK_N) {
+            v = __fmul_rn(g_tbl[i], p);
+            if (c >= 128) v = -v;
+        } else {
+            v = (c == 255) ? -p : p;
+        }
+        lut[e] = v;
+    }
+    __syncthreads();
+    const int64_t split = K / nranks;
+    const int64_t tm = blockIdx.x / tiles_k, tk = blockIdx.x % tiles_k;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int64_t m_in = tm * 32 + tx;
+#pragma unroll
+    for (int j = ty; j < 32; j += 8) {
+        const int64_t k = tk * 32 + j;
+        float x = 0.0f;
+        if (m_in < M && k < K) {
+            int r = split > 0 ? (int)(k / split) : nranks - 1;
+            if (r > nranks - 1) r = nranks - 1;
+            if (r == own_rank && own_fp32) x = own_fp32[m_in + (k - split * own_rank) * M];
+            else x = lut[(r << 8) + codes[m_in + k * M]];
+        }
+        tile[j][tx] = x;
+    }
+    __syncthreads();
+    const int64_t k_out = tk * 32 + tx;
+#pragma unroll
+    for (int j = ty; j < 32; j += 8) {
+        const int64_t m = tm * 32 + j;
+        if (m < M && k_out < Kpad) {
+            const float x = tile[tx][j];
+            const uint32_t h = to_tf32(x);
+            hi[m * Kpad + k_out] = __uint_as_float(h);
+            if (lo) lo[m * Kpad + k_out] = __uint_as_float(to_tf32(x - __uint_as_float(h)));
+        }
+    }
+}
+
 // Same planes for a transposed activation operand: op(A)(m, k) = A[k + m * lda] is already K-major, so this is a
 // plain copy-and-split.
 __global__ void __launch_bounds__(256)
@@ -873,7 +927,13 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
     {
         const int64_t tiles_k = Kpad / 32, tiles_mm = (M + 31) / 32;
         CN_REQUIRE(tiles_k * tiles_mm < (1LL << 31), CN_ERR_UNSUPPORTED, "cn_gemm_f32: activation matrix too large for the split pre-pass");
-        if (transA) {
+        if (ws->coded_src) {
+            const cn_coded_src *cs = ws->coded_src;
+            ws->coded_src = nullptr;
+            CN_REQUIRE(!transA && lda == M, CN_ERR_UNSUPPORTED, "coded activations must be untransposed with ld = rows");
+            cn_act_split_coded_kernel<<<(unsigned)(tiles_k * tiles_mm), 256, (size_t)cs->nranks * 256 * sizeof(float), s>>>(
+                cs->codes, cs->scales, ctx->d_tbl, cs->own_fp32, cs->own_rank, cs->nranks, M, K, Kpad, hi, lo, tiles_k);
+        } else if (transA) {
             int64_t blocks = (M * Kpad + 255) / 256, cap = (int64_t)ctx->sm_count * 16;
             cn_act_split_t_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(A, lda, M, K, Kpad, hi, lo);
         } else {

@@ -225,6 +225,26 @@ int cn_sym_free(cn_context *ctx, void *ptr);
 int cn_dotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_total, const float *d_A,
                   const float *d_Wshard, float *d_C, const cn_epilogue *epi, int mode, int exchange, void *stream);
 
+/* The 8-bit exchange with the decode moved into the consumer (the reference's commented 8-bit ring,
+ * source/clusterNet.cpp:670-677, decompresses every received slot before hStackN; here the codes stay codes until the
+ * next product reads them).  cn_coded describes a gathered M x n_total matrix held as codes: column block r (the
+ * columns rank r owns) was coded with scale scales[r]; own_fp32 holds this rank's own block in exact fp32.
+ * All buffers belong to the caller: codes M*n_total bytes, scales nranks floats, own_fp32 M*cols_local floats. */
+typedef struct cn_coded {
+    uint8_t *codes;
+    float *scales;
+    float *own_fp32;
+    int64_t rows, cols;   /* M, n_total */
+} cn_coded;
+/* Producer: local GEMM into out->own_fp32 (with the fused epilogue), absmax -> scale, compress, all-gather of codes
+ * and scales.  No decode, no fp32 copy of the peers' blocks. */
+int cn_dotmpi_to_coded_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_total, const float *d_A, const float *d_Wshard,
+                           cn_coded *out, const cn_epilogue *epi, int mode, void *stream);
+/* Consumer: C = act(A . W + bias) with A given as codes; the GEMM's activation pre-pass decodes them (own block from
+ * own_fp32) while it transposes and splits.  exchange as in cn_dotmpi_f32 (0: fp32 gather of C, 1: 8-bit gather). */
+int cn_dotmpi_from_coded_f32(cn_context *ctx, const cn_coded *A, int64_t n_total, const float *d_Wshard, float *d_C,
+                             const cn_epilogue *epi, int mode, int exchange, void *stream);
+
 /* dotTMPI: replaces ClusterNet::dotTMPI (source/clusterNet.cpp:511,628-642,698-727), the backward product through a
  * column-sharded weight: out (M x R) = A (M x n_total) . B^T, where this rank holds the R x cols_local block of the
  * R x n_total matrix B.  Each rank multiplies its column slice of A with its shard (transposed) and the full-size

@@ -129,6 +129,22 @@ def run_nccl():
     ref = oracle.gemm_f64(At, Bn, transA=True)[:, s0:s0 + c0]
     assert np.abs(ctx.to_numpy(osh) - ref).max() / np.abs(ref).max() < 1e-5
     ctx.gemm_check()
+    # two chained layers with the 8-bit exchange decoded inside the second GEMM's pre-pass == the same chain with the
+    # codes decoded to fp32 first (exchange = 1); the coded form never writes the peers' fp32 blocks
+    M, K, N1c, N2c = 128, 640, 1024 + 8 * world, 512
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    Wa = rng.uniform(-1, 1, (K, N1c)).astype(np.float32)
+    Wb = rng.uniform(-1, 1, (N1c, N2c)).astype(np.float32)
+    dA = ctx.colmajor(A)
+    s1, c1 = ctx.shard_cols(N1c, rank, world)
+    s2, c2 = ctx.shard_cols(N2c, rank, world)
+    dWa, dWb = ctx.colmajor(np.ascontiguousarray(Wa[:, s1:s1 + c1])), ctx.colmajor(np.ascontiguousarray(Wb[:, s2:s2 + c2]))
+    h1 = ctx.dotmpi(dA, dWa, N1c, activation=_lib.ACT_RELU, exchange=1)
+    ref2 = ctx.dotmpi(h1, dWb, N2c)
+    coded, keep = ctx.dotmpi_to_coded(dA, dWa, N1c, activation=_lib.ACT_RELU, rank=rank, nranks=world)
+    got2 = ctx.dotmpi_from_coded(coded, dWb, N2c)
+    ctx.gemm_check()
+    assert torch.equal(got2, ref2), float((got2 - ref2).abs().max())
     # 8-bit gradient exchange: own gradient + decode(encode(peer gradient)) in rank order, fixed and gathered scales
     n = 70001
     grads = [np.random.default_rng(100 + r).standard_normal(n).astype(np.float32) * np.float32(0.01 * (r + 1)) for r in range(world)]

@@ -152,3 +152,21 @@ def test_single_rank_dotmpi_equals_dot(ctx):
     assert torch.equal(C1, C2)
     want = np.float64(np.float32(0.3)) * np.float64(np.float32(1.1748345)) * 400
     assert np.abs(ctx.to_numpy(C2) - want).max() / want < 1e-5
+
+
+def test_coded_chain_on_one_rank_is_exact(ctx):
+    """With one rank the whole matrix is the rank's own block, kept in fp32: the coded chain equals the plain chain."""
+    rng = np.random.default_rng(11)
+    A = ctx.colmajor(rng.uniform(-1, 1, (128, 320)).astype(np.float32))
+    W1 = ctx.colmajor(rng.uniform(-1, 1, (320, 512)).astype(np.float32))
+    W2 = ctx.colmajor(rng.uniform(-1, 1, (512, 256)).astype(np.float32))
+    ref = ctx.gemm(ctx.gemm(A, W1, activation=_lib.ACT_RELU), W2)
+    coded, keep = ctx.dotmpi_to_coded(A, W1, 512, activation=_lib.ACT_RELU)
+    got = ctx.dotmpi_from_coded(coded, W2, 256)
+    ctx.gemm_check()
+    assert torch.equal(got, ref)
+    # the codes are the compressor's output for the fp32 block with its absmax as the scale
+    codes, scales, own = keep
+    p = float(scales[0].item())
+    assert p == float(own.abs().max().item())
+    assert np.array_equal(codes.cpu().numpy().ravel(), oracle.compress(ctx.codebook, own.cpu().numpy().ravel(), p))
