@@ -276,7 +276,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default="3xtf32", choices=["3xtf32", "tf32"])
-    ap.add_argument("--exchange", default="fp32", choices=["fp32", "8bit"])
+    ap.add_argument("--exchange", default="fp32", choices=["fp32", "8bit", "8bit-fused"],
+                    help="fp32: gather C in fp32; 8bit: gather codes, decode to fp32; 8bit-fused: layer-1 output stays coded and is\n"
+                         "decoded inside layer 2's GEMM pre-pass")
     ap.add_argument("--nccl-gather", action="store_true", help="gather C with ncclAllGather instead of the fused peer stores")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-codec", action="store_true")
@@ -335,7 +337,7 @@ def main():
     d_stage_out = torch.empty((M, N2), dtype=torch.float32, device="cuda")
     batch = ctx.empty(M, K1)
     # outputs in symmetric buffers: the all-gather of each layer is fused into the GEMM epilogue (stores to peer memory)
-    fused = world > 1 and exchange == 0 and not args.nccl_gather
+    fused = world > 1 and args.exchange != "8bit" and not args.nccl_gather
     out1 = ctx.sym_empty(M, N1) if fused else ctx.empty(M, N1)
     out2 = ctx.sym_empty(M, N2) if fused else ctx.empty(M, N2)
     sp = ctx.stream_ptr()
@@ -346,7 +348,19 @@ def main():
         if world > 1:
             ctx.bcast(batch, 0)
 
+    coded = None
+    if args.exchange == "8bit-fused":
+        c_codes = torch.empty((N1, M), dtype=torch.uint8, device="cuda")
+        c_scales = torch.zeros(world, dtype=torch.float32, device="cuda")
+        c_own = torch.empty((c1, M), dtype=torch.float32, device="cuda")
+        coded = _lib.Coded(c_codes.data_ptr(), c_scales.data_ptr(), c_own.data_ptr(), M, N1)
+        no_epi = cn.Epilogue(None, 0, 0, None)
+
     def two_layers():
+        if coded is not None:
+            cn.check(lib.cn_dotmpi_to_coded_f32(ctx.h, M, K1, N1, batch.data_ptr(), W1.data_ptr(), ctypes.byref(coded), ctypes.byref(no_epi), mode, sp))
+            cn.check(lib.cn_dotmpi_from_coded_f32(ctx.h, ctypes.byref(coded), N2, W2.data_ptr(), out2.data_ptr(), ctypes.byref(no_epi), mode, 0, sp))
+            return
         ctx.dotmpi(batch, W1, N1, out=out1, mode=mode, exchange=exchange)
         ctx.dotmpi(out1, W2, N2, out=out2, mode=mode, exchange=exchange)
 
@@ -449,6 +463,12 @@ def main():
         scale = float(out_dev.abs().max().item())
         return float(np.abs(got - ref).max() / scale)
 
+    if coded is not None:   # out1 was never materialised: rebuild this rank's view of it for the check
+        out1[s1:s1 + c1] = c_own
+        for r in range(world):
+            if r != rank:
+                sr, cr = ctx.shard_cols(N1, r, world)
+                ctx.decompress(c_codes[sr:sr + cr], c_scales[r:r + 1], out=out1[sr:sr + cr])
     err1 = sampled_error(batch, W1, out1, s1, c1, K1)
     err2 = sampled_error(out1, W2, out2, s2, c2, N1)
 
