@@ -23,6 +23,16 @@
 #define LUT_SHIFT 16
 #define LUT_MAX 2816
 
+// The small per-codebook tables travel as kernel parameters (constant bank): read from global memory they would be a
+// cold DRAM miss on the critical path of every launch's table build.
+struct CodecConst {
+    uint32_t thr[128];   // 127 thresholds + pad
+    uint32_t lc[128];    // level codes
+};
+struct DecodeConst {
+    float tbl[128];      // codebook (126 used)
+};
+
 struct CodecTables {
     uint2 lut[LUT_MAX];     // {boundary bits (0 = none), code_below | code_above << 16}
     uint32_t X[128];        // per-launch boundaries in |x| space (bit patterns), [127] = pad
@@ -100,8 +110,7 @@ __device__ __forceinline__ uint32_t fast_code4(const float4 q, uint32_t pb, uint
 template <bool PRECISION_ON_DEVICE>
 __global__ void __launch_bounds__(CODEC_THREADS, 1)
 cn_compress_kernel(const float *__restrict__ A, float precision_arg, const float *__restrict__ d_precision,
-                   int64_t n, uint8_t *__restrict__ out, const uint32_t *__restrict__ g_thr,
-                   const uint8_t *__restrict__ g_level_codes, int vector_ok)
+                   int64_t n, uint8_t *__restrict__ out, const __grid_constant__ CodecConst cc, int vector_ok)
 {
     __shared__ CodecTables t;
     const int tid = threadIdx.x;
@@ -128,12 +137,12 @@ cn_compress_kernel(const float *__restrict__ A, float precision_arg, const float
     }
 
     if (tid < 128) {
-        t.T[tid] = g_thr[tid];
-        t.lc[tid] = g_level_codes[tid];
+        t.T[tid] = cc.thr[tid];
+        t.lc[tid] = cc.lc[tid];
         uint32_t xb = 0xffffffffu;
         bool good = true;
         if (tid < CN_NUM_THR && p_ok) {
-            const float T = __uint_as_float(g_thr[tid]);
+            const float T = __uint_as_float(cc.thr[tid]);
             xb = __float_as_uint(__fmul_rn(T, ap));
             // smallest |x| with fl(|x|/|p|) >= T.  The product is within a few ulps of it: walk down while the lower
             // neighbour still reaches T, and up only if nothing was found below (then xb itself may fall short).
@@ -245,7 +254,7 @@ cn_compress_kernel(const float *__restrict__ A, float precision_arg, const float
 template <bool PRECISION_ON_DEVICE>
 __global__ void __launch_bounds__(CODEC_THREADS, 1)
 cn_decompress_kernel(const uint8_t *__restrict__ codes, float precision_arg, const float *__restrict__ d_precision,
-                     int64_t n, float *__restrict__ out, const float *__restrict__ g_tbl, int vector_ok)
+                     int64_t n, float *__restrict__ out, const __grid_constant__ DecodeConst dc, int vector_ok)
 {
     __shared__ float lut[256];
     const int tid = threadIdx.x;
@@ -254,7 +263,7 @@ cn_decompress_kernel(const uint8_t *__restrict__ codes, float precision_arg, con
         float v = 0.0f;
         const int i = tid & 127;
         if (i < CN_CODEBOOK_N) {
-            v = __fmul_rn(g_tbl[i], p);
+            v = __fmul_rn(dc.tbl[i], p);
             if (tid >= 128) v = -v;
         } else {
             v = (tid == 255) ? -p : p;   // 126, 127, 254 -> +precision; 255 -> -precision
@@ -385,10 +394,12 @@ static int compress_impl(cn_context *ctx, const float *d_A, float precision, con
     CN_REQUIRE(d_A && d_codes, CN_ERR_ARG, "cn_compress_8bit: null buffer");
     int vector_ok = ((uintptr_t)d_A % 16 == 0) && ((uintptr_t)d_codes % 4 == 0);
     int grid = codec_grid(ctx, n, CODEC_THREADS, 4, 1);
+    CodecConst cc;
+    for (int i = 0; i < 128; ++i) { cc.thr[i] = ctx->h_thr[i]; cc.lc[i] = ctx->h_level_codes[i]; }
     if (d_precision)
-        cn_compress_kernel<true><<<grid, CODEC_THREADS, 0, cn_stream(stream)>>>(d_A, 0.f, d_precision, n, d_codes, ctx->d_thr, ctx->d_level_codes, vector_ok);
+        cn_compress_kernel<true><<<grid, CODEC_THREADS, 0, cn_stream(stream)>>>(d_A, 0.f, d_precision, n, d_codes, cc, vector_ok);
     else
-        cn_compress_kernel<false><<<grid, CODEC_THREADS, 0, cn_stream(stream)>>>(d_A, precision, nullptr, n, d_codes, ctx->d_thr, ctx->d_level_codes, vector_ok);
+        cn_compress_kernel<false><<<grid, CODEC_THREADS, 0, cn_stream(stream)>>>(d_A, precision, nullptr, n, d_codes, cc, vector_ok);
     CN_CUDA(cudaGetLastError());
     cn_count_launch();
     return CN_OK;
@@ -414,10 +425,12 @@ static int decompress_impl(cn_context *ctx, const uint8_t *d_codes, float precis
     CN_REQUIRE(d_out && d_codes, CN_ERR_ARG, "cn_decompress_8bit: null buffer");
     int vector_ok = ((uintptr_t)d_out % 16 == 0) && ((uintptr_t)d_codes % 4 == 0);
     int grid = codec_grid(ctx, n, CODEC_THREADS, 4, 1);   // 1024 threads x 64 registers fill an SM: one resident CTA
+    DecodeConst dc;
+    for (int i = 0; i < 128; ++i) dc.tbl[i] = ctx->h_tbl[i];
     if (d_precision)
-        cn_decompress_kernel<true><<<grid, CODEC_THREADS, 0, cn_stream(stream)>>>(d_codes, 0.f, d_precision, n, d_out, ctx->d_tbl, vector_ok);
+        cn_decompress_kernel<true><<<grid, CODEC_THREADS, 0, cn_stream(stream)>>>(d_codes, 0.f, d_precision, n, d_out, dc, vector_ok);
     else
-        cn_decompress_kernel<false><<<grid, CODEC_THREADS, 0, cn_stream(stream)>>>(d_codes, precision, nullptr, n, d_out, ctx->d_tbl, vector_ok);
+        cn_decompress_kernel<false><<<grid, CODEC_THREADS, 0, cn_stream(stream)>>>(d_codes, precision, nullptr, n, d_out, dc, vector_ok);
     CN_CUDA(cudaGetLastError());
     cn_count_launch();
     return CN_OK;
