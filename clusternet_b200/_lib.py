@@ -33,6 +33,7 @@ _SIGNATURES = {
     "cn_version": (c_int, []),
     "cn_compiled_arch": (c_int, []),
     "cn_kernel_launches": (c_uint64, []),
+    "cn_diag_wait_probe": (c_int, [c_void_p, c_int64, c_void_p]),
     "cn_gemm_profile_enable": (c_int, [c_void_p, c_int]),
     "cn_gemm_profile_read": (c_int, [c_void_p, c_void_p, c_int, ctypes.POINTER(c_int)]),
     "cn_context_create": (c_int, [c_int, c_void_p, ctypes.POINTER(c_void_p)]),
@@ -62,6 +63,8 @@ _SIGNATURES = {
     "cn_rand_int": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_uint64, c_uint64, c_void_p]),
     "cn_uniform_sqrt_weight": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_uint64, c_uint64, c_void_p]),
     "cn_dropout": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_float, c_uint64, c_uint64, c_void_p]),
+    "cn_dropout_dp": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_float, c_void_p, c_uint64, c_void_p]),
+    "cn_seed_advance": (c_int, [c_void_p, c_void_p, c_void_p]),
     "cn_comm_get_unique_id": (c_int, [c_void_p]),
     "cn_comm_init_rank": (c_int, [c_void_p, c_void_p, c_int, c_int]),
     "cn_comm_destroy": (c_int, [c_void_p]),

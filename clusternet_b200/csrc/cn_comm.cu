@@ -561,3 +561,33 @@ extern "C" int cn_dotmpi_from_coded_f32(cn_context *ctx, const cn_coded *A, int6
     }
     return cn_dotmpi_f32(ctx, M, K, n_total, Af, d_Wshard, d_C, epi, mode, exchange, stream);
 }
+
+// ---- diagnostics: the bounded wait on a cross-GPU flag, exercised without a peer.
+// Waits for an epoch that nothing will ever write into this context's own probe word, with a caller-chosen cycle
+// limit; when the limit runs out the kernel records status 10 and returns, exactly like cn_flag_barrier_kernel does
+// when a peer never signals.  Lets a host program (and the tests) see that a missing rank surfaces as CN_ERR_TIMEOUT
+// from cn_gemm_check_status instead of a hang.
+__global__ void cn_wait_probe_kernel(const unsigned int *flag, unsigned int epoch, long long limit_cycles, unsigned int *status)
+{
+    const volatile unsigned int *f = flag;
+    const long long t0 = clock64();
+    while ((int)(*f - epoch) < 0) {
+        if (clock64() - t0 > limit_cycles) { atomicMax(status, 10u); break; }
+        __nanosleep(200);
+    }
+}
+
+extern "C" int cn_diag_wait_probe(cn_context *ctx, int64_t limit_cycles, void *stream)
+{
+    CN_REQUIRE(ctx && limit_cycles > 0 && limit_cycles <= 4000000000LL, CN_ERR_ARG, "cn_diag_wait_probe: limit must be in 1 .. 4e9 cycles");
+    if (!ctx->gemm) ctx->gemm = new cn_gemm_workspace();
+    if (!ctx->gemm->d_status) {
+        CN_CUDA(cudaMalloc(&ctx->gemm->d_status, 64 + CN_GEMM_MAX_TICKETS * sizeof(unsigned int)));
+        CN_CUDA(cudaMemset(ctx->gemm->d_status, 0, 64 + CN_GEMM_MAX_TICKETS * sizeof(unsigned int)));
+    }
+    // word 8 of the status block is never written: the probe waits for it to reach 1
+    cn_wait_probe_kernel<<<1, 1, 0, cn_stream(stream)>>>(ctx->gemm->d_status + 8, 1u, (long long)limit_cycles, ctx->gemm->d_status);
+    CN_CUDA(cudaGetLastError());
+    cn_count_launch();
+    return CN_OK;
+}

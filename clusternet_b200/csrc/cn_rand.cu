@@ -32,9 +32,10 @@ __device__ __forceinline__ float u01(uint32_t x) { return fmaf((float)x, 2.32830
 enum { RAND_UNIFORM = 0, RAND_NORMAL = 1, RAND_SQRT_WEIGHT = 2, RAND_DROPOUT = 3, RAND_INT = 4 };
 
 template <int KIND>
-__global__ void cn_rand_kernel(const float *__restrict__ A, float *__restrict__ out, int64_t n, uint64_t seed, uint64_t offset,
-                               float p0, float p1)
+__global__ void cn_rand_kernel(const float *__restrict__ A, float *__restrict__ out, int64_t n, uint64_t seed_arg, uint64_t offset,
+                               float p0, float p1, const uint64_t *__restrict__ d_seed)
 {
+    const uint64_t seed = d_seed ? *d_seed : seed_arg;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     const int64_t ngroups = (n + 3) >> 2;
     for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < ngroups; g += stride) {
@@ -63,13 +64,14 @@ __global__ void cn_rand_kernel(const float *__restrict__ A, float *__restrict__ 
 }
 
 template <int KIND>
-static int rand_launch(cn_context *ctx, const float *A, float *out, int64_t n, uint64_t seed, uint64_t offset, float p0, float p1, void *stream)
+static int rand_launch(cn_context *ctx, const float *A, float *out, int64_t n, uint64_t seed, uint64_t offset, float p0, float p1, void *stream,
+                       const uint64_t *d_seed = nullptr)
 {
     CN_REQUIRE(ctx && n >= 0 && (n == 0 || out), CN_ERR_ARG, "rand: bad argument");
     if (n == 0) return CN_OK;
     int64_t blocks = ((n + 3) / 4 + 255) / 256;
     int64_t cap = (int64_t)ctx->sm_count * 8;
-    cn_rand_kernel<KIND><<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, cn_stream(stream)>>>(A, out, n, seed, offset, p0, p1);
+    cn_rand_kernel<KIND><<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, cn_stream(stream)>>>(A, out, n, seed, offset, p0, p1, d_seed);
     CN_CUDA(cudaGetLastError());
     cn_count_launch();
     return CN_OK;
@@ -107,4 +109,24 @@ extern "C" int cn_rand_int(cn_context *ctx, float *d_A, int64_t n, int low, int 
 {
     CN_REQUIRE(high >= low, CN_ERR_ARG, "cn_rand_int: high < low");
     return rand_launch<RAND_INT>(ctx, nullptr, d_A, n, seed, offset, (float)low, (float)(high - low + 1), stream);
+}
+
+// dropout whose seed lives in device memory, so that a step captured once (for instance in a CUDA graph) draws new
+// masks every time it runs: cn_seed_advance bumps the seed on the stream.
+extern "C" int cn_dropout_dp(cn_context *ctx, const float *d_A, float *d_out, int64_t n, float rate, const uint64_t *d_seed, uint64_t offset, void *stream)
+{
+    CN_REQUIRE(d_seed, CN_ERR_ARG, "cn_dropout_dp: null seed pointer");
+    CN_REQUIRE(n == 0 || d_A, CN_ERR_ARG, "cn_dropout_dp: null input");
+    return rand_launch<RAND_DROPOUT>(ctx, d_A, d_out, n, 0, offset, rate, 0.f, stream, d_seed);
+}
+
+__global__ void cn_seed_advance_kernel(uint64_t *seed) { *seed += 0x9E3779B97F4A7C15ull; }
+
+extern "C" int cn_seed_advance(cn_context *ctx, uint64_t *d_seed, void *stream)
+{
+    CN_REQUIRE(ctx && d_seed, CN_ERR_ARG, "cn_seed_advance: null argument");
+    cn_seed_advance_kernel<<<1, 1, 0, cn_stream(stream)>>>(d_seed);
+    CN_CUDA(cudaGetLastError());
+    cn_count_launch();
+    return CN_OK;
 }

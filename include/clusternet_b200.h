@@ -153,6 +153,11 @@ const char *cn_gemm_last_path(const cn_context *ctx);
  * CN_ERR_TIMEOUT if any launch since the last check gave up (the output of that launch is then undefined),
  * CN_OK otherwise.  No counterpart in the reference (cublasSgemm reports nothing). */
 int cn_gemm_check_status(cn_context *ctx, void *stream);
+/* Diagnostics for failure handling: queues a one-thread kernel that waits, like the cross-GPU flag barrier of the fused
+ * gather, for a signal that never comes, gives up after `limit_cycles` SM clock cycles and records the time-out; the
+ * next cn_gemm_check_status then returns CN_ERR_TIMEOUT.  Shows (and lets tests assert) that a rank that never signals
+ * becomes a host-visible error and not a hang.  The reference has no counterpart: its MPI waits are unbounded. */
+int cn_diag_wait_probe(cn_context *ctx, int64_t limit_cycles, void *stream);
 /* Timing of the tensor-core kernel alone: while enabled, every launch of the main GEMM kernel (not its activation
  * pre-pass) is bracketed by CUDA events on the launching stream.  cn_gemm_profile_read waits for the recorded
  * launches, writes up to `max` durations in milliseconds, in launch order, and clears the record.
@@ -183,6 +188,11 @@ int cn_uniform_sqrt_weight(cn_context *ctx, float *d_A, int64_t n, int64_t fan_i
 /* dropout (source/clusterNet.cpp:842-872, kDropout source/clusterKernels.cu:939-947):
  * out[i] = u[i] > rate ? A[i] : 0, u uniform in (0,1]; no rescale. */
 int cn_dropout(cn_context *ctx, const float *d_A, float *d_out, int64_t n, float rate, uint64_t seed, uint64_t offset, void *stream);
+
+/* dropout with its seed in device memory and a call that advances that seed on the stream: a training step recorded
+ * once (CUDA graph) then draws fresh masks on every replay.  No counterpart in the reference (cuRAND host generator). */
+int cn_dropout_dp(cn_context *ctx, const float *d_A, float *d_out, int64_t n, float rate, const uint64_t *d_seed, uint64_t offset, void *stream);
+int cn_seed_advance(cn_context *ctx, uint64_t *d_seed, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Communicator (one process per GPU).  Replaces ClusterNet::init_MPI / shutdown_MPI

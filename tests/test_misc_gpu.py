@@ -170,3 +170,16 @@ def test_coded_chain_on_one_rank_is_exact(ctx):
     p = float(scales[0].item())
     assert p == float(own.abs().max().item())
     assert np.array_equal(codes.cpu().numpy().ravel(), oracle.compress(ctx.codebook, own.cpu().numpy().ravel(), p))
+
+
+def test_bounded_wait_surfaces_as_timeout_status(ctx):
+    """A device-side wait for a signal that never arrives (a peer that died between steps) ends by itself after its
+    cycle limit and is reported by the next status check; the context stays usable."""
+    ctx.gemm_check()                                                    # clean before
+    cn.check(ctx.lib.cn_diag_wait_probe(ctx.h, 2_000_000, ctx.stream_ptr()))      # ~1 ms
+    with pytest.raises(cn.CnError) as e:
+        ctx.gemm_check()
+    assert e.value.status == _lib.CN_ERR_TIMEOUT
+    ctx.gemm_check()                                                    # the status word was cleared
+    a = ctx.rand(4, 4, seed=1)                                          # and the GPU still works
+    assert float(a.sum()) > 0
