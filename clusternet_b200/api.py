@@ -29,6 +29,27 @@ def load_codebook(path=None):
     return tbl
 
 
+def read_hdf5(path, dataset="/Default"):
+    """Dense dataset of an HDF5 file as a float32 (rows, cols) array; read_hdf5 of the reference (source/util.cu:100-131)."""
+    import ctypes
+    lib = load()
+    p, r, c = ctypes.c_void_p(), ctypes.c_int64(), ctypes.c_int64()
+    check(lib.cn_hdf5_read_f32(str(path).encode(), dataset.encode(), ctypes.byref(p), ctypes.byref(r), ctypes.byref(c)))
+    try:
+        flat = np.ctypeslib.as_array(ctypes.cast(p, ctypes.POINTER(ctypes.c_float)), shape=(r.value * c.value,))
+        return flat.reshape(r.value, c.value).copy()
+    finally:
+        lib.cn_host_free(p)
+
+
+def write_hdf5(path, a, dataset="/Default"):
+    """write_hdf5 of the reference (source/util.cu:202-216): one float32 rank-2 dataset in a new file."""
+    a = np.ascontiguousarray(a, np.float32)
+    if a.ndim == 1:
+        a = a.reshape(-1, 1)
+    check(load().cn_hdf5_write_f32(str(path).encode(), dataset.encode(), a.ctypes.data, a.shape[0], a.shape[1]))
+
+
 def _ptr(t):
     if t is None:
         return None

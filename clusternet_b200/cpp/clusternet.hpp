@@ -82,6 +82,20 @@ inline Matrix *empty_cpu(int64_t rows, int64_t cols)
     return m;
 }
 
+// read_hdf5 / write_hdf5 (source/util.cu:100-131,202-216) without libhdf5: pinned host matrix, row-major, dataset "/Default"
+inline Matrix *read_hdf5(const char *filepath, const char *tag)
+{
+    float *data = nullptr;
+    int64_t rows = 0, cols = 0;
+    cn_detail::check(cn_hdf5_read_f32(filepath, tag, &data, &rows, &cols));
+    Matrix *out = empty_pinned(rows, cols);
+    memcpy(out->data, data, out->bytes);
+    cn_host_free(data);
+    return out;
+}
+inline Matrix *read_hdf5(const char *filepath) { return read_hdf5(filepath, "/Default"); }
+inline void write_hdf5(const char *filepath, Matrix *A) { cn_detail::check(cn_hdf5_write_f32(filepath, "/Default", A->data, A->rows, A->cols)); }
+
 class ClusterNet {
 public:
     int MYRANK = 0, NODES = 1, MYGPUID = 0, MPI_SIZE = 1, GPU_COUNT = 1;
@@ -311,6 +325,14 @@ public:
     Matrix *CURRENT_BATCH = nullptr, *CURRENT_BATCH_Y = nullptr, *CURRENT_BATCH_CV = nullptr, *CURRENT_BATCH_CV_Y = nullptr;
     int64_t TOTAL_BATCHES = 0, TOTAL_BATCHES_CV = 0, BATCH_SIZE = 0, BATCH_SIZE_CV = 0, TRAIN_SET_ROWS = 0, CV_SET_ROWS = 0;
     bool SKIP_LAST_BATCH = false;
+
+    // data set read from two HDF5 files (source/batchAllocator.cpp:62-99; the csv branch of the reference is not built)
+    void init(std::string path_X, std::string path_y, float cross_validation_size, int64_t batch_size, int64_t cv_batch_size,
+              ClusterNet *cluster, BatchAllocationMethod_t method = Single_GPU)
+    {
+        if (path_X.find("hdf5") == std::string::npos) throw "Only the cvs and hdf5 formats are supported!";
+        init(read_hdf5(path_X.c_str()), read_hdf5(path_y.c_str()), cross_validation_size, batch_size, cv_batch_size, cluster, method);
+    }
 
     // X, y: HOST row-major matrices holding the whole data set (source/batchAllocator.cpp:21-30,101-139)
     void init(Matrix *X, Matrix *y, float cross_validation_size, int64_t batch_size, int64_t cv_batch_size, ClusterNet *cluster,

@@ -2,6 +2,7 @@
 #include <math.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 #include "cn_internal.h"
 
@@ -47,36 +48,281 @@ extern "C" int cn_version(void) { return 100; }
 extern "C" int cn_compiled_arch(void) { return 100; }
 
 // ------------------------------------------------------------------------------------------------
-// Codebook file.  The reference loads dataset "/Default" of source/8bit_floats.hdf5 through libhdf5
-// (source/clusterNet.cpp:73, source/util.cu:100-131).  That file is a version-0 HDF5 container whose
-// only dataset (126 x 1 float32, little endian, contiguous layout) occupies the last 504 bytes, so
-// the payload is read from the tail after checking the container signature.  A raw 504-byte dump of
-// the table is accepted as well.
+// Minimal HDF5 reader for the files the reference reads with libhdf5 (read_hdf5 of dataset "/Default",
+// source/util.cu:100-131): version-0 superblock, root group with a symbol table (B-tree + local heap), version-1
+// object headers, a simple dataspace of rank 1 or 2, an integer or IEEE float datatype of 4 or 8 bytes (little
+// endian), contiguous or compact layout.  That covers what numpy / h5py write for dense arrays, including the
+// reference's codebook (source/8bit_floats.hdf5) and its test fixtures.  Everything is bounds-checked; anything
+// else is reported as unsupported.
+// ------------------------------------------------------------------------------------------------
+namespace {
+struct H5 {
+    std::vector<unsigned char> b;
+    bool ok(uint64_t off, uint64_t len) const { return off <= b.size() && len <= b.size() - off; }
+    uint64_t u(uint64_t off, int n) const
+    {
+        uint64_t v = 0;
+        for (int i = n - 1; i >= 0; --i) v = (v << 8) | b[off + i];
+        return v;
+    }
+};
+
+struct H5Dataset {
+    int rank = 0;
+    uint64_t dims[2] = {1, 1};
+    int type_class = -1, type_size = 0, type_signed = 0;
+    uint64_t data_addr = 0, data_size = 0;
+    bool have_space = false, have_type = false, have_layout = false;
+};
+
+bool h5_parse_messages(const H5 &f, uint64_t p, uint64_t end, int &left, H5Dataset &d, int depth)
+{
+    while (left > 0 && p + 8 <= end) {
+        if (!f.ok(p, 8)) return false;
+        const unsigned type = (unsigned)f.u(p, 2);
+        const uint64_t size = f.u(p + 2, 2), body = p + 8;
+        if (!f.ok(body, size)) return false;
+        --left;
+        if (type == 0x1 && size >= 8) {   // dataspace
+            const int ver = f.b[body], rank = f.b[body + 1];
+            const uint64_t dp = body + (ver == 1 ? 8 : 4);
+            if (rank < 1 || rank > 2 || !f.ok(dp, 8ull * rank)) return false;
+            d.rank = rank;
+            for (int i = 0; i < rank; ++i) d.dims[i] = f.u(dp + 8ull * i, 8);
+            d.have_space = true;
+        } else if (type == 0x3 && size >= 8) {   // datatype
+            d.type_class = f.b[body] & 0x0f;
+            const unsigned bits0 = f.b[body + 1];
+            if (bits0 & 1) return false;   // big endian
+            d.type_signed = (bits0 >> 3) & 1;
+            d.type_size = (int)f.u(body + 4, 4);
+            d.have_type = true;
+        } else if (type == 0x8 && size >= 2) {   // data layout
+            const int ver = f.b[body], cls = f.b[body + 1];
+            if (ver != 3) return false;
+            if (cls == 1 && size >= 18) { d.data_addr = f.u(body + 2, 8); d.data_size = f.u(body + 10, 8); }
+            else if (cls == 0 && size >= 4) { d.data_size = f.u(body + 2, 2); d.data_addr = body + 4; }
+            else return false;   // chunked
+            d.have_layout = true;
+        } else if (type == 0x10 && size >= 16 && depth < 8) {   // header continuation
+            const uint64_t off = f.u(body, 8), len = f.u(body + 8, 8);
+            if (!f.ok(off, len) || !h5_parse_messages(f, off, off + len, left, d, depth + 1)) return false;
+        }
+        p = body + size;
+    }
+    return true;
+}
+
+// object-header address of `name` in the group whose B-tree / heap are given; 0 when not found
+uint64_t h5_find(const H5 &f, uint64_t tree, uint64_t heap_data, const char *name, int depth)
+{
+    if (depth > 8 || !f.ok(tree, 24) || memcmp(&f.b[tree], "TREE", 4) != 0 || f.b[tree + 4] != 0) return 0;
+    const int level = f.b[tree + 5], entries = (int)f.u(tree + 6, 2);
+    for (int e = 0; e < entries; ++e) {
+        const uint64_t cp = tree + 24 + 8 + 16ull * e;   // key0, child0, key1, child1, ...
+        if (!f.ok(cp, 8)) return 0;
+        const uint64_t child = f.u(cp, 8);
+        if (level > 0) {
+            const uint64_t r = h5_find(f, child, heap_data, name, depth + 1);
+            if (r) return r;
+            continue;
+        }
+        if (!f.ok(child, 8) || memcmp(&f.b[child], "SNOD", 4) != 0) return 0;
+        const int nsym = (int)f.u(child + 6, 2);
+        for (int k = 0; k < nsym; ++k) {
+            const uint64_t ent = child + 8 + 40ull * k;
+            if (!f.ok(ent, 40)) return 0;
+            const uint64_t noff = heap_data + f.u(ent, 8);
+            const size_t nl = strlen(name);
+            if (f.ok(noff, nl + 1) && memcmp(&f.b[noff], name, nl + 1) == 0) return f.u(ent + 8, 8);
+        }
+    }
+    return 0;
+}
+}  // namespace
+
+extern "C" int cn_hdf5_read_f32(const char *path, const char *dataset, float **data_out, int64_t *rows, int64_t *cols)
+{
+    CN_REQUIRE(path && dataset && data_out && rows && cols, CN_ERR_ARG, "cn_hdf5_read_f32: null argument");
+    *data_out = nullptr;
+    H5 f;
+    {
+        FILE *fp = fopen(path, "rb");
+        CN_REQUIRE(fp, CN_ERR_ARG, "cn_hdf5_read_f32: cannot open %s", path);
+        fseek(fp, 0, SEEK_END);
+        const long sz = ftell(fp);
+        fseek(fp, 0, SEEK_SET);
+        if (sz > 0) f.b.resize((size_t)sz);
+        const size_t got = sz > 0 ? fread(f.b.data(), 1, (size_t)sz, fp) : 0;
+        fclose(fp);
+        CN_REQUIRE(sz >= 96 && got == (size_t)sz, CN_ERR_ARG, "cn_hdf5_read_f32: %s is too short", path);
+    }
+    static const unsigned char sig[8] = {0x89, 'H', 'D', 'F', '\r', '\n', 0x1a, '\n'};
+    CN_REQUIRE(memcmp(f.b.data(), sig, 8) == 0, CN_ERR_ARG, "cn_hdf5_read_f32: %s has no HDF5 signature", path);
+    CN_REQUIRE(f.b[8] == 0 && f.b[13] == 8 && f.b[14] == 8, CN_ERR_UNSUPPORTED,
+               "cn_hdf5_read_f32: %s: only version-0 superblocks with 8-byte offsets are read", path);
+    // root symbol-table entry at byte 56: object header address, cache type, scratch = B-tree and heap addresses
+    uint64_t tree = 0, heap = 0;
+    if (f.u(72, 4) == 1) {
+        tree = f.u(80, 8);
+        heap = f.u(88, 8);
+    } else {
+        const uint64_t oh = f.u(64, 8);   // symbol-table message (0x11) of the root object header
+        CN_REQUIRE(f.ok(oh, 16) && f.b[oh] == 1, CN_ERR_UNSUPPORTED, "cn_hdf5_read_f32: %s: unsupported root object header", path);
+        uint64_t p = oh + 16, end = p + f.u(oh + 8, 4);
+        int left = (int)f.u(oh + 2, 2);
+        while (left-- > 0 && f.ok(p, 8)) {
+            const unsigned type = (unsigned)f.u(p, 2);
+            const uint64_t size = f.u(p + 2, 2);
+            if (type == 0x11 && f.ok(p + 8, 16)) { tree = f.u(p + 8, 8); heap = f.u(p + 16, 8); }
+            p += 8 + size;
+            if (p > end) break;
+        }
+    }
+    CN_REQUIRE(tree && heap && f.ok(heap, 32) && memcmp(&f.b[heap], "HEAP", 4) == 0, CN_ERR_UNSUPPORTED,
+               "cn_hdf5_read_f32: %s: root group has no symbol table", path);
+    const uint64_t heap_data = f.u(heap + 24, 8);
+    const char *name = dataset[0] == '/' ? dataset + 1 : dataset;
+    const uint64_t oh = h5_find(f, tree, heap_data, name, 0);
+    CN_REQUIRE(oh && f.ok(oh, 16) && f.b[oh] == 1, CN_ERR_ARG, "cn_hdf5_read_f32: dataset '%s' not found in %s", dataset, path);
+    H5Dataset d;
+    int left = (int)f.u(oh + 2, 2);
+    const uint64_t hsize = f.u(oh + 8, 4);
+    CN_REQUIRE(f.ok(oh + 16, hsize) && h5_parse_messages(f, oh + 16, oh + 16 + hsize, left, d, 0) && d.have_space && d.have_type && d.have_layout,
+               CN_ERR_UNSUPPORTED, "cn_hdf5_read_f32: dataset '%s' of %s uses a feature this reader does not have (chunking, big endian, rank > 2)", dataset, path);
+    CN_REQUIRE(d.dims[0] < (1ull << 31) && d.dims[1] < (1ull << 31), CN_ERR_UNSUPPORTED, "cn_hdf5_read_f32: dimension of 2^31 or more");
+    const uint64_t n = d.dims[0] * (d.rank == 2 ? d.dims[1] : 1);
+    CN_REQUIRE((d.type_class == 0 || d.type_class == 1) && (d.type_size == 4 || d.type_size == 8), CN_ERR_UNSUPPORTED,
+               "cn_hdf5_read_f32: datatype class %d size %d", d.type_class, d.type_size);
+    CN_REQUIRE(n > 0 && n < (1ull << 40) && f.ok(d.data_addr, n * (uint64_t)d.type_size) && d.data_size >= n * (uint64_t)d.type_size,
+               CN_ERR_ARG, "cn_hdf5_read_f32: data of '%s' lies outside %s", dataset, path);
+    float *out = (float *)malloc(n * sizeof(float));
+    CN_REQUIRE(out, CN_ERR_NOMEM, "cn_hdf5_read_f32: out of memory");
+    const unsigned char *src = &f.b[d.data_addr];
+    for (uint64_t i = 0; i < n; ++i) {
+        if (d.type_class == 1) {
+            if (d.type_size == 4) { float v; memcpy(&v, src + 4 * i, 4); out[i] = v; }
+            else { double v; memcpy(&v, src + 8 * i, 8); out[i] = (float)v; }
+        } else if (d.type_size == 4) {
+            if (d.type_signed) { int32_t v; memcpy(&v, src + 4 * i, 4); out[i] = (float)v; }
+            else { uint32_t v; memcpy(&v, src + 4 * i, 4); out[i] = (float)v; }
+        } else {
+            if (d.type_signed) { int64_t v; memcpy(&v, src + 8 * i, 8); out[i] = (float)v; }
+            else { uint64_t v; memcpy(&v, src + 8 * i, 8); out[i] = (float)v; }
+        }
+    }
+    *data_out = out;
+    *rows = (int64_t)d.dims[0];
+    *cols = d.rank == 2 ? (int64_t)d.dims[1] : 1;
+    return CN_OK;
+}
+
+extern "C" void cn_host_free(void *p) { free(p); }
+
+// Writer for the same subset (write_hdf5, source/util.cu:202-216): one rank-2 float32 dataset, contiguous, in the
+// root group of a version-0 file.  Block order and sizes follow what libhdf5 1.8 writes for such a file: superblock
+// with the root symbol-table entry, root object header, group B-tree node (internal K = 16), local heap with its
+// data segment, dataset object header, symbol-table node (leaf K = 4), data.
+namespace {
+struct H5Out {
+    std::vector<unsigned char> b;
+    void put(uint64_t v, int n) { for (int i = 0; i < n; ++i) b.push_back((unsigned char)(v >> (8 * i))); }
+    void str(const char *s, size_t n) { b.insert(b.end(), s, s + n); }
+    void pad_to(size_t off) { b.resize(off, 0); }
+};
+}  // namespace
+
+extern "C" int cn_hdf5_write_f32(const char *path, const char *dataset, const float *data, int64_t rows, int64_t cols)
+{
+    CN_REQUIRE(path && dataset && data && rows > 0 && cols > 0, CN_ERR_ARG, "cn_hdf5_write_f32: bad argument");
+    const char *name = dataset[0] == '/' ? dataset + 1 : dataset;
+    const size_t nl = strlen(name);
+    CN_REQUIRE(nl > 0 && nl < 64 && !strchr(name, '/'), CN_ERR_ARG, "cn_hdf5_write_f32: dataset name must be one path component shorter than 64 bytes");
+    const uint64_t UNDEF = ~0ull;
+    const uint64_t root_oh = 96, tree = 136, heap = 680, heap_data = 712, heap_size = 88, ds_oh = 800, snod = 928, data_addr = 2048;
+    const uint64_t nbytes = (uint64_t)rows * (uint64_t)cols * 4;
+    H5Out o;
+    // superblock, version 0
+    static const char sig[8] = {(char)0x89, 'H', 'D', 'F', '\r', '\n', 0x1a, '\n'};
+    o.str(sig, 8);
+    o.put(0, 1); o.put(0, 1); o.put(0, 1); o.put(0, 1); o.put(0, 1);   // versions: superblock, free space, root entry, -, shared header
+    o.put(8, 1); o.put(8, 1); o.put(0, 1);                           // offset size, length size, -
+    o.put(4, 2); o.put(16, 2); o.put(0, 4);                          // group leaf K, group internal K, consistency flags
+    o.put(0, 8); o.put(UNDEF, 8); o.put(data_addr + nbytes, 8); o.put(UNDEF, 8);   // base, free-space info, end of file, driver info
+    o.put(0, 8); o.put(root_oh, 8); o.put(1, 4); o.put(0, 4); o.put(tree, 8); o.put(heap, 8);   // root symbol-table entry
+    // root object header: one symbol-table message
+    o.pad_to(root_oh);
+    o.put(1, 1); o.put(0, 1); o.put(1, 2); o.put(1, 4); o.put(24, 4); o.put(0, 4);
+    o.put(0x11, 2); o.put(16, 2); o.put(0, 4); o.put(tree, 8); o.put(heap, 8);
+    // group B-tree node, level 0, one child
+    o.pad_to(tree);
+    o.str("TREE", 4); o.put(0, 1); o.put(0, 1); o.put(1, 2); o.put(UNDEF, 8); o.put(UNDEF, 8);
+    o.put(0, 8); o.put(snod, 8); o.put(8, 8);   // key 0 (empty name), child, key 1 (the dataset's name)
+    // local heap: empty name at 0, the dataset's name at 8, the rest one free block
+    o.pad_to(heap);
+    const uint64_t name_end = 8 + ((nl + 1 + 7) & ~(size_t)7);
+    CN_REQUIRE(name_end + 16 <= heap_size, CN_ERR_ARG, "cn_hdf5_write_f32: dataset name too long");
+    o.str("HEAP", 4); o.put(0, 4); o.put(heap_size, 8); o.put(name_end, 8); o.put(heap_data, 8);
+    o.pad_to(heap_data + 8);
+    o.str(name, nl);
+    o.pad_to(heap_data + name_end);
+    o.put(1, 8); o.put(heap_size - name_end, 8);   // free block: no next block, its size
+    // dataset object header: fill value, datatype (IEEE float32 little endian), dataspace, contiguous layout
+    o.pad_to(ds_oh);
+    o.put(1, 1); o.put(0, 1); o.put(4, 2); o.put(1, 4); o.put(16 + 32 + 32 + 32, 4); o.put(0, 4);
+    o.put(0x5, 2); o.put(8, 2); o.put(1, 4); o.put(2, 1); o.put(2, 1); o.put(2, 1); o.put(1, 1); o.put(0, 4);
+    o.put(0x3, 2); o.put(24, 2); o.put(1, 4);
+    o.put(0x11, 1); o.put(0x20, 1); o.put(31, 1); o.put(0, 1); o.put(4, 4);
+    o.put(0, 2); o.put(32, 2); o.put(23, 1); o.put(8, 1); o.put(0, 1); o.put(23, 1); o.put(127, 4); o.put(0, 4);
+    o.put(0x1, 2); o.put(24, 2); o.put(0, 4);
+    o.put(1, 1); o.put(2, 1); o.put(0, 1); o.put(0, 5); o.put((uint64_t)rows, 8); o.put((uint64_t)cols, 8);
+    o.put(0x8, 2); o.put(24, 2); o.put(1, 4);
+    o.put(3, 1); o.put(1, 1); o.put(data_addr, 8); o.put(nbytes, 8); o.put(0, 6);
+    // symbol-table node: one entry
+    o.pad_to(snod);
+    o.str("SNOD", 4); o.put(1, 1); o.put(0, 1); o.put(1, 2);
+    o.put(8, 8); o.put(ds_oh, 8); o.put(0, 4); o.put(0, 4); o.put(0, 8); o.put(0, 8);
+    o.pad_to(data_addr);
+    FILE *fp = fopen(path, "wb");
+    CN_REQUIRE(fp, CN_ERR_ARG, "cn_hdf5_write_f32: cannot create %s", path);
+    const bool ok = fwrite(o.b.data(), 1, o.b.size(), fp) == o.b.size() && fwrite(data, 1, nbytes, fp) == nbytes;
+    const bool closed = fclose(fp) == 0;
+    CN_REQUIRE(ok && closed, CN_ERR_ARG, "cn_hdf5_write_f32: short write to %s", path);
+    return CN_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Codebook file: dataset "/Default" (126 x 1 float32) of the reference's source/8bit_floats.hdf5, which the
+// reference loads at source/clusterNet.cpp:73, or a raw 504-byte dump of the same table.
 // ------------------------------------------------------------------------------------------------
 extern "C" int cn_codebook_load(const char *path, float *tbl)
 {
     CN_REQUIRE(path && tbl, CN_ERR_ARG, "cn_codebook_load: null argument");
-    static const unsigned char sig[8] = {0x89, 'H', 'D', 'F', '\r', '\n', 0x1a, '\n'};
     FILE *f = fopen(path, "rb");
     CN_REQUIRE(f, CN_ERR_ARG, "cn_codebook_load: cannot open %s", path);
     fseek(f, 0, SEEK_END);
-    long size = ftell(f);
+    const long size = ftell(f);
     const long payload = CN_CODEBOOK_N * 4;
     if (size == payload) {
         fseek(f, 0, SEEK_SET);
+        const size_t got = fread(tbl, 4, CN_CODEBOOK_N, f);
+        fclose(f);
+        CN_REQUIRE(got == CN_CODEBOOK_N, CN_ERR_ARG, "cn_codebook_load: short read from %s", path);
     } else {
-        unsigned char head[8];
-        fseek(f, 0, SEEK_SET);
-        if (size < 8 + payload || fread(head, 1, 8, f) != 8 || memcmp(head, sig, 8) != 0) {
-            fclose(f);
-            cn_set_error("cn_codebook_load: %s is neither an HDF5 container nor a 504-byte table", path);
+        fclose(f);
+        float *data = nullptr;
+        int64_t rows = 0, cols = 0;
+        int st = cn_hdf5_read_f32(path, "Default", &data, &rows, &cols);
+        if (st != CN_OK) {
+            std::string why = cn_last_error();
+            cn_set_error("cn_codebook_load: %s is neither a 504-byte table nor a readable HDF5 file (%s)", path, why.c_str());
             return CN_ERR_ARG;
         }
-        fseek(f, size - payload, SEEK_SET);
+        const bool shape_ok = rows * cols == CN_CODEBOOK_N;
+        if (shape_ok) memcpy(tbl, data, payload);
+        free(data);
+        CN_REQUIRE(shape_ok, CN_ERR_ARG, "cn_codebook_load: /Default of %s has %lld x %lld entries, expected 126", path, (long long)rows, (long long)cols);
     }
-    size_t got = fread(tbl, 4, CN_CODEBOOK_N, f);
-    fclose(f);
-    CN_REQUIRE(got == CN_CODEBOOK_N, CN_ERR_ARG, "cn_codebook_load: short read from %s", path);
     for (int i = 0; i < CN_CODEBOOK_N; ++i) {
         bool ok = tbl[i] > 0.f && tbl[i] < 1.f && (i == 0 || tbl[i] > tbl[i - 1]);
         CN_REQUIRE(ok, CN_ERR_ARG, "cn_codebook_load: entry %d of %s is not an increasing value in (0,1)", i, path);

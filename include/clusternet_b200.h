@@ -56,6 +56,16 @@ int cn_context_device(const cn_context *ctx);
  * 504-byte dump (replaces read_hdf5 of "/Default", source/util.cu:100-131). */
 int cn_codebook_load(const char *path, float *codebook126);
 
+/* Host-only (no GPU needed): reads a dense dataset of an HDF5 file into a malloc'd row-major float array; replaces
+ * read_hdf5 (source/util.cu:100-131, libhdf5) for the files numpy / h5py write: version-0 superblock, contiguous or
+ * compact layout, rank 1 or 2, little-endian 4- or 8-byte float or integer data (converted to float, as
+ * H5T_NATIVE_FLOAT does).  Release the array with cn_host_free. */
+int cn_hdf5_read_f32(const char *path, const char *dataset, float **data_out, int64_t *rows, int64_t *cols);
+void cn_host_free(void *p);
+/* Host-only: writes one rank-2 float32 dataset (row-major `data`) into a new version-0 HDF5 file; replaces write_hdf5
+ * (source/util.cu:202-216).  cn_hdf5_read_f32 reads it back bit for bit. */
+int cn_hdf5_write_f32(const char *path, const char *dataset, const float *data, int64_t rows, int64_t cols);
+
 /* Host-only helper (no GPU needed): derives, from the codebook, the 127 ascending magnitude
  * thresholds (fp32 bit patterns) at which kCompression_8bit's answer changes, and the 128 codes of
  * the levels they separate (254, 0..125, 127).  code(|a|) = level_codes[#{j : thr[j] <= bits(|a|)}].

@@ -95,6 +95,30 @@ int main(int argc, char **argv)
         }
         Matrix *hcv = gpu.to_host(b.CURRENT_BATCH_CV);
         CHECK(hcv->rows == 64 && hcv->data[0] == (float)(800 * cols));
+
+        // ---- the same data set through files: write_hdf5, then BatchAllocator::init(path_X, path_y, ...)
+        if (argc > 3) {
+            // the reference's own fixture and check (tests/util_test.cu:18-20): element i of the h5py file is i
+            Matrix *F = read_hdf5(argv[3]);
+            CHECK(F->rows == 10 && F->cols == 50);
+            for (int64_t i = 0; i < F->size; ++i) CHECK(F->data[i] == (float)i);
+            const std::string px = std::string(argv[2]) + "/X.hdf5", py = std::string(argv[2]) + "/y.hdf5";
+            write_hdf5(px.c_str(), X);
+            write_hdf5(py.c_str(), y);
+            BatchAllocator fb;
+            fb.init(px, py, 0.2f, 128, 64, &gpu, Single_GPU);
+            CHECK(fb.TRAIN_SET_ROWS == 800 && fb.TOTAL_BATCHES == 7);
+            fb.broadcast_batch_to_processes();
+            fb.allocate_next_batch_async();
+            fb.replace_current_batch_with_next();
+            Matrix *hb = gpu.to_host(fb.CURRENT_BATCH), *hy = gpu.to_host(fb.CURRENT_BATCH_Y);
+            CHECK(hb->rows == 128 && hb->cols == cols && hy->rows == 128);
+            for (int64_t e = 0; e < hb->size; ++e) CHECK(hb->data[e] == (float)(128 * cols + e));
+            for (int64_t e = 0; e < hy->size; ++e) CHECK(hy->data[e] == (float)(128 + e));
+            bool threw = false;
+            try { fb.init(std::string("X.bin"), py, 0.2f, 128, 64, &gpu, Single_GPU); } catch (const char *) { threw = true; }
+            CHECK(threw);
+        }
         CHECK(gpu.tock() > 0.0f);
         printf("All tests passed\n");
         return 0;

@@ -29,9 +29,9 @@ def test_codebook_loader_reads_raw_and_hdf5_container(built_lib, codebook, tmp_p
     raw = os.path.join(ROOT, "tests", "golden", "codebook_126.f32")
     assert built_lib.cn_codebook_load(raw.encode(), tbl.ctypes.data) == 0
     assert np.array_equal(tbl, codebook)
-    # a container with the HDF5 signature and the table as its last 504 bytes (the reference file's layout)
+    # an HDF5 file with the table as its 126 x 1 /Default dataset (the reference file's layout)
     fake = tmp_path / "c.hdf5"
-    fake.write_bytes(b"\x89HDF\r\n\x1a\n" + bytes(2136) + codebook.tobytes())
+    clusternet_b200.write_hdf5(fake, codebook.reshape(126, 1))
     tbl2 = np.zeros(126, np.float32)
     assert built_lib.cn_codebook_load(str(fake).encode(), tbl2.ctypes.data) == 0
     assert np.array_equal(tbl2, codebook)
@@ -42,6 +42,66 @@ def test_codebook_loader_reads_raw_and_hdf5_container(built_lib, codebook, tmp_p
     assert b"neither" in built_lib.cn_last_error()
     # the packaged copy is the same table
     assert np.array_equal(clusternet_b200.load_codebook(), codebook)
+
+
+def test_hdf5_reader_on_the_reference_fixture_and_round_trips(built_lib, tmp_path):
+    # the reference's own check (tests/util_test.cu:18-20): element i of numpy_arange_as_h5py.hdf5 is i (float64 on disk)
+    a = clusternet_b200.read_hdf5(os.path.join(ROOT, "tests", "golden", "numpy_arange_as_h5py.hdf5"))
+    assert a.dtype == np.float32 and a.shape == (10, 50)
+    assert np.array_equal(a.ravel(), np.arange(500, dtype=np.float32))
+    rng = np.random.default_rng(5)
+    for shape in [(1, 1), (7, 1), (1, 9), (33, 17), (500, 784)]:
+        x = rng.standard_normal(shape).astype(np.float32)
+        path = tmp_path / f"m{shape[0]}x{shape[1]}.hdf5"
+        clusternet_b200.write_hdf5(path, x)
+        assert np.array_equal(clusternet_b200.read_hdf5(path), x)
+        assert os.path.getsize(path) == 2048 + x.nbytes
+    clusternet_b200.write_hdf5(tmp_path / "named.hdf5", x, "/labels")
+    assert np.array_equal(clusternet_b200.read_hdf5(tmp_path / "named.hdf5", "labels"), x)
+    with pytest.raises(_lib.CnError, match="not found"):
+        clusternet_b200.read_hdf5(tmp_path / "named.hdf5")
+
+
+def test_hdf5_reader_rejects_damaged_files(built_lib, tmp_path):
+    good = open(os.path.join(ROOT, "tests", "golden", "numpy_arange_as_h5py.hdf5"), "rb").read()
+    cases = {
+        "short": good[:64],
+        "nosig": b"\0" * 8 + good[8:],
+        "truncated_data": good[:3000],
+        "truncated_meta": good[:700],
+        "v2_superblock": good[:8] + b"\x02" + good[9:],
+    }
+    for name, blob in cases.items():
+        path = tmp_path / (name + ".hdf5")
+        path.write_bytes(blob)
+        with pytest.raises(_lib.CnError):
+            clusternet_b200.read_hdf5(path)
+    # every single-byte corruption of the metadata is either read consistently or refused, never a crash
+    rng = np.random.default_rng(11)
+    for _ in range(300):
+        blob = bytearray(good)
+        off = int(rng.integers(8, 1400))
+        blob[off] = int(rng.integers(0, 256))
+        path = tmp_path / "fuzz.hdf5"
+        path.write_bytes(bytes(blob))
+        try:
+            out = clusternet_b200.read_hdf5(path)
+            assert out.ndim == 2
+        except _lib.CnError:
+            pass
+    with pytest.raises(_lib.CnError):
+        clusternet_b200.read_hdf5(tmp_path / "missing.hdf5")
+
+
+def test_hdf5_datasets_of_the_reference_when_mounted(built_lib):
+    ref = "/root/reference/tests"
+    if not os.path.exists(ref):
+        pytest.skip("reference tree not mounted")
+    X = clusternet_b200.read_hdf5(os.path.join(ref, "mnist_mini_X.hdf5"))
+    y = clusternet_b200.read_hdf5(os.path.join(ref, "mnist_mini_y.hdf5"))
+    assert X.shape == (500, 784) and y.shape == (500, 1)
+    assert X.min() >= 0.0 and X.max() <= 1.0 and set(np.unique(y)) <= set(range(10))
+    assert list(y[:5, 0]) == [5, 0, 4, 1, 9]      # the first MNIST labels
 
 
 def test_codebook_matches_reference_file_when_mounted(codebook):
