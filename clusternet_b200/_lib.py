@@ -95,6 +95,12 @@ _SIGNATURES = {
     "cn_sub": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "cn_mul": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "cn_scalar_mul": (c_int, [c_void_p, c_void_p, c_float, c_void_p, c_int64, c_void_p]),
+    "cn_div": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "cn_scalar_add": (c_int, [c_void_p, c_void_p, c_float, c_void_p, c_int64, c_void_p]),
+    "cn_abs": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "cn_square": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "cn_max_f32": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "cn_nesterov_update": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int64, c_float, c_int64, c_void_p]),
     "cn_activation_gradient": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p]),
     "cn_rmsprop_update": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_int64, c_void_p]),
     "cn_grad_sync_8bit": (c_int, [c_void_p, c_void_p, c_int64, c_float, c_void_p]),

@@ -19,6 +19,9 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <stdio.h>
+#include <unistd.h>
+
 #include <memory>
 #include <string>
 
@@ -43,6 +46,29 @@ inline void check(int status)
 inline void cuda(cudaError_t e)
 {
     if (e != cudaSuccess) throw cudaGetErrorString(e);
+}
+// The reference's free functions (zeros, to_gpu, add, ...) work on "the current device" without naming an object; here
+// they use the context of the most recently constructed ClusterNet, or one made on first use from CN_CODEBOOK.
+inline std::shared_ptr<cn_context> &current_slot()
+{
+    static std::shared_ptr<cn_context> slot;
+    return slot;
+}
+inline cn_context *current()
+{
+    std::shared_ptr<cn_context> &slot = current_slot();
+    if (!slot) {
+        const char *path = getenv("CN_CODEBOOK");
+        if (!path) throw "clusternet: construct a ClusterNet or set CN_CODEBOOK before calling the free functions";
+        float tbl[126];
+        check(cn_codebook_load(path, tbl));
+        int dev = 0;
+        cuda(cudaGetDevice(&dev));
+        cn_context *c = nullptr;
+        check(cn_context_create(dev, tbl, &c));
+        slot = std::shared_ptr<cn_context>(c, [](cn_context *p) { cn_context_destroy(p); });
+    }
+    return slot.get();
 }
 inline Matrix *header(int64_t rows, int64_t cols)
 {
@@ -116,13 +142,30 @@ public:
         cn_context *c = nullptr;
         cn_detail::check(cn_context_create(MYGPUID, tbl, &c));
         ctx_ = std::shared_ptr<cn_context>(c, [](cn_context *p) { cn_context_destroy(p); });
+        cn_detail::current_slot() = ctx_;
         if (nccl_id128 && MPI_SIZE > 1) cn_detail::check(cn_comm_init_rank(c, nccl_id128, MYRANK, MPI_SIZE));
         seed_ = (uint64_t)seed + 10000ull * MYRANK + 12345ull;
         same_seed_ = 12345ull;
     }
+    // ClusterNet(argc, argv, seed) / ClusterNet(argc, argv) of the reference (source/clusterNet.cpp:11-36), which call
+    // init_MPI: here one process per GPU with RANK / WORLD_SIZE / LOCAL_RANK in the environment (as torchrun or mpirun
+    // wrappers set them), the codebook from CN_CODEBOOK, and the communicator id handed from rank 0 to the others
+    // through the file named by CN_NCCL_ID_FILE (a path all ranks of the node can reach; written once, atomically).
+    ClusterNet(int /*argc*/, char ** /*argv*/, int seed = 1234) : ClusterNet(seed, nullptr, nullptr)
+    {
+        if (MPI_SIZE > 1) init_comm_from_file();
+    }
 
     cn_context *context() const { return ctx_.get(); }
     void shutdown_MPI() { cn_comm_destroy(ctx_.get()); }
+
+    // ---- batch allocator spelled as in the reference's README (gpu.init_batch_allocator(X, y, 128); gpu.m_total_batches;
+    //      gpu.allocate_next_batch_async(); gpu.m_current_batch_X; gpu.replace_current_batch_with_next()); bodies below
+    Matrix *m_current_batch_X = nullptr, *m_current_batch_y = nullptr;
+    int64_t m_total_batches = 0;
+    inline void init_batch_allocator(Matrix *X, Matrix *y, int64_t batch_size);
+    inline void allocate_next_batch_async();
+    inline void replace_current_batch_with_next();
 
     // ---- layout boundary (to_gpu / to_host)
     Matrix *to_gpu(const Matrix *host)
@@ -181,7 +224,7 @@ public:
     // fused form: out = act(A.B + bias), optional maxout
     void dot(Matrix *A, Matrix *B, Matrix *out, const cn_epilogue &epi) { gemm(A, B, out, 0, 0, &epi); }
 
-    Matrix *dotMPI(Matrix *A, Matrix *B) { Matrix *out = empty(A->rows, B->cols_distributed); dotMPI(A, B, out); return out; }
+    Matrix *dotMPI(Matrix *A, Matrix *B) { Matrix *out = empty(A->rows, B->isDistributed == 1 ? B->cols_distributed : B->cols); dotMPI(A, B, out); return out; }
     void dotMPI(Matrix *A, Matrix *B, Matrix *out, int exchange_8bit = 0)
     {
         if (out->isDistributed == 1 && B->isDistributed != 1) {   // full B, sharded out: local product, no exchange
@@ -189,7 +232,14 @@ public:
             cn_detail::check(cn_dot_sharded_out_f32(ctx_.get(), 0, A->rows, A->cols, B->cols, A->data, B->data, out->data, GEMM_MODE, nullptr));
             return;
         }
-        if (B->isDistributed != 1) throw "dotMPI: B must be a distributed (column-sharded) matrix";
+        if (B->isDistributed != 1) {   // full B on every rank: each rank multiplies its own column block of it (:612-619)
+            if (A->cols != B->rows || out->rows != A->rows || out->cols != B->cols) throw "Matrix *size* error";
+            int64_t start = 0, cnt = 0;
+            cn_detail::check(cn_shard_cols(B->cols, MYRANK, MPI_SIZE, &start, &cnt));
+            cn_detail::check(cn_dotmpi_f32(ctx_.get(), A->rows, A->cols, B->cols, A->data, B->data + start * B->rows, out->data, nullptr,
+                                          GEMM_MODE, exchange_8bit, nullptr));
+            return;
+        }
         if (A->cols != B->rows || out->rows != A->rows || out->cols != B->cols_distributed) throw "Matrix *size* error";
         cn_detail::check(cn_dotmpi_f32(ctx_.get(), A->rows, A->cols, B->cols_distributed, A->data, B->data, out->data, nullptr,
                                       GEMM_MODE, exchange_8bit, nullptr));
@@ -289,7 +339,34 @@ public:
 
 private:
     std::shared_ptr<cn_context> ctx_;   // ClusterNet objects are copied by value all over the reference's code
+    std::shared_ptr<class BatchAllocator> batches_;
     uint64_t seed_ = 0, offset_ = 0, same_seed_ = 12345, same_offset_ = 0;
+
+    void init_comm_from_file()
+    {
+        const char *path = getenv("CN_NCCL_ID_FILE");
+        if (!path) throw "ClusterNet: WORLD_SIZE > 1 needs CN_NCCL_ID_FILE (a file path shared by the ranks)";
+        unsigned char id[128];
+        if (MYRANK == 0) {
+            cn_detail::check(cn_comm_get_unique_id(id));
+            const std::string tmp = std::string(path) + ".tmp";
+            FILE *f = fopen(tmp.c_str(), "wb");
+            if (!f || fwrite(id, 1, 128, f) != 128 || fclose(f) != 0) throw "ClusterNet: cannot write CN_NCCL_ID_FILE";
+            if (rename(tmp.c_str(), path) != 0) throw "ClusterNet: cannot publish CN_NCCL_ID_FILE";
+        } else {
+            bool got = false;
+            for (int tries = 0; tries < 1200 && !got; ++tries) {   // up to two minutes
+                FILE *f = fopen(path, "rb");
+                if (f) {
+                    got = fread(id, 1, 128, f) == 128;
+                    fclose(f);
+                }
+                if (!got) usleep(100000);
+            }
+            if (!got) throw "ClusterNet: rank 0 never published CN_NCCL_ID_FILE";
+        }
+        cn_detail::check(cn_comm_init_rank(ctx_.get(), id, MYRANK, MPI_SIZE));
+    }
 
     uint64_t next_offset(int64_t n)
     {
@@ -396,6 +473,195 @@ private:
         publish(X, Y, dx, dy, n);
     }
 };
+
+inline void ClusterNet::init_batch_allocator(Matrix *X, Matrix *y, int64_t batch_size)
+{
+    batches_ = std::make_shared<BatchAllocator>();
+    batches_->init(X, y, 0.0f, batch_size, 0, this, Single_GPU);
+    m_total_batches = batches_->TOTAL_BATCHES;
+    m_current_batch_X = batches_->CURRENT_BATCH;
+    m_current_batch_y = batches_->CURRENT_BATCH_Y;
+}
+inline void ClusterNet::allocate_next_batch_async() { batches_->allocate_next_batch_async(); }
+inline void ClusterNet::replace_current_batch_with_next() { batches_->replace_current_batch_with_next(); }
+
+// ------------------------------------------------------------------------------------------------------------
+// Free functions of source/basicOps.cuh that sit on the dot / codec / training-step path, same names and argument
+// order; device matrices are column-major, everything runs on the NULL stream as in the reference.
+// ------------------------------------------------------------------------------------------------------------
+inline Matrix *fill_matrix(int64_t rows, int64_t cols, float v)
+{
+    Matrix *m = empty(rows, cols);
+    cn_detail::check(cn_fill_f32(cn_detail::current(), m->data, m->size, v, nullptr));
+    return m;
+}
+inline void fill_matrix(Matrix *A, const float v) { cn_detail::check(cn_fill_f32(cn_detail::current(), A->data, A->size, v, nullptr)); }
+inline Matrix *zeros(int64_t rows, int64_t cols) { return fill_matrix(rows, cols, 0.0f); }
+inline Matrix *ones(int64_t rows, int64_t cols) { return fill_matrix(rows, cols, 1.0f); }
+
+// layout boundary (source/basicOps.cu:14-137)
+inline void to_col_major(Matrix *A, Matrix *out) { cn_detail::check(cn_to_col_major(cn_detail::current(), A->data, out->data, A->rows, A->cols, nullptr)); }
+inline Matrix *to_col_major(Matrix *A) { Matrix *out = empty(A->rows, A->cols); to_col_major(A, out); return out; }
+inline Matrix *to_row_major(Matrix *A)
+{
+    Matrix *out = empty(A->rows, A->cols);
+    cn_detail::check(cn_to_row_major(cn_detail::current(), A->data, out->data, A->rows, A->cols, nullptr));
+    return out;
+}
+// transpose of a column-major matrix: its row-major image read as a column-major cols x rows matrix
+inline Matrix *T(Matrix *A)
+{
+    Matrix *out = to_row_major(A);
+    out->rows = A->cols;
+    out->cols = A->rows;
+    return out;
+}
+inline Matrix *to_gpu(Matrix *A, int is_col_major)
+{
+    Matrix *raw = empty(A->rows, A->cols);
+    cn_detail::cuda(cudaMemcpy(raw->data, A->data, A->bytes, cudaMemcpyDefault));
+    if (is_col_major) return raw;
+    Matrix *out = to_col_major(raw);
+    cn_detail::cuda(cudaStreamSynchronize(nullptr));
+    cudaFree(raw->data);
+    free(raw);
+    return out;
+}
+inline Matrix *to_gpu(Matrix *A) { return to_gpu(A, 0); }
+inline Matrix *to_host(Matrix *A, int is_row_major)
+{
+    Matrix *src = is_row_major ? A : to_row_major(A);
+    Matrix *out = empty_cpu(A->rows, A->cols);
+    cn_detail::cuda(cudaMemcpy(out->data, src->data, A->bytes, cudaMemcpyDefault));
+    if (!is_row_major) {
+        cudaFree(src->data);
+        free(src);
+    }
+    return out;
+}
+inline Matrix *to_host(Matrix *A) { return to_host(A, 0); }
+
+// slices and stacks of column-major matrices are plain copies (source/basicOps.cu:153-160,499-523,562-572)
+inline Matrix *slice_cols(Matrix *A, int64_t start, int64_t end)   // columns start..end, both included
+{
+    if (start < 0 || end < start || end >= A->cols) throw "slice_cols: range outside the matrix";
+    Matrix *out = empty(A->rows, end - start + 1);
+    cn_detail::cuda(cudaMemcpyAsync(out->data, A->data + start * A->rows, out->bytes, cudaMemcpyDeviceToDevice, nullptr));
+    return out;
+}
+inline Matrix *slice_rows(Matrix *A, int64_t start, int64_t end)   // rows start..end, both included
+{
+    if (start < 0 || end < start || end >= A->rows) throw "slice_rows: range outside the matrix";
+    Matrix *out = empty(end - start + 1, A->cols);
+    cn_detail::cuda(cudaMemcpy2DAsync(out->data, (size_t)out->rows * 4, A->data + start, (size_t)A->rows * 4, (size_t)out->rows * 4,
+                                      (size_t)A->cols, cudaMemcpyDeviceToDevice, nullptr));
+    return out;
+}
+inline void hStack(Matrix *A, Matrix *B, Matrix *out)
+{
+    if (A->rows != B->rows || out->rows != A->rows || out->cols != A->cols + B->cols) throw "Wrong merge sizes!";
+    cn_detail::cuda(cudaMemcpyAsync(out->data, A->data, A->bytes, cudaMemcpyDeviceToDevice, nullptr));
+    cn_detail::cuda(cudaMemcpyAsync(out->data + A->size, B->data, B->bytes, cudaMemcpyDeviceToDevice, nullptr));
+}
+inline Matrix *hStack(Matrix *A, Matrix *B) { Matrix *out = empty(A->rows, A->cols + B->cols); hStack(A, B, out); return out; }
+// the first matrices_count - 1 blocks hold general_size elements each, the last one the rest (the remainder shard)
+inline void hStackN(Matrix **arrA, int64_t general_size, Matrix *out, int matrices_count)
+{
+    int64_t done = 0;
+    for (int i = 0; i < matrices_count; ++i) {
+        const int64_t n = i + 1 < matrices_count ? general_size : out->size - done;
+        if (n < 0 || n > arrA[i]->size) throw "hStackN: block larger than its source";
+        cn_detail::cuda(cudaMemcpyAsync(out->data + done, arrA[i]->data, (size_t)n * 4, cudaMemcpyDeviceToDevice, nullptr));
+        done += n;
+    }
+}
+
+// elementwise (source/basicOps.cu:574-760)
+#define CN_FACADE_BINARY(name, fn)                                                                                         \
+    inline void name(Matrix *A, Matrix *B, Matrix *out)                                                                   \
+    {                                                                                                                     \
+        if (A->rows != B->rows || A->cols != B->cols || out->rows != A->rows || out->cols != A->cols) throw "Matrix *size* error"; \
+        cn_detail::check(fn(cn_detail::current(), A->data, B->data, out->data, A->size, nullptr));                       \
+    }                                                                                                                     \
+    inline Matrix *name(Matrix *A, Matrix *B) { Matrix *out = empty(A->rows, A->cols); name(A, B, out); return out; }
+CN_FACADE_BINARY(add, cn_add)
+CN_FACADE_BINARY(sub, cn_sub)
+CN_FACADE_BINARY(mul, cn_mul)
+CN_FACADE_BINARY(div, cn_div)
+#undef CN_FACADE_BINARY
+#define CN_FACADE_UNARY(name, call)                                                                  \
+    inline void name(Matrix *A, Matrix *out) { cn_detail::check(call); }                             \
+    inline Matrix *name(Matrix *A) { Matrix *out = empty(A->rows, A->cols); name(A, out); return out; }
+CN_FACADE_UNARY(abs, cn_abs(cn_detail::current(), A->data, out->data, A->size, nullptr))
+CN_FACADE_UNARY(square, cn_square(cn_detail::current(), A->data, out->data, A->size, nullptr))
+CN_FACADE_UNARY(logistic, cn_bias_activation(cn_detail::current(), A->data, nullptr, CN_ACT_LOGISTIC, out->data, A->rows, A->cols, nullptr))
+CN_FACADE_UNARY(rectified_linear, cn_bias_activation(cn_detail::current(), A->data, nullptr, CN_ACT_RELU, out->data, A->rows, A->cols, nullptr))
+CN_FACADE_UNARY(doubleRectifiedLinear, cn_bias_activation(cn_detail::current(), A->data, nullptr, CN_ACT_DOUBLE_RELU, out->data, A->rows, A->cols, nullptr))
+CN_FACADE_UNARY(LinearUnit, cn_bias_activation(cn_detail::current(), A->data, nullptr, CN_ACT_LINEAR, out->data, A->rows, A->cols, nullptr))
+CN_FACADE_UNARY(logisticGrad, cn_activation_gradient(cn_detail::current(), A->data, CN_ACT_LOGISTIC, out->data, A->size, nullptr))
+CN_FACADE_UNARY(rectified_linear_derivative, cn_activation_gradient(cn_detail::current(), A->data, CN_ACT_RELU, out->data, A->size, nullptr))
+CN_FACADE_UNARY(double_rectified_linear_derivative, cn_activation_gradient(cn_detail::current(), A->data, CN_ACT_DOUBLE_RELU, out->data, A->size, nullptr))
+CN_FACADE_UNARY(softmax, cn_softmax(cn_detail::current(), A->data, out->data, A->rows, A->cols, nullptr))
+#undef CN_FACADE_UNARY
+inline void scalarMul(Matrix *A, float a, Matrix *out) { cn_detail::check(cn_scalar_mul(cn_detail::current(), A->data, a, out->data, A->size, nullptr)); }
+inline Matrix *scalarMul(Matrix *A, float a) { Matrix *out = empty(A->rows, A->cols); scalarMul(A, a, out); return out; }
+inline void scalarAdd(Matrix *A, float a, Matrix *out) { cn_detail::check(cn_scalar_add(cn_detail::current(), A->data, a, out->data, A->size, nullptr)); }
+inline Matrix *scalarAdd(Matrix *A, float a) { Matrix *out = empty(A->rows, A->cols); scalarAdd(A, a, out); return out; }
+// max() seeds its reduction with -1.0f and blocks until the value is on the host, as thrust::reduce does
+inline float max(Matrix *A)
+{
+    float *d = nullptr, h = 0.f;
+    cn_detail::cuda(cudaMalloc((void **)&d, 4));
+    cn_detail::check(cn_max_f32(cn_detail::current(), A->data, A->size, d, nullptr));
+    cn_detail::cuda(cudaMemcpy(&h, d, 4, cudaMemcpyDeviceToHost));
+    cudaFree(d);
+    return h;
+}
+// bias row vector v (1 x cols) added to every row of A (source/basicOps.cu:966-974)
+inline void addMatrixVector(Matrix *A, Matrix *v, Matrix *out)
+{
+    if (A->cols != v->cols) throw "Error dimensions do not match";
+    cn_detail::check(cn_bias_activation(cn_detail::current(), A->data, v->data, CN_ACT_LINEAR, out->data, A->rows, A->cols, nullptr));
+}
+inline Matrix *addMatrixVector(Matrix *A, Matrix *v) { Matrix *out = empty(A->rows, A->cols); addMatrixVector(A, v, out); return out; }
+// maximum over groups of maxout_level consecutive columns, plus the winning column index as a float (:1272-1299)
+inline void maxout(Matrix *A, Matrix *out, Matrix *outargmax, int maxout_level)
+{
+    if (maxout_level <= 0 || A->cols % maxout_level != 0) throw "maxout: columns must be a multiple of the maxout level";
+    cn_detail::check(cn_maxout(cn_detail::current(), A->data, out->data, outargmax->data, A->rows, A->cols, maxout_level, nullptr));
+}
+inline Matrix **maxout(Matrix *A, int maxout_level)
+{
+    if (maxout_level <= 0 || A->cols % maxout_level != 0) throw "maxout: columns must be a multiple of the maxout level";
+    Matrix **pair = (Matrix **)malloc(sizeof(Matrix *) * 2);
+    pair[0] = empty(A->rows, A->cols / maxout_level);
+    pair[1] = empty(A->rows, A->cols / maxout_level);
+    maxout(A, pair[0], pair[1], maxout_level);
+    return pair;
+}
+inline void create_t_matrix(Matrix *labels, Matrix *out) { cn_detail::check(cn_create_t_matrix(cn_detail::current(), labels->data, out->data, out->rows, out->cols, nullptr)); }
+inline Matrix *create_t_matrix(Matrix *labels, int max_label) { Matrix *out = empty(labels->rows, max_label); create_t_matrix(labels, out); return out; }
+// optimiser steps with the reference's full argument lists (:1185-1197); RMS_multiplier etc. unused by a kernel stay unused
+inline void RMSprop_with_weight_update(Matrix *RMS, Matrix *grad, Matrix *w, Matrix * /*m*/, float RMS_multiplier, float learning_rate,
+                                       int /*batch_size*/, float /*momentum*/)
+{
+    cn_detail::check(cn_rmsprop_update(cn_detail::current(), RMS->data, grad->data, w->data, RMS_multiplier, learning_rate, RMS->size, nullptr));
+}
+inline void Nesterov_weight_update(Matrix *RMS, Matrix *grad, Matrix *w, Matrix *m, float /*RMS_multiplier*/, float learning_rate, int batch_size,
+                                   float momentum)
+{
+    cn_detail::check(cn_nesterov_update(cn_detail::current(), grad->data, w->data, m->data, learning_rate, batch_size, momentum, RMS->size, nullptr));
+}
+// codec with an explicit table argument, as ::compression_8bit / ::decompression_8bit take it (:1163-1176); the table the
+// context was created with is the one used, tbl_flt is accepted for source compatibility
+inline void compression_8bit(Matrix * /*tbl_flt*/, Matrix *A, float precision, Matrix *out)
+{
+    cn_detail::check(cn_compress_8bit(cn_detail::current(), A->data, precision, A->size, out->char_data, nullptr));
+}
+inline void decompression_8bit(Matrix * /*tbl_flt*/, Matrix *A, float precision, Matrix *out)
+{
+    cn_detail::check(cn_decompress_8bit(cn_detail::current(), A->char_data, precision, A->size, out->data, nullptr));
+}
 
 
 // ------------------------------------------------------------------------------------------------------------

@@ -314,8 +314,12 @@ cn_decompress_kernel(const uint8_t *__restrict__ codes, float precision_arg, con
     for (int64_t i = (nvec << 2) + (int64_t)blockIdx.x * blockDim.x + tid; i < n; i += stride) out[i] = lut[codes[i]];
 }
 
-// absmax: one pass; every CTA leaves its partial maximum in the scratch array, the CTA that draws the
-// last ticket folds the partials, writes the result and resets the ticket for the next launch.
+// absmax (ABS) or plain max: one pass; every CTA leaves its partial maximum in the scratch array, the CTA that draws
+// the last ticket folds the partials, writes the result and resets the ticket for the next launch.
+template <bool ABS>
+__device__ __forceinline__ float absmax_term(float x) { return ABS ? fabsf(x) : x; }
+
+template <bool ABS>
 __global__ void __launch_bounds__(ABSMAX_THREADS)
 cn_absmax_kernel(const float *__restrict__ A, int64_t n, float *__restrict__ out, float *__restrict__ partials,
                  unsigned int *__restrict__ ticket, int vector_ok)
@@ -330,10 +334,10 @@ cn_absmax_kernel(const float *__restrict__ A, int64_t n, float *__restrict__ out
     int64_t v = (int64_t)blockIdx.x * blockDim.x + tid;
     for (; v + 3 * stride < nvec; v += 4 * stride) {
         float4 q0 = __ldcs(A4 + v), q1 = __ldcs(A4 + v + stride), q2 = __ldcs(A4 + v + 2 * stride), q3 = __ldcs(A4 + v + 3 * stride);
-        m = fmaxf(m, fmaxf(fmaxf(fabsf(q0.x), fabsf(q0.y)), fmaxf(fabsf(q0.z), fabsf(q0.w))));
-        m = fmaxf(m, fmaxf(fmaxf(fabsf(q1.x), fabsf(q1.y)), fmaxf(fabsf(q1.z), fabsf(q1.w))));
-        m = fmaxf(m, fmaxf(fmaxf(fabsf(q2.x), fabsf(q2.y)), fmaxf(fabsf(q2.z), fabsf(q2.w))));
-        m = fmaxf(m, fmaxf(fmaxf(fabsf(q3.x), fabsf(q3.y)), fmaxf(fabsf(q3.z), fabsf(q3.w))));
+        m = fmaxf(m, fmaxf(fmaxf(absmax_term<ABS>(q0.x), absmax_term<ABS>(q0.y)), fmaxf(absmax_term<ABS>(q0.z), absmax_term<ABS>(q0.w))));
+        m = fmaxf(m, fmaxf(fmaxf(absmax_term<ABS>(q1.x), absmax_term<ABS>(q1.y)), fmaxf(absmax_term<ABS>(q1.z), absmax_term<ABS>(q1.w))));
+        m = fmaxf(m, fmaxf(fmaxf(absmax_term<ABS>(q2.x), absmax_term<ABS>(q2.y)), fmaxf(absmax_term<ABS>(q2.z), absmax_term<ABS>(q2.w))));
+        m = fmaxf(m, fmaxf(fmaxf(absmax_term<ABS>(q3.x), absmax_term<ABS>(q3.y)), fmaxf(absmax_term<ABS>(q3.z), absmax_term<ABS>(q3.w))));
     }
     if (v < nvec) {   // last, partial group: all its loads are issued before any is used
         float4 q[3];
@@ -341,9 +345,9 @@ cn_absmax_kernel(const float *__restrict__ A, int64_t n, float *__restrict__ out
         for (int u = 0; u < 3; ++u) q[u] = (v + u * stride < nvec) ? __ldcs(A4 + v + u * stride) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int u = 0; u < 3; ++u)
-            if (v + u * stride < nvec) m = fmaxf(m, fmaxf(fmaxf(fabsf(q[u].x), fabsf(q[u].y)), fmaxf(fabsf(q[u].z), fabsf(q[u].w))));
+            if (v + u * stride < nvec) m = fmaxf(m, fmaxf(fmaxf(absmax_term<ABS>(q[u].x), absmax_term<ABS>(q[u].y)), fmaxf(absmax_term<ABS>(q[u].z), absmax_term<ABS>(q[u].w))));
     }
-    for (int64_t i = (nvec << 2) + (int64_t)blockIdx.x * blockDim.x + tid; i < n; i += stride) m = fmaxf(m, fabsf(A[i]));
+    for (int64_t i = (nvec << 2) + (int64_t)blockIdx.x * blockDim.x + tid; i < n; i += stride) m = fmaxf(m, absmax_term<ABS>(A[i]));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     if ((tid & 31) == 0) warp_max[tid >> 5] = m;
@@ -456,7 +460,21 @@ extern "C" int cn_absmax_f32(cn_context *ctx, const float *d_A, int64_t n, float
     // four), eight per SM stream best on large ones (1 GiB: 6737 GB/s vs 6332)
     int grid = codec_grid(ctx, n, ABSMAX_THREADS, 16, n < (1LL << 27) ? 2 : 8);
     if (grid > CN_MAX_PARTIALS) grid = CN_MAX_PARTIALS;
-    cn_absmax_kernel<<<grid, ABSMAX_THREADS, 0, cn_stream(stream)>>>(d_A, n, d_out, ctx->d_partials, ctx->d_ticket, vector_ok);
+    cn_absmax_kernel<true><<<grid, ABSMAX_THREADS, 0, cn_stream(stream)>>>(d_A, n, d_out, ctx->d_partials, ctx->d_ticket, vector_ok);
+    CN_CUDA(cudaGetLastError());
+    cn_count_launch();
+    return CN_OK;
+}
+
+// max() of the reference (source/basicOps.cu:1076-1081): thrust::reduce seeded with -1.0f, so the result is never below -1
+extern "C" int cn_max_f32(cn_context *ctx, const float *d_A, int64_t n, float *d_out, void *stream)
+{
+    CN_REQUIRE(ctx && d_out, CN_ERR_ARG, "cn_max_f32: null argument");
+    CN_REQUIRE(n >= 0 && (n == 0 || d_A), CN_ERR_ARG, "cn_max_f32: bad input");
+    int vector_ok = ((uintptr_t)d_A % 16 == 0);
+    int grid = codec_grid(ctx, n, ABSMAX_THREADS, 16, n < (1LL << 27) ? 2 : 8);
+    if (grid > CN_MAX_PARTIALS) grid = CN_MAX_PARTIALS;
+    cn_absmax_kernel<false><<<grid, ABSMAX_THREADS, 0, cn_stream(stream)>>>(d_A, n, d_out, ctx->d_partials, ctx->d_ticket, vector_ok);
     CN_CUDA(cudaGetLastError());
     cn_count_launch();
     return CN_OK;
@@ -525,7 +543,7 @@ extern "C" int cn_absmax_f32_noalloc(const float *d_A, int64_t n, float *d_out, 
     if (need < 1) need = 1;
     const int grid = (int)(need < cap ? need : cap);
     const int vector_ok = ((uintptr_t)d_A % 16 == 0);
-    cn_absmax_kernel<<<grid, ABSMAX_THREADS, 0, cn_stream(stream)>>>(d_A, n, d_out, reinterpret_cast<float *>(nd.scratch),
+    cn_absmax_kernel<true><<<grid, ABSMAX_THREADS, 0, cn_stream(stream)>>>(d_A, n, d_out, reinterpret_cast<float *>(nd.scratch),
                                                                      nd.scratch + CN_ABSMAX_NOALLOC_MAX_CTAS, vector_ok);
     CN_CUDA(cudaGetLastError());
     cn_count_launch();

@@ -35,7 +35,8 @@ __global__ void cn_t_matrix_kernel(const float *__restrict__ labels, float *__re
     }
 }
 
-enum { EW_ADD = 0, EW_SUB = 1, EW_MUL = 2, EW_SCALAR_MUL = 3, EW_GRAD_RELU = 4, EW_GRAD_LOGISTIC = 5, EW_GRAD_DOUBLE_RELU = 6 };
+enum { EW_ADD = 0, EW_SUB = 1, EW_MUL = 2, EW_SCALAR_MUL = 3, EW_GRAD_RELU = 4, EW_GRAD_LOGISTIC = 5, EW_GRAD_DOUBLE_RELU = 6,
+       EW_ABS = 7, EW_DIV = 8, EW_SCALAR_ADD = 9, EW_SQUARE = 10 };
 
 template <int OP>
 __global__ void cn_ew_kernel(const float *__restrict__ A, const float *__restrict__ B, float s, float *__restrict__ out, int64_t n)
@@ -50,13 +51,29 @@ __global__ void cn_ew_kernel(const float *__restrict__ A, const float *__restric
         else if (OP == EW_SCALAR_MUL) r = a * s;
         else if (OP == EW_GRAD_RELU) r = a > 0.0f ? 1.0f : 0.0f;
         else if (OP == EW_GRAD_LOGISTIC) r = a * (1.0f - a);
+        else if (OP == EW_ABS) r = fabsf(a);
+        else if (OP == EW_DIV) r = fdividef(a, B[i]);   // kDiv divides with fdividef (source/clusterKernels.cu:341-348)
+        else if (OP == EW_SCALAR_ADD) r = a + s;
+        else if (OP == EW_SQUARE) r = powf(a, 2.0f);    // kSquare (source/clusterKernels.cu:420-427)
         else r = (a > 0.0f && a < 1.0f) ? 1.0f : 0.0f;
         out[i] = r;
     }
 }
 
+// kNesterov_weight_update (source/clusterKernels.cu:1064-1077): g = lr * grad / batch_size; m = momentum * m - g; w -= g
+__global__ void cn_nesterov_kernel(const float *__restrict__ grad, float *__restrict__ w, float *__restrict__ m, float lr, float batch_size,
+                                   float momentum, int64_t n)
+{
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float g = lr * fdividef(grad[i], batch_size);
+        m[i] = (momentum * m[i]) - g;
+        w[i] -= g;
+    }
+}
+
 // kRMSprop_with_weight_update: RMS = m*RMS + (1-m)*g^2 ; w -= lr * g / (sqrt(RMS) + 1e-8).  The reference divides with
-// fdividef and squares with powf(g, 2); both are reproduced (powf(x, 2.0f) equals x*x in CUDA's implementation).
+// fdividef and squares with powf(g, 2.0f); both are reproduced as written.
 __global__ void cn_rmsprop_kernel(float *__restrict__ RMS, const float *__restrict__ grad, float *__restrict__ w, float rms_mult, float lr, int64_t n)
 {
     const float rec = 1.0f - rms_mult;
@@ -140,6 +157,22 @@ extern "C" int cn_add(cn_context *ctx, const float *a, const float *b, float *ou
 extern "C" int cn_sub(cn_context *ctx, const float *a, const float *b, float *out, int64_t n, void *stream) { return ew_launch<EW_SUB>(ctx, a, b, 0.f, out, n, stream, true); }
 extern "C" int cn_mul(cn_context *ctx, const float *a, const float *b, float *out, int64_t n, void *stream) { return ew_launch<EW_MUL>(ctx, a, b, 0.f, out, n, stream, true); }
 extern "C" int cn_scalar_mul(cn_context *ctx, const float *a, float s, float *out, int64_t n, void *stream) { return ew_launch<EW_SCALAR_MUL>(ctx, a, nullptr, s, out, n, stream, false); }
+
+extern "C" int cn_div(cn_context *ctx, const float *a, const float *b, float *out, int64_t n, void *stream) { return ew_launch<EW_DIV>(ctx, a, b, 0.f, out, n, stream, true); }
+extern "C" int cn_scalar_add(cn_context *ctx, const float *a, float s, float *out, int64_t n, void *stream) { return ew_launch<EW_SCALAR_ADD>(ctx, a, nullptr, s, out, n, stream, false); }
+extern "C" int cn_abs(cn_context *ctx, const float *a, float *out, int64_t n, void *stream) { return ew_launch<EW_ABS>(ctx, a, nullptr, 0.f, out, n, stream, false); }
+extern "C" int cn_square(cn_context *ctx, const float *a, float *out, int64_t n, void *stream) { return ew_launch<EW_SQUARE>(ctx, a, nullptr, 0.f, out, n, stream, false); }
+
+extern "C" int cn_nesterov_update(cn_context *ctx, const float *d_grad, float *d_w, float *d_m, float learning_rate, int64_t batch_size,
+                                  float momentum, int64_t n, void *stream)
+{
+    CN_REQUIRE(ctx && n >= 0 && batch_size > 0 && (n == 0 || (d_grad && d_w && d_m)), CN_ERR_ARG, "cn_nesterov_update: bad argument");
+    if (n == 0) return CN_OK;
+    cn_nesterov_kernel<<<ew_grid(ctx, n), 256, 0, cn_stream(stream)>>>(d_grad, d_w, d_m, learning_rate, (float)batch_size, momentum, n);
+    CN_CUDA(cudaGetLastError());
+    cn_count_launch();
+    return CN_OK;
+}
 
 extern "C" int cn_activation_gradient(cn_context *ctx, const float *d_activation, int activation, float *d_out, int64_t n, void *stream)
 {

@@ -290,6 +290,16 @@ int cn_add(cn_context *ctx, const float *d_a, const float *d_b, float *d_out, in
 int cn_sub(cn_context *ctx, const float *d_a, const float *d_b, float *d_out, int64_t n, void *stream);
 int cn_mul(cn_context *ctx, const float *d_a, const float *d_b, float *d_out, int64_t n, void *stream);
 int cn_scalar_mul(cn_context *ctx, const float *d_a, float s, float *d_out, int64_t n, void *stream);
+/* div (kDiv :341-348, fdividef), scalarAdd (kScalarAdd), abs (kAbs :429-436), square (kSquare :420-427, powf(x,2)). */
+int cn_div(cn_context *ctx, const float *d_a, const float *d_b, float *d_out, int64_t n, void *stream);
+int cn_scalar_add(cn_context *ctx, const float *d_a, float s, float *d_out, int64_t n, void *stream);
+int cn_abs(cn_context *ctx, const float *d_a, float *d_out, int64_t n, void *stream);
+int cn_square(cn_context *ctx, const float *d_a, float *d_out, int64_t n, void *stream);
+/* max (source/basicOps.cu:1076-1081): thrust::reduce with maximum, seeded with -1.0f, into *d_out (device). */
+int cn_max_f32(cn_context *ctx, const float *d_A, int64_t n, float *d_out, void *stream);
+/* Nesterov_weight_update (kNesterov_weight_update, :1064-1077): g = lr grad / batch_size; m = momentum m - g; w -= g. */
+int cn_nesterov_update(cn_context *ctx, const float *d_grad, float *d_w, float *d_m, float learning_rate, int64_t batch_size,
+                       float momentum, int64_t n, void *stream);
 /* derivative of the unit from its activation (Layer::activation_gradient, source/Layer.cpp:180-200): ReLU x>0?1:0
  * (kRectifiedLinear_Derivative :813-821), logistic a(1-a), double ReLU 0<a<1?1:0. */
 int cn_activation_gradient(cn_context *ctx, const float *d_activation, int activation, float *d_out, int64_t n, void *stream);

@@ -180,6 +180,19 @@ def rmsprop_update(rms, grad, w, rms_mult, lr):
     return r, (w - np.float32(lr) * (grad / (np.sqrt(r) + np.float32(1.0e-08)))).astype(np.float32)
 
 
+def nesterov_update(grad, w, m, lr, batch_size, momentum):
+    """kNesterov_weight_update (source/clusterKernels.cu:1064-1077) in fp32: returns the new (w, m)."""
+    grad, w, m = grad.astype(np.float32), w.astype(np.float32), m.astype(np.float32)
+    g = (np.float32(lr) * (grad / np.float32(batch_size))).astype(np.float32)
+    return (w - g).astype(np.float32), (np.float32(momentum) * m - g).astype(np.float32)
+
+
+def max_seeded(a):
+    """max (source/basicOps.cu:1076-1081): a maximum reduction seeded with -1.0f."""
+    a = np.asarray(a, np.float32).ravel()
+    return np.float32(max(np.float32(-1.0), a.max())) if a.size else np.float32(-1.0)
+
+
 def mlp_step_gradients(X, y, weights, dropout=0.0):
     """Forward / backward of the reference's Layer chain (source/Layer.cpp:250-261,314-339) for ReLU hidden layers and a
     softmax output, biases zero, dropout rate 0 (activations pass unchanged): returns the softmax output and the weight

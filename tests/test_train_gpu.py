@@ -51,6 +51,45 @@ def test_elementwise_and_activation_gradients(ctx):
     assert ctx.lib.cn_activation_gradient(ctx.h, da.data_ptr(), _lib.ACT_LINEAR, out.data_ptr(), a.size, sp) == _lib.CN_ERR_ARG
 
 
+def test_abs_div_square_scalar_add_and_seeded_max(ctx):
+    rng = np.random.default_rng(7)
+    a = rng.standard_normal(70001).astype(np.float32)
+    b = (rng.standard_normal(70001).astype(np.float32) + np.float32(3.0))
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    out = torch.empty_like(da)
+    sp = ctx.stream_ptr()
+    cn.check(ctx.lib.cn_abs(ctx.h, da.data_ptr(), out.data_ptr(), a.size, sp))
+    assert np.array_equal(out.cpu().numpy(), np.abs(a))
+    cn.check(ctx.lib.cn_square(ctx.h, da.data_ptr(), out.data_ptr(), a.size, sp))
+    sq = (a.astype(np.float64) ** 2)              # the reference squares with powf(x, 2.0f): within 2 ulp of the product
+    assert np.all(np.abs(out.cpu().numpy() - sq) <= 2 * np.spacing((a * a).astype(np.float32)))
+    cn.check(ctx.lib.cn_scalar_add(ctx.h, da.data_ptr(), 0.1748345, out.data_ptr(), a.size, sp))
+    assert np.array_equal(out.cpu().numpy(), a + np.float32(0.1748345))
+    cn.check(ctx.lib.cn_div(ctx.h, da.data_ptr(), db.data_ptr(), out.data_ptr(), a.size, sp))
+    want = a / b                                  # the reference divides with fdividef: 2 ulp
+    assert np.abs(out.cpu().numpy() - want).max() <= 3e-7 * np.abs(want).max() + 1e-30
+    assert np.all(np.abs(out.cpu().numpy() - want) <= 4 * np.spacing(np.abs(want)))
+    res = torch.full((1,), 99.0, device="cuda")
+    for arr in (a, -np.abs(a) - np.float32(2.0), a[:1], a[:33], np.full(5000, -0.25, np.float32)):
+        d = torch.from_numpy(np.ascontiguousarray(arr)).cuda()
+        cn.check(ctx.lib.cn_max_f32(ctx.h, d.data_ptr(), arr.size, res.data_ptr(), sp))
+        assert res.item() == oracle.max_seeded(arr)
+    cn.check(ctx.lib.cn_max_f32(ctx.h, None, 0, res.data_ptr(), sp))
+    assert res.item() == -1.0
+
+
+def test_nesterov_update(ctx):
+    rng = np.random.default_rng(8)
+    n = 30011
+    g, w, m = (rng.standard_normal(n).astype(np.float32) for _ in range(3))
+    dg, dw, dm = (torch.from_numpy(x.copy()).cuda() for x in (g, w, m))
+    cn.check(ctx.lib.cn_nesterov_update(ctx.h, dg.data_ptr(), dw.data_ptr(), dm.data_ptr(), 0.003, 128, 0.9, n, ctx.stream_ptr()))
+    w_want, m_want = oracle.nesterov_update(g, w, m, 0.003, 128, 0.9)
+    assert np.abs(dw.cpu().numpy() - w_want).max() <= 1e-6
+    assert np.abs(dm.cpu().numpy() - m_want).max() <= 1e-6
+    assert ctx.lib.cn_nesterov_update(ctx.h, dg.data_ptr(), dw.data_ptr(), dm.data_ptr(), 0.003, 0, 0.9, n, ctx.stream_ptr()) == _lib.CN_ERR_ARG
+
+
 def test_rmsprop_update(ctx):
     rng = np.random.default_rng(2)
     n = 50001
