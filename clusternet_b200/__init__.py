@@ -6,6 +6,6 @@ memory in torch tensors and passes raw pointers down.
 """
 from . import _lib
 from ._lib import CnError, Epilogue, load, check
-from .api import Context, codebook_path, load_codebook, read_hdf5, write_hdf5
+from .api import Context, codebook_path, load_codebook, read_hdf5, read_sparse_hdf5, write_hdf5
 
-__all__ = ["Context", "CnError", "Epilogue", "load", "check", "codebook_path", "load_codebook", "read_hdf5", "write_hdf5"]
+__all__ = ["Context", "CnError", "Epilogue", "load", "check", "codebook_path", "load_codebook", "read_hdf5", "read_sparse_hdf5", "write_hdf5"]

@@ -29,17 +29,32 @@ def load_codebook(path=None):
     return tbl
 
 
-def read_hdf5(path, dataset="/Default"):
-    """Dense dataset of an HDF5 file as a float32 (rows, cols) array; read_hdf5 of the reference (source/util.cu:100-131)."""
+def read_hdf5(path, dataset="/Default", dtype=np.float32):
+    """Dense dataset of an HDF5 file as a (rows, cols) array, float32 (read_hdf5 of the reference,
+    source/util.cu:100-131) or int32 (the index datasets of its CSR files)."""
     import ctypes
     lib = load()
+    dtype = np.dtype(dtype)
+    if dtype not in (np.dtype(np.float32), np.dtype(np.int32)):
+        raise TypeError("read_hdf5 returns float32 or int32")
+    fn, ctype = (lib.cn_hdf5_read_f32, ctypes.c_float) if dtype == np.float32 else (lib.cn_hdf5_read_i32, ctypes.c_int32)
     p, r, c = ctypes.c_void_p(), ctypes.c_int64(), ctypes.c_int64()
-    check(lib.cn_hdf5_read_f32(str(path).encode(), dataset.encode(), ctypes.byref(p), ctypes.byref(r), ctypes.byref(c)))
+    check(fn(str(path).encode(), dataset.encode(), ctypes.byref(p), ctypes.byref(r), ctypes.byref(c)))
     try:
-        flat = np.ctypeslib.as_array(ctypes.cast(p, ctypes.POINTER(ctypes.c_float)), shape=(r.value * c.value,))
+        flat = np.ctypeslib.as_array(ctypes.cast(p, ctypes.POINTER(ctype)), shape=(r.value * c.value,))
         return flat.reshape(r.value, c.value).copy()
     finally:
         lib.cn_host_free(p)
+
+
+def read_sparse_hdf5(path):
+    """CSR matrix written by scipy + h5py (read_sparse_hdf5 of the reference, source/util.cu:133-198):
+    returns (data float32, indices int32, indptr int32, (rows, cols))."""
+    data = read_hdf5(path, "/data").ravel()
+    indices = read_hdf5(path, "/indices", np.int32).ravel()
+    indptr = read_hdf5(path, "/indptr", np.int32).ravel()
+    shape = read_hdf5(path, "/shape", np.int32).ravel()
+    return data, indices, indptr, (int(shape[0]), int(shape[1]))
 
 
 def write_hdf5(path, a, dataset="/Default"):

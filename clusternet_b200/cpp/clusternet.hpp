@@ -36,6 +36,13 @@ typedef struct Matrix {
     int isDistributed;
     int64_t cols_distributed;
     unsigned char *char_data;
+    // CSR fields of the reference's descriptor (source/basicOps.cuh:25-42); only read_sparse_hdf5 fills them here, every
+    // compute function takes dense matrices (isSparse == 0)
+    int isSparse;
+    size_t ptr_bytes;
+    size_t idx_bytes;
+    int *ptr_rows;
+    int *idx_cols;
 } Matrix;
 
 namespace cn_detail {
@@ -120,6 +127,35 @@ inline Matrix *read_hdf5(const char *filepath, const char *tag)
     return out;
 }
 inline Matrix *read_hdf5(const char *filepath) { return read_hdf5(filepath, "/Default"); }
+// read_sparse_hdf5 (source/util.cu:133-198): CSR matrix from /data, /indices, /indptr, /shape into pinned host memory
+inline Matrix *read_sparse_hdf5(const char *filepath)
+{
+    float *data = nullptr;
+    int32_t *idx = nullptr, *ptr = nullptr, *shape = nullptr;
+    int64_t n = 0, nidx = 0, nptr = 0, nshape = 0, one = 0;
+    cn_detail::check(cn_hdf5_read_f32(filepath, "/data", &data, &n, &one));
+    cn_detail::check(cn_hdf5_read_i32(filepath, "/indices", &idx, &nidx, &one));
+    cn_detail::check(cn_hdf5_read_i32(filepath, "/indptr", &ptr, &nptr, &one));
+    cn_detail::check(cn_hdf5_read_i32(filepath, "/shape", &shape, &nshape, &one));
+    if (nshape != 2 || nidx != n || nptr != shape[0] + 1) throw "read_sparse_hdf5: inconsistent CSR datasets";
+    Matrix *out = cn_detail::header(shape[0], shape[1]);
+    out->isSparse = 1;
+    out->size = n;
+    out->bytes = (size_t)n * sizeof(float);
+    out->idx_bytes = (size_t)nidx * sizeof(int);
+    out->ptr_bytes = (size_t)nptr * sizeof(int);
+    cn_detail::cuda(cudaHostAlloc((void **)&out->data, out->bytes ? out->bytes : 4, cudaHostAllocPortable));
+    cn_detail::cuda(cudaHostAlloc((void **)&out->idx_cols, out->idx_bytes ? out->idx_bytes : 4, cudaHostAllocPortable));
+    cn_detail::cuda(cudaHostAlloc((void **)&out->ptr_rows, out->ptr_bytes, cudaHostAllocPortable));
+    memcpy(out->data, data, out->bytes);
+    memcpy(out->idx_cols, idx, out->idx_bytes);
+    memcpy(out->ptr_rows, ptr, out->ptr_bytes);
+    cn_host_free(data);
+    cn_host_free(idx);
+    cn_host_free(ptr);
+    cn_host_free(shape);
+    return out;
+}
 inline void write_hdf5(const char *filepath, Matrix *A) { cn_detail::check(cn_hdf5_write_f32(filepath, "/Default", A->data, A->rows, A->cols)); }
 
 class ClusterNet {

@@ -141,26 +141,25 @@ uint64_t h5_find(const H5 &f, uint64_t tree, uint64_t heap_data, const char *nam
 }
 }  // namespace
 
-extern "C" int cn_hdf5_read_f32(const char *path, const char *dataset, float **data_out, int64_t *rows, int64_t *cols)
+namespace {
+// Loads the file, finds the dataset and checks that its data lie inside the file; n = number of elements.
+int h5_locate(const char *path, const char *dataset, H5 &f, H5Dataset &d, uint64_t &n)
 {
-    CN_REQUIRE(path && dataset && data_out && rows && cols, CN_ERR_ARG, "cn_hdf5_read_f32: null argument");
-    *data_out = nullptr;
-    H5 f;
     {
         FILE *fp = fopen(path, "rb");
-        CN_REQUIRE(fp, CN_ERR_ARG, "cn_hdf5_read_f32: cannot open %s", path);
+        CN_REQUIRE(fp, CN_ERR_ARG, "cn_hdf5_read: cannot open %s", path);
         fseek(fp, 0, SEEK_END);
         const long sz = ftell(fp);
         fseek(fp, 0, SEEK_SET);
         if (sz > 0) f.b.resize((size_t)sz);
         const size_t got = sz > 0 ? fread(f.b.data(), 1, (size_t)sz, fp) : 0;
         fclose(fp);
-        CN_REQUIRE(sz >= 96 && got == (size_t)sz, CN_ERR_ARG, "cn_hdf5_read_f32: %s is too short", path);
+        CN_REQUIRE(sz >= 96 && got == (size_t)sz, CN_ERR_ARG, "cn_hdf5_read: %s is too short", path);
     }
     static const unsigned char sig[8] = {0x89, 'H', 'D', 'F', '\r', '\n', 0x1a, '\n'};
-    CN_REQUIRE(memcmp(f.b.data(), sig, 8) == 0, CN_ERR_ARG, "cn_hdf5_read_f32: %s has no HDF5 signature", path);
+    CN_REQUIRE(memcmp(f.b.data(), sig, 8) == 0, CN_ERR_ARG, "cn_hdf5_read: %s has no HDF5 signature", path);
     CN_REQUIRE(f.b[8] == 0 && f.b[13] == 8 && f.b[14] == 8, CN_ERR_UNSUPPORTED,
-               "cn_hdf5_read_f32: %s: only version-0 superblocks with 8-byte offsets are read", path);
+               "cn_hdf5_read: %s: only version-0 superblocks with 8-byte offsets are read", path);
     // root symbol-table entry at byte 56: object header address, cache type, scratch = B-tree and heap addresses
     uint64_t tree = 0, heap = 0;
     if (f.u(72, 4) == 1) {
@@ -168,7 +167,7 @@ extern "C" int cn_hdf5_read_f32(const char *path, const char *dataset, float **d
         heap = f.u(88, 8);
     } else {
         const uint64_t oh = f.u(64, 8);   // symbol-table message (0x11) of the root object header
-        CN_REQUIRE(f.ok(oh, 16) && f.b[oh] == 1, CN_ERR_UNSUPPORTED, "cn_hdf5_read_f32: %s: unsupported root object header", path);
+        CN_REQUIRE(f.ok(oh, 16) && f.b[oh] == 1, CN_ERR_UNSUPPORTED, "cn_hdf5_read: %s: unsupported root object header", path);
         uint64_t p = oh + 16, end = p + f.u(oh + 8, 4);
         int left = (int)f.u(oh + 2, 2);
         while (left-- > 0 && f.ok(p, 8)) {
@@ -180,41 +179,71 @@ extern "C" int cn_hdf5_read_f32(const char *path, const char *dataset, float **d
         }
     }
     CN_REQUIRE(tree && heap && f.ok(heap, 32) && memcmp(&f.b[heap], "HEAP", 4) == 0, CN_ERR_UNSUPPORTED,
-               "cn_hdf5_read_f32: %s: root group has no symbol table", path);
+               "cn_hdf5_read: %s: root group has no symbol table", path);
     const uint64_t heap_data = f.u(heap + 24, 8);
     const char *name = dataset[0] == '/' ? dataset + 1 : dataset;
     const uint64_t oh = h5_find(f, tree, heap_data, name, 0);
-    CN_REQUIRE(oh && f.ok(oh, 16) && f.b[oh] == 1, CN_ERR_ARG, "cn_hdf5_read_f32: dataset '%s' not found in %s", dataset, path);
-    H5Dataset d;
+    CN_REQUIRE(oh && f.ok(oh, 16) && f.b[oh] == 1, CN_ERR_ARG, "cn_hdf5_read: dataset '%s' not found in %s", dataset, path);
     int left = (int)f.u(oh + 2, 2);
     const uint64_t hsize = f.u(oh + 8, 4);
     CN_REQUIRE(f.ok(oh + 16, hsize) && h5_parse_messages(f, oh + 16, oh + 16 + hsize, left, d, 0) && d.have_space && d.have_type && d.have_layout,
-               CN_ERR_UNSUPPORTED, "cn_hdf5_read_f32: dataset '%s' of %s uses a feature this reader does not have (chunking, big endian, rank > 2)", dataset, path);
-    CN_REQUIRE(d.dims[0] < (1ull << 31) && d.dims[1] < (1ull << 31), CN_ERR_UNSUPPORTED, "cn_hdf5_read_f32: dimension of 2^31 or more");
-    const uint64_t n = d.dims[0] * (d.rank == 2 ? d.dims[1] : 1);
+               CN_ERR_UNSUPPORTED, "cn_hdf5_read: dataset '%s' of %s uses a feature this reader does not have (chunking, big endian, rank > 2)", dataset, path);
+    CN_REQUIRE(d.dims[0] < (1ull << 31) && d.dims[1] < (1ull << 31), CN_ERR_UNSUPPORTED, "cn_hdf5_read: dimension of 2^31 or more");
+    n = d.dims[0] * (d.rank == 2 ? d.dims[1] : 1);
     CN_REQUIRE((d.type_class == 0 || d.type_class == 1) && (d.type_size == 4 || d.type_size == 8), CN_ERR_UNSUPPORTED,
-               "cn_hdf5_read_f32: datatype class %d size %d", d.type_class, d.type_size);
+               "cn_hdf5_read: datatype class %d size %d", d.type_class, d.type_size);
     CN_REQUIRE(n > 0 && n < (1ull << 40) && f.ok(d.data_addr, n * (uint64_t)d.type_size) && d.data_size >= n * (uint64_t)d.type_size,
-               CN_ERR_ARG, "cn_hdf5_read_f32: data of '%s' lies outside %s", dataset, path);
-    float *out = (float *)malloc(n * sizeof(float));
-    CN_REQUIRE(out, CN_ERR_NOMEM, "cn_hdf5_read_f32: out of memory");
+               CN_ERR_ARG, "cn_hdf5_read: data of '%s' lies outside %s", dataset, path);
+    return CN_OK;
+}
+
+// element i of the dataset converted to T the way H5Dread converts to a native type (value conversion, no scaling)
+template <typename T>
+void h5_convert(const H5 &f, const H5Dataset &d, uint64_t n, T *out)
+{
     const unsigned char *src = &f.b[d.data_addr];
     for (uint64_t i = 0; i < n; ++i) {
         if (d.type_class == 1) {
-            if (d.type_size == 4) { float v; memcpy(&v, src + 4 * i, 4); out[i] = v; }
-            else { double v; memcpy(&v, src + 8 * i, 8); out[i] = (float)v; }
+            if (d.type_size == 4) { float v; memcpy(&v, src + 4 * i, 4); out[i] = (T)v; }
+            else { double v; memcpy(&v, src + 8 * i, 8); out[i] = (T)v; }
         } else if (d.type_size == 4) {
-            if (d.type_signed) { int32_t v; memcpy(&v, src + 4 * i, 4); out[i] = (float)v; }
-            else { uint32_t v; memcpy(&v, src + 4 * i, 4); out[i] = (float)v; }
+            if (d.type_signed) { int32_t v; memcpy(&v, src + 4 * i, 4); out[i] = (T)v; }
+            else { uint32_t v; memcpy(&v, src + 4 * i, 4); out[i] = (T)v; }
         } else {
-            if (d.type_signed) { int64_t v; memcpy(&v, src + 8 * i, 8); out[i] = (float)v; }
-            else { uint64_t v; memcpy(&v, src + 8 * i, 8); out[i] = (float)v; }
+            if (d.type_signed) { int64_t v; memcpy(&v, src + 8 * i, 8); out[i] = (T)v; }
+            else { uint64_t v; memcpy(&v, src + 8 * i, 8); out[i] = (T)v; }
         }
     }
+}
+
+template <typename T>
+int h5_read(const char *path, const char *dataset, T **data_out, int64_t *rows, int64_t *cols)
+{
+    CN_REQUIRE(path && dataset && data_out && rows && cols, CN_ERR_ARG, "cn_hdf5_read: null argument");
+    *data_out = nullptr;
+    H5 f;
+    H5Dataset d;
+    uint64_t n = 0;
+    int st = h5_locate(path, dataset, f, d, n);
+    if (st != CN_OK) return st;
+    T *out = (T *)malloc(n * sizeof(T));
+    CN_REQUIRE(out, CN_ERR_NOMEM, "cn_hdf5_read: out of memory");
+    h5_convert(f, d, n, out);
     *data_out = out;
     *rows = (int64_t)d.dims[0];
     *cols = d.rank == 2 ? (int64_t)d.dims[1] : 1;
     return CN_OK;
+}
+}  // namespace
+
+extern "C" int cn_hdf5_read_f32(const char *path, const char *dataset, float **data_out, int64_t *rows, int64_t *cols)
+{
+    return h5_read<float>(path, dataset, data_out, rows, cols);
+}
+// the same for index data (the CSR files' /indices, /indptr, /shape): integers stay exact beyond 2^24
+extern "C" int cn_hdf5_read_i32(const char *path, const char *dataset, int32_t **data_out, int64_t *rows, int64_t *cols)
+{
+    return h5_read<int32_t>(path, dataset, data_out, rows, cols);
 }
 
 extern "C" void cn_host_free(void *p) { free(p); }

@@ -61,6 +61,9 @@ int cn_codebook_load(const char *path, float *codebook126);
  * compact layout, rank 1 or 2, little-endian 4- or 8-byte float or integer data (converted to float, as
  * H5T_NATIVE_FLOAT does).  Release the array with cn_host_free. */
 int cn_hdf5_read_f32(const char *path, const char *dataset, float **data_out, int64_t *rows, int64_t *cols);
+/* The same with 32-bit integer output, for the index datasets of the CSR files (/indices, /indptr, /shape of
+ * read_sparse_hdf5, source/util.cu:133-198). */
+int cn_hdf5_read_i32(const char *path, const char *dataset, int32_t **data_out, int64_t *rows, int64_t *cols);
 void cn_host_free(void *p);
 /* Host-only: writes one rank-2 float32 dataset (row-major `data`) into a new version-0 HDF5 file; replaces write_hdf5
  * (source/util.cu:202-216).  cn_hdf5_read_f32 reads it back bit for bit. */

@@ -102,6 +102,12 @@ int main(int argc, char **argv)
             Matrix *F = read_hdf5(argv[3]);
             CHECK(F->rows == 10 && F->cols == 50);
             for (int64_t i = 0; i < F->size; ++i) CHECK(F->data[i] == (float)i);
+            if (argc > 4) {   // CSR fixture of the reference (tests/util_test.cu:22-44)
+                Matrix *S = read_sparse_hdf5(argv[4]);
+                CHECK(S->isSparse == 1 && S->rows == 10 && S->cols == 50 && S->size == 499 && S->ptr_bytes == 11 * sizeof(int));
+                for (int64_t i = 0; i < S->size; ++i) CHECK(S->data[i] == (float)(i + 1) && S->idx_cols[i] == (int)((i + 1) % 50));
+                for (int r = 0; r <= 10; ++r) CHECK(S->ptr_rows[r] == (r == 0 ? 0 : 50 * r - 1));
+            }
             const std::string px = std::string(argv[2]) + "/X.hdf5", py = std::string(argv[2]) + "/y.hdf5";
             write_hdf5(px.c_str(), X);
             write_hdf5(py.c_str(), y);

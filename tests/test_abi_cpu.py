@@ -62,6 +62,21 @@ def test_hdf5_reader_on_the_reference_fixture_and_round_trips(built_lib, tmp_pat
         clusternet_b200.read_hdf5(tmp_path / "named.hdf5")
 
 
+def test_sparse_hdf5_reader_on_the_reference_fixture(built_lib):
+    # the reference's own (commented) check, tests/util_test.cu:22-44: a 10 x 50 arange stored as scipy CSR through h5py
+    data, indices, indptr, shape = clusternet_b200.read_sparse_hdf5(os.path.join(ROOT, "tests", "golden", "scipy_sparse_arange_as_h5py.hdf5"))
+    assert shape == (10, 50) and data.dtype == np.float32 and indices.dtype == np.int32 and indptr.dtype == np.int32
+    assert np.array_equal(data, np.arange(1, 500, dtype=np.float32))
+    assert np.array_equal(indices, np.arange(1, 500, dtype=np.int32) % 50)
+    assert np.array_equal(indptr, np.array([0] + [50 * r - 1 for r in range(1, 11)], np.int32))
+    dense = np.zeros(shape, np.float32)
+    for r in range(shape[0]):
+        dense[r, indices[indptr[r]:indptr[r + 1]]] = data[indptr[r]:indptr[r + 1]]
+    assert np.array_equal(dense, np.arange(500, dtype=np.float32).reshape(10, 50))
+    with pytest.raises(TypeError):
+        clusternet_b200.read_hdf5(os.path.join(ROOT, "tests", "golden", "numpy_arange_as_h5py.hdf5"), dtype=np.float64)
+
+
 def test_hdf5_reader_rejects_damaged_files(built_lib, tmp_path):
     good = open(os.path.join(ROOT, "tests", "golden", "numpy_arange_as_h5py.hdf5"), "rb").read()
     cases = {

@@ -15,7 +15,8 @@ def test_cpp_facade_program(built_lib, tmp_path):
                            os.path.join(ROOT, "tests", "facade_test.cu"), "-o", exe, f"-L{libdir}", "-lclusternet_b200",
                            "-Xlinker", f"-rpath={libdir}"])
     r = subprocess.run([exe, os.path.join(ROOT, "tests", "golden", "codebook_126.f32"), str(tmp_path),
-                        os.path.join(ROOT, "tests", "golden", "numpy_arange_as_h5py.hdf5")], capture_output=True, text=True, timeout=300)
+                        os.path.join(ROOT, "tests", "golden", "numpy_arange_as_h5py.hdf5"),
+                        os.path.join(ROOT, "tests", "golden", "scipy_sparse_arange_as_h5py.hdf5")], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "All tests passed" in r.stdout, r.stdout + r.stderr
 
 
