@@ -168,3 +168,14 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(RuntimeError, match="no fallback"):
         _lib.load()
+
+
+@pytest.mark.parametrize("program", ["facade_test", "layer_test", "readme_test"])
+def test_facade_programs_compile_and_link(built_lib, tmp_path, program):
+    """The header-only facade and the programs written against it build without a GPU (they run in the GPU tests)."""
+    import subprocess
+    libdir = os.path.join(ROOT, "clusternet_b200")
+    r = subprocess.run(["/usr/local/cuda/bin/nvcc", "-std=c++17", "-O0", "-gencode", "arch=compute_100a,code=sm_100a",
+                        os.path.join(ROOT, "tests", program + ".cu"), "-o", str(tmp_path / program), f"-L{libdir}", "-lclusternet_b200"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-3000:]
