@@ -71,6 +71,7 @@ _SIGNATURES = {
     "cn_seed_advance": (c_int, [c_void_p, c_void_p, c_void_p]),
     "cn_comm_get_unique_id": (c_int, [c_void_p]),
     "cn_comm_init_rank": (c_int, [c_void_p, c_void_p, c_int, c_int]),
+    "cn_comm_sync": (c_int, [c_void_p, c_void_p, c_int]),
     "cn_comm_destroy": (c_int, [c_void_p]),
     "cn_comm_rank": (c_int, [c_void_p]),
     "cn_comm_size": (c_int, [c_void_p]),

@@ -12,6 +12,8 @@
 #include <dlfcn.h>
 #include <nccl.h>
 #include <string.h>
+#include <time.h>
+#include <unistd.h>
 #include <vector>
 #include "cn_gemm.h"
 
@@ -26,6 +28,8 @@ struct NcclApi {
     ncclResult_t (*GroupStart)() = nullptr;
     ncclResult_t (*GroupEnd)() = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;   // optional: used by cn_comm_sync only
+    ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
 };
 
 static NcclApi g_nccl;
@@ -49,6 +53,8 @@ static int nccl_load()
     CN_SYM(GroupEnd, "ncclGroupEnd");
     CN_SYM(GetErrorString, "ncclGetErrorString");
 #undef CN_SYM
+    *(void **)(&g_nccl.CommGetAsyncError) = dlsym(h, "ncclCommGetAsyncError");
+    *(void **)(&g_nccl.CommAbort) = dlsym(h, "ncclCommAbort");
     g_nccl.handle = h;
     return CN_OK;
 }
@@ -81,7 +87,13 @@ struct cn_comm_state {
     std::vector<unsigned int *> peer_flags;
     unsigned int **d_peer_flags = nullptr;   // device copy of peer_flags
     unsigned int epoch = 0;
+    bool aborted = false;   // cn_comm_sync gave up on a collective: only cn_comm_destroy is accepted from here on
 };
+
+// Refuses work on a communicator that cn_comm_sync has aborted; a context without communicator passes (single rank).
+#define CN_COMM_ALIVE(ctx)                                                                                             \
+    CN_REQUIRE(!((ctx)->comm && (ctx)->comm->aborted), CN_ERR_NCCL,                                                    \
+               "the communicator was aborted after a failed or timed-out collective: call cn_comm_destroy, then cn_comm_init_rank again")
 
 static void sym_release(cn_comm_state *c, cn_sym_buf &b)
 {
@@ -97,7 +109,7 @@ void cn_comm_state_free(cn_context *ctx)
     cudaDeviceSynchronize();
     for (auto &b : ctx->comm->sym) sym_release(ctx->comm, b);
     cudaFree(ctx->comm->d_peer_flags);
-    if (ctx->comm->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(ctx->comm->comm);
+    if (ctx->comm->comm && !ctx->comm->aborted && g_nccl.CommDestroy) g_nccl.CommDestroy(ctx->comm->comm);
     cudaFree(ctx->comm->d_scales);
     delete ctx->comm;
     ctx->comm = nullptr;
@@ -151,6 +163,50 @@ extern "C" int cn_comm_destroy(cn_context *ctx)
     return CN_OK;
 }
 
+// Bounded host-side wait for the work queued on `stream`, for loops in which a peer may have left: polls the stream and
+// the communicator's asynchronous error state; on an NCCL error, or when timeout_ms passes with the stream still busy,
+// the communicator is aborted (ncclCommAbort ends NCCL kernels that wait for a peer), the status says which, and every
+// later collective call on this context fails until the communicator is destroyed and created again.  The reference
+// blocks forever in MPI_Barrier / MPI_Wait in that situation (source/clusterNet.cpp:663-690).
+extern "C" int cn_comm_sync(cn_context *ctx, void *stream, int timeout_ms)
+{
+    CN_REQUIRE(ctx && timeout_ms > 0, CN_ERR_ARG, "cn_comm_sync: bad argument");
+    cudaStream_t s = cn_stream(stream);
+    cn_comm_state *c = ctx->comm;
+    timespec t0;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    for (;;) {
+        cudaError_t q = cudaStreamQuery(s);
+        if (q == cudaSuccess) return CN_OK;
+        if (q != cudaErrorNotReady) return cn_cuda_fail(q, "cn_comm_sync");
+        ncclResult_t async = ncclSuccess;
+        if (c && c->comm && !c->aborted && g_nccl.CommGetAsyncError) {
+            if (g_nccl.CommGetAsyncError(c->comm, &async) != ncclSuccess) async = ncclSystemError;
+            if (async == ncclInProgress) async = ncclSuccess;
+        }
+        timespec t1;
+        clock_gettime(CLOCK_MONOTONIC, &t1);
+        const double ms = (t1.tv_sec - t0.tv_sec) * 1e3 + (t1.tv_nsec - t0.tv_nsec) * 1e-6;
+        const bool timed_out = ms > (double)timeout_ms;
+        if (async != ncclSuccess || timed_out) {
+            bool did_abort = false;
+            if (c && c->comm && !c->aborted) {
+                if (g_nccl.CommAbort) g_nccl.CommAbort(c->comm);
+                c->aborted = true;
+                did_abort = true;
+            }
+            if (async != ncclSuccess) {
+                cn_set_error("cn_comm_sync: NCCL reported asynchronous error %d (%s)%s", (int)async, g_nccl.GetErrorString(async),
+                             did_abort ? "; communicator aborted" : "");
+                return CN_ERR_NCCL;
+            }
+            cn_set_error("cn_comm_sync: stream still busy after %d ms%s", timeout_ms, did_abort ? "; communicator aborted" : "");
+            return CN_ERR_TIMEOUT;
+        }
+        usleep(50);
+    }
+}
+
 extern "C" int cn_comm_rank(const cn_context *ctx) { return (ctx && ctx->comm) ? ctx->comm->rank : 0; }
 extern "C" int cn_comm_size(const cn_context *ctx) { return (ctx && ctx->comm) ? ctx->comm->nranks : 1; }
 
@@ -167,6 +223,7 @@ extern "C" int cn_bcast_f32(cn_context *ctx, float *d_buf, int64_t n, int root, 
 {
     CN_REQUIRE(ctx && n >= 0 && (n == 0 || d_buf), CN_ERR_ARG, "cn_bcast_f32: bad argument");
     if (!ctx->comm || ctx->comm->nranks == 1 || n == 0) return CN_OK;
+    CN_COMM_ALIVE(ctx);
     CN_REQUIRE(root >= 0 && root < ctx->comm->nranks, CN_ERR_ARG, "cn_bcast_f32: root %d", root);
     CN_NCCL(g_nccl.Broadcast(d_buf, d_buf, (size_t)n, ncclFloat, root, ctx->comm->comm, cn_stream(stream)));
     return CN_OK;
@@ -177,6 +234,7 @@ static int allgather_blocks(cn_context *ctx, void *base, int64_t M, int64_t n_to
 {
     cn_comm_state *c = ctx->comm;
     if (!c || c->nranks == 1) return CN_OK;
+    CN_COMM_ALIVE(ctx);
     const int G = c->nranks;
     const int64_t split = n_total / G;
     if (n_total % G == 0) {
@@ -219,6 +277,7 @@ extern "C" int cn_allgather_scalar_f32(cn_context *ctx, float *d_vals, void *str
 {
     CN_REQUIRE(ctx && d_vals, CN_ERR_ARG, "cn_allgather_scalar_f32: bad argument");
     if (!ctx->comm || ctx->comm->nranks == 1) return CN_OK;
+    CN_COMM_ALIVE(ctx);
     CN_NCCL(g_nccl.AllGather(d_vals + ctx->comm->rank, d_vals, 1, ncclFloat, ctx->comm->comm, cn_stream(stream)));
     return CN_OK;
 }
@@ -227,6 +286,7 @@ extern "C" int cn_allreduce_sum_f32(cn_context *ctx, float *d_buf, int64_t n, vo
 {
     CN_REQUIRE(ctx && n >= 0 && (n == 0 || d_buf), CN_ERR_ARG, "cn_allreduce_sum_f32: bad argument");
     if (!ctx->comm || ctx->comm->nranks == 1 || n == 0) return CN_OK;
+    CN_COMM_ALIVE(ctx);
     CN_NCCL(g_nccl.AllReduce(d_buf, d_buf, (size_t)n, ncclFloat, ncclSum, ctx->comm->comm, cn_stream(stream)));
     return CN_OK;
 }
@@ -237,6 +297,7 @@ extern "C" int cn_allreduce_sum_f32(cn_context *ctx, float *d_buf, int64_t n, vo
 static int sym_alloc_impl(cn_context *ctx, size_t bytes, cn_sym_buf *out)
 {
     cn_comm_state *c = ctx->comm;
+    CN_COMM_ALIVE(ctx);
     const int G = c->nranks;
     cn_sym_buf b;
     b.bytes = bytes;
@@ -369,6 +430,7 @@ extern "C" int cn_dotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_to
     CN_REQUIRE(M >= 0 && K >= 0 && n_total >= 0, CN_ERR_SHAPE, "cn_dotmpi_f32: negative dimension");
     CN_REQUIRE(exchange == 0 || exchange == 1, CN_ERR_ARG, "cn_dotmpi_f32: exchange must be 0 (fp32) or 1 (8-bit)");
     CN_REQUIRE(!epi || epi->maxout_level <= 1, CN_ERR_UNSUPPORTED, "cn_dotmpi_f32: maxout is not available on the sharded product");
+    CN_COMM_ALIVE(ctx);
     const int G = ctx->comm ? ctx->comm->nranks : 1, rank = ctx->comm ? ctx->comm->rank : 0;
     int64_t start, cnt;
     cn_shard_cols(n_total, rank, G, &start, &cnt);
@@ -486,6 +548,7 @@ int cn_comm_gather_codes(cn_context *ctx, uint8_t *d_codes_all, int64_t n, float
 {
     cn_comm_state *c = ctx->comm;
     if (!c || c->nranks == 1) return CN_OK;
+    CN_COMM_ALIVE(ctx);
     CN_NCCL(g_nccl.GroupStart());
     ncclResult_t r1 = g_nccl.AllGather(d_codes_all + (size_t)c->rank * n, d_codes_all, (size_t)n, ncclUint8, c->comm, cn_stream(stream));
     ncclResult_t r2 = d_scales ? g_nccl.AllGather(d_scales + c->rank, d_scales, 1, ncclFloat, c->comm, cn_stream(stream)) : ncclSuccess;

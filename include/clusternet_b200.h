@@ -214,6 +214,12 @@ int cn_seed_advance(cn_context *ctx, uint64_t *d_seed, void *stream);
  * ------------------------------------------------------------------------------------------- */
 int cn_comm_get_unique_id(void *id128);
 int cn_comm_init_rank(cn_context *ctx, const void *id128, int rank, int nranks);
+/* Host-side wait with a limit, for loops in which a peer may have died: returns CN_OK when everything queued on
+ * `stream` has finished; on an asynchronous NCCL error (CN_ERR_NCCL) or after timeout_ms with the stream still busy
+ * (CN_ERR_TIMEOUT) it aborts the communicator so that the collectives in flight end; afterwards every collective call
+ * on the context fails until cn_comm_destroy + cn_comm_init_rank.  Without a communicator it is a plain bounded wait.
+ * The reference has no counterpart: its MPI_Barrier / MPI_Wait (source/clusterNet.cpp:663-690) block forever. */
+int cn_comm_sync(cn_context *ctx, void *stream, int timeout_ms);
 int cn_comm_destroy(cn_context *ctx);
 int cn_comm_rank(const cn_context *ctx);
 int cn_comm_size(const cn_context *ctx);

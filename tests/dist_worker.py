@@ -170,6 +170,27 @@ def run_nccl():
     assert float(t[0]) == world * (world + 1) / 2
     dist.barrier()
     ctx.sym_free_all()
+
+    # ---- bounded host wait and recovery.  No rank fails here: the stream is kept busy by a plain delay kernel, the
+    # short limit runs out on every rank, cn_comm_sync aborts the (idle, healthy) communicator, later collectives are
+    # refused, and a new communicator is made on the same context.
+    assert ctx.lib.cn_comm_sync(ctx.h, ctx.stream_ptr(), 2000) == 0
+    torch.cuda._sleep(int(0.4 * 1.9e9))                      # ~0.2-0.4 s of device time, then the stream drains by itself
+    assert ctx.lib.cn_comm_sync(ctx.h, ctx.stream_ptr(), 20) == _lib.CN_ERR_TIMEOUT
+    assert b"communicator aborted" in ctx.lib.cn_last_error()
+    torch.cuda.synchronize()
+    assert ctx.lib.cn_allreduce_sum_f32(ctx.h, t.data_ptr(), t.numel(), ctx.stream_ptr()) == _lib.CN_ERR_NCCL
+    assert b"cn_comm_destroy" in ctx.lib.cn_last_error()
+    dist.barrier()
+    cn.check(ctx.lib.cn_comm_destroy(ctx.h))
+    ids = [ctx.unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(ids, src=0)
+    ctx.comm_init(ids[0], rank, world)
+    t.fill_(float(rank + 1))
+    cn.check(ctx.lib.cn_allreduce_sum_f32(ctx.h, t.data_ptr(), t.numel(), ctx.stream_ptr()))
+    cn.check(ctx.lib.cn_comm_sync(ctx.h, ctx.stream_ptr(), 10000))
+    assert float(t[0]) == world * (world + 1) / 2
+    dist.barrier()
     cn.check(ctx.lib.cn_comm_destroy(ctx.h))
     if rank == 0:
         print("NCCL-OK")

@@ -183,3 +183,16 @@ def test_bounded_wait_surfaces_as_timeout_status(ctx):
     ctx.gemm_check()                                                    # the status word was cleared
     a = ctx.rand(4, 4, seed=1)                                          # and the GPU still works
     assert float(a.sum()) > 0
+
+
+def test_comm_sync_is_a_bounded_wait_without_a_communicator(ctx):
+    """cn_comm_sync: done at once on an idle stream; CN_ERR_TIMEOUT while a (finite) delay kernel runs; fine again after."""
+    sp = ctx.stream_ptr()
+    assert ctx.lib.cn_comm_sync(ctx.h, sp, 1000) == 0
+    torch.cuda._sleep(int(0.3 * 1.9e9))
+    assert ctx.lib.cn_comm_sync(ctx.h, sp, 10) == _lib.CN_ERR_TIMEOUT
+    assert b"still busy" in ctx.lib.cn_last_error() and b"aborted" not in ctx.lib.cn_last_error()
+    assert ctx.lib.cn_comm_sync(ctx.h, sp, 20000) == 0
+    assert ctx.lib.cn_comm_sync(ctx.h, sp, 0) == _lib.CN_ERR_ARG
+    x = torch.ones(1024, device="cuda")
+    assert float(ctx.absmax(x).item()) == 1.0          # the context is still usable
