@@ -56,6 +56,7 @@ _SIGNATURES = {
     "cn_upload_row_major": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "cn_download_row_major": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "cn_fill_f32": (c_int, [c_void_p, c_void_p, c_int64, c_float, c_void_p]),
+    "cn_arange_f32": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "cn_gemm_f32": (c_int, [c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                             c_void_p, c_int64, ctypes.POINTER(Epilogue), c_int, c_void_p]),
     "cn_gemm_last_path": (c_char_p, [c_void_p]),

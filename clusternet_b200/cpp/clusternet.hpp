@@ -438,75 +438,145 @@ public:
     Matrix *CURRENT_BATCH = nullptr, *CURRENT_BATCH_Y = nullptr, *CURRENT_BATCH_CV = nullptr, *CURRENT_BATCH_CV_Y = nullptr;
     int64_t TOTAL_BATCHES = 0, TOTAL_BATCHES_CV = 0, BATCH_SIZE = 0, BATCH_SIZE_CV = 0, TRAIN_SET_ROWS = 0, CV_SET_ROWS = 0;
     bool SKIP_LAST_BATCH = false;
+    BatchAllocationMethod_t BATCH_METHOD = Single_GPU;
 
-    // data set read from two HDF5 files (source/batchAllocator.cpp:62-99; the csv branch of the reference is not built)
+    // data set read from two HDF5 files (source/batchAllocator.cpp:62-99; the csv branch of the reference is not built).
+    // As in the reference only rank 0 reads the files unless every process serves itself (Single_GPU).
     void init(std::string path_X, std::string path_y, float cross_validation_size, int64_t batch_size, int64_t cv_batch_size,
               ClusterNet *cluster, BatchAllocationMethod_t method = Single_GPU)
     {
         if (path_X.find("hdf5") == std::string::npos) throw "Only the cvs and hdf5 formats are supported!";
-        init(read_hdf5(path_X.c_str()), read_hdf5(path_y.c_str()), cross_validation_size, batch_size, cv_batch_size, cluster, method);
+        const bool reads = method == Single_GPU || cluster->MPI_SIZE == 1 || cluster->MYRANK == 0;
+        Matrix *X = reads ? read_hdf5(path_X.c_str()) : empty_cpu(1, 1);
+        Matrix *y = reads ? read_hdf5(path_y.c_str()) : empty_cpu(1, 1);
+        init(X, y, cross_validation_size, batch_size, cv_batch_size, cluster, method);
     }
 
-    // X, y: HOST row-major matrices holding the whole data set (source/batchAllocator.cpp:21-30,101-139)
-    void init(Matrix *X, Matrix *y, float cross_validation_size, int64_t batch_size, int64_t cv_batch_size, ClusterNet *cluster,
-              BatchAllocationMethod_t = Single_GPU)
+    // without a ClusterNet (source/batchAllocator.cpp:21-30): one GPU, the context of the free functions
+    void init(Matrix *X, Matrix *y, float cross_validation_size, int64_t batch_size, int64_t cv_batch_size)
     {
+        init_impl(X, y, cross_validation_size, batch_size, cv_batch_size, cn_detail::current(), 0, 1, Single_GPU);
+    }
+
+    // X, y: HOST row-major matrices holding the whole data set (source/batchAllocator.cpp:31-60,101-139).  With
+    // Single_GPU every process serves its own X, y.  With Batch_split / Distributed_weights and several processes only
+    // rank 0's X, y are used (the others may pass anything): the data set's dimensions and then every batch travel from
+    // rank 0 to the other GPUs (MPI_get_dataset_dimensions and the MPI sends of broadcast_batch_to_processes there,
+    // one NCCL broadcast over NVLink per batch here).
+    void init(Matrix *X, Matrix *y, float cross_validation_size, int64_t batch_size, int64_t cv_batch_size, ClusterNet *cluster,
+              BatchAllocationMethod_t method = Single_GPU)
+    {
+        init_impl(X, y, cross_validation_size, batch_size, cv_batch_size, cluster->context(), cluster->MYRANK, cluster->MPI_SIZE, method);
+    }
+
+    // The host-side staging memcpy and the asynchronous copies are one step here, and the broadcast to the other
+    // processes happens when the batch becomes current; these calls are kept so that the reference's loop
+    // (tests/batchAllocator_test.cu:44-76) compiles unchanged.
+    void broadcast_batch_to_processes() {}
+    void broadcast_batch_cv_to_processes() {}
+    void allocate_next_batch_async() { if (root_) cn_detail::check(cn_batch_copy_next_async(train_.get())); }
+    void allocate_next_cv_batch_async() { if (root_) cn_detail::check(cn_batch_copy_next_async(cv_.get())); }
+    void replace_current_batch_with_next() { swap(train_.get(), CURRENT_BATCH, CURRENT_BATCH_Y, recv_x_, recv_y_, SKIP_LAST_BATCH); }
+    void replace_current_cv_batch_with_next() { swap(cv_.get(), CURRENT_BATCH_CV, CURRENT_BATCH_CV_Y, recv_cv_x_, recv_cv_y_, false); }
+
+private:
+    std::shared_ptr<cn_batch> train_, cv_;
+    cn_context *ctx_ = nullptr;
+    int64_t cols_x_ = 0, cols_y_ = 0;
+    bool root_ = true, bcast_ = false;
+    Matrix *recv_x_ = nullptr, *recv_y_ = nullptr, *recv_cv_x_ = nullptr, *recv_cv_y_ = nullptr;   // receive buffers of the other ranks
+    float *d_hdr_ = nullptr;
+
+    void init_impl(Matrix *X, Matrix *y, float cross_validation_size, int64_t batch_size, int64_t cv_batch_size, cn_context *ctx, int rank,
+                   int nranks, BatchAllocationMethod_t method)
+    {
+        ctx_ = ctx;
+        BATCH_METHOD = method;
+        bcast_ = method != Single_GPU && nranks > 1;
+        root_ = !bcast_ || rank == 0;
         BATCH_SIZE = batch_size;
         BATCH_SIZE_CV = cv_batch_size;
-        TRAIN_SET_ROWS = (int64_t)ceilf(X->rows * (1.0f - cross_validation_size));
-        CV_SET_ROWS = X->rows - TRAIN_SET_ROWS;
-        if (BATCH_SIZE_CV > X->rows * cross_validation_size) throw "Cross validation batch size must be smaller than the cross validation set.";
-        if (BATCH_SIZE > TRAIN_SET_ROWS) throw "ERROR: Batch size must be smaller than the training set.";
-        cn_batch *t = nullptr, *c = nullptr;
-        cn_detail::check(cn_batch_create(cluster->context(), X->data, y->data, TRAIN_SET_ROWS, X->cols, y->cols, batch_size, 0, &t));
-        train_ = std::shared_ptr<cn_batch>(t, [](cn_batch *p) { cn_batch_destroy(p); });
-        if (CV_SET_ROWS > 0) {
-            cn_detail::check(cn_batch_create(cluster->context(), X->data + (size_t)TRAIN_SET_ROWS * X->cols,
-                                            y->data + (size_t)TRAIN_SET_ROWS * y->cols, CV_SET_ROWS, X->cols, y->cols, cv_batch_size, 0, &c));
-            cv_ = std::shared_ptr<cn_batch>(c, [](cn_batch *p) { cn_batch_destroy(p); });
+        cn_detail::cuda(cudaMalloc((void **)&d_hdr_, 8 * sizeof(float)));
+        // data set dimensions from rank 0; rows as two 16-bit halves so that they stay exact as floats
+        float meta[4] = {(float)(X->rows >> 16), (float)(X->rows & 0xffff), (float)X->cols, (float)y->cols};
+        if (bcast_) {
+            cn_detail::cuda(cudaMemcpy(d_hdr_, meta, sizeof(meta), cudaMemcpyHostToDevice));
+            cn_detail::check(cn_bcast_f32(ctx_, d_hdr_, 4, 0, nullptr));
+            cn_detail::cuda(cudaMemcpy(meta, d_hdr_, sizeof(meta), cudaMemcpyDeviceToHost));
         }
-        TOTAL_BATCHES = cn_batch_total_batches(t);
-        TOTAL_BATCHES_CV = c ? cn_batch_total_batches(c) : 0;
-        cols_x_ = X->cols;
-        cols_y_ = y->cols;
+        const int64_t rows = ((int64_t)meta[0] << 16) + (int64_t)meta[1];
+        cols_x_ = (int64_t)meta[2];
+        cols_y_ = (int64_t)meta[3];
+        TRAIN_SET_ROWS = (int64_t)ceilf(rows * (1.0f - cross_validation_size));
+        CV_SET_ROWS = rows - TRAIN_SET_ROWS;
+        if (BATCH_SIZE_CV > rows * cross_validation_size) throw "Cross validation batch size must be smaller than the cross validation set.";
+        if (BATCH_SIZE > TRAIN_SET_ROWS) throw "ERROR: Batch size must be smaller than the training set.";
+        TOTAL_BATCHES = (TRAIN_SET_ROWS + batch_size - 1) / batch_size;
+        TOTAL_BATCHES_CV = (CV_SET_ROWS > 0 && cv_batch_size > 0) ? (CV_SET_ROWS + cv_batch_size - 1) / cv_batch_size : 0;
         CURRENT_BATCH = cn_detail::header(0, 0);
         CURRENT_BATCH_Y = cn_detail::header(0, 0);
         CURRENT_BATCH_CV = cn_detail::header(0, 0);
         CURRENT_BATCH_CV_Y = cn_detail::header(0, 0);
-        float *dx, *dy;
-        int64_t n;
-        cn_detail::check(cn_batch_current(t, &dx, &dy, &n));
-        publish(CURRENT_BATCH, CURRENT_BATCH_Y, dx, dy, n);
-        if (c) {
-            cn_detail::check(cn_batch_current(c, &dx, &dy, &n));
-            publish(CURRENT_BATCH_CV, CURRENT_BATCH_CV_Y, dx, dy, n);
+        cn_batch *t = nullptr, *c = nullptr;
+        if (root_) {
+            cn_detail::check(cn_batch_create(ctx_, X->data, y->data, TRAIN_SET_ROWS, cols_x_, cols_y_, batch_size, 0, &t));
+            train_ = std::shared_ptr<cn_batch>(t, [](cn_batch *p) { cn_batch_destroy(p); });
+            if (TOTAL_BATCHES_CV > 0) {
+                cn_detail::check(cn_batch_create(ctx_, X->data + (size_t)TRAIN_SET_ROWS * cols_x_, y->data + (size_t)TRAIN_SET_ROWS * cols_y_,
+                                                CV_SET_ROWS, cols_x_, cols_y_, cv_batch_size, 0, &c));
+                cv_ = std::shared_ptr<cn_batch>(c, [](cn_batch *p) { cn_batch_destroy(p); });
+            }
+        } else {
+            recv_x_ = empty(batch_size, cols_x_);
+            recv_y_ = empty(batch_size, cols_y_);
+            if (TOTAL_BATCHES_CV > 0) {
+                recv_cv_x_ = empty(cv_batch_size, cols_x_);
+                recv_cv_y_ = empty(cv_batch_size, cols_y_);
+            }
+        }
+        float *dx = nullptr, *dy = nullptr;
+        int64_t n = 0;
+        if (root_) cn_detail::check(cn_batch_current(t, &dx, &dy, &n));
+        share(CURRENT_BATCH, CURRENT_BATCH_Y, recv_x_, recv_y_, dx, dy, n);
+        if (TOTAL_BATCHES_CV > 0) {
+            if (root_) cn_detail::check(cn_batch_current(c, &dx, &dy, &n));
+            share(CURRENT_BATCH_CV, CURRENT_BATCH_CV_Y, recv_cv_x_, recv_cv_y_, dx, dy, n);
         }
     }
-    // The host-side staging memcpy and the asynchronous copies are one step here; the first call is kept so that
-    // the reference's loop (source/tests/batchAllocator_test.cu:44-76) compiles unchanged.
-    void broadcast_batch_to_processes() {}
-    void broadcast_batch_cv_to_processes() {}
-    void allocate_next_batch_async() { cn_detail::check(cn_batch_copy_next_async(train_.get())); }
-    void allocate_next_cv_batch_async() { cn_detail::check(cn_batch_copy_next_async(cv_.get())); }
-    void replace_current_batch_with_next() { swap(train_.get(), CURRENT_BATCH, CURRENT_BATCH_Y, SKIP_LAST_BATCH); }
-    void replace_current_cv_batch_with_next() { swap(cv_.get(), CURRENT_BATCH_CV, CURRENT_BATCH_CV_Y, false); }
-
-private:
-    std::shared_ptr<cn_batch> train_, cv_;
-    int64_t cols_x_ = 0, cols_y_ = 0;
-
     void publish(Matrix *X, Matrix *Y, float *dx, float *dy, int64_t n)
     {
         X->rows = n; X->cols = cols_x_; X->size = n * cols_x_; X->bytes = (size_t)X->size * 4; X->data = dx;
         Y->rows = n; Y->cols = cols_y_; Y->size = n * cols_y_; Y->bytes = (size_t)Y->size * 4; Y->data = dy;
     }
-    void swap(cn_batch *b, Matrix *X, Matrix *Y, bool skip_last)
+    // makes (dx, dy, n) of rank 0 the current batch everywhere: row count first, then the two blocks
+    void share(Matrix *X, Matrix *Y, Matrix *rx, Matrix *ry, float *dx, float *dy, int64_t n)
     {
-        float *dx, *dy;
-        int64_t n;
-        cn_detail::check(cn_batch_set_skip_last(b, skip_last ? 1 : 0));
-        cn_detail::check(cn_batch_swap(b, nullptr, &dx, &dy, &n));
+        if (bcast_) {
+            float nf = (float)n;
+            if (root_) cn_detail::cuda(cudaMemcpy(d_hdr_, &nf, sizeof(float), cudaMemcpyHostToDevice));
+            cn_detail::check(cn_bcast_f32(ctx_, d_hdr_, 1, 0, nullptr));
+            if (!root_) {
+                cn_detail::cuda(cudaMemcpy(&nf, d_hdr_, sizeof(float), cudaMemcpyDeviceToHost));
+                n = (int64_t)nf;
+                dx = rx->data;
+                dy = ry->data;
+            }
+        }
         publish(X, Y, dx, dy, n);
+        if (bcast_) {
+            cn_detail::check(cn_bcast_f32(ctx_, dx, n * cols_x_, 0, nullptr));
+            cn_detail::check(cn_bcast_f32(ctx_, dy, n * cols_y_, 0, nullptr));
+        }
+    }
+    void swap(cn_batch *b, Matrix *X, Matrix *Y, Matrix *rx, Matrix *ry, bool skip_last)
+    {
+        float *dx = nullptr, *dy = nullptr;
+        int64_t n = 0;
+        if (root_) {
+            cn_detail::check(cn_batch_set_skip_last(b, skip_last ? 1 : 0));
+            cn_detail::check(cn_batch_swap(b, nullptr, &dx, &dy, &n));
+        }
+        share(X, Y, rx, ry, dx, dy, n);
     }
 };
 
@@ -533,6 +603,14 @@ inline Matrix *fill_matrix(int64_t rows, int64_t cols, float v)
 }
 inline void fill_matrix(Matrix *A, const float v) { cn_detail::check(cn_fill_f32(cn_detail::current(), A->data, A->size, v, nullptr)); }
 inline Matrix *zeros(int64_t rows, int64_t cols) { return fill_matrix(rows, cols, 0.0f); }
+// to_host(arange(rows, cols)) reads start, start + 1, ... in row-major order (source/basicOps.cu:205-212)
+inline Matrix *arange(int64_t start, int64_t rows, int64_t cols)
+{
+    Matrix *m = empty(rows, cols);
+    cn_detail::check(cn_arange_f32(cn_detail::current(), m->data, start, rows, cols, nullptr));
+    return m;
+}
+inline Matrix *arange(int64_t rows, int64_t cols) { return arange(0, rows, cols); }
 inline Matrix *ones(int64_t rows, int64_t cols) { return fill_matrix(rows, cols, 1.0f); }
 
 // layout boundary (source/basicOps.cu:14-137)

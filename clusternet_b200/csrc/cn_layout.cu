@@ -79,6 +79,27 @@ extern "C" int cn_download_row_major(cn_context *ctx, const float *d_src, float 
     return CN_OK;
 }
 
+// kArange (source/clusterKernels.cu:925-937): the column-major image of the row-major counter start, start+1, ...
+__global__ void cn_arange_kernel(float *__restrict__ out, int64_t start, int64_t rows, int64_t cols, int64_t n)
+{
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        out[i] = (float)((i % rows) * cols + (i / rows) + start);
+}
+
+extern "C" int cn_arange_f32(cn_context *ctx, float *d_A, int64_t start, int64_t rows, int64_t cols, void *stream)
+{
+    CN_REQUIRE(ctx && rows >= 0 && cols >= 0 && (rows * cols == 0 || d_A), CN_ERR_ARG, "cn_arange_f32: bad argument");
+    const int64_t n = rows * cols;
+    if (n == 0) return CN_OK;
+    int64_t blocks = (n + 1023) / 1024;
+    int64_t cap = (int64_t)ctx->sm_count * 8;
+    cn_arange_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, cn_stream(stream)>>>(d_A, start, rows, cols, n);
+    CN_CUDA(cudaGetLastError());
+    cn_count_launch();
+    return CN_OK;
+}
+
 extern "C" int cn_fill_f32(cn_context *ctx, float *d_A, int64_t n, float value, void *stream)
 {
     CN_REQUIRE(ctx && n >= 0 && (n == 0 || d_A), CN_ERR_ARG, "cn_fill_f32: bad argument");

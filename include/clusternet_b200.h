@@ -124,6 +124,9 @@ int cn_upload_row_major(cn_context *ctx, const float *h_src, float *d_stage, flo
 /* Download: the inverse; h_dst receives row-major data once the stream has drained. */
 int cn_download_row_major(cn_context *ctx, const float *d_src, float *d_stage, float *h_dst, int64_t rows, int64_t cols, void *stream);
 int cn_fill_f32(cn_context *ctx, float *d_A, int64_t n, float value, void *stream);
+/* arange (source/basicOps.cu:205-212, kArange source/clusterKernels.cu:925-937): col-major rows x cols matrix whose
+ * row-major reading is start, start+1, ... */
+int cn_arange_f32(cn_context *ctx, float *d_A, int64_t start, int64_t rows, int64_t cols, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * GEMM.  Replaces the cublasSgemm call of ClusterNet::dot (source/clusterNet.cpp:404-487) and the

@@ -170,7 +170,7 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
         _lib.load()
 
 
-@pytest.mark.parametrize("program", ["facade_test", "layer_test", "readme_test"])
+@pytest.mark.parametrize("program", ["facade_test", "layer_test", "readme_test", "batch_test"])
 def test_facade_programs_compile_and_link(built_lib, tmp_path, program):
     """The header-only facade and the programs written against it build without a GPU (they run in the GPU tests)."""
     import subprocess

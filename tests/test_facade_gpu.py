@@ -54,18 +54,20 @@ def _run_ranks(exe, tmp_path, nranks):
     return outs
 
 
-def test_readme_program_one_process(built_lib, tmp_path):
-    exe = _build(tmp_path, "readme_test")
+@pytest.mark.parametrize("program", ["readme_test", "batch_test"])
+def test_reference_style_program_one_process(built_lib, tmp_path, program):
+    exe = _build(tmp_path, program)
     for code, out in _run_ranks(exe, tmp_path, 1):
         assert code == 0 and "All tests passed" in out, out[-3000:]
 
 
-def test_readme_program_one_process_per_gpu(built_lib, tmp_path):
+@pytest.mark.parametrize("program", ["readme_test", "batch_test"])
+def test_reference_style_program_one_process_per_gpu(built_lib, tmp_path, program):
     import torch
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
-    exe = _build(tmp_path, "readme_test")
+    exe = _build(tmp_path, program)
     outs = _run_ranks(exe, tmp_path, min(n, 4))
     report = "\n".join(f"[rank {r}: exit {code}] {out[-1500:]}" for r, (code, out) in enumerate(outs))
     assert all(code == 0 and "All tests passed" in out for code, out in outs), report
