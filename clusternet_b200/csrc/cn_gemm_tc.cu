@@ -798,7 +798,16 @@ cn_splitk_reduce_kernel(const ReduceParams p)
         if (n >= p.N || m >= p.M) continue;
         const float *src = p.partials + (size_t)ticket * p.splits * tile_elems + (size_t)n_local * TC_BM + m_local;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int sp = 0; sp < p.splits; ++sp) {
+        int sp = 0;
+        // four loads in flight at a time; the additions stay in split order, so the sum does not depend on the grouping
+        for (; sp + 4 <= p.splits; sp += 4) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)(sp + u) * tile_elems));
+#pragma unroll
+            for (int u = 0; u < 4; ++u) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
+        }
+        for (; sp < p.splits; ++sp) {
             const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)sp * tile_elems));
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
