@@ -535,6 +535,9 @@ def main():
                      "traffic_source": "ncu dram__bytes_read+write of a 4096-column case, scaled by W bytes",
                      "ms_per_launch": l1_ms, "layer2_ms_per_launch": l2_ms,
                      "peak_source": f"{peaks['source']}: bf16_tflops {peaks['bf16_tflops']} / 2 (TF32 rate)" + (" / 3 (three TF32 products per tile)" if args.mode == "3xtf32" else ""),
+                     # the same against the power-capped (seconds-long) cuBLAS figure, for runs whose clocks show sw_power_cap
+                     "peak_sustained": peaks["bf16_tflops_sustained"] / 2.0 / (3.0 if args.mode == "3xtf32" else 1.0),
+                     "frac_sustained": (achieved / (peaks["bf16_tflops_sustained"] / 2.0 / (3.0 if args.mode == "3xtf32" else 1.0))) if achieved else None,
                      "hbm_frac_layer1": (4.0 * K1 * (N1 / world) / (l1_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]) if l1_ms else None},
     }
     if train:
