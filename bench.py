@@ -9,7 +9,8 @@ One process per GPU (torchrun sets RANK / LOCAL_RANK / WORLD_SIZE for N > 1).  R
   value     whole-job TFLOP/s of the two dotMPI calls with the batch and the weights resident in HBM
             (2*M*N*K flops, the three TF32 products of the 3xTF32 mode counted once), CUDA events, max over ranks
   e2e       the same two calls through the C ABI starting from a pinned HOST batch (row-major) and ending with the
-            row-major result in pinned host memory: upload + transpose, broadcast, two dotMPI, transpose + download
+            row-major result in pinned host memory: upload + transpose, broadcast, two dotMPI, transpose + download;
+            the upload of the next batch and the download of the previous result run on side streams
   roofline  the tensor-core kernel of layer 1 alone, timed by events around its launches inside the timed region
   codec     8-bit compress / decompress / absmax GB/s on config 2 (4096 x 4096, rotating buffers) and on 1 GiB
   cpu_baseline  multithreaded fp32 sgemm (numpy / OpenBLAS) of a column sample of the same product on the host cores
@@ -451,6 +452,27 @@ def main():
         cn.check(lib.cn_batch_create(ctx.h, h_set.data_ptr(), h_lab.data_ptr(), 2 * M, K1, 1, M, 0, ctypes.byref(bh)))
     px, py, pn = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_int64()
 
+    # The result leaves the same way the batch arrives: on a side stream.  The step's output is transposed into a staging
+    # buffer on the compute stream; the device->host copy of that buffer runs on the copy stream while the next step
+    # computes, and the staging buffer is not rewritten before that copy has finished (two events).
+    copy_stream = torch.cuda.Stream() if rank == 0 else None
+    ev_staged, ev_drained = torch.cuda.Event(), torch.cuda.Event()
+    if rank == 0:
+        ev_drained.record(torch.cuda.current_stream())
+
+    def download_overlapped():
+        if rank != 0:
+            return
+        main = torch.cuda.current_stream()
+        main.wait_event(ev_drained)
+        cn.check(lib.cn_to_row_major(ctx.h, out2.data_ptr(), d_stage_out.data_ptr(), M, N2, sp))
+        ev_staged.record(main)
+        copy_stream.wait_event(ev_staged)
+        err = cudart.cudaMemcpyAsync(ctypes.c_void_p(h_out.data_ptr()), ctypes.c_void_p(d_stage_out.data_ptr()),
+                                     ctypes.c_size_t(M * N2 * 4), 2, ctypes.c_void_p(copy_stream.cuda_stream))
+        assert err == 0, f"cudaMemcpyAsync (device to host) failed: {err}"
+        ev_drained.record(copy_stream)
+
     def e2e_step():
         if rank == 0:
             cn.check(lib.cn_batch_copy_next_async(bh))                     # prefetch of the NEXT batch (side stream)
@@ -459,7 +481,7 @@ def main():
         if world > 1:
             ctx.bcast(batch, 0)
         two_layers()
-        download()
+        download_overlapped()
         if rank == 0:
             cn.check(lib.cn_batch_swap(bh, sp, ctypes.byref(px), ctypes.byref(py), ctypes.byref(pn)))
 
@@ -471,6 +493,8 @@ def main():
     e2.record()
     for _ in range(args.steps):
         e2e_step()
+    if rank == 0:
+        torch.cuda.current_stream().wait_event(ev_drained)   # the last step's result must be on the host inside the timed region
     e3.record()
     barrier()
     ms_e2e = max_over_ranks(e2.elapsed_time(e3))
