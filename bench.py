@@ -384,12 +384,15 @@ def main():
         coded = _lib.Coded(c_codes.data_ptr(), c_scales.data_ptr(), c_own.data_ptr(), M, N1)
         no_epi = cn.Epilogue(None, 0, 0, None)
 
-    def two_layers():
+    def two_layers(a_ptr=None):
+        """The two sharded products; a_ptr: device address of the column-major batch (default: the resident copy)."""
+        a_ptr = ctypes.c_void_p(a_ptr if a_ptr is not None else batch.data_ptr())
         if coded is not None:
-            cn.check(lib.cn_dotmpi_to_coded_f32(ctx.h, M, K1, N1, batch.data_ptr(), W1.data_ptr(), ctypes.byref(coded), ctypes.byref(no_epi), mode, sp))
+            cn.check(lib.cn_dotmpi_to_coded_f32(ctx.h, M, K1, N1, a_ptr, W1.data_ptr(), ctypes.byref(coded), ctypes.byref(no_epi), mode, sp))
             cn.check(lib.cn_dotmpi_from_coded_f32(ctx.h, ctypes.byref(coded), N2, W2.data_ptr(), out2.data_ptr(), ctypes.byref(no_epi), mode, 0, sp))
             return
-        ctx.dotmpi(batch, W1, N1, out=out1, mode=mode, exchange=exchange)
+        plain = cn.Epilogue(None, 0, 0, None)
+        cn.check(lib.cn_dotmpi_f32(ctx.h, M, K1, N1, a_ptr, W1.data_ptr(), out1.data_ptr(), ctypes.byref(plain), mode, exchange, sp))
         ctx.dotmpi(out1, W2, N2, out=out2, mode=mode, exchange=exchange)
 
     def download():
@@ -474,13 +477,16 @@ def main():
         ev_drained.record(copy_stream)
 
     def e2e_step():
+        # rank 0 multiplies the allocator's current batch where it lies and broadcasts it from there; the other ranks
+        # receive into their resident buffer
+        a_ptr = batch.data_ptr()
         if rank == 0:
             cn.check(lib.cn_batch_copy_next_async(bh))                     # prefetch of the NEXT batch (side stream)
             cn.check(lib.cn_batch_current(bh, ctypes.byref(px), ctypes.byref(py), ctypes.byref(pn)))
-            cudart.cudaMemcpyAsync(ctypes.c_void_p(batch.data_ptr()), px, ctypes.c_size_t(M * K1 * 4), 3, sp)   # current batch -> A
+            a_ptr = px.value
         if world > 1:
-            ctx.bcast(batch, 0)
-        two_layers()
+            cn.check(lib.cn_bcast_f32(ctx.h, ctypes.c_void_p(a_ptr), M * K1, 0, sp))
+        two_layers(a_ptr)
         download_overlapped()
         if rank == 0:
             cn.check(lib.cn_batch_swap(bh, sp, ctypes.byref(px), ctypes.byref(py), ctypes.byref(pn)))
