@@ -1,7 +1,7 @@
 """Extracts the 126-entry dynamic-float codebook from the reference's HDF5 file into a raw
 little-endian float32 dump (504 bytes), checking both sha256 sums.
 
-    python tests/golden/make_codebook.py [/root/reference/source/8bit_floats.hdf5]
+    python tests/golden/make_codebook.py [<reference tree>/source/8bit_floats.hdf5]
 
 The file is a version-0 HDF5 container; its only dataset (/Default, 126 x 1 float32, contiguous) is the
 last 504 bytes.  The dump is written to tests/golden/codebook_126.f32 and to clusternet_b200/data/.
