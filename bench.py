@@ -183,6 +183,25 @@ def codec_bench(ctx, torch, peaks):
             ms = e0.elapsed_time(e1) / iters
             gbs = n * bytes_per / ms / 1e6
             res[name] = {"GB/s": round(gbs, 1), "us": round(ms * 1e3, 2), "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4)}
+        # the pipeline a caller runs when the scale is not known beforehand: absmax, then the compressor with the scale
+        # taken from device memory (no host synchronisation); 9 algorithmic bytes per element (4 + 4 read, 1 written)
+        scale = torch.zeros(1, device="cuda")
+
+        def pipeline(i):
+            ctx.absmax(xs[i], out=scale)
+            ctx.compress(xs[i], scale, out=codes[i])
+        for i in range(sets):
+            pipeline(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for it in range(iters):
+            pipeline(it % sets)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        res["absmax_then_compress"] = {"GB/s": round(n * 9 / ms / 1e6, 1), "us": round(ms * 1e3, 2),
+                                       "frac_of_hbm_peak": round(n * 9 / ms / 1e6 / peaks["hbm_gbs"], 4)}
         # yardstick at the same size: a plain device copy (read + write bytes) through torch, same rotation of buffers.
         # At 64 MiB a launch lasts ~20 us, so launch ramp and tail weigh on every kernel, the copy included.
         for i in range(sets):
