@@ -2,8 +2,12 @@
 #include <math.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <fcntl.h>
 #include <stdlib.h>
 #include <string.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
 #include "cn_internal.h"
 
 #include <atomic>
@@ -56,9 +60,15 @@ extern "C" int cn_compiled_arch(void) { return 100; }
 // else is reported as unsupported.
 // ------------------------------------------------------------------------------------------------
 namespace {
+// The file is mapped read-only, not read: a data set of several GB is converted straight from the page cache.
 struct H5 {
-    std::vector<unsigned char> b;
-    bool ok(uint64_t off, uint64_t len) const { return off <= b.size() && len <= b.size() - off; }
+    const unsigned char *b = nullptr;
+    uint64_t size = 0;
+    ~H5() { if (b) munmap((void *)b, size); }
+    H5() = default;
+    H5(const H5 &) = delete;
+    H5 &operator=(const H5 &) = delete;
+    bool ok(uint64_t off, uint64_t len) const { return off <= size && len <= size - off; }
     uint64_t u(uint64_t off, int n) const
     {
         uint64_t v = 0;
@@ -146,18 +156,19 @@ namespace {
 int h5_locate(const char *path, const char *dataset, H5 &f, H5Dataset &d, uint64_t &n)
 {
     {
-        FILE *fp = fopen(path, "rb");
-        CN_REQUIRE(fp, CN_ERR_ARG, "cn_hdf5_read: cannot open %s", path);
-        fseek(fp, 0, SEEK_END);
-        const long sz = ftell(fp);
-        fseek(fp, 0, SEEK_SET);
-        if (sz > 0) f.b.resize((size_t)sz);
-        const size_t got = sz > 0 ? fread(f.b.data(), 1, (size_t)sz, fp) : 0;
-        fclose(fp);
-        CN_REQUIRE(sz >= 96 && got == (size_t)sz, CN_ERR_ARG, "cn_hdf5_read: %s is too short", path);
+        const int fd = open(path, O_RDONLY);
+        CN_REQUIRE(fd >= 0, CN_ERR_ARG, "cn_hdf5_read: cannot open %s", path);
+        struct stat sb;
+        const bool stat_ok = fstat(fd, &sb) == 0 && sb.st_size >= 96;
+        void *m = stat_ok ? mmap(nullptr, (size_t)sb.st_size, PROT_READ, MAP_PRIVATE, fd, 0) : MAP_FAILED;
+        close(fd);
+        CN_REQUIRE(stat_ok, CN_ERR_ARG, "cn_hdf5_read: %s is too short", path);
+        CN_REQUIRE(m != MAP_FAILED, CN_ERR_ARG, "cn_hdf5_read: cannot map %s", path);
+        f.b = (const unsigned char *)m;
+        f.size = (uint64_t)sb.st_size;
     }
     static const unsigned char sig[8] = {0x89, 'H', 'D', 'F', '\r', '\n', 0x1a, '\n'};
-    CN_REQUIRE(memcmp(f.b.data(), sig, 8) == 0, CN_ERR_ARG, "cn_hdf5_read: %s has no HDF5 signature", path);
+    CN_REQUIRE(memcmp(f.b, sig, 8) == 0, CN_ERR_ARG, "cn_hdf5_read: %s has no HDF5 signature", path);
     CN_REQUIRE(f.b[8] == 0 && f.b[13] == 8 && f.b[14] == 8, CN_ERR_UNSUPPORTED,
                "cn_hdf5_read: %s: only version-0 superblocks with 8-byte offsets are read", path);
     // root symbol-table entry at byte 56: object header address, cache type, scratch = B-tree and heap addresses
