@@ -41,6 +41,8 @@ _SIGNATURES = {
     "cn_context_device": (c_int, [c_void_p]),
     "cn_codebook_load": (c_int, [c_char_p, c_void_p]),
     "cn_hdf5_read_f32": (c_int, [c_char_p, c_char_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64), ctypes.POINTER(c_int64)]),
+    "cn_hdf5_dims": (c_int, [c_char_p, c_char_p, ctypes.POINTER(c_int64), ctypes.POINTER(c_int64)]),
+    "cn_hdf5_read_f32_into": (c_int, [c_char_p, c_char_p, c_void_p, c_int64]),
     "cn_hdf5_read_i32": (c_int, [c_char_p, c_char_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64), ctypes.POINTER(c_int64)]),
     "cn_host_free": (None, [c_void_p]),
     "cn_hdf5_write_f32": (c_int, [c_char_p, c_char_p, c_void_p, c_int64, c_int64]),

@@ -118,12 +118,10 @@ inline Matrix *empty_cpu(int64_t rows, int64_t cols)
 // read_hdf5 / write_hdf5 (source/util.cu:100-131,202-216) without libhdf5: pinned host matrix, row-major, dataset "/Default"
 inline Matrix *read_hdf5(const char *filepath, const char *tag)
 {
-    float *data = nullptr;
     int64_t rows = 0, cols = 0;
-    cn_detail::check(cn_hdf5_read_f32(filepath, tag, &data, &rows, &cols));
+    cn_detail::check(cn_hdf5_dims(filepath, tag, &rows, &cols));
     Matrix *out = empty_pinned(rows, cols);
-    memcpy(out->data, data, out->bytes);
-    cn_host_free(data);
+    cn_detail::check(cn_hdf5_read_f32_into(filepath, tag, out->data, out->size));
     return out;
 }
 inline Matrix *read_hdf5(const char *filepath) { return read_hdf5(filepath, "/Default"); }

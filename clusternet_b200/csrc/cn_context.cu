@@ -251,6 +251,33 @@ extern "C" int cn_hdf5_read_f32(const char *path, const char *dataset, float **d
 {
     return h5_read<float>(path, dataset, data_out, rows, cols);
 }
+// Shape alone, and conversion into a buffer of the caller (e.g. pinned memory), so that a large data set is neither
+// allocated nor copied twice.
+extern "C" int cn_hdf5_dims(const char *path, const char *dataset, int64_t *rows, int64_t *cols)
+{
+    CN_REQUIRE(path && dataset && rows && cols, CN_ERR_ARG, "cn_hdf5_dims: null argument");
+    H5 f;
+    H5Dataset d;
+    uint64_t n = 0;
+    int st = h5_locate(path, dataset, f, d, n);
+    if (st != CN_OK) return st;
+    *rows = (int64_t)d.dims[0];
+    *cols = d.rank == 2 ? (int64_t)d.dims[1] : 1;
+    return CN_OK;
+}
+extern "C" int cn_hdf5_read_f32_into(const char *path, const char *dataset, float *dst, int64_t capacity)
+{
+    CN_REQUIRE(path && dataset && dst && capacity >= 0, CN_ERR_ARG, "cn_hdf5_read_f32_into: bad argument");
+    H5 f;
+    H5Dataset d;
+    uint64_t n = 0;
+    int st = h5_locate(path, dataset, f, d, n);
+    if (st != CN_OK) return st;
+    CN_REQUIRE(n <= (uint64_t)capacity, CN_ERR_SHAPE, "cn_hdf5_read_f32_into: data set has %llu elements, the buffer %lld",
+               (unsigned long long)n, (long long)capacity);
+    h5_convert(f, d, n, dst);
+    return CN_OK;
+}
 // the same for index data (the CSR files' /indices, /indptr, /shape): integers stay exact beyond 2^24
 extern "C" int cn_hdf5_read_i32(const char *path, const char *dataset, int32_t **data_out, int64_t *rows, int64_t *cols)
 {

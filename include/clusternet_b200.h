@@ -61,6 +61,10 @@ int cn_codebook_load(const char *path, float *codebook126);
  * compact layout, rank 1 or 2, little-endian 4- or 8-byte float or integer data (converted to float, as
  * H5T_NATIVE_FLOAT does).  Release the array with cn_host_free. */
 int cn_hdf5_read_f32(const char *path, const char *dataset, float **data_out, int64_t *rows, int64_t *cols);
+/* Shape of a dataset, and conversion straight into a caller's buffer of `capacity` floats (e.g. pinned memory, as the
+ * reference's read_hdf5 allocates it with cudaHostAlloc, source/util.cu:112-116). */
+int cn_hdf5_dims(const char *path, const char *dataset, int64_t *rows, int64_t *cols);
+int cn_hdf5_read_f32_into(const char *path, const char *dataset, float *dst, int64_t capacity);
 /* The same with 32-bit integer output, for the index datasets of the CSR files (/indices, /indptr, /shape of
  * read_sparse_hdf5, source/util.cu:133-198). */
 int cn_hdf5_read_i32(const char *path, const char *dataset, int32_t **data_out, int64_t *rows, int64_t *cols);

@@ -56,6 +56,15 @@ def test_hdf5_reader_on_the_reference_fixture_and_round_trips(built_lib, tmp_pat
         clusternet_b200.write_hdf5(path, x)
         assert np.array_equal(clusternet_b200.read_hdf5(path), x)
         assert os.path.getsize(path) == 2048 + x.nbytes
+    # shape query and conversion into a caller's buffer
+    import ctypes
+    r, c = ctypes.c_int64(), ctypes.c_int64()
+    assert built_lib.cn_hdf5_dims(str(path).encode(), b"/Default", ctypes.byref(r), ctypes.byref(c)) == 0
+    assert (r.value, c.value) == x.shape
+    buf = np.full(x.size + 3, -7.0, np.float32)
+    assert built_lib.cn_hdf5_read_f32_into(str(path).encode(), b"/Default", buf.ctypes.data, buf.size) == 0
+    assert np.array_equal(buf[:x.size].reshape(x.shape), x) and np.all(buf[x.size:] == -7.0)
+    assert built_lib.cn_hdf5_read_f32_into(str(path).encode(), b"/Default", buf.ctypes.data, x.size - 1) == _lib.CN_ERR_SHAPE
     clusternet_b200.write_hdf5(tmp_path / "named.hdf5", x, "/labels")
     assert np.array_equal(clusternet_b200.read_hdf5(tmp_path / "named.hdf5", "labels"), x)
     with pytest.raises(_lib.CnError, match="not found"):
