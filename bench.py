@@ -2,21 +2,28 @@
 """Benchmark of the dot / dotMPI hot path: the README two-layer skinny product
 (128 x 100000) . (100000 x 40000) . (40000 x 20000), fp32, W column-sharded over the ranks.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--mode 3xtf32|tf32] [--exchange fp32|8bit]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--mode 3xtf32|tf32] [--exchange fp32|8bit|8bit-fused]
 
-One process per GPU (torchrun sets RANK / LOCAL_RANK / WORLD_SIZE for N > 1).  Rank 0 prints one JSON line.
+One process per GPU (torchrun sets RANK / LOCAL_RANK / WORLD_SIZE for N > 1).  Rank 0 prints one JSON line and the
+process exits non-zero when an accuracy or multi-rank check of that line fails.
 
   value     whole-job TFLOP/s of the two dotMPI calls with the batch and the weights resident in HBM
             (2*M*N*K flops, the three TF32 products of the 3xTF32 mode counted once), CUDA events, max over ranks
-  e2e       the same two calls through the C ABI starting from a pinned HOST batch (row-major) and ending with the
-            row-major result in pinned host memory: upload + transpose, broadcast, two dotMPI, transpose + download;
-            the upload of the next batch and the download of the previous result run on side streams
+  e2e       the same two products through the C ABI starting from a pinned, row-major HOST data set and ending with the
+            row-major result in pinned host memory.  Every rank holds the data set (as every process of the reference
+            does with the Matrix* form of BatchAllocator::init), uploads 1/N of the rows of each batch over its own PCIe
+            link on the allocator's side stream and exchanges the blocks over NVLink; the product reads the row-major
+            batch as a transposed operand (TdotMPI form), the result is transposed and copied back on a copy stream
+  accuracy  max |C - C64| / max |C| on columns sampled from EVERY rank's shard of both layers: each rank computes the fp64
+            product of its own weight columns on the host, rank 0 compares them with its gathered copy (so columns that
+            crossed NVLink are checked), and all ranks' gathered copies are compared bit for bit through checksums
+  tf32      the same step in the single-pass TF32 mode, with its own (looser) bound and its HBM roofline
   roofline  the tensor-core kernel of layer 1 alone, timed by events around its launches inside the timed region
   codec     8-bit compress / decompress / absmax GB/s on config 2 (4096 x 4096, rotating buffers) and on 1 GiB
-  cpu_baseline  multithreaded fp32 sgemm (numpy / OpenBLAS) of a column sample of the same product on the host cores
+  cpu_baseline  multithreaded fp32 sgemm (numpy / OpenBLAS) with the flops of the whole step on the host cores
 
 --impl reference times the CPU stand-in of the reference path (clusterNet itself is CUDA + MPI only and cannot be
-built here): the same sgemm on a bounded column sample per step.
+built here): the same sgemm routine, all host threads, one whole step's flops per step.
 """
 import argparse
 import ctypes
@@ -33,6 +40,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 M, K1, N1, N2 = 128, 100000, 40000, 20000
+TOL = {"3xtf32": 1e-5, "tf32": 2e-3}     # max |C - C64| / max |C|: the fp32-level bound, and the stated TF32 bound
 
 
 def set_sizes(k1, n1, n2):
@@ -98,67 +106,81 @@ class ClockSampler:
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_sgemm_sample(seconds_target=12.0, threads=None):
-    """Multithreaded fp32 sgemm of column samples of both layers; returns TFLOP/s and a description."""
+# ------------------------------------------------------------------------------------------------ CPU arm
+def cpu_sgemm_steps(steps, warmup):
+    """The ONE CPU routine, used by both `--impl reference` and the cpu_baseline leg: multithreaded fp32 sgemm
+    (numpy / OpenBLAS) with the flops of one whole step per step.  The weights are a block of 10000 columns per
+    layer that is multiplied 4 (layer 1) and 2 (layer 2) times per step: 40000 and 20000 columns of work without 19 GB of
+    host memory; each block (4 GB, 1.6 GB) is far larger than the CPU caches, so it streams from DRAM like distinct
+    columns would.  The thread count is set explicitly (a launcher such as torchrun exports OMP_NUM_THREADS=1)."""
+    from threadpoolctl import threadpool_info, threadpool_limits
     cores = len(os.sched_getaffinity(0))
+    blk = 10000
+    reps1, reps2 = max(1, N1 // blk), max(1, N2 // blk)
+    blk1, blk2 = N1 // reps1, N2 // reps2
     rng = np.random.default_rng(0)
+    lim1, lim2 = 4.0 * np.sqrt(6.0 / (K1 + N1)), 4.0 * np.sqrt(6.0 / (N1 + N2))
     batch = rng.random((M, K1), dtype=np.float32)
-    lim1 = 4.0 * np.sqrt(6.0 / (K1 + N1))
-    probe_cols = 256
-    W = rng.uniform(-lim1, lim1, (K1, probe_cols)).astype(np.float32)
-    t = time.perf_counter(); batch @ W; dt = time.perf_counter() - t
-    t = time.perf_counter(); batch @ W; dt = min(dt, time.perf_counter() - t)
-    rate = 2.0 * M * K1 * probe_cols / dt
-    cols1 = int(min(N1, max(probe_cols, seconds_target * 0.8 * rate / (2.0 * M * K1) / 3)))
-    cols1 = max(256, cols1 // 256 * 256)
-    W1 = rng.uniform(-lim1, lim1, (K1, cols1)).astype(np.float32)
-    lim2 = 4.0 * np.sqrt(6.0 / (N1 + N2))
-    cols2 = max(128, cols1 // 2)
-    W2 = rng.uniform(-lim2, lim2, (N1, cols2)).astype(np.float32)
     act = rng.random((M, N1), dtype=np.float32)
-    best = None
-    for _ in range(3):
-        t = time.perf_counter()
-        batch @ W1
-        act @ W2
-        d = time.perf_counter() - t
-        best = d if best is None else min(best, d)
-    flops = 2.0 * M * K1 * cols1 + 2.0 * M * N1 * cols2
-    return flops / best / 1e12, cores, f"numpy float32 @ (OpenBLAS): 128x{K1} . {K1}x{cols1} + 128x{N1} . {N1}x{cols2} column sample, best of 3"
+    W1 = rng.random((K1, blk1), dtype=np.float32)
+    W1 *= np.float32(2 * lim1); W1 -= np.float32(lim1)
+    W2 = rng.random((N1, blk2), dtype=np.float32)
+    W2 *= np.float32(2 * lim2); W2 -= np.float32(lim2)
+    o1, o2 = np.empty((M, blk1), np.float32), np.empty((M, blk2), np.float32)
+
+    def step():
+        for _ in range(reps1):
+            np.matmul(batch, W1, out=o1)
+        for _ in range(reps2):
+            np.matmul(act, W2, out=o2)
+
+    with threadpool_limits(limits=cores):
+        used = max([d.get("num_threads", 1) for d in threadpool_info() if d.get("user_api") == "blas"] or [1])
+        for _ in range(warmup):
+            step()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        dt = time.perf_counter() - t0
+    flops = 2.0 * M * (K1 * blk1 * reps1 + N1 * blk2 * reps2)
+    sample = (f"per step {reps1} x (128x{K1} . {K1}x{blk1}) + {reps2} x (128x{N1} . {N1}x{blk2}) = {flops / FLOPS_STEP:.3f} of the step's flops; "
+              f"numpy float32 matmul (OpenBLAS), {used} threads, mean of {steps} steps after {warmup} warm-up")
+    return {"value": flops * steps / dt / 1e12, "ms_per_step": dt / steps * 1e3, "cores": used, "sample": sample,
+            "fraction_of_config": flops / FLOPS_STEP, "host_cores_available": cores}
 
 
 def run_reference(args, rank):
-    """CPU stand-in of the reference path: rank 0 alone, bounded column sample per step."""
+    """CPU stand-in of the reference path: rank 0 alone."""
     if rank != 0:
         return
-    cores = len(os.sched_getaffinity(0))
-    rng = np.random.default_rng(0)
-    batch = rng.random((M, K1), dtype=np.float32)
-    lim1, lim2 = 4.0 * np.sqrt(6.0 / (K1 + N1)), 4.0 * np.sqrt(6.0 / (N1 + N2))
-    cols1, cols2 = 1024, 512
-    W1 = rng.uniform(-lim1, lim1, (K1, cols1)).astype(np.float32)
-    W2 = rng.uniform(-lim2, lim2, (N1, cols2)).astype(np.float32)
-    act = rng.random((M, N1), dtype=np.float32)
-    for _ in range(args.warmup):
-        batch @ W1; act @ W2
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        batch @ W1; act @ W2
-    dt = time.perf_counter() - t0
-    flops = (2.0 * M * K1 * cols1 + 2.0 * M * N1 * cols2) * args.steps
-    v = flops / dt / 1e12
-    sample = f"per step 128x{K1} . {K1}x{cols1} and 128x{N1} . {N1}x{cols2} (column sample of both layers), numpy float32 @ on the host"
+    r = cpu_sgemm_steps(args.steps, max(args.warmup, 1))
     print(json.dumps({
-        "impl": "reference", "metric": "dotMPI TFLOP/s", "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic", "config": {"workload": "README dotMPI two-layer skinny GEMM: 128x100000 . 100000x40000 . 40000x20000, W column-sharded",
-                   "note": "host CPU stand-in: clusterNet has no CPU path and cannot be built here (MPI, HDF5 absent)"},
-        "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
-        "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+        "impl": "reference", "metric": "dotMPI TFLOP/s", "value": r["value"], "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"README dotMPI two-layer skinny GEMM: 128x{K1} . {K1}x{N1} . {N1}x{N2}, W column-sharded",
+                   "note": "host CPU stand-in: clusterNet has no CPU path and cannot be built here (MPI, HDF5 absent)",
+                   "fraction_of_config_per_step": r["fraction_of_config"]},
+        "cpu_baseline": {"value": r["value"], "unit": "TFLOP/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]},
+        "e2e": {"value": r["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------ helpers
+def cuda_time(torch, fn, iters, warm=1):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
 
 
 def codec_bench(ctx, torch, peaks):
-    """compress / decompress / absmax GB/s: config 2 (4096^2, five rotating buffer sets so that no launch finds its
+    """compress / decompress / absmax GB/s: config 2 (4096^2, six rotating buffer sets so that no launch finds its
     input in L2) and a 1 GiB tensor."""
     out = {}
     for label, n, sets, iters in (("config2_4096x4096", 4096 * 4096, 6, 30), ("1GiB", 1 << 28, 2, 6)):
@@ -168,9 +190,17 @@ def codec_bench(ctx, torch, peaks):
         pm = ctx.absmax(xs[0])
         p = float(pm.item())
         res = {}
+        scale = torch.zeros(1, device="cuda")
+
+        def pipeline(i):
+            # what a caller runs when the scale is not known beforehand: absmax, then the compressor with the scale taken
+            # from device memory (no host synchronisation); 9 algorithmic bytes per element (4 + 4 read, 1 written)
+            ctx.absmax(xs[i], out=scale)
+            ctx.compress(xs[i], scale, out=codes[i])
         for name, fn, bytes_per in (("compress", lambda i: ctx.compress(xs[i], p, out=codes[i]), 5),
                                     ("decompress", lambda i: ctx.decompress(codes[i], p, out=outs[i]), 5),
-                                    ("absmax", lambda i: ctx.absmax(xs[i], out=pm), 4)):
+                                    ("absmax", lambda i: ctx.absmax(xs[i], out=pm), 4),
+                                    ("absmax_then_compress", pipeline, 9)):
             for i in range(sets):
                 fn(i)
             torch.cuda.synchronize()
@@ -183,25 +213,6 @@ def codec_bench(ctx, torch, peaks):
             ms = e0.elapsed_time(e1) / iters
             gbs = n * bytes_per / ms / 1e6
             res[name] = {"GB/s": round(gbs, 1), "us": round(ms * 1e3, 2), "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4)}
-        # the pipeline a caller runs when the scale is not known beforehand: absmax, then the compressor with the scale
-        # taken from device memory (no host synchronisation); 9 algorithmic bytes per element (4 + 4 read, 1 written)
-        scale = torch.zeros(1, device="cuda")
-
-        def pipeline(i):
-            ctx.absmax(xs[i], out=scale)
-            ctx.compress(xs[i], scale, out=codes[i])
-        for i in range(sets):
-            pipeline(i)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for it in range(iters):
-            pipeline(it % sets)
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / iters
-        res["absmax_then_compress"] = {"GB/s": round(n * 9 / ms / 1e6, 1), "us": round(ms * 1e3, 2),
-                                       "frac_of_hbm_peak": round(n * 9 / ms / 1e6 / peaks["hbm_gbs"], 4)}
         # yardstick at the same size: a plain device copy (read + write bytes) through torch, same rotation of buffers.
         # At 64 MiB a launch lasts ~20 us, so launch ramp and tail weigh on every kernel, the copy included.
         for i in range(sets):
@@ -231,8 +242,19 @@ def train_step_bench(ctx, cn, _lib, torch, dist, world, rank, steps=30):
     y = torch.randint(0, 10, (B,), device="cuda").float()
     W = [ctx.uniform_sqrt_weight(sizes[i], sizes[i + 1], seed=7 + i) for i in range(3)]     # same weights on every rank
     bias = [torch.zeros(sizes[i + 1], device="cuda") for i in range(3)]
-    rms = [torch.zeros_like(w) for w in W]
-    grad = [torch.zeros_like(w) for w in W]
+    # gradients, RMS state and weights of the three layers each live in ONE packed buffer, so that the exchange and the
+    # update are one call each per step (cn_grad_sync_8bit_multi: a scale per layer, one gather, one decode-sum pass)
+    numel = [w.numel() for w in W]
+    offs = [0, numel[0], numel[0] + numel[1]]
+    total = sum(numel)
+    Wp = torch.empty(total, device="cuda")
+    for i in range(3):
+        Wp[offs[i]:offs[i] + numel[i]] = W[i].reshape(-1)
+    W = [Wp[offs[i]:offs[i] + numel[i]].view(sizes[i + 1], sizes[i]) for i in range(3)]
+    rms_p = torch.zeros(total, device="cuda")
+    grad_p = torch.zeros(total, device="cuda")
+    grad = [grad_p[offs[i]:offs[i] + numel[i]].view(sizes[i + 1], sizes[i]) for i in range(3)]
+    seg = (ctypes.c_int64 * 3)(*numel)
     act = [X] + [ctx.empty(B, sizes[i + 1]) for i in range(3)]
     out = [ctx.empty(B, s) for s in sizes]
     err = [None] + [ctx.empty(B, sizes[i + 1]) for i in range(3)]
@@ -241,12 +263,12 @@ def train_step_bench(ctx, cn, _lib, torch, dist, world, rank, steps=30):
 
     def one_step():
         sp = ctx.stream_ptr()                                                    # the capture stream while recording
-        # forward: (wait for the previous exchange + update), fused dot+bias+activation, dropout
+        # the previous step's gradients: one exchange and one update over the packed buffers (first step: all zero)
+        cn.check(lib.cn_grad_sync_8bit_multi(h, grad_p.data_ptr(), seg, 3, 0.0, sp))
+        cn.check(lib.cn_rmsprop_update(h, rms_p.data_ptr(), grad_p.data_ptr(), Wp.data_ptr(), 0.9, 0.006, total, sp))
+        # forward: fused dot+bias+activation, dropout
         cn.check(lib.cn_dropout_dp(h, act[0].data_ptr(), out[0].data_ptr(), act[0].numel(), drops[0], d_seed.data_ptr(), 0, sp))
         for l in range(3):
-            if True:   # first step: the gradients are zero, the exchange and the update are no-ops on the weights
-                cn.check(lib.cn_grad_sync_8bit(h, grad[l].data_ptr(), grad[l].numel(), 0.0, sp))
-                cn.check(lib.cn_rmsprop_update(h, rms[l].data_ptr(), grad[l].data_ptr(), W[l].data_ptr(), 0.9, 0.006, W[l].numel(), sp))
             last = l == 2
             ctx.gemm(out[l], W[l], out=(out[l + 1] if last else act[l + 1]), bias=bias[l],
                      activation=_lib.ACT_LINEAR if last else _lib.ACT_RELU)
@@ -316,6 +338,14 @@ def train_step_bench(ctx, cn, _lib, torch, dist, world, rank, steps=30):
             "flops_per_step_per_gpu": 6.0 * 128 * (784 * 1200 + 1200 * 1200 + 1200 * 10)}
 
 
+def sample_cols(ncols, n_random, seed):
+    """Columns of a shard to check: both ends, the neighbours of the first tile edges, and random ones."""
+    rng_s = np.random.default_rng(seed)
+    fixed = [0, 1, 127, 128, 129, 255, 256, 257, ncols - 2, ncols - 1]
+    cols = np.unique(np.concatenate([fixed, rng_s.integers(0, max(ncols, 1), n_random)]))
+    return cols[(cols >= 0) & (cols < ncols)]
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -330,6 +360,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-codec", action="store_true")
     ap.add_argument("--no-train-step", action="store_true", help="skip the config-4 training-step measurement")
+    ap.add_argument("--no-extras", action="store_true", help="skip the TF32 leg, config 1, the config-5 sweep and the GPU comparators")
     ap.add_argument("--only-codec", action="store_true", help="run the codec measurements alone (small profiler captures)")
     ap.add_argument("--k1", type=int, default=K1, help="profiling aid: inner dimension of layer 1")
     ap.add_argument("--n1", type=int, default=N1, help="profiling aid: columns of W1 (headline: 40000)")
@@ -368,6 +399,7 @@ def main():
         return
     mode = _lib.GEMM_3XTF32 if args.mode == "3xtf32" else _lib.GEMM_TF32
     exchange = 1 if args.exchange == "8bit" else 0
+    cudart = ctypes.CDLL("libcudart.so.12")
 
     # ---- workload: weights sharded by columns, created on the owning rank (distributed_uniformSqrtWeight)
     s1, c1 = ctx.shard_cols(N1, rank, world)
@@ -377,8 +409,10 @@ def main():
     cn.check(lib.cn_uniform_sqrt_weight(ctx.h, W1.data_ptr(), W1.numel(), K1, N1, seed, 0, ctx.stream_ptr()))
     W2 = ctx.empty(N1, c2)
     cn.check(lib.cn_uniform_sqrt_weight(ctx.h, W2.data_ptr(), W2.numel(), N1, N2, seed + 1, 0, ctx.stream_ptr()))
-    # batch: uniform [0,1) seed 0 on the host (row-major, pinned), as a user of the reference would hold it
-    h_batch = torch.from_numpy(np.random.default_rng(0).random((M, K1), dtype=np.float32)).pin_memory()
+    # data set of two batches, uniform [0,1) seed 0, on the host (row-major, pinned) of EVERY rank
+    h_batch = torch.from_numpy(np.random.default_rng(0).random((M, K1), dtype=np.float32))
+    h_set = torch.cat([h_batch, h_batch.flip(0)], 0).pin_memory()
+    h_lab = torch.zeros((2 * M, 1), dtype=torch.float32).pin_memory()
     h_out = torch.empty((M, N2), dtype=torch.float32).pin_memory()
     d_stage_in = torch.empty((M, K1), dtype=torch.float32, device="cuda")
     d_stage_out = torch.empty((M, N2), dtype=torch.float32, device="cuda")
@@ -389,11 +423,9 @@ def main():
     out2 = ctx.sym_empty(M, N2) if fused else ctx.empty(M, N2)
     sp = ctx.stream_ptr()
 
-    def upload():
-        if rank == 0:
-            cn.check(lib.cn_upload_row_major(ctx.h, h_batch.data_ptr(), d_stage_in.data_ptr(), batch.data_ptr(), M, K1, sp))
-        if world > 1:
-            ctx.bcast(batch, 0)
+    def upload(which=0):
+        """Plain (untimed) upload of batch `which` of the data set into the resident column-major copy, on every rank."""
+        cn.check(lib.cn_upload_row_major(ctx.h, h_set[which * M:(which + 1) * M].data_ptr(), d_stage_in.data_ptr(), batch.data_ptr(), M, K1, sp))
 
     coded = None
     if args.exchange == "8bit-fused":
@@ -401,22 +433,22 @@ def main():
         c_scales = torch.zeros(world, dtype=torch.float32, device="cuda")
         c_own = torch.empty((c1, M), dtype=torch.float32, device="cuda")
         coded = _lib.Coded(c_codes.data_ptr(), c_scales.data_ptr(), c_own.data_ptr(), M, N1)
-        no_epi = cn.Epilogue(None, 0, 0, None)
+    no_epi = cn.Epilogue(None, 0, 0, None)
 
-    def two_layers(a_ptr=None):
-        """The two sharded products; a_ptr: device address of the column-major batch (default: the resident copy)."""
+    def two_layers(a_ptr=None, gemm_mode=None, row_major=False):
+        """The two sharded products.  a_ptr: device address of the batch (default: the resident column-major copy);
+        row_major: a_ptr is the row-major batch, read as a transposed operand."""
+        gm = mode if gemm_mode is None else gemm_mode
         a_ptr = ctypes.c_void_p(a_ptr if a_ptr is not None else batch.data_ptr())
         if coded is not None:
-            cn.check(lib.cn_dotmpi_to_coded_f32(ctx.h, M, K1, N1, a_ptr, W1.data_ptr(), ctypes.byref(coded), ctypes.byref(no_epi), mode, sp))
-            cn.check(lib.cn_dotmpi_from_coded_f32(ctx.h, ctypes.byref(coded), N2, W2.data_ptr(), out2.data_ptr(), ctypes.byref(no_epi), mode, 0, sp))
+            cn.check(lib.cn_dotmpi_to_coded_f32(ctx.h, M, K1, N1, a_ptr, W1.data_ptr(), ctypes.byref(coded), ctypes.byref(no_epi), gm, sp))
+            cn.check(lib.cn_dotmpi_from_coded_f32(ctx.h, ctypes.byref(coded), N2, W2.data_ptr(), out2.data_ptr(), ctypes.byref(no_epi), gm, 0, sp))
             return
-        plain = cn.Epilogue(None, 0, 0, None)
-        cn.check(lib.cn_dotmpi_f32(ctx.h, M, K1, N1, a_ptr, W1.data_ptr(), out1.data_ptr(), ctypes.byref(plain), mode, exchange, sp))
-        ctx.dotmpi(out1, W2, N2, out=out2, mode=mode, exchange=exchange)
-
-    def download():
-        if rank == 0:
-            cn.check(lib.cn_download_row_major(ctx.h, out2.data_ptr(), d_stage_out.data_ptr(), h_out.data_ptr(), M, N2, sp))
+        if row_major:
+            cn.check(lib.cn_tdotmpi_f32(ctx.h, M, K1, N1, a_ptr, K1, W1.data_ptr(), out1.data_ptr(), ctypes.byref(no_epi), gm, exchange, sp))
+        else:
+            cn.check(lib.cn_dotmpi_f32(ctx.h, M, K1, N1, a_ptr, W1.data_ptr(), out1.data_ptr(), ctypes.byref(no_epi), gm, exchange, sp))
+        ctx.dotmpi(out1, W2, N2, out=out2, mode=gm, exchange=exchange)
 
     def barrier():
         if world > 1:
@@ -430,7 +462,63 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    upload()
+    def decoded_out1():
+        """With the coded exchange out1 is never materialised: rebuild this rank's view of it for the checks."""
+        if coded is None:
+            return
+        out1[s1:s1 + c1] = c_own
+        for r in range(world):
+            if r != rank:
+                sr, cr = ctx.shard_cols(N1, r, world)
+                ctx.decompress(c_codes[sr:sr + cr], c_scales[r:r + 1], out=out1[sr:sr + cr])
+
+    # ---- accuracy over every rank's shard.  Rank r computes, in fp64 on the host, the product of the layer's input with a
+    # sample of ITS OWN weight columns; rank 0 compares all ranks' references with the values in its own gathered copy of
+    # the output, so that columns which arrived from a peer are checked; the gathered copies of all ranks are compared
+    # with each other through a checksum of their bit patterns.
+    def layer_check(act_dev, W_dev, out_dev, col0, ncols_local, seed_):
+        cols = sample_cols(ncols_local, max(6, 54 // world), seed_ + rank)
+        a64 = act_dev.T.double().cpu().numpy()                                # (M, K)
+        w64 = W_dev[torch.from_numpy(cols).cuda()].double().cpu().numpy().T   # (K, ncols)
+        mine = (cols + col0, a64 @ w64)
+        allrefs = [mine]
+        if world > 1:
+            allrefs = [None] * world if rank == 0 else None
+            dist.gather_object(mine, allrefs, dst=0)
+        bits = out_dev.view(torch.int32).to(torch.int64)
+        digest = torch.stack([bits.sum(), (bits * torch.arange(1, bits.shape[1] + 1, device="cuda")).sum()])
+        same = True
+        if world > 1:
+            digests = [torch.zeros_like(digest) for _ in range(world)]
+            dist.all_gather(digests, digest)
+            same = all(bool(torch.equal(d, digests[0])) for d in digests)
+        if rank != 0:
+            return None
+        scale = float(out_dev.abs().max().item())
+        worst, nchecked = 0.0, 0
+        for gcols, ref in allrefs:
+            got = out_dev[torch.from_numpy(gcols).cuda()].double().cpu().numpy().T
+            worst = max(worst, float(np.abs(got - ref).max() / scale))
+            nchecked += len(gcols)
+        return {"err": worst, "columns": nchecked, "replicas_identical": same}
+
+    def accuracy(bound, label):
+        decoded_out1()
+        r1 = layer_check(batch, W1, out1, s1, c1, 7)
+        r2 = layer_check(out1, W2, out2, s2, c2, 11)
+        if rank != 0:
+            return None
+        # with an 8-bit exchange the peers' blocks of out1 are quantised: layer 1 is then checked on rank 0's own shard only
+        lossy = args.exchange != "fp32" and world > 1
+        ok = (r1["err"] <= bound or lossy) and r2["err"] <= bound and r1["replicas_identical"] and r2["replicas_identical"]
+        return {"metric": "max |C - C64| / max |C| over sampled columns of every rank's shard (fp64 host product of the same inputs), "
+                          "compared in rank 0's gathered copy; layer 2 takes the layer-1 output as its input",
+                "mode": label, "layer1": r1["err"], "layer2": r2["err"], "bound": bound, "ok": bool(ok),
+                "shards_checked": world, "columns_checked": [r1["columns"], r2["columns"]],
+                "gathered_copies_identical_on_all_ranks": bool(r1["replicas_identical"] and r2["replicas_identical"]),
+                **({"note": "8-bit exchange: the peers' blocks of layer 1 carry the codec's quantisation error by design"} if lossy else {})}
+
+    upload(0)
     for _ in range(args.warmup):
         two_layers()
     ctx.gemm_check()
@@ -462,16 +550,54 @@ def main():
     l2_ms = max_over_ranks(float(np.mean(kern_ms[1::2]))) if kern_ms else None
     ctx.gemm_check()
     clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+    # the outputs of the last timed step were computed from the resident batch: check them now, before anything else runs
+    acc_main = accuracy(TOL[args.mode], args.mode)
 
-    # ---- timed region 2: end to end from host memory through the C ABI.  The host holds a (pinned, row-major) data set
-    # of two batches; every step one batch is copied host->device by the asynchronous batch allocator on its side
-    # stream (the copy of step i+1 runs while step i computes, as allocate_next_batch_async is meant to be used),
-    # transposed into the current batch, broadcast, multiplied twice, and the result is transposed and copied back.
-    h_set = torch.cat([h_batch, h_batch.flip(0)], 0).pin_memory() if rank == 0 else None
-    h_lab = torch.zeros((2 * M, 1), dtype=torch.float32).pin_memory() if rank == 0 else None
+    # ---- the same step in the other precision mode (3xTF32 <-> TF32), reported separately with its own bound
+    other = None
+    if not args.no_extras and coded is None:
+        oname = "tf32" if args.mode == "3xtf32" else "3xtf32"
+        omode = _lib.GEMM_TF32 if oname == "tf32" else _lib.GEMM_3XTF32
+        for _ in range(2):
+            two_layers(gemm_mode=omode)
+        cn.check(lib.cn_gemm_profile_enable(ctx.h, 1))
+        barrier()
+        o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        osteps = max(5, args.steps // 2)
+        o0.record()
+        for _ in range(osteps):
+            two_layers(gemm_mode=omode)
+        o1.record()
+        barrier()
+        oms = max_over_ranks(o0.elapsed_time(o1)) / osteps
+        obuf = (ctypes.c_float * (4 * osteps + 8))()
+        cn.check(lib.cn_gemm_profile_read(ctx.h, obuf, len(obuf), ctypes.byref(cnt)))
+        cn.check(lib.cn_gemm_profile_enable(ctx.h, 0))
+        ok_ms = [obuf[i] for i in range(min(cnt.value, len(obuf)))]
+        ol1 = max_over_ranks(float(np.mean(ok_ms[0::2]))) if ok_ms else None
+        ctx.gemm_check()
+        oacc = accuracy(TOL[oname], oname)
+        if rank == 0:
+            w_bytes_rank = 4.0 * K1 * (N1 / world)
+            tensor_peak = peaks["bf16_tflops"] / 2.0 / (3.0 if oname == "3xtf32" else 1.0)
+            hbm_bound = 2.0 * M / 4.0 * peaks["hbm_gbs"] / 1e3          # 64 flop per W byte x HBM GB/s -> TFLOP/s
+            l1_tf = 2.0 * M * K1 * (N1 / world) / (ol1 * 1e-3) / 1e12 if ol1 else None
+            other = {"mode": oname, "value": FLOPS_STEP / (oms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": oms, "steps": osteps,
+                     "accuracy": oacc,
+                     "roofline": {"kernel": "cn_gemm_tc_kernel (layer 1, per rank)", "bound": "hbm" if hbm_bound < tensor_peak else "tensor",
+                                  "tensor_peak_tflops": tensor_peak, "hbm_bound_tflops": hbm_bound,
+                                  "achieved_tflops": l1_tf, "ms_per_launch": ol1,
+                                  "achieved": (w_bytes_rank / (ol1 * 1e-3) / 1e9) if ol1 else None, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                  "frac": (w_bytes_rank / (ol1 * 1e-3) / 1e9 / peaks["hbm_gbs"]) if ol1 else None,
+                                  "note": "64 flop per weight byte: the single-pass TF32 mode streams W at the HBM roofline before it reaches the tensor peak; "
+                                          "achieved = W bytes of the launch / its duration"}}
+        two_layers()   # leave out1 / out2 in the main mode again
+
+    # ---- timed region 2: end to end from host memory through the C ABI (see the module docstring)
+    use_rm = coded is None
+    bflags = _lib.BATCH_SHARDED_UPLOAD | (_lib.BATCH_NO_COL_MAJOR if use_rm else 0)
     bh = ctypes.c_void_p()
-    if rank == 0:
-        cn.check(lib.cn_batch_create(ctx.h, h_set.data_ptr(), h_lab.data_ptr(), 2 * M, K1, 1, M, 0, ctypes.byref(bh)))
+    cn.check(lib.cn_batch_create_ex(ctx.h, h_set.data_ptr(), h_lab.data_ptr(), 2 * M, K1, 1, M, 0, bflags, ctypes.byref(bh)))
     px, py, pn = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_int64()
 
     # The result leaves the same way the batch arrives: on a side stream.  The step's output is transposed into a staging
@@ -485,32 +611,29 @@ def main():
     def download_overlapped():
         if rank != 0:
             return
-        main = torch.cuda.current_stream()
-        main.wait_event(ev_drained)
+        main_s = torch.cuda.current_stream()
+        main_s.wait_event(ev_drained)
         cn.check(lib.cn_to_row_major(ctx.h, out2.data_ptr(), d_stage_out.data_ptr(), M, N2, sp))
-        ev_staged.record(main)
+        ev_staged.record(main_s)
         copy_stream.wait_event(ev_staged)
         err = cudart.cudaMemcpyAsync(ctypes.c_void_p(h_out.data_ptr()), ctypes.c_void_p(d_stage_out.data_ptr()),
                                      ctypes.c_size_t(M * N2 * 4), 2, ctypes.c_void_p(copy_stream.cuda_stream))
         assert err == 0, f"cudaMemcpyAsync (device to host) failed: {err}"
         ev_drained.record(copy_stream)
 
-    def e2e_step():
-        # rank 0 multiplies the allocator's current batch where it lies and broadcasts it from there; the other ranks
-        # receive into their resident buffer
-        a_ptr = batch.data_ptr()
-        if rank == 0:
-            cn.check(lib.cn_batch_copy_next_async(bh))                     # prefetch of the NEXT batch (side stream)
-            cn.check(lib.cn_batch_current(bh, ctypes.byref(px), ctypes.byref(py), ctypes.byref(pn)))
-            a_ptr = px.value
-        if world > 1:
-            cn.check(lib.cn_bcast_f32(ctx.h, ctypes.c_void_p(a_ptr), M * K1, 0, sp))
-        two_layers(a_ptr)
-        download_overlapped()
-        if rank == 0:
-            cn.check(lib.cn_batch_swap(bh, sp, ctypes.byref(px), ctypes.byref(py), ctypes.byref(pn)))
+    e2e_batches = []
 
-    cudart = ctypes.CDLL("libcudart.so.12")
+    def e2e_step():
+        cn.check(lib.cn_batch_copy_next_async(bh))                     # upload of the NEXT batch (side stream, all ranks)
+        if use_rm:
+            cn.check(lib.cn_batch_current_row_major(bh, ctypes.byref(px), ctypes.byref(pn)))
+        else:
+            cn.check(lib.cn_batch_current(bh, ctypes.byref(px), ctypes.byref(py), ctypes.byref(pn)))
+        two_layers(px.value, row_major=use_rm)
+        download_overlapped()
+        cn.check(lib.cn_batch_swap(bh, sp, ctypes.byref(px), ctypes.byref(py), ctypes.byref(pn)))
+        e2e_batches.append(len(e2e_batches) % 2)                       # the allocator walks batch 0, 1, 0, 1, ...
+
     for _ in range(2):
         e2e_step()
     barrier()
@@ -523,32 +646,30 @@ def main():
     e3.record()
     barrier()
     ms_e2e = max_over_ranks(e2.elapsed_time(e3))
-    checksum = float(h_out.double().abs().mean())
+    ctx.gemm_check()
+    lib.cn_batch_destroy(bh)
+    barrier()
+    # the end-to-end result, as it arrived on the host, against the resident path on the batch that step used: the two
+    # paths differ only in how the batch reaches the product, so they must agree bit for bit; the resident recomputation
+    # is then checked against fp64 like the main result
+    last = e2e_batches[-1]
+    upload(last)
+    two_layers()
+    ctx.gemm_check()
+    acc_e2e = accuracy(TOL[args.mode], args.mode)
+    e2e_match = None
     if rank == 0:
-        lib.cn_batch_destroy(bh)
+        cn.check(lib.cn_to_row_major(ctx.h, out2.data_ptr(), d_stage_out.data_ptr(), M, N2, sp))
+        torch.cuda.synchronize()
+        e2e_match = bool(torch.equal(d_stage_out.cpu(), h_out))
+    checksum = float(h_out.double().abs().mean())
+    upload(0)
 
-    # ---- accuracy on sampled columns against an fp64 host product (rank 0's shard edges + random columns)
-    def sampled_error(act_dev, W_dev, out_dev, col0, ncols_local, kdim):
-        rng_s = np.random.default_rng(7)
-        cols = np.unique(np.concatenate([[0, 1, 127, 128, 129, ncols_local - 1], rng_s.integers(0, ncols_local, 58)]))
-        cols = cols[(cols >= 0) & (cols < ncols_local)]
-        a64 = act_dev.T.double().cpu().numpy()                      # (M, kdim)
-        w64 = W_dev[torch.from_numpy(cols).cuda()].double().cpu().numpy().T   # (kdim, ncols)
-        ref = a64 @ w64
-        got = out_dev[torch.from_numpy(cols + col0).cuda()].double().cpu().numpy().T
-        scale = float(out_dev.abs().max().item())
-        return float(np.abs(got - ref).max() / scale)
-
-    if coded is not None:   # out1 was never materialised: rebuild this rank's view of it for the check
-        out1[s1:s1 + c1] = c_own
-        for r in range(world):
-            if r != rank:
-                sr, cr = ctx.shard_cols(N1, r, world)
-                ctx.decompress(c_codes[sr:sr + cr], c_scales[r:r + 1], out=out1[sr:sr + cr])
-    err1 = sampled_error(batch, W1, out1, s1, c1, K1)
-    err2 = sampled_error(out1, W2, out2, s2, c2, N1)
-
+    multi = multi_rank_checks(ctx, cn, _lib, torch, dist, world, rank) if world > 1 else None
     train = None if (args.no_train_step or not headline) else train_step_bench(ctx, cn, _lib, torch, dist if world > 1 else None, world, rank)
+    extras = None
+    if not args.no_extras and headline:
+        extras = extra_measurements(ctx, cn, _lib, torch, dist, world, rank, peaks)
 
     if rank != 0:
         if world > 1:
@@ -562,6 +683,7 @@ def main():
     peak = tf32_peak / 3.0 if args.mode == "3xtf32" else tf32_peak
     l1_flops_rank = 2.0 * M * K1 * (N1 // world if world > 1 else N1)
     achieved = l1_flops_rank / (l1_ms * 1e-3) / 1e12 if l1_ms else None
+    e2e_ok = bool(e2e_match and acc_e2e["ok"])
     line = {
         "metric": "dotMPI TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
@@ -571,35 +693,351 @@ def main():
                    "gemm_mode": args.mode, "exchange": args.exchange, "gather": ("fused peer stores" if fused else ("nccl" if world > 1 else "none")), "parallelism": f"tp{world} (columns of W)",
                    "l2": f"inputs larger than L2 ({4e-9 * (K1 * N1 + N1 * N2):.1f} GB of weights stream once per step)", "flops_per_step": FLOPS_STEP},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": M * K1 * 4,
-                "d2h_bytes_per_step": M * N2 * 4, "result_checksum": checksum},
-        "accuracy": {"metric": "max |C - C64| / max |C| over 64 sampled columns of rank 0's shard, fp64 host product of the same inputs",
-                     "layer1": err1, "layer2": err2},
+                "h2d_bytes_per_step_per_rank": M * K1 * 4 // world, "d2h_bytes_per_step": M * N2 * 4, "result_checksum": checksum,
+                "upload": (f"each of the {world} ranks uploads 1/{world} of the batch rows over its own PCIe link, blocks exchanged over NVLink" if world > 1
+                           else "one rank, whole batch") + ("; row-major batch read as a transposed operand" if use_rm else ""),
+                "host_result_equals_resident_path_bitwise": e2e_match, "accuracy_of_that_batch": acc_e2e, "ok": e2e_ok},
+        "accuracy": acc_main,
         "gpu_launches": int(launches),
         "clocks": clocks,
-        "roofline": {"kernel": "cn_gemm_tc_kernel (layer 1, per rank)", "bound": "tensor", "achieved": achieved, "peak": peak,
+        "roofline": {"kernel": "cn_gemm_tc_kernel (layer 1, per rank; with its split-K reduction)", "bound": "tensor", "achieved": achieved, "peak": peak,
                      "unit": "TFLOP/s", "frac": (achieved / peak) if achieved else None,
-                     # DRAM bytes per launch: ncu capture of 128x100000x4096 (profiles/gemm_tc_kernel_128x100000x4096.md:
-                     # 1.772 GB for 1.6384 GB of W), scaled by the W bytes of this rank's layer-1 launch
+                     # DRAM bytes per launch: one ncu capture of a 128 x 100000 x 4096 launch read 1.772 GB for 1.6384 GB of
+                     # W; scaled here by the W bytes of this rank's layer-1 launch
                      "traffic": 1.772e9 / 1.6384e9 * 4.0 * K1 * (N1 // world if world > 1 else N1),
                      "traffic_source": "ncu dram__bytes_read+write of a 4096-column case, scaled by W bytes",
                      "ms_per_launch": l1_ms, "layer2_ms_per_launch": l2_ms,
-                     "peak_source": f"{peaks['source']}: bf16_tflops {peaks['bf16_tflops']} / 2 (TF32 rate)" + (" / 3 (three TF32 products per tile)" if args.mode == "3xtf32" else ""),
-                     # the same against the power-capped (seconds-long) cuBLAS figure, for runs whose clocks show sw_power_cap
-                     "peak_sustained": peaks["bf16_tflops_sustained"] / 2.0 / (3.0 if args.mode == "3xtf32" else 1.0),
+                     "peak_source": f"{peaks['source']} burst: bf16_tflops {peaks['bf16_tflops']} / 2 (TF32 rate)" + (" / 3 (three TF32 products per tile)" if args.mode == "3xtf32" else ""),
+                     # side note: the same against the power-capped (seconds-long) cuBLAS figure
                      "frac_sustained": (achieved / (peaks["bf16_tflops_sustained"] / 2.0 / (3.0 if args.mode == "3xtf32" else 1.0))) if achieved else None,
                      "hbm_frac_layer1": (4.0 * K1 * (N1 / world) / (l1_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]) if l1_ms else None},
     }
+    if other:
+        line[other["mode"]] = other
+    if multi:
+        line["multi_rank_checks"] = multi
     if train:
         line["train_step"] = train
+    if extras:
+        line.update(extras)
     if not args.no_codec and world == 1:
         line["codec"] = codec_bench(ctx, torch, peaks)
     if not args.no_cpu_baseline and world == 1:
-        v, cores, sample = cpu_sgemm_sample()
-        line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample}
+        torch.cuda.synchronize()
+        r = cpu_sgemm_steps(steps=5, warmup=1)
+        line["cpu_baseline"] = {"value": r["value"], "unit": "TFLOP/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]}
+    failed = []
+    if not acc_main["ok"]:
+        failed.append("accuracy")
+    if not e2e_ok:
+        failed.append("e2e")
+    if other and not other["accuracy"]["ok"]:
+        failed.append(other["mode"] + ".accuracy")
+    if multi and not multi["ok"]:
+        failed.append("multi_rank_checks")
+    line["checks_failed"] = failed
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if failed:
+        print(f"bench.py: FAILED checks: {failed}", file=sys.stderr, flush=True)
+        sys.exit(3)
+
+
+def multi_rank_checks(ctx, cn, _lib, torch, dist, world, rank):
+    """Correctness of everything that crosses GPUs, small and exact, on every bench run with more than one rank:
+    the reference's own multi-rank pins (tests/clusterNet_test.cu:257-276: dotMPI == dot elementwise on constant
+    matrices; :338-394: all-ones sharded weight, dot -> 8783, dotTMPI -> 317, dot into the sharded matrix -> 17) and the
+    8-bit paths, each checked against the same computation composed from single-GPU kernels."""
+    res = {"ranks": world}
+    dev = "cuda"
+
+    def all_true(flag):
+        t = torch.tensor([1 if flag else 0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item())
+    # dotMPI == dot, elementwise exact, 200x400 . 400x800 constants; plain NCCL gather and the fused peer-store gather
+    A = torch.full((400, 200), 0.3, device=dev)
+    B = torch.full((800, 400), 1.1748345, device=dev)
+    s0, c0 = ctx.shard_cols(800, rank, world)
+    full = ctx.gemm(A, B)
+    C = ctx.dotmpi(A, B[s0:s0 + c0].contiguous(), 800)
+    Cs = ctx.sym_empty(200, 800)
+    Cs.zero_()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ctx.dotmpi(A, B[s0:s0 + c0].contiguous(), 800, out=Cs)
+    ctx.gemm_check()
+    res["dotmpi_equals_dot_exact"] = all_true(torch.equal(C, full))
+    res["fused_gather_equals_nccl_gather_exact"] = all_true(torch.equal(Cs, C))
+    # random data, uneven shards (N % G != 0), bias + ReLU through the fused gather and through NCCL: identical, and
+    # equal to the unsharded product up to the split-K schedule
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)
+    Mx, Kx, Nx = 128, 4096, 2048 + 256 * world + 4
+    A = torch.rand((Kx, Mx), device=dev, generator=g) * 2 - 1
+    W = torch.rand((Nx, Kx), device=dev, generator=g) * 2 - 1
+    bias = torch.rand(Nx, device=dev, generator=g)
+    s0, c0 = ctx.shard_cols(Nx, rank, world)
+    Wsh = W[s0:s0 + c0].contiguous()
+    full = ctx.gemm(A, W, bias=bias, activation=_lib.ACT_RELU)
+    Cn = ctx.dotmpi(A, Wsh, Nx, bias=bias, activation=_lib.ACT_RELU)
+    Cf = ctx.sym_empty(Mx, Nx)
+    ok_f = True
+    for rep in range(2):
+        Cf.zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        ctx.dotmpi(A, Wsh, Nx, out=Cf, bias=bias, activation=_lib.ACT_RELU)
+        ctx.gemm_check()
+        ok_f = ok_f and bool(torch.equal(Cf, Cn))
+    res["uneven_shards_fused_equals_nccl_exact"] = all_true(ok_f)
+    ref = torch.relu(A.double().T @ W.double().T + bias.double())            # (M, N) fp64 on the GPU (library, checker only)
+    err = float(((Cn.T.double() - ref).abs().max() / ref.abs().max()).item())
+    res["uneven_shards_vs_fp64"] = err
+    res["uneven_shards_vs_unsharded"] = float(((Cn - full).abs().max() / ref.abs().max()).item())
+    # TdotMPI (transposed first operand, sharded B) == dotMPI
+    At = A.T.contiguous()                                                     # stored K x M column-major = (M, K) tensor
+    Ct = ctx.empty(Mx, Nx)
+    epi = cn.Epilogue(bias.data_ptr(), _lib.ACT_RELU, 0, None)
+    cn.check(ctx.lib.cn_tdotmpi_f32(ctx.h, Mx, Kx, Nx, At.data_ptr(), Kx, Wsh.data_ptr(), Ct.data_ptr(), ctypes.byref(epi), _lib.GEMM_3XTF32, 0,
+                                    ctx.stream_ptr()))
+    res["tdotmpi_equals_dotmpi_exact"] = all_true(torch.equal(Ct, Cn))
+    # all-ones 8783 x 317 sharded weight
+    s0, c0 = ctx.shard_cols(317, rank, world)
+    m1 = torch.ones((c0, 8783), device=dev)
+    m2, m3, m4 = torch.ones((8783, 111), device=dev), torch.ones((317, 17), device=dev), torch.ones((17, 8783), device=dev)
+    ok = True
+    for _ in range(2):
+        d = ctx.dotmpi(m2, m1, 317)
+        ok = ok and bool((d == 8783.0).all())
+        t = ctx.dottmpi(m3, m1)
+        ok = ok and bool((t == 317.0).all())
+        ctx.dot_sharded_out(m4, m3, m1)
+        ok = ok and bool((m1 == 17.0).all())
+        m1.fill_(1.0)
+    res["ones_8783_317_17_exact"] = all_true(ok)
+    # dotTMPI on random data against fp64
+    Ar = torch.rand((400, 64), device=dev, generator=g) * 2 - 1               # A 64 x 400
+    Bf = torch.rand((400, 96), device=dev, generator=g) * 2 - 1               # B 96 x 400 (full), sharded by columns
+    s0, c0 = ctx.shard_cols(400, rank, world)
+    got = ctx.dottmpi(Ar, Bf[s0:s0 + c0].contiguous())
+    ref = Ar.double().T @ Bf.double()                                         # (64 x 400) . (400 x 96)
+    res["dottmpi_vs_fp64"] = float(((got.T.double() - ref).abs().max() / ref.abs().max()).item())
+    # 8-bit exchange of C: own block exact, peers' blocks = decompress(compress(block, absmax(block))) with the single-GPU kernels
+    C8 = ctx.dotmpi(A, Wsh, Nx, bias=bias, activation=_lib.ACT_RELU, exchange=1)
+    ok = True
+    for r in range(world):
+        sr, cr = ctx.shard_cols(Nx, r, world)
+        blk = Cn[sr:sr + cr].contiguous()
+        if r == rank:
+            ok = ok and bool(torch.equal(C8[sr:sr + cr], blk))
+        else:
+            pm = ctx.absmax(blk)
+            ok = ok and bool(torch.equal(C8[sr:sr + cr], ctx.decompress(ctx.compress(blk, pm), pm)))
+    res["exchange_8bit_equals_single_gpu_codec_exact"] = all_true(ok)
+    # 8-bit exchange decoded in the consumer's prologue == decoding first
+    W2 = torch.rand((512, Nx), device=dev, generator=g) * 2 - 1
+    s2, c2 = ctx.shard_cols(512, rank, world)
+    W2sh = W2[s2:s2 + c2].contiguous()
+    ref2 = ctx.dotmpi(C8, W2sh, 512)
+    coded, keep = ctx.dotmpi_to_coded(A, Wsh, Nx, bias=bias, activation=_lib.ACT_RELU, rank=rank, nranks=world)
+    got2 = ctx.dotmpi_from_coded(coded, W2sh, 512)
+    ctx.gemm_check()
+    res["coded_chain_equals_decode_first_exact"] = all_true(torch.equal(got2, ref2))
+    # 8-bit gradient exchange: own gradient + decode(encode(peer gradient)) in rank order, single call and packed call
+    n = 70001
+    grads = []
+    for r in range(world):
+        gg = torch.Generator(device=dev)
+        gg.manual_seed(100 + r)
+        grads.append(torch.randn(n, device=dev, generator=gg) * (0.01 * (r + 1)))
+    want = grads[rank].clone()
+    for r in range(world):
+        if r != rank:
+            pm = ctx.absmax(grads[r])
+            want = want + ctx.decompress(ctx.compress(grads[r], pm), pm)
+    gmine = grads[rank].clone()
+    cn.check(ctx.lib.cn_grad_sync_8bit(ctx.h, gmine.data_ptr(), n, 0.0, ctx.stream_ptr()))
+    res["grad_sync_8bit_equals_single_gpu_codec_exact"] = all_true(torch.equal(gmine, want))
+    segs = [30001, 40000]
+    gpk = grads[rank].clone()
+    seg = (ctypes.c_int64 * 2)(*segs)
+    cn.check(ctx.lib.cn_grad_sync_8bit_multi(ctx.h, gpk.data_ptr(), seg, 2, 0.0, ctx.stream_ptr()))
+    want2 = grads[rank].clone()
+    o = 0
+    for sz in segs:
+        for r in range(world):
+            if r != rank:
+                piece = grads[r][o:o + sz].contiguous()
+                pm = ctx.absmax(piece)
+                want2[o:o + sz] += ctx.decompress(ctx.compress(piece, pm), pm)
+        o += sz
+    res["grad_sync_packed_equals_single_gpu_codec_exact"] = all_true(torch.equal(gpk, want2))
+    ctx.gemm_check()
+    torch.cuda.synchronize()
+    dist.barrier()
+    exact = [k for k in res if k.endswith("_exact")]
+    res["ok"] = bool(all(res[k] for k in exact) and res["uneven_shards_vs_fp64"] <= 1e-5 and res["dottmpi_vs_fp64"] <= 1e-5
+                     and res["uneven_shards_vs_unsharded"] <= 2e-6)
+    return res
+
+
+def extra_measurements(ctx, cn, _lib, torch, dist, world, rank, peaks):
+    """Config 1 latency, config-5 sweep points and, on one GPU, the same-box comparators (library kernels and the
+    reference's own codec kernels) - all outside the product's timed regions; a few seconds in total."""
+    out = {}
+    dev = "cuda"
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+
+    def rnd(rows, cols):
+        return torch.rand((cols, rows), device=dev, generator=g) * 2 - 1       # column-major rows x cols
+
+    def sampled_err(A, W, C, nrow=64, ncol=32):
+        """max |C - C64| / max |C| on a sample of rows and columns, fp64 product on the GPU (checker only)."""
+        Mx, Nx = A.shape[1], W.shape[0]
+        ri = torch.randint(0, Mx, (min(nrow, Mx),), device=dev, generator=g)
+        ci = torch.randint(0, Nx, (min(ncol, Nx),), device=dev, generator=g)
+        ref = A[:, ri].double().T @ W[ci].double().T
+        got = C[ci][:, ri].double().T
+        return float(((got - ref).abs().max() / C.abs().max().double()).item())
+    if rank == 0:
+        # config 1: 128x784 . 784x1024 + bias + ReLU, uniform(-1, 1)
+        A, W, b = rnd(128, 784), rnd(784, 1024), torch.rand(1024, device=dev, generator=g) * 2 - 1
+        C = ctx.empty(128, 1024)
+        c1res = {"workload": "config 1: 128x784 . 784x1024 + bias + ReLU"}
+        for name, md in (("3xtf32", _lib.GEMM_3XTF32), ("tf32", _lib.GEMM_TF32), ("fp32_simt", _lib.GEMM_FP32_SIMT)):
+            ms = cuda_time(torch, lambda: ctx.gemm(A, W, out=C, bias=b, activation=_lib.ACT_RELU, mode=md), 50, 3)
+            ref = torch.relu(A.double().T @ W.double().T + b.double())
+            c1res[name] = {"us": round(ms * 1e3, 2), "err": float(((C.T.double() - ref).abs().max() / ref.abs().max()).item())}
+        ms = cuda_time(torch, lambda: torch.relu(torch.addmm(b, A.T, W.T)), 50, 3)
+        c1res["torch_addmm_relu_fp32"] = {"us": round(ms * 1e3, 2), "note": "library comparator (cuBLAS sgemm + elementwise), not on the product path"}
+        out["config1"] = c1res
+    # config 5 sweep (the points that fit a few seconds): square n^3 and skinny 128 x n x n, both modes, on rank 0's GPU;
+    # with more than one rank the skinny 40000 point also runs sharded, with and without the 8-bit gather
+    sweep = []
+    if rank == 0:
+        free = torch.cuda.mem_get_info()[0]
+        pts = [("square", 4096, 4096, 4096), ("square", 8192, 8192, 8192), ("skinny", 128, 10000, 10000), ("skinny", 128, 40000, 40000)]
+        if world == 1 and free > 60e9:
+            pts.append(("skinny", 128, 100000, 100000))
+        for kind, Mx, Kx, Nx in pts:
+            A, W = rnd(Mx, Kx), ctx.empty(Kx, Nx)
+            cn.check(ctx.lib.cn_rand_uniform(ctx.h, W.data_ptr(), W.numel(), 77, 0, ctx.stream_ptr()))
+            W.mul_(2).sub_(1)
+            C = ctx.empty(Mx, Nx)
+            entry = {"shape": f"{Mx}x{Kx} . {Kx}x{Nx}", "kind": kind}
+            for name, md in (("3xtf32", _lib.GEMM_3XTF32), ("tf32", _lib.GEMM_TF32)):
+                iters = 3 if Kx * Nx > 2e9 else 8
+                ms = cuda_time(torch, lambda: ctx.gemm(A, W, out=C, mode=md), iters, 2)
+                entry[name] = {"TFLOP/s": round(2.0 * Mx * Kx * Nx / (ms * 1e-3) / 1e12, 1), "ms": round(ms, 4), "err": sampled_err(A, W, C)}
+            ctx.gemm_check()
+            sweep.append(entry)
+            del A, W, C
+            torch.cuda.empty_cache()
+    if world > 1:
+        Mx, Kx, Nx = 128, 40000, 40000
+        s0, c0 = ctx.shard_cols(Nx, rank, world)
+        A = ctx.empty(Mx, Kx)
+        cn.check(ctx.lib.cn_rand_uniform(ctx.h, A.data_ptr(), A.numel(), 5, 0, ctx.stream_ptr()))   # same seed: same A on every rank
+        Wsh = ctx.empty(Kx, c0)
+        cn.check(ctx.lib.cn_rand_uniform(ctx.h, Wsh.data_ptr(), Wsh.numel(), 1000 + rank, 0, ctx.stream_ptr()))
+        Cs = ctx.sym_empty(Mx, Nx)
+        Cp = ctx.empty(Mx, Nx)
+        entry = {"shape": f"{Mx}x{Kx} . {Kx}x{Nx} sharded over {world} ranks", "kind": "skinny, dotMPI"}
+        for name, fn in (("fp32_fused_gather", lambda: ctx.dotmpi(A, Wsh, Nx, out=Cs)),
+                         ("fp32_nccl_gather", lambda: ctx.dotmpi(A, Wsh, Nx, out=Cp)),
+                         ("8bit_gather", lambda: ctx.dotmpi(A, Wsh, Nx, out=Cp, exchange=1))):
+            torch.cuda.synchronize()
+            dist.barrier()
+            ms = cuda_time(torch, fn, 8, 2)
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            entry[name] = {"TFLOP/s": round(2.0 * Mx * Kx * Nx / (float(t.item()) * 1e-3) / 1e12, 1), "ms": round(float(t.item()), 4)}
+        ctx.gemm_check()
+        if rank == 0:
+            sweep.append(entry)
+    if rank == 0:
+        out["sweep"] = sweep
+    if world == 1:
+        out["gpu_comparators"] = gpu_comparators(ctx, cn, _lib, torch, peaks)
+    return out
+
+
+def gpu_comparators(ctx, cn, _lib, torch, peaks):
+    """Same-box comparators, bench-only and labelled: (1) the library call the reference makes for its product,
+    cublasSgemm (source/clusterNet.cpp:459-461), reached through torch.matmul with TF32 off, on the per-rank shapes of
+    both layers; (2) the reference's own codec kernels compiled for sm_100a (oracle/_ref, test infrastructure) timed on
+    config 2 and on the reference's compression_test shape (source/test.cu:2037-2057: 5120 x 5120, N(0,1)/10, precision
+    0.1), beside the product's kernels on the same data.  Nothing here is on the product path."""
+    res = {"note": "library / reference kernels timed for comparison only; never linked into or called by the product"}
+    dev = "cuda"
+    prev = torch.backends.cuda.matmul.allow_tf32
+    try:
+        sg = {}
+        for label, Mx, Kx, Nx in (("layer1_128x100000x40000", M, K1, N1), ("layer2_128x40000x20000", M, N1, N2)):
+            A = torch.rand((Mx, Kx), device=dev)
+            W = torch.rand((Nx, Kx), device=dev)
+            entry = {}
+            for name, tf in (("cublas_sgemm_fp32", False), ("cublas_tf32", True)):
+                torch.backends.cuda.matmul.allow_tf32 = tf
+                ms = cuda_time(torch, lambda: torch.matmul(A, W.T), 3, 1)
+                entry[name] = {"TFLOP/s": round(2.0 * Mx * Kx * Nx / (ms * 1e-3) / 1e12, 1), "ms": round(ms, 3)}
+            Ac, Wc, C = A.T.contiguous(), W, ctx.empty(Mx, Nx)     # column-major views of the same data
+            for name, md in (("ours_3xtf32", _lib.GEMM_3XTF32), ("ours_tf32", _lib.GEMM_TF32)):
+                ms = cuda_time(torch, lambda: ctx.gemm(Ac, Wc, out=C, mode=md), 3, 1)
+                entry[name] = {"TFLOP/s": round(2.0 * Mx * Kx * Nx / (ms * 1e-3) / 1e12, 1), "ms": round(ms, 3)}
+            sg[label] = entry
+            del A, W, Ac, C
+            torch.cuda.empty_cache()
+        res["sgemm"] = sg
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    ref_path = os.path.join(ROOT, "oracle", "_ref", "libcnref.so")
+    if not os.path.exists(ref_path):
+        res["reference_codec_kernels"] = "oracle/_ref/libcnref.so is not built on this box"
+        return res
+    ref = ctypes.CDLL(ref_path)
+    if not hasattr(ref, "ref_compression_8bit_async"):
+        res["reference_codec_kernels"] = "oracle/_ref/libcnref.so predates the asynchronous launchers: rebuild it (make -C oracle ref)"
+        return res
+    ref.ref_compression_8bit_async.restype = None
+    ref.ref_decompression_8bit_async.restype = None
+    tbl = torch.from_numpy(ctx.codebook.copy()).cuda()
+    codec = {}
+    for label, n, p, sigma in (("config2_4096x4096", 4096 * 4096, None, 0.1), ("compression_test_5120x5120_precision_0.1", 5120 * 5120, 0.1, 0.1)):
+        sets = 5
+        xs = [torch.randn(n, device=dev) * sigma for _ in range(sets)]
+        codes = [torch.empty(n, dtype=torch.uint8, device=dev) for _ in range(sets)]
+        outs = [torch.empty(n, device=dev) for _ in range(sets)]
+        prec = p if p is not None else float(ctx.absmax(xs[0]).item())
+        entry = {"precision": prec}
+        k = [0]
+
+        def rot(fn):
+            def run():
+                fn(k[0] % sets)
+                k[0] += 1
+            return run
+        pairs = (("compress", 5, lambda i: ctx.compress(xs[i], prec, out=codes[i]),
+                  lambda i: ref.ref_compression_8bit_async(ctypes.c_void_p(tbl.data_ptr()), ctypes.c_void_p(xs[i].data_ptr()), ctypes.c_float(prec), n,
+                                                     ctypes.c_void_p(codes[i].data_ptr()))),
+                 ("decompress", 5, lambda i: ctx.decompress(codes[i], prec, out=outs[i]),
+                  lambda i: ref.ref_decompression_8bit_async(ctypes.c_void_p(tbl.data_ptr()), ctypes.c_void_p(codes[i].data_ptr()), ctypes.c_float(prec), n,
+                                                       ctypes.c_void_p(outs[i].data_ptr()))))
+        for name, bpe, ours, theirs in pairs:
+            ms_o = cuda_time(torch, rot(ours), 20, sets)
+            ms_r = cuda_time(torch, rot(theirs), 10, sets)     # the reference launches on the NULL stream, which orders with torch's
+            entry[name] = {"ours_us": round(ms_o * 1e3, 2), "ours_GB/s": round(n * bpe / ms_o / 1e6, 1),
+                           "reference_kernel_us": round(ms_r * 1e3, 2), "reference_kernel_GB/s": round(n * bpe / ms_r / 1e6, 1),
+                           "speedup": round(ms_r / ms_o, 2)}
+        codec[label] = entry
+        del xs, codes, outs
+        torch.cuda.empty_cache()
+    res["reference_codec_kernels"] = codec
+    return res
 
 
 if __name__ == "__main__":

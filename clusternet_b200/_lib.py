@@ -17,6 +17,7 @@ c_uint64 = ctypes.c_uint64
 CN_OK, CN_ERR_ARG, CN_ERR_SHAPE, CN_ERR_CUDA, CN_ERR_NCCL, CN_ERR_TIMEOUT, CN_ERR_UNSUPPORTED, CN_ERR_NOMEM = range(8)
 GEMM_3XTF32, GEMM_TF32, GEMM_FP32_SIMT = 0, 1, 2
 ACT_LINEAR, ACT_RELU, ACT_LOGISTIC, ACT_DOUBLE_RELU = 0, 1, 2, 3
+BATCH_KEEP_ROW_MAJOR, BATCH_NO_COL_MAJOR, BATCH_SHARDED_UPLOAD = 1, 2, 4
 
 
 class Coded(ctypes.Structure):
@@ -35,6 +36,7 @@ _SIGNATURES = {
     "cn_kernel_launches": (c_uint64, []),
     "cn_diag_wait_probe": (c_int, [c_void_p, c_int64, c_void_p]),
     "cn_gemm_profile_enable": (c_int, [c_void_p, c_int]),
+    "cn_gemm_set_tuning": (c_int, [c_void_p, c_int, c_int, c_int]),
     "cn_gemm_profile_read": (c_int, [c_void_p, c_void_p, c_int, ctypes.POINTER(c_int)]),
     "cn_context_create": (c_int, [c_int, c_void_p, ctypes.POINTER(c_void_p)]),
     "cn_context_destroy": (c_int, [c_void_p]),
@@ -88,6 +90,8 @@ _SIGNATURES = {
     "cn_sym_free": (c_int, [c_void_p, c_void_p]),
     "cn_dotmpi_f32": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, ctypes.POINTER(Epilogue),
                               c_int, c_int, c_void_p]),
+    "cn_tdotmpi_f32": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p, ctypes.POINTER(Epilogue),
+                               c_int, c_int, c_void_p]),
     "cn_dotmpi_to_coded_f32": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, ctypes.POINTER(Coded),
                                        ctypes.POINTER(Epilogue), c_int, c_void_p]),
     "cn_dotmpi_from_coded_f32": (c_int, [c_void_p, ctypes.POINTER(Coded), c_int64, c_void_p, c_void_p, ctypes.POINTER(Epilogue),
@@ -109,7 +113,10 @@ _SIGNATURES = {
     "cn_activation_gradient": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p]),
     "cn_rmsprop_update": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_int64, c_void_p]),
     "cn_grad_sync_8bit": (c_int, [c_void_p, c_void_p, c_int64, c_float, c_void_p]),
+    "cn_grad_sync_8bit_multi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
     "cn_batch_create": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, ctypes.POINTER(c_void_p)]),
+    "cn_batch_create_ex": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int, ctypes.POINTER(c_void_p)]),
+    "cn_batch_current_row_major": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64)]),
     "cn_batch_destroy": (c_int, [c_void_p]),
     "cn_batch_total_batches": (c_int64, [c_void_p]),
     "cn_batch_current": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64)]),

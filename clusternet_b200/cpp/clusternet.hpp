@@ -437,6 +437,11 @@ public:
     int64_t TOTAL_BATCHES = 0, TOTAL_BATCHES_CV = 0, BATCH_SIZE = 0, BATCH_SIZE_CV = 0, TRAIN_SET_ROWS = 0, CV_SET_ROWS = 0;
     bool SKIP_LAST_BATCH = false;
     BatchAllocationMethod_t BATCH_METHOD = Single_GPU;
+    // Set before init: with Batch_split / Distributed_weights every process passes the whole data set (as in
+    // tests/batchAllocator_test.cu:22-114, where each process makes its own X, y) and uploads only its 1/G of the rows of
+    // each batch over its own PCIe link; the blocks are exchanged over NVLink (CN_BATCH_SHARDED_UPLOAD).  Default: only
+    // rank 0's data set is used and every batch is broadcast from it.
+    bool EVERY_RANK_HOLDS_DATA = false;
 
     // data set read from two HDF5 files (source/batchAllocator.cpp:62-99; the csv branch of the reference is not built).
     // As in the reference only rank 0 reads the files unless every process serves itself (Single_GPU).
@@ -490,8 +495,10 @@ private:
     {
         ctx_ = ctx;
         BATCH_METHOD = method;
-        bcast_ = method != Single_GPU && nranks > 1;
+        const bool sharded = EVERY_RANK_HOLDS_DATA && method != Single_GPU && nranks > 1;
+        bcast_ = method != Single_GPU && nranks > 1 && !sharded;
         root_ = !bcast_ || rank == 0;
+        const int flags = sharded ? CN_BATCH_SHARDED_UPLOAD : 0;
         BATCH_SIZE = batch_size;
         BATCH_SIZE_CV = cv_batch_size;
         cn_detail::cuda(cudaMalloc((void **)&d_hdr_, 8 * sizeof(float)));
@@ -517,11 +524,11 @@ private:
         CURRENT_BATCH_CV_Y = cn_detail::header(0, 0);
         cn_batch *t = nullptr, *c = nullptr;
         if (root_) {
-            cn_detail::check(cn_batch_create(ctx_, X->data, y->data, TRAIN_SET_ROWS, cols_x_, cols_y_, batch_size, 0, &t));
+            cn_detail::check(cn_batch_create_ex(ctx_, X->data, y->data, TRAIN_SET_ROWS, cols_x_, cols_y_, batch_size, 0, flags, &t));
             train_ = std::shared_ptr<cn_batch>(t, [](cn_batch *p) { cn_batch_destroy(p); });
             if (TOTAL_BATCHES_CV > 0) {
-                cn_detail::check(cn_batch_create(ctx_, X->data + (size_t)TRAIN_SET_ROWS * cols_x_, y->data + (size_t)TRAIN_SET_ROWS * cols_y_,
-                                                CV_SET_ROWS, cols_x_, cols_y_, cv_batch_size, 0, &c));
+                cn_detail::check(cn_batch_create_ex(ctx_, X->data + (size_t)TRAIN_SET_ROWS * cols_x_, y->data + (size_t)TRAIN_SET_ROWS * cols_y_,
+                                                   CV_SET_ROWS, cols_x_, cols_y_, cv_batch_size, 0, flags, &c));
                 cv_ = std::shared_ptr<cn_batch>(c, [](cn_batch *p) { cn_batch_destroy(p); });
             }
         } else {

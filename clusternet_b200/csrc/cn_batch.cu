@@ -7,6 +7,19 @@
 // (cudaStreamWaitEvent instead of cudaStreamSynchronize), the device buffers are sized once for a full batch so
 // the short last batch needs no cudaFree / cudaMalloc, and the next copy is ordered after the transposes that
 // read the previous one.
+//
+// Options of cn_batch_create_ex (flags):
+//   CN_BATCH_KEEP_ROW_MAJOR  the row-major device copy of the CURRENT batch stays valid until the next swap (two
+//                            row-major buffers that alternate), so that a product can read the batch as a transposed
+//                            operand (cn_tdotmpi_f32 / cn_gemm_f32 with transA) without the col-major detour;
+//   CN_BATCH_NO_COL_MAJOR    X is not transposed into col-major at the swap at all (implies the former);
+//   CN_BATCH_SHARDED_UPLOAD  every rank of the communicator holds the data set (the reference's Matrix* form of init,
+//                            source/batchAllocator.cpp:411-440, where the rank-0 guard around the staging memcpy is
+//                            commented out): rank r copies only rows [r*floor(B/G), ...) of the batch over its own
+//                            PCIe link and pushes that block into every peer's buffer over NVLink (copy engine, peer
+//                            addresses of a symmetric buffer), framed by two bounded cross-GPU flag exchanges on the
+//                            copy stream ("your buffer may be overwritten" / "my block has arrived").  One link no
+//                            longer carries the whole batch.
 #include <string.h>
 #include "cn_internal.h"
 
@@ -23,6 +36,15 @@ struct cn_batch {
     bool direct = false;         // the data set itself is pinned: copy from it, no staging memcpy
     float *p_X = nullptr, *p_y = nullptr;     // pinned staging
     float *dn_X = nullptr, *dn_y = nullptr;   // device, next batch, row-major
+    // options (cn_batch_create_ex)
+    int flags = 0;
+    float *rm[2] = {nullptr, nullptr};        // row-major X buffers that alternate (dn_X points at the one being filled)
+    bool rm_sym = false;                      // rm[] came from cn_sym_alloc
+    int fill = 0;                             // index of the buffer the next copy goes to
+    float *cur_rm = nullptr;                  // row-major copy of the current batch
+    int G = 1, rank = 0, slot = 0;
+    unsigned int epoch = 0;
+    float *peer_rm[2][8] = {};                // peer addresses of rm[0], rm[1]
     float *dc_X = nullptr, *dc_y = nullptr;   // device, current batch, column-major
     cudaStream_t s_X = nullptr, s_y = nullptr;
     cudaEvent_t e_X = nullptr, e_y = nullptr, e_consumed = nullptr;
@@ -41,7 +63,15 @@ extern "C" int cn_batch_destroy(cn_batch *b)
     if (b->s_X) cudaStreamSynchronize(b->s_X);
     if (b->s_y) cudaStreamSynchronize(b->s_y);
     cudaFreeHost(b->p_X); cudaFreeHost(b->p_y);
-    cudaFree(b->dn_X); cudaFree(b->dn_y); cudaFree(b->dc_X); cudaFree(b->dc_y);
+    if (b->rm[0] || b->rm[1]) {
+        for (int i = 0; i < 2; ++i) {
+            if (!b->rm[i]) continue;
+            if (b->rm_sym) cn_sym_free(b->ctx, b->rm[i]); else cudaFree(b->rm[i]);
+        }
+    } else {
+        cudaFree(b->dn_X);
+    }
+    cudaFree(b->dn_y); cudaFree(b->dc_X); cudaFree(b->dc_y);
     if (b->s_X) cudaStreamDestroy(b->s_X);
     if (b->s_y) cudaStreamDestroy(b->s_y);
     if (b->e_X) cudaEventDestroy(b->e_X);
@@ -54,7 +84,20 @@ extern "C" int cn_batch_destroy(cn_batch *b)
 extern "C" int cn_batch_create(cn_context *ctx, const float *h_X, const float *h_y, int64_t rows, int64_t cols_X, int64_t cols_y,
                                int64_t batch_size, int skip_last_batch, cn_batch **out)
 {
+    return cn_batch_create_ex(ctx, h_X, h_y, rows, cols_X, cols_y, batch_size, skip_last_batch, 0, out);
+}
+
+extern "C" int cn_batch_create_ex(cn_context *ctx, const float *h_X, const float *h_y, int64_t rows, int64_t cols_X, int64_t cols_y,
+                                  int64_t batch_size, int skip_last_batch, int flags, cn_batch **out)
+{
     CN_REQUIRE(ctx && h_X && h_y && out, CN_ERR_ARG, "cn_batch_create: null argument");
+    CN_REQUIRE((flags & ~(CN_BATCH_KEEP_ROW_MAJOR | CN_BATCH_NO_COL_MAJOR | CN_BATCH_SHARDED_UPLOAD)) == 0, CN_ERR_ARG,
+               "cn_batch_create_ex: unknown flag bits 0x%x", flags);
+    if (flags & CN_BATCH_NO_COL_MAJOR) flags |= CN_BATCH_KEEP_ROW_MAJOR;
+    const int G = cn_comm_size(ctx);
+    if (G == 1) flags &= ~CN_BATCH_SHARDED_UPLOAD;   // nothing to share the upload with
+    if (flags & CN_BATCH_SHARDED_UPLOAD) flags |= CN_BATCH_KEEP_ROW_MAJOR;
+    CN_REQUIRE(G <= 8, CN_ERR_UNSUPPORTED, "cn_batch_create_ex: at most 8 ranks");
     CN_REQUIRE(rows > 0 && cols_X > 0 && cols_y > 0 && batch_size > 0, CN_ERR_ARG, "cn_batch_create: non-positive size");
     // "ERROR: Batch size must be smaller than the training set." (source/batchAllocator.cpp:135-139)
     CN_REQUIRE(batch_size <= rows, CN_ERR_SHAPE, "Batch size must be smaller than the training set.");
@@ -64,6 +107,9 @@ extern "C" int cn_batch_create(cn_context *ctx, const float *h_X, const float *h
     b->h_X = h_X; b->h_y = h_y;
     b->rows = rows; b->cols_X = cols_X; b->cols_y = cols_y; b->batch = batch_size;
     b->skip_last = skip_last_batch;
+    b->flags = flags;
+    b->G = G;
+    b->rank = cn_comm_rank(ctx);
     b->total_batches = (rows + batch_size - 1) / batch_size;
     const size_t bx = (size_t)batch_size * cols_X * sizeof(float), by = (size_t)batch_size * cols_y * sizeof(float);
     cudaError_t e;
@@ -77,8 +123,10 @@ extern "C" int cn_batch_create(cn_context *ctx, const float *h_X, const float *h
     }
     if ((!b->direct && (e = cudaHostAlloc(&b->p_X, bx, cudaHostAllocPortable)) != cudaSuccess) ||
         (!b->direct && (e = cudaHostAlloc(&b->p_y, by, cudaHostAllocPortable)) != cudaSuccess) ||
-        (e = cudaMalloc(&b->dn_X, bx)) != cudaSuccess || (e = cudaMalloc(&b->dn_y, by)) != cudaSuccess ||
-        (e = cudaMalloc(&b->dc_X, bx)) != cudaSuccess || (e = cudaMalloc(&b->dc_y, by)) != cudaSuccess ||
+        (!(flags & CN_BATCH_KEEP_ROW_MAJOR) && (e = cudaMalloc(&b->dn_X, bx)) != cudaSuccess) ||
+        (e = cudaMalloc(&b->dn_y, by)) != cudaSuccess ||
+        (!(flags & CN_BATCH_NO_COL_MAJOR) && (e = cudaMalloc(&b->dc_X, bx)) != cudaSuccess) ||
+        (e = cudaMalloc(&b->dc_y, by)) != cudaSuccess ||
         (e = cudaStreamCreateWithFlags(&b->s_X, cudaStreamNonBlocking)) != cudaSuccess ||
         (e = cudaStreamCreateWithFlags(&b->s_y, cudaStreamNonBlocking)) != cudaSuccess ||
         (e = cudaEventCreateWithFlags(&b->e_X, cudaEventDisableTiming)) != cudaSuccess ||
@@ -87,6 +135,31 @@ extern "C" int cn_batch_create(cn_context *ctx, const float *h_X, const float *h
         cn_batch_destroy(b);
         return cn_cuda_fail(e, "cn_batch_create");
     }
+    if (flags & CN_BATCH_KEEP_ROW_MAJOR) {
+        for (int i = 0; i < 2; ++i) {
+            int st2;
+            if (flags & CN_BATCH_SHARDED_UPLOAD) {
+                void *p = nullptr;
+                st2 = cn_sym_alloc(ctx, bx, &p);   // collective: every rank creates its allocator at the same point
+                b->rm[i] = (float *)p;
+                b->rm_sym = true;
+                void *peers[8] = {};
+                if (st2 == CN_OK && !cn_comm_sym_peers(ctx, p, bx, peers)) {
+                    cn_set_error("cn_batch_create_ex: symmetric buffer not found");
+                    st2 = CN_ERR_CUDA;
+                }
+                for (int r = 0; r < G; ++r) b->peer_rm[i][r] = (float *)peers[r];
+            } else {
+                st2 = cudaMalloc(&b->rm[i], bx) == cudaSuccess ? CN_OK : cn_cuda_fail(cudaGetLastError(), "cn_batch_create_ex");
+            }
+            if (st2 != CN_OK) { cn_batch_destroy(b); return st2; }
+        }
+        b->dn_X = b->rm[0];
+        if (flags & CN_BATCH_SHARDED_UPLOAD) {
+            int st2 = cn_comm_flag_slots(ctx, 2, &b->slot);
+            if (st2 != CN_OK) { cn_batch_destroy(b); return st2; }
+        }
+    }
     // first batch: staged, copied and transposed before returning, as BatchAllocator::init does
     b->next_batch = 0;
     int st = cn_batch_copy_next_async(b);
@@ -94,6 +167,16 @@ extern "C" int cn_batch_create(cn_context *ctx, const float *h_X, const float *h
     int64_t r;
     if (st == CN_OK) st = cn_batch_swap(b, nullptr, &dx, &dy, &r);
     if (st == CN_OK && cudaStreamSynchronize(nullptr) != cudaSuccess) st = cn_cuda_fail(cudaGetLastError(), "cn_batch_create");
+    if (st == CN_OK && (flags & CN_BATCH_SHARDED_UPLOAD)) {
+        unsigned int *d_status = nullptr;   // the first exchange must not have timed out
+        unsigned int h = 0;
+        st = cn_status_block(ctx, &d_status);
+        if (st == CN_OK && cudaMemcpy(&h, d_status, sizeof(h), cudaMemcpyDeviceToHost) != cudaSuccess) st = cn_cuda_fail(cudaGetLastError(), "cn_batch_create_ex");
+        if (st == CN_OK && h != 0) {
+            cn_set_error("cn_batch_create_ex: a peer did not take part in the first batch exchange (status %u)", h);
+            st = CN_ERR_TIMEOUT;
+        }
+    }
     if (st != CN_OK) { cn_batch_destroy(b); return st; }
     *out = b;
     return CN_OK;
@@ -117,18 +200,35 @@ extern "C" int cn_batch_current(const cn_batch *b, float **d_X, float **d_y, int
     return CN_OK;
 }
 
+extern "C" int cn_batch_current_row_major(const cn_batch *b, float **d_X_row_major, int64_t *batch_rows)
+{
+    CN_REQUIRE(b, CN_ERR_ARG, "cn_batch_current_row_major: null handle");
+    CN_REQUIRE(b->flags & CN_BATCH_KEEP_ROW_MAJOR, CN_ERR_ARG, "cn_batch_current_row_major: the allocator was created without CN_BATCH_KEEP_ROW_MAJOR");
+    if (d_X_row_major) *d_X_row_major = b->cur_rm;
+    if (batch_rows) *batch_rows = b->cur_rows;
+    return CN_OK;
+}
+
 extern "C" int cn_batch_copy_next_async(cn_batch *b)
 {
     CN_REQUIRE(b, CN_ERR_ARG, "cn_batch_copy_next_async: null handle");
     const int64_t idx = b->next_batch, r = rows_of_batch(b, idx);
     const float *src_X = b->h_X + (size_t)idx * b->batch * b->cols_X, *src_y = b->h_y + (size_t)idx * b->batch * b->cols_y;
+    // rows of the batch this rank uploads itself: all of them, or its block of floor(r / G) rows (last rank: + remainder)
+    int64_t row0 = 0, nrows = r;
+    if (b->flags & CN_BATCH_SHARDED_UPLOAD) {
+        const int64_t split = r / b->G;
+        row0 = split * b->rank;
+        nrows = (b->rank == b->G - 1) ? r - row0 : split;
+    }
+    const size_t off_X = (size_t)row0 * b->cols_X, bytes_X = (size_t)nrows * b->cols_X * sizeof(float);
     if (!b->direct) {
         // the staging buffers are free once the previous copy out of them has finished
         if (b->copy_pending) {
             CN_CUDA(cudaEventSynchronize(b->e_X));
             CN_CUDA(cudaEventSynchronize(b->e_y));
         }
-        memcpy(b->p_X, src_X, (size_t)r * b->cols_X * sizeof(float));
+        memcpy(b->p_X + off_X, src_X + off_X, bytes_X);
         memcpy(b->p_y, src_y, (size_t)r * b->cols_y * sizeof(float));
         src_X = b->p_X;
         src_y = b->p_y;
@@ -136,7 +236,22 @@ extern "C" int cn_batch_copy_next_async(cn_batch *b)
     // do not overwrite the device "next" buffers while the last swap's transposes may still read them
     CN_CUDA(cudaStreamWaitEvent(b->s_X, b->e_consumed, 0));
     CN_CUDA(cudaStreamWaitEvent(b->s_y, b->e_consumed, 0));
-    CN_CUDA(cudaMemcpyAsync(b->dn_X, src_X, (size_t)r * b->cols_X * sizeof(float), cudaMemcpyHostToDevice, b->s_X));
+    if (b->flags & CN_BATCH_SHARDED_UPLOAD) {
+        // (1) every peer's buffer of this parity must be free: its last reader was the batch before the current one, and
+        //     each rank says so only after its own e_consumed (waited for above); (2) own block over this rank's PCIe
+        //     link; (3) the block into every peer's buffer over NVLink; (4) "my block has arrived everywhere"
+        const unsigned int epoch = ++b->epoch;
+        int st = cn_comm_flag_barrier(b->ctx, b->slot, epoch, b->s_X);
+        if (st != CN_OK) return st;
+        if (bytes_X) CN_CUDA(cudaMemcpyAsync(b->dn_X + off_X, src_X + off_X, bytes_X, cudaMemcpyHostToDevice, b->s_X));
+        for (int p = 1; p < b->G && bytes_X; ++p) {
+            const int peer = (b->rank + p) % b->G;   // staggered so that the ranks do not all write to the same GPU at once
+            CN_CUDA(cudaMemcpyAsync(b->peer_rm[b->fill][peer] + off_X, b->dn_X + off_X, bytes_X, cudaMemcpyDeviceToDevice, b->s_X));
+        }
+        if ((st = cn_comm_flag_barrier(b->ctx, b->slot + 1, epoch, b->s_X)) != CN_OK) return st;
+    } else {
+        CN_CUDA(cudaMemcpyAsync(b->dn_X, src_X, (size_t)r * b->cols_X * sizeof(float), cudaMemcpyHostToDevice, b->s_X));
+    }
     CN_CUDA(cudaMemcpyAsync(b->dn_y, src_y, (size_t)r * b->cols_y * sizeof(float), cudaMemcpyHostToDevice, b->s_y));
     CN_CUDA(cudaEventRecord(b->e_X, b->s_X));
     CN_CUDA(cudaEventRecord(b->e_y, b->s_y));
@@ -152,11 +267,19 @@ extern "C" int cn_batch_swap(cn_batch *b, void *stream, float **d_X, float **d_y
     cudaStream_t s = cn_stream(stream);
     CN_CUDA(cudaStreamWaitEvent(s, b->e_X, 0));
     CN_CUDA(cudaStreamWaitEvent(s, b->e_y, 0));
-    int st = cn_to_col_major(b->ctx, b->dn_X, b->dc_X, b->next_rows, b->cols_X, stream);
+    int st = CN_OK;
+    if (!(b->flags & CN_BATCH_NO_COL_MAJOR)) st = cn_to_col_major(b->ctx, b->dn_X, b->dc_X, b->next_rows, b->cols_X, stream);
     if (st == CN_OK) st = cn_to_col_major(b->ctx, b->dn_y, b->dc_y, b->next_rows, b->cols_y, stream);
     if (st != CN_OK) return st;
+    // everything queued on the compute stream so far - the transposes above and the caller's work on the batch that was
+    // current until now - precedes this event; the next copy waits for it before it overwrites a buffer
     CN_CUDA(cudaEventRecord(b->e_consumed, s));
     b->cur_rows = b->next_rows;
+    if (b->flags & CN_BATCH_KEEP_ROW_MAJOR) {   // the filled buffer becomes the current one, the other one is filled next
+        b->cur_rm = b->rm[b->fill];
+        b->fill ^= 1;
+        b->dn_X = b->rm[b->fill];
+    }
     // counter and wrap-around exactly as replace_current_batch_with_next (source/batchAllocator.cpp:1036-1052)
     b->next_batch += 1;
     if ((b->next_batch + 1) == b->total_batches && b->skip_last) b->next_batch = 0;

@@ -87,6 +87,7 @@ struct cn_comm_state {
     std::vector<unsigned int *> peer_flags;
     unsigned int **d_peer_flags = nullptr;   // device copy of peer_flags
     unsigned int epoch = 0;
+    int next_flag_slot = 2;   // slots 0 and 1 frame the fused gather; the batch allocators reserve theirs from here
     bool aborted = false;   // cn_comm_sync gave up on a collective: only cn_comm_destroy is accepted from here on
 };
 
@@ -307,13 +308,18 @@ static int sym_alloc_impl(cn_context *ctx, size_t bytes, cn_sym_buf *out)
     // exchange the IPC handles: every rank contributes 64 bytes
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "cudaIpcMemHandle_t is expected to be 64 bytes");
     cudaIpcMemHandle_t mine;
-    CN_CUDA(cudaIpcGetMemHandle(&mine, b.base));
     unsigned char *d_h = nullptr;
-    CN_CUDA(cudaMalloc(&d_h, 64 * (size_t)G));
-    CN_CUDA(cudaMemcpy(d_h + 64 * c->rank, &mine, 64, cudaMemcpyHostToDevice));
+    cudaError_t e = cudaIpcGetMemHandle(&mine, b.base);
+    if (e == cudaSuccess) e = cudaMalloc(&d_h, 64 * (size_t)G);
+    if (e == cudaSuccess) e = cudaMemcpy(d_h + 64 * c->rank, &mine, 64, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        cudaFree(d_h);
+        cudaFree(b.base);
+        return cn_cuda_fail(e, "cn_sym_alloc");
+    }
     ncclResult_t r = g_nccl.AllGather(d_h + 64 * c->rank, d_h, 64, ncclUint8, c->comm, nullptr);
     std::vector<cudaIpcMemHandle_t> all(G);
-    cudaError_t e = cudaMemcpy(all.data(), d_h, 64 * (size_t)G, cudaMemcpyDeviceToHost);   // synchronises the default stream
+    e = cudaMemcpy(all.data(), d_h, 64 * (size_t)G, cudaMemcpyDeviceToHost);   // synchronises the default stream
     cudaFree(d_h);
     if (r != ncclSuccess || e != cudaSuccess) {
         cudaFree(b.base);
@@ -345,22 +351,34 @@ extern "C" int cn_sym_alloc(cn_context *ctx, size_t bytes, void **ptr)
     CN_REQUIRE(c->nranks - 1 <= CN_MAX_PEERS, CN_ERR_UNSUPPORTED, "cn_sym_alloc: at most %d ranks", CN_MAX_PEERS + 1);
     int st;
     if (!c->flags) {   // first use: the flag words, zeroed, and the device table of their peer addresses
+        // Everything is built in locals and published (c->flags, c->d_peer_flags) only after every step, the closing
+        // barrier included, has succeeded: a failed set-up leaves the context without flags, so the fused path stays off.
         cn_sym_buf f;
         if ((st = sym_alloc_impl(ctx, 4096, &f)) != CN_OK) return st;
-        CN_CUDA(cudaMemset(f.base, 0, 4096));
-        c->flags = (unsigned int *)f.base;
-        for (void *q : f.peer) c->peer_flags.push_back((unsigned int *)q);
-        CN_CUDA(cudaMalloc(&c->d_peer_flags, sizeof(unsigned int *) * c->nranks));
-        CN_CUDA(cudaMemcpy(c->d_peer_flags, c->peer_flags.data(), sizeof(unsigned int *) * c->nranks, cudaMemcpyHostToDevice));
-        c->sym.push_back(f);
-        // nobody may signal into flags that a slower rank has not zeroed yet
+        unsigned int **d_tab = nullptr;
         float *d_tmp = nullptr;
-        CN_CUDA(cudaMalloc(&d_tmp, 4));
-        CN_CUDA(cudaMemset(d_tmp, 0, 4));
-        ncclResult_t r = g_nccl.AllReduce(d_tmp, d_tmp, 1, ncclFloat, ncclSum, c->comm, nullptr);
-        cudaError_t e = cudaDeviceSynchronize();
+        std::vector<unsigned int *> tab;
+        for (void *q : f.peer) tab.push_back((unsigned int *)q);
+        cudaError_t e = cudaMemset(f.base, 0, 4096);
+        if (e == cudaSuccess) e = cudaMalloc(&d_tab, sizeof(unsigned int *) * c->nranks);
+        if (e == cudaSuccess) e = cudaMemcpy(d_tab, tab.data(), sizeof(unsigned int *) * c->nranks, cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) e = cudaMalloc(&d_tmp, 4);
+        if (e == cudaSuccess) e = cudaMemset(d_tmp, 0, 4);
+        // nobody may signal into flags that a slower rank has not zeroed yet
+        ncclResult_t r = e == cudaSuccess ? g_nccl.AllReduce(d_tmp, d_tmp, 1, ncclFloat, ncclSum, c->comm, nullptr) : ncclSuccess;
+        if (e == cudaSuccess) e = cudaDeviceSynchronize();
         cudaFree(d_tmp);
-        CN_REQUIRE(r == ncclSuccess && e == cudaSuccess, CN_ERR_NCCL, "cn_sym_alloc: barrier after flag set-up failed");
+        if (e != cudaSuccess || r != ncclSuccess) {
+            cudaFree(d_tab);
+            sym_release(c, f);
+            cudaGetLastError();
+            cn_set_error("cn_sym_alloc: set-up of the cross-GPU flags failed (cuda %d, nccl %d)", (int)e, (int)r);
+            return e != cudaSuccess ? CN_ERR_CUDA : CN_ERR_NCCL;
+        }
+        c->sym.push_back(f);
+        c->peer_flags = tab;
+        c->d_peer_flags = d_tab;
+        c->flags = (unsigned int *)f.base;
     }
     cn_sym_buf b;
     if ((st = sym_alloc_impl(ctx, bytes, &b)) != CN_OK) return st;
@@ -423,8 +441,10 @@ static bool sym_lookup(cn_comm_state *c, const void *p, size_t bytes, float **pe
     return false;
 }
 
-extern "C" int cn_dotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_total, const float *d_A, const float *d_Wshard,
-                             float *d_C, const cn_epilogue *epi, int mode, int exchange, void *stream)
+// transA = 0: A stored M x K (leading dimension lda >= M); transA = 1: A stored K x M (lda >= K), the product uses its
+// transpose (TdotMPI, source/clusterNet.cpp:510).
+static int dotmpi_impl(cn_context *ctx, int transA, int64_t M, int64_t K, int64_t n_total, const float *d_A, int64_t lda,
+                       const float *d_Wshard, float *d_C, const cn_epilogue *epi, int mode, int exchange, void *stream)
 {
     CN_REQUIRE(ctx, CN_ERR_ARG, "cn_dotmpi_f32: null context");
     CN_REQUIRE(M >= 0 && K >= 0 && n_total >= 0, CN_ERR_SHAPE, "cn_dotmpi_f32: negative dimension");
@@ -449,7 +469,7 @@ extern "C" int cn_dotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_to
     // Whether to push is decided from values that are equal on every rank (shapes, mode), so that all ranks take the
     // same branch: the narrowest shard must still be a shape the tensor-core kernel takes.
     const bool shape_ok = mode != CN_GEMM_FP32_SIMT && (n_total / G) >= 16 && K >= 32 && (K & 3) == 0 && M >= 1;
-    if (G > 1 && exchange == 0 && shape_ok && ctx->comm->flags &&
+    if (G > 1 && exchange == 0 && shape_ok && ctx->comm->flags && ctx->comm->d_peer_flags &&
         sym_lookup(ctx->comm, d_C, (size_t)M * n_total * sizeof(float), po.C)) {
         cn_comm_state *c = ctx->comm;
         cudaStream_t s = cn_stream(stream);
@@ -462,13 +482,8 @@ extern "C" int cn_dotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_to
         po.epoch = epoch;
         po.peer_flags = c->d_peer_flags;   // the GEMM kernel raises this rank's "ready" flag itself when it starts
         bool pushed = false;
-        st = cn_gemm_dispatch(ctx, 0, 0, M, cnt, K, d_A, M, d_Wshard, K, slice, M, &local, mode, stream, &po, &pushed);
+        st = cn_gemm_dispatch(ctx, transA, 0, M, cnt, K, d_A, lda, d_Wshard, K, slice, M, &local, mode, stream, &po, &pushed);
         if (st != CN_OK) return st;
-        if (!ctx->gemm) ctx->gemm = new cn_gemm_workspace();
-        if (!ctx->gemm->d_status) {
-            CN_CUDA(cudaMalloc(&ctx->gemm->d_status, 64 + CN_GEMM_MAX_TICKETS * sizeof(unsigned int)));
-            CN_CUDA(cudaMemset(ctx->gemm->d_status, 0, 64 + CN_GEMM_MAX_TICKETS * sizeof(unsigned int)));
-        }
         // a rank whose operands the tensor-core kernel refused (a misaligned shard pointer) cannot fall back on its own:
         // the peers are already past the point of calling a collective
         CN_REQUIRE(pushed, CN_ERR_UNSUPPORTED, "cn_dotmpi_f32: this rank's shard cannot take the fused path (16-byte alignment of W)");
@@ -477,7 +492,7 @@ extern "C" int cn_dotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_to
         cn_count_launch();
         return CN_OK;
     }
-    st = cn_gemm_f32(ctx, 0, 0, M, cnt, K, d_A, M, d_Wshard, K, slice, M, &local, mode, stream);
+    st = cn_gemm_f32(ctx, transA, 0, M, cnt, K, d_A, lda, d_Wshard, K, slice, M, &local, mode, stream);
     if (st != CN_OK || G == 1) return st;
     if (exchange == 0) return cn_allgather_cols_f32(ctx, d_C, M, n_total, stream);
 
@@ -499,6 +514,58 @@ extern "C" int cn_dotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_to
         if ((st = cn_decompress_8bit_dp(ctx, codes + (size_t)M * s0, scales + r, M * c0, d_C + (size_t)M * s0, stream)) != CN_OK) return st;
     }
     return CN_OK;
+}
+
+bool cn_comm_sym_peers(cn_context *ctx, const void *local, size_t bytes, void **peers_out)
+{
+    cn_comm_state *c = ctx->comm;
+    if (!c) return false;
+    for (auto &b : c->sym) {
+        const char *lo = (const char *)b.base;
+        if ((const char *)local >= lo && (const char *)local + bytes <= lo + b.bytes) {
+            const size_t off = (const char *)local - lo;
+            for (int r = 0; r < c->nranks; ++r) peers_out[r] = (char *)b.peer[r] + off;
+            return true;
+        }
+    }
+    return false;
+}
+
+int cn_comm_flag_slots(cn_context *ctx, int count, int *first_slot)
+{
+    cn_comm_state *c = ctx->comm;
+    CN_REQUIRE(c && c->flags, CN_ERR_ARG, "flag slots need a communicator with symmetric buffers (cn_sym_alloc)");
+    CN_REQUIRE((c->next_flag_slot + count) * c->nranks <= 1024, CN_ERR_UNSUPPORTED, "out of cross-GPU flag slots");
+    *first_slot = c->next_flag_slot;
+    c->next_flag_slot += count;
+    return CN_OK;
+}
+
+int cn_comm_flag_barrier(cn_context *ctx, int slot, unsigned int epoch, cudaStream_t s)
+{
+    cn_comm_state *c = ctx->comm;
+    CN_REQUIRE(c && c->flags && c->d_peer_flags, CN_ERR_ARG, "flag barrier needs a communicator with symmetric buffers");
+    CN_COMM_ALIVE(ctx);
+    unsigned int *d_status = nullptr;
+    int st = cn_status_block(ctx, &d_status);
+    if (st != CN_OK) return st;
+    cn_flag_barrier_kernel<<<1, 32, 0, s>>>(c->d_peer_flags, c->flags, c->nranks, c->rank, slot, epoch, d_status);
+    CN_CUDA(cudaGetLastError());
+    cn_count_launch();
+    return CN_OK;
+}
+
+extern "C" int cn_dotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_total, const float *d_A, const float *d_Wshard,
+                             float *d_C, const cn_epilogue *epi, int mode, int exchange, void *stream)
+{
+    return dotmpi_impl(ctx, 0, M, K, n_total, d_A, M, d_Wshard, d_C, epi, mode, exchange, stream);
+}
+
+extern "C" int cn_tdotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_total, const float *d_At, int64_t lda,
+                              const float *d_Wshard, float *d_C, const cn_epilogue *epi, int mode, int exchange, void *stream)
+{
+    CN_REQUIRE(lda >= K, CN_ERR_SHAPE, "cn_tdotmpi_f32: leading dimension smaller than K");
+    return dotmpi_impl(ctx, 1, M, K, n_total, d_At, lda, d_Wshard, d_C, epi, mode, exchange, stream);
 }
 
 extern "C" int cn_dottmpi_f32(cn_context *ctx, int64_t M, int64_t n_total, int64_t R, const float *d_A, const float *d_Bshard,
@@ -557,6 +624,16 @@ int cn_comm_gather_codes(cn_context *ctx, uint8_t *d_codes_all, int64_t n, float
     return CN_OK;
 }
 
+// blocks: nranks blocks of block_bytes bytes, block [rank] filled
+int cn_comm_gather_blocks(cn_context *ctx, uint8_t *d_blocks, size_t block_bytes, void *stream)
+{
+    cn_comm_state *c = ctx->comm;
+    if (!c || c->nranks == 1) return CN_OK;
+    CN_COMM_ALIVE(ctx);
+    CN_NCCL(g_nccl.AllGather(d_blocks + (size_t)c->rank * block_bytes, d_blocks, block_bytes, ncclUint8, c->comm, cn_stream(stream)));
+    return CN_OK;
+}
+
 // ---- 8-bit exchange with the decode inside the consumer GEMM
 extern "C" int cn_dotmpi_to_coded_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_total, const float *d_A, const float *d_Wshard,
                                       cn_coded *out, const cn_epilogue *epi, int mode, void *stream)
@@ -593,7 +670,7 @@ extern "C" int cn_dotmpi_from_coded_f32(cn_context *ctx, const cn_coded *A, int6
     cn_shard_cols(n_total, rank, G, &start, &cnt);
     if (mode != CN_GEMM_FP32_SIMT && cnt > 0 &&
         cn_gemm_tc_supported(ctx, 0, 0, M, cnt, K, A->own_fp32, M, d_Wshard, K, d_C, M)) {
-        if (!ctx->gemm) ctx->gemm = new cn_gemm_workspace();
+        if (!ctx->gemm) ctx->gemm = cn_gemm_workspace_new();
         cn_coded_src src;
         src.codes = A->codes;
         src.scales = A->scales;
@@ -643,13 +720,11 @@ __global__ void cn_wait_probe_kernel(const unsigned int *flag, unsigned int epoc
 extern "C" int cn_diag_wait_probe(cn_context *ctx, int64_t limit_cycles, void *stream)
 {
     CN_REQUIRE(ctx && limit_cycles > 0 && limit_cycles <= 4000000000LL, CN_ERR_ARG, "cn_diag_wait_probe: limit must be in 1 .. 4e9 cycles");
-    if (!ctx->gemm) ctx->gemm = new cn_gemm_workspace();
-    if (!ctx->gemm->d_status) {
-        CN_CUDA(cudaMalloc(&ctx->gemm->d_status, 64 + CN_GEMM_MAX_TICKETS * sizeof(unsigned int)));
-        CN_CUDA(cudaMemset(ctx->gemm->d_status, 0, 64 + CN_GEMM_MAX_TICKETS * sizeof(unsigned int)));
-    }
+    unsigned int *d_status = nullptr;
+    int st = cn_status_block(ctx, &d_status);
+    if (st != CN_OK) return st;
     // word 8 of the status block is never written: the probe waits for it to reach 1
-    cn_wait_probe_kernel<<<1, 1, 0, cn_stream(stream)>>>(ctx->gemm->d_status + 8, 1u, (long long)limit_cycles, ctx->gemm->d_status);
+    cn_wait_probe_kernel<<<1, 1, 0, cn_stream(stream)>>>(d_status + 8, 1u, (long long)limit_cycles, d_status);
     CN_CUDA(cudaGetLastError());
     cn_count_launch();
     return CN_OK;

@@ -5,6 +5,7 @@
 // kernel can take (see cn_gemm_tc.cu) go there; everything else — tiny matrices such as the reference's
 // 2x3 . 3x2 known-answer tests, a weight pitch that is not a multiple of 4 — runs on the fp32 FMA kernel
 // below, which accumulates along k in order and therefore reproduces plain fp32 dot products exactly.
+#include <stdlib.h>
 #include "cn_epilogue.cuh"
 #include "cn_gemm.h"
 
@@ -95,9 +96,42 @@ static int simt_launch(cn_context *ctx, int transA, int transB, int64_t M, int64
     return CN_OK;
 }
 
+cn_gemm_workspace *cn_gemm_workspace_new()
+{
+    cn_gemm_workspace *w = new cn_gemm_workspace();
+    if (const char *e = getenv("CN_GEMM_NT")) w->force_nt = atoi(e);
+    if (const char *e = getenv("CN_GEMM_SPLITS")) w->force_splits = atoi(e);
+    if (const char *e = getenv("CN_GEMM_CHAIN")) w->force_chain = atoi(e);
+    return w;
+}
+
+extern "C" int cn_gemm_set_tuning(cn_context *ctx, int tiles_per_cta, int k_splits, int chain_k_blocks)
+{
+    CN_REQUIRE(ctx, CN_ERR_ARG, "cn_gemm_set_tuning: null context");
+    CN_REQUIRE(tiles_per_cta >= 0 && tiles_per_cta <= 2 && k_splits >= 0 && chain_k_blocks >= 0, CN_ERR_ARG,
+               "cn_gemm_set_tuning: tiles_per_cta must be 0, 1 or 2, the other two non-negative");
+    if (!ctx->gemm) ctx->gemm = cn_gemm_workspace_new();
+    ctx->gemm->force_nt = tiles_per_cta;
+    ctx->gemm->force_splits = k_splits;
+    ctx->gemm->force_chain = chain_k_blocks;
+    return CN_OK;
+}
+
+int cn_status_block(cn_context *ctx, unsigned int **d_status)
+{
+    if (!ctx->gemm) ctx->gemm = cn_gemm_workspace_new();
+    cn_gemm_workspace *w = ctx->gemm;
+    if (!w->d_status) {
+        CN_CUDA(cudaMalloc(&w->d_status, 64 + CN_GEMM_MAX_TICKETS * sizeof(unsigned int)));
+        CN_CUDA(cudaMemset(w->d_status, 0, 64 + CN_GEMM_MAX_TICKETS * sizeof(unsigned int)));
+    }
+    *d_status = w->d_status;
+    return CN_OK;
+}
+
 int cn_gemm_scratch(cn_context *ctx, int slot, size_t bytes, void **out)
 {
-    if (!ctx->gemm) ctx->gemm = new cn_gemm_workspace();
+    if (!ctx->gemm) ctx->gemm = cn_gemm_workspace_new();
     cn_gemm_workspace *w = ctx->gemm;
     if (w->bytes[slot] < bytes) {
         // grown buffers may still be in use by kernels queued earlier: drain before freeing

@@ -28,10 +28,16 @@ struct cn_gemm_workspace {
     unsigned int *d_status = nullptr;   // word 0: set by a kernel whose bounded wait ran out
     void *encode_fn = nullptr;          // cuTensorMapEncodeTiled, resolved once
     const cn_coded_src *coded_src = nullptr;   // one-shot: see cn_coded_src
+    // test and sweep knobs (0 = automatic choice): W tiles per CTA, K splits, K blocks per accumulation chain.  Seeded once,
+    // when the workspace is made, from CN_GEMM_NT / CN_GEMM_SPLITS / CN_GEMM_CHAIN; changed with cn_gemm_set_tuning.
+    int force_nt = 0, force_splits = 0, force_chain = 0;
     bool profile = false;               // bracket main-kernel launches with events
     std::vector<cudaEvent_t> prof_events;   // start, stop, start, stop, ...
     size_t prof_used = 0;
 };
+
+// The only way a workspace is made: reads the environment knobs once.
+cn_gemm_workspace *cn_gemm_workspace_new();
 
 // Grow-only scratch buffers owned by the context.
 int cn_gemm_scratch(cn_context *ctx, int slot, size_t bytes, void **out);

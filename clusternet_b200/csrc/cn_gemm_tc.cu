@@ -316,20 +316,34 @@ cn_act_split_coded_kernel(const uint8_t *__restrict__ codes, const float *__rest
     }
 }
 
-// Same planes for a transposed activation operand: op(A)(m, k) = A[k + m * lda] is already K-major, so this is a
-// plain copy-and-split.
+// Same planes for a transposed activation operand: op(A)(m, k) = A[k + m * lda] is already K-major (this is also what
+// a row-major M x K batch looks like), so this is a copy-and-split: four consecutive k per thread, 16-byte loads and
+// stores when the row pitch and the base allow, one block row per m.
 __global__ void __launch_bounds__(256)
 cn_act_split_t_kernel(const float *__restrict__ A, int64_t lda, int64_t M, int64_t K, int64_t Kpad,
-                      float *__restrict__ hi, float *__restrict__ lo)
+                      float *__restrict__ hi, float *__restrict__ lo, int vec_ok)
 {
-    const int64_t total = M * Kpad;
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int64_t m = i / Kpad, k = i - m * Kpad;
-        const float x = k < K ? A[k + m * lda] : 0.0f;
-        const uint32_t h = to_tf32(x);
-        hi[i] = __uint_as_float(h);
-        if (lo) lo[i] = __uint_as_float(to_tf32(x - __uint_as_float(h)));
+    const int64_t k4 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (k4 >= Kpad) return;
+    for (int64_t m = blockIdx.y; m < M; m += gridDim.y) {
+        const float *src = A + m * lda + k4;
+        float x[4];
+        if (vec_ok && k4 + 3 < K) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(src));
+            x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) x[e] = (k4 + e < K) ? src[e] : 0.0f;
+        }
+        uint32_t h[4], l[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            h[e] = to_tf32(x[e]);
+            l[e] = to_tf32(x[e] - __uint_as_float(h[e]));
+        }
+        const int64_t o = m * Kpad + k4;   // Kpad is a multiple of 32 and the planes are 256-byte aligned
+        *reinterpret_cast<uint4 *>(hi + o) = make_uint4(h[0], h[1], h[2], h[3]);
+        if (lo) *reinterpret_cast<uint4 *>(lo + o) = make_uint4(l[0], l[1], l[2], l[3]);
     }
 }
 
@@ -400,7 +414,6 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     if (kb_end > p.kb_total) kb_end = p.kb_total;
     const int num_kb = kb_end - kb_begin;   // >= 1 by construction on the host
     const int chain_kb = p.chain_kb;
-    const int num_chains = (num_kb + chain_kb - 1) / chain_kb;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::W_STAGES; ++s) { mbar_init(wfull_bar(s), 1); mbar_init(wempty_bar(s), 128); }
@@ -469,7 +482,10 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                 constexpr uint32_t idesc = make_idesc_tf32(TC_BN, TC_BM);
                 bool ok = true;
                 // chain bookkeeping without divisions: position inside the chain, accumulator buffer and its phase
-                int chain_pos = 0, ab = 0;
+                // W tile 1 starts half a chain into its schedule, so that the two tiles never reach a chain end (and the
+                // wait for their drain warps) on the same K block: while one tile's accumulator is read out, the MMAs of
+                // the other keep the tensor pipe busy
+                int chain_pos = (NT == 2 && w == 1) ? chain_kb / 2 : 0, ab = 0;
                 uint32_t aph = 0;
                 // operands of the first K block
                 ok = mbar_wait(afull_bar(0), 0u, abort_flag, p.status, 2u) && mbar_wait(tfull_bar(0), 0u, abort_flag, p.status, 3u);
@@ -583,7 +599,9 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
 #pragma unroll
         for (int i = 0; i < TC_BM; ++i) acc[i] = 0.0f;
         bool ok = true;
-        for (int c = 0; c < num_chains && ok; ++c) {
+        // chains of this W tile: tile 1's first chain is the short one (see the MMA issuer)
+        const int my_chains = (num_kb + ((NT == 2 && w == 1) ? chain_kb / 2 : 0) + chain_kb - 1) / chain_kb;
+        for (int c = 0; c < my_chains && ok; ++c) {
             const int ab = c % Cfg::ACC_BUFS;
             const uint32_t aph = (uint32_t)(c / Cfg::ACC_BUFS) & 1u;
             ok = mbar_wait<TC_DRAIN_SLEEP_NS>(accfull_bar(w, ab), aph, abort_flag, p.status, 6u);
@@ -610,6 +628,22 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                 "selp.u32 %0, 1, 0, po;\n\t}"
                 : "=r"(all_ok) : "r"((uint32_t)ok), "r"(1 + w) : "memory");
             ok = all_ok != 0;
+        }
+        if (ok && NT == 2 && w == 1) {
+            // This warpgroup stages its output tile in the activation ring.  Its own accumulator being complete says
+            // nothing about the other tile's MMAs, which read the same ring stages: wait until the last K block's stage
+            // has been released by both issuers (their commits arrive in issue order, so every earlier stage is free too).
+            const int last = num_kb - 1;
+            ok = mbar_wait(aempty_bar(last % Cfg::A_STAGES), (uint32_t)(last / Cfg::A_STAGES) & 1u, abort_flag, p.status, 11u);
+            uint32_t all_ok;
+            asm volatile(
+                "{\n\t.reg .pred pi, po;\n\t"
+                "setp.ne.u32 pi, %1, 0;\n\t"
+                "bar.red.and.pred po, %2, 128, pi;\n\t"
+                "selp.u32 %0, 1, 0, po;\n\t}"
+                : "=r"(all_ok) : "r"((uint32_t)ok), "r"(1 + w) : "memory");
+            ok = all_ok != 0;
+            tc_fence_after();
         }
         if (ok) {
             const int64_t ticket_id = tile_id * NT + w;
@@ -837,7 +871,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 
 static int get_encode_fn(cn_context *ctx, EncodeTiledFn *out)
 {
-    if (!ctx->gemm) ctx->gemm = new cn_gemm_workspace();
+    if (!ctx->gemm) ctx->gemm = cn_gemm_workspace_new();
     if (!ctx->gemm->encode_fn) {
         void *fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
@@ -919,10 +953,9 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
     int st = get_encode_fn(ctx, &enc);
     if (st != CN_OK) return st;
     cn_gemm_workspace *ws = ctx->gemm;
-    if (!ws->d_status) {
-        // status word + ticket counters; the kernels leave every ticket at zero again
-        CN_CUDA(cudaMalloc(&ws->d_status, 64 + CN_GEMM_MAX_TICKETS * sizeof(unsigned int)));
-        CN_CUDA(cudaMemset(ws->d_status, 0, 64 + CN_GEMM_MAX_TICKETS * sizeof(unsigned int)));
+    {
+        unsigned int *d_status = nullptr;
+        if ((st = cn_status_block(ctx, &d_status)) != CN_OK) return st;
     }
     const bool mode3x = mode == CN_GEMM_3XTF32;
     const int64_t Kpad = (K + TC_BK - 1) / TC_BK * TC_BK;
@@ -943,8 +976,9 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
             cn_act_split_coded_kernel<<<(unsigned)(tiles_k * tiles_mm), 256, (size_t)cs->nranks * 256 * sizeof(float), s>>>(
                 cs->codes, cs->scales, ctx->d_tbl, cs->own_fp32, cs->own_rank, cs->nranks, M, K, Kpad, hi, lo, tiles_k);
         } else if (transA) {
-            int64_t blocks = (M * Kpad + 255) / 256, cap = (int64_t)ctx->sm_count * 16;
-            cn_act_split_t_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(A, lda, M, K, Kpad, hi, lo);
+            const int vec_ok = ((lda & 3) == 0) && ((reinterpret_cast<uintptr_t>(A) & 15u) == 0);
+            dim3 grid((unsigned)((Kpad / 4 + 255) / 256), (unsigned)(M < 65535 ? M : 65535));
+            cn_act_split_t_kernel<<<grid, 256, 0, s>>>(A, lda, M, K, Kpad, hi, lo, vec_ok);
         } else {
             cn_act_split_kernel<<<(unsigned)(tiles_k * tiles_mm), 256, 0, s>>>(A, lda, M, K, Kpad, hi, lo, tiles_k);
         }
@@ -955,12 +989,12 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
     // 2. tiling
     const int prm_maxout = epi ? epi->maxout_level : 1;
     int nt = (N >= 2048) ? 2 : 1;
-    if (const char *e = getenv("CN_GEMM_NT")) { int v = atoi(e); if (v == 1 || v == 2) nt = v; }
+    if (ws->force_nt == 1 || ws->force_nt == 2) nt = ws->force_nt;
     const int64_t tiles_n = (N + nt * TC_BN - 1) / (nt * TC_BN), tiles_m = (M + TC_BM - 1) / TC_BM;
     const int64_t tiles = tiles_n * tiles_m;
     const int kb_total = (int)(Kpad / TC_BK);
     int splits = pick_splits(tiles, kb_total, ctx->sm_count);
-    if (const char *e = getenv("CN_GEMM_SPLITS")) { int v = atoi(e); if (v >= 1 && v <= kb_total) splits = v; }
+    if (ws->force_splits >= 1 && ws->force_splits <= kb_total) splits = ws->force_splits;
     if (prm_maxout > 1) splits = 1;   // the split-K reduction kernel has no maxout; such layers are small
     int kb_per_split = (kb_total + splits - 1) / splits;
     splits = (kb_total + kb_per_split - 1) / kb_per_split;   // no empty split
@@ -976,7 +1010,7 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
     prm.tiles_n = tiles_n; prm.tiles_m = tiles_m;
     prm.splits = splits; prm.kb_per_split = kb_per_split; prm.kb_total = kb_total;
     prm.chain_kb = TC_CHAIN_DEFAULT;
-    if (const char *e = getenv("CN_GEMM_CHAIN")) { int v = atoi(e); if (v >= 1) prm.chain_kb = v; }
+    if (ws->force_chain >= 1) prm.chain_kb = ws->force_chain;
     prm.partials = nullptr;
     prm.status = ws->d_status;
     prm.npeers = 0;
@@ -1068,7 +1102,7 @@ extern "C" int cn_gemm_check_status(cn_context *ctx, void *stream)
 extern "C" int cn_gemm_profile_enable(cn_context *ctx, int enable)
 {
     CN_REQUIRE(ctx, CN_ERR_ARG, "cn_gemm_profile_enable: null context");
-    if (!ctx->gemm) ctx->gemm = new cn_gemm_workspace();
+    if (!ctx->gemm) ctx->gemm = cn_gemm_workspace_new();
     ctx->gemm->profile = enable != 0;
     return CN_OK;
 }

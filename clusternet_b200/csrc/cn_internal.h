@@ -63,7 +63,16 @@ struct cn_context {
 
 // cn_gemm.cu
 void cn_gemm_workspace_free(cn_context *ctx);
+// Device status block of the context (word 0: code of the first bounded wait that ran out, read by cn_gemm_check_status),
+// allocated and zeroed on first use.
+int cn_status_block(cn_context *ctx, unsigned int **d_status);
 // cn_comm.cu
 void cn_comm_state_free(cn_context *ctx);
+// Addresses of a symmetric buffer on every rank ([nranks] entries, own rank = local); false if `local` is not inside one.
+bool cn_comm_sym_peers(cn_context *ctx, const void *local, size_t bytes, void **peers_out);
+// Reserves `count` consecutive flag slots of the context's cross-GPU flag block (same call order on every rank).
+int cn_comm_flag_slots(cn_context *ctx, int count, int *first_slot);
+// Queues the one-warp kernel that raises this rank's flag of `slot` on every peer and waits (bounded) for theirs.
+int cn_comm_flag_barrier(cn_context *ctx, int slot, unsigned int epoch, cudaStream_t s);
 
 static inline cudaStream_t cn_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }

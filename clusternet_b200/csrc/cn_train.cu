@@ -115,6 +115,45 @@ cn_decode_sum_kernel(float *__restrict__ grad, const uint8_t *__restrict__ codes
     }
 }
 
+// The same for a packed buffer of several tensors (segments), each coded with its own scale per rank.  A rank's block of
+// the gathered buffer is [codes of all segments][one scale per segment]; seg_end[s] is the end offset of segment s.
+#define CN_SYNC_MAX_SEGMENTS 8
+struct SegParams {
+    int nseg;
+    int64_t seg_end[CN_SYNC_MAX_SEGMENTS];
+};
+
+__global__ void __launch_bounds__(512)
+cn_decode_sum_multi_kernel(float *__restrict__ grad, const uint8_t *__restrict__ blocks, size_t block_bytes, size_t scales_off,
+                           const float *__restrict__ g_tbl, int64_t n, int nranks, int my_rank, const SegParams sp)
+{
+    extern __shared__ float lut[];   // (segment, rank) x 256
+    for (int e = threadIdx.x; e < sp.nseg * nranks * 256; e += blockDim.x) {
+        const int sr = e >> 8, c = e & 255, i = c & 127;
+        const int seg = sr / nranks, r = sr - seg * nranks;
+        const float p = reinterpret_cast<const float *>(blocks + (size_t)r * block_bytes + scales_off)[seg];
+        float v;
+        if (i < CN_CODEBOOK_N) {
+            v = __fmul_rn(g_tbl[i], p);
+            if (c >= 128) v = -v;
+        } else {
+            v = (c == 255) ? -p : p;
+        }
+        lut[e] = v;
+    }
+    __syncthreads();
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        int seg = 0;
+        while (seg + 1 < sp.nseg && i >= sp.seg_end[seg]) ++seg;
+        const float *l = lut + (size_t)seg * nranks * 256;
+        float g = grad[i];
+        for (int r = 0; r < nranks; ++r)
+            if (r != my_rank) g += l[(r << 8) + blocks[(size_t)r * block_bytes + i]];
+        grad[i] = g;
+    }
+}
+
 static int ew_grid(const cn_context *ctx, int64_t n)
 {
     int64_t blocks = (n + 255) / 256, cap = (int64_t)ctx->sm_count * 8;
@@ -222,6 +261,63 @@ extern "C" int cn_grad_sync_8bit(cn_context *ctx, float *d_grad, int64_t n, floa
     int64_t blocks = (n + 511) / 512, cap = (int64_t)ctx->sm_count * 4;
     cn_decode_sum_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 512, (size_t)G * 256 * sizeof(float), cn_stream(stream)>>>(
         d_grad, codes, scales, ctx->d_tbl, n, G, rank);
+    CN_CUDA(cudaGetLastError());
+    cn_count_launch();
+    return CN_OK;
+}
+
+int cn_comm_gather_blocks(cn_context *ctx, uint8_t *d_blocks, size_t block_bytes, void *stream);
+
+// Several tensors that lie back to back in one buffer (the gradients of all layers of a step), each coded with its own
+// scale exactly as cn_grad_sync_8bit would code it alone, but exchanged with ONE all-gather and summed in ONE pass.
+extern "C" int cn_grad_sync_8bit_multi(cn_context *ctx, float *d_grad, const int64_t *segment_sizes, int num_segments,
+                                       float fixed_precision, void *stream)
+{
+    CN_REQUIRE(ctx && segment_sizes && num_segments >= 1, CN_ERR_ARG, "cn_grad_sync_8bit_multi: bad argument");
+    int rank = 0, G = 1;
+    float *unused = nullptr;
+    cn_comm_info(ctx, &rank, &G, &unused);
+    int64_t n = 0;
+    for (int s = 0; s < num_segments; ++s) {
+        CN_REQUIRE(segment_sizes[s] >= 0, CN_ERR_ARG, "cn_grad_sync_8bit_multi: negative segment size");
+        n += segment_sizes[s];
+    }
+    if (G == 1 || n == 0) return CN_OK;
+    CN_REQUIRE(d_grad, CN_ERR_ARG, "cn_grad_sync_8bit_multi: null buffer");
+    if (num_segments > CN_SYNC_MAX_SEGMENTS || (size_t)num_segments * G * 1024 > 48 * 1024) {
+        // too many tables for one pass: segment by segment
+        int64_t off = 0;
+        for (int s = 0; s < num_segments; ++s) {
+            int st = cn_grad_sync_8bit(ctx, d_grad + off, segment_sizes[s], fixed_precision, stream);
+            if (st != CN_OK) return st;
+            off += segment_sizes[s];
+        }
+        return CN_OK;
+    }
+    const size_t scales_off = ((size_t)n + 15) & ~(size_t)15;
+    const size_t block_bytes = scales_off + (((size_t)num_segments * sizeof(float) + 15) & ~(size_t)15);
+    void *buf = nullptr;
+    int st = cn_gemm_scratch(ctx, CN_GEMM_SLOT_EXCHANGE, (size_t)G * block_bytes, &buf);
+    if (st != CN_OK) return st;
+    uint8_t *blocks = (uint8_t *)buf, *mine = blocks + (size_t)rank * block_bytes;
+    float *my_scales = reinterpret_cast<float *>(mine + scales_off);
+    SegParams sp;
+    sp.nseg = num_segments;
+    int64_t off = 0;
+    for (int s = 0; s < num_segments; ++s) {
+        const int64_t sz = segment_sizes[s];
+        if (fixed_precision > 0.0f) st = cn_fill_f32(ctx, my_scales + s, 1, fixed_precision, stream);
+        else st = cn_absmax_f32(ctx, d_grad + off, sz, my_scales + s, stream);
+        if (st == CN_OK && sz > 0) st = cn_compress_8bit_dp(ctx, d_grad + off, my_scales + s, sz, mine + off, stream);
+        if (st != CN_OK) return st;
+        off += sz;
+        sp.seg_end[s] = off;
+    }
+    for (int s = num_segments; s < CN_SYNC_MAX_SEGMENTS; ++s) sp.seg_end[s] = off;
+    if ((st = cn_comm_gather_blocks(ctx, blocks, block_bytes, stream)) != CN_OK) return st;
+    int64_t nblocks = (n + 511) / 512, cap = (int64_t)ctx->sm_count * 4;
+    cn_decode_sum_multi_kernel<<<(unsigned)(nblocks < cap ? nblocks : cap), 512, (size_t)num_segments * G * 256 * sizeof(float), cn_stream(stream)>>>(
+        d_grad, blocks, block_bytes, scales_off, ctx->d_tbl, n, G, rank, sp);
     CN_CUDA(cudaGetLastError());
     cn_count_launch();
     return CN_OK;

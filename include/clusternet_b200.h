@@ -178,12 +178,20 @@ int cn_gemm_check_status(cn_context *ctx, void *stream);
  * next cn_gemm_check_status then returns CN_ERR_TIMEOUT.  Shows (and lets tests assert) that a rank that never signals
  * becomes a host-visible error and not a hang.  The reference has no counterpart: its MPI waits are unbounded. */
 int cn_diag_wait_probe(cn_context *ctx, int64_t limit_cycles, void *stream);
-/* Timing of the tensor-core kernel alone: while enabled, every launch of the main GEMM kernel (not its activation
- * pre-pass) is bracketed by CUDA events on the launching stream.  cn_gemm_profile_read waits for the recorded
- * launches, writes up to `max` durations in milliseconds, in launch order, and clears the record.
+/* Timing of the tensor-core product without its activation pre-pass: while enabled, every launch of the main GEMM
+ * kernel together with the split-K reduction kernel that follows it (when K is split) is bracketed by CUDA events on
+ * the launching stream.  cn_gemm_profile_read waits for the recorded launches, writes up to `max` durations in
+ * milliseconds, in launch order, and clears the record.
  * Takes the place of the reference's tick/tock around a dot call (source/clusterNet.cpp:798-840). */
 int cn_gemm_profile_enable(cn_context *ctx, int enable);
 int cn_gemm_profile_read(cn_context *ctx, float *ms_out, int max, int *count);
+
+/* Test and sweep knobs of the tensor-core kernel, per context; 0 leaves the library's own choice.  tiles_per_cta: 1 or 2
+ * weight tiles of 128 columns per CTA; k_splits: number of K ranges the product is cut into (split-K); chain_k_blocks:
+ * K blocks of 32 accumulated in tensor memory before the sum is folded into fp32 registers.  The environment
+ * variables CN_GEMM_NT / CN_GEMM_SPLITS / CN_GEMM_CHAIN give the initial values, read once per context.  No counterpart
+ * in the reference (cuBLAS picks its kernels itself). */
+int cn_gemm_set_tuning(cn_context *ctx, int tiles_per_cta, int k_splits, int chain_k_blocks);
 
 /* The same elementwise ops as stand-alone kernels over an existing col-major matrix (the reference's
  * un-fused call sites, e.g. source/Layer.cpp:257-259). */
@@ -261,6 +269,12 @@ int cn_sym_free(cn_context *ctx, void *ptr);
 int cn_dotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_total, const float *d_A,
                   const float *d_Wshard, float *d_C, const cn_epilogue *epi, int mode, int exchange, void *stream);
 
+/* TdotMPI with a column-sharded B (source/clusterNet.cpp:510: dotMPI with the first operand transposed): the same
+ * product and exchange as cn_dotmpi_f32, with A given transposed - d_At is the column-major K x M array (leading
+ * dimension lda >= K), which is also what a row-major M x K matrix, e.g. the batch as the host holds it, looks like. */
+int cn_tdotmpi_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_total, const float *d_At, int64_t lda,
+                   const float *d_Wshard, float *d_C, const cn_epilogue *epi, int mode, int exchange, void *stream);
+
 /* The 8-bit exchange with the decode moved into the consumer (the reference's commented 8-bit ring,
  * source/clusterNet.cpp:670-677, decompresses every received slot before hStackN; here the codes stay codes until the
  * next product reads them).  cn_coded describes a gathered M x n_total matrix held as codes: column block r (the
@@ -329,6 +343,12 @@ int cn_rmsprop_update(cn_context *ctx, float *d_rms, const float *d_grad, float 
  * each rank's absmax and gathers the scales (what the reference's commented-out code intended; as committed it decodes
  * with an uninitialised array). */
 int cn_grad_sync_8bit(cn_context *ctx, float *d_grad, int64_t n, float fixed_precision, void *stream);
+/* The same exchange for several tensors that lie back to back in d_grad (segment_sizes is a HOST array of num_segments
+ * element counts, e.g. the weight gradients of all layers of a step): every segment is coded with its own scale and the
+ * result equals num_segments calls of cn_grad_sync_8bit bit for bit, but there is one all-gather and one decode-and-sum
+ * pass per step instead of one per layer (the reference exchanges layer by layer, source/Layer.cpp:341-390). */
+int cn_grad_sync_8bit_multi(cn_context *ctx, float *d_grad, const int64_t *segment_sizes, int num_segments,
+                            float fixed_precision, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Batch allocator (dense path).  Replaces BatchAllocator::init / init_batch_buffer /
@@ -341,6 +361,26 @@ int cn_grad_sync_8bit(cn_context *ctx, float *d_grad, int64_t n, float fixed_pre
 typedef struct cn_batch cn_batch;
 int cn_batch_create(cn_context *ctx, const float *h_X, const float *h_y, int64_t rows, int64_t cols_X, int64_t cols_y,
                     int64_t batch_size, int skip_last_batch, cn_batch **out);
+/* cn_batch_create with options (flags, OR-ed):
+ *   CN_BATCH_KEEP_ROW_MAJOR  the row-major device copy of the current batch stays valid until the next swap (two buffers
+ *       alternate); cn_batch_current_row_major returns it.  Read as a column-major cols_X x rows matrix it is the
+ *       transposed operand of cn_tdotmpi_f32 / cn_gemm_f32(transA = 1), so a product that consumes the batch needs no
+ *       col-major copy of it (the reference always makes one: to_col_major in replace_current_batch_with_next,
+ *       source/batchAllocator.cpp:986-990).
+ *   CN_BATCH_NO_COL_MAJOR    X is not transposed at the swap; cn_batch_current / cn_batch_swap return d_X = NULL.
+ *   CN_BATCH_SHARDED_UPLOAD  collective over the context's communicator; EVERY rank passes the same host data set (the
+ *       Matrix* form of BatchAllocator::init, in which every process holds the data and stages its own batches,
+ *       source/batchAllocator.cpp:411-440).  Rank r uploads only its block of floor(batch/G) rows (last rank: plus the
+ *       remainder) over its own PCIe link and writes that block into every peer's buffer over NVLink; two bounded
+ *       cross-GPU flag exchanges on the copy stream order the writes (a peer that never takes part surfaces as
+ *       CN_ERR_TIMEOUT from cn_gemm_check_status).  Ignored with one rank. */
+#define CN_BATCH_KEEP_ROW_MAJOR 1
+#define CN_BATCH_NO_COL_MAJOR 2
+#define CN_BATCH_SHARDED_UPLOAD 4
+int cn_batch_create_ex(cn_context *ctx, const float *h_X, const float *h_y, int64_t rows, int64_t cols_X, int64_t cols_y,
+                       int64_t batch_size, int skip_last_batch, int flags, cn_batch **out);
+/* Row-major device copy (batch_rows x cols_X, leading dimension cols_X) of the current batch; needs CN_BATCH_KEEP_ROW_MAJOR. */
+int cn_batch_current_row_major(const cn_batch *b, float **d_X_row_major, int64_t *batch_rows);
 int cn_batch_destroy(cn_batch *b);
 int64_t cn_batch_total_batches(const cn_batch *b);
 /* The batch that is current now (after cn_batch_create: the first batch, as BatchAllocator::init leaves it). */

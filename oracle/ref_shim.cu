@@ -50,6 +50,25 @@ int ref_decompression_8bit(float *d_tbl, unsigned char *d_codes, float precision
     return (int)cudaDeviceSynchronize();
 }
 
+/* The same two launchers without the device synchronisation, for timing a series of launches with events */
+void ref_compression_8bit_async(float *d_tbl, float *d_A, float precision, int n, unsigned char *d_out)
+{
+    Matrix tbl = wrap(d_tbl, 126, 1);
+    Matrix A = wrap(d_A, n, 1);
+    Matrix out = wrap(0, n, 1);
+    out.char_data = d_out;
+    compression_8bit(&tbl, &A, precision, &out);
+}
+
+void ref_decompression_8bit_async(float *d_tbl, unsigned char *d_codes, float precision, int n, float *d_out)
+{
+    Matrix tbl = wrap(d_tbl, 126, 1);
+    Matrix A = wrap(0, n, 1);
+    A.char_data = d_codes;
+    Matrix out = wrap(d_out, n, 1);
+    decompression_8bit(&tbl, &A, precision, &out);
+}
+
 /* abs + max: source/basicOps.cu:810-822,1076-1081 */
 float ref_absmax(float *d_A, float *d_tmp, int n)
 {

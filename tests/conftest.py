@@ -8,6 +8,14 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 
+def reference_dir():
+    """The reference source tree when one is at hand ($CN_REFERENCE_DIR, else `reference` beside the repository)."""
+    for cand in (os.environ.get("CN_REFERENCE_DIR"), os.path.join(os.path.dirname(ROOT), "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "source")):
+            return cand
+    return None
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (sm_100a)")
 

@@ -1,7 +1,7 @@
 """Generates golden vectors for the 8-bit codec by running the REFERENCE's own kernels (kCompression_8bit,
 kDecompression_8bit, abs + max), recompiled for sm_100a into oracle/_ref/libcnref.so, on a GPU.
 
-    python tests/golden/make_codec_golden.py [output.npz]        (needs a GPU and oracle/_ref/libcnref.so)
+    python tests/golden/make_codec_golden.py output.npz        (needs a GPU and oracle/_ref/libcnref.so)
 
 Inputs: 60000 values ~ N(0, 0.1) from numpy's default_rng(1) plus every codebook entry, every midpoint of adjacent
 entries, the two range thresholds and a few magnitudes, each with its +-2 ulp neighbours and both signs, plus
@@ -35,7 +35,9 @@ def inputs(tbl):
 
 
 def main():
-    out_path = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "codec_ref_golden.npz")
+    if len(sys.argv) != 2:
+        sys.exit(__doc__)
+    out_path = sys.argv[1]
     L = ctypes.CDLL(os.path.join(ROOT, "oracle", "_ref", "libcnref.so"))
     L.ref_absmax.restype = ctypes.c_float
     tbl = np.fromfile(os.path.join(ROOT, "tests", "golden", "codebook_126.f32"), dtype="<f4")

@@ -118,9 +118,10 @@ def test_hdf5_reader_rejects_damaged_files(built_lib, tmp_path):
 
 
 def test_hdf5_datasets_of_the_reference_when_mounted(built_lib):
-    ref = "/root/reference/tests"
-    if not os.path.exists(ref):
+    from conftest import reference_dir
+    if not reference_dir():
         pytest.skip("reference tree not mounted")
+    ref = os.path.join(reference_dir(), "tests")
     X = clusternet_b200.read_hdf5(os.path.join(ref, "mnist_mini_X.hdf5"))
     y = clusternet_b200.read_hdf5(os.path.join(ref, "mnist_mini_y.hdf5"))
     assert X.shape == (500, 784) and y.shape == (500, 1)
@@ -129,9 +130,10 @@ def test_hdf5_datasets_of_the_reference_when_mounted(built_lib):
 
 
 def test_codebook_matches_reference_file_when_mounted(codebook):
-    ref = "/root/reference/source/8bit_floats.hdf5"
-    if not os.path.exists(ref):
+    from conftest import reference_dir
+    if not reference_dir():
         pytest.skip("reference tree not mounted")
+    ref = os.path.join(reference_dir(), "source", "8bit_floats.hdf5")
     import hashlib
     blob = open(ref, "rb").read()
     assert hashlib.sha256(blob).hexdigest() == "d584e1a65e8d1f0b48e53dcf814ea2d3bd43982b6088c7c1159e616e4418ae7b"

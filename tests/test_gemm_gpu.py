@@ -89,9 +89,16 @@ def test_config1_dot_bias_relu(ctx):
 
 
 @pytest.mark.parametrize("splits,nt", [(1, 1), (3, 1), (7, 1), (1, 2), (4, 2)])
-def test_split_k_and_tile_variants(ctx, splits, nt, monkeypatch):
-    monkeypatch.setenv("CN_GEMM_SPLITS", str(splits))
-    monkeypatch.setenv("CN_GEMM_NT", str(nt))
+def test_split_k_and_tile_variants(ctx, splits, nt):
+    from clusternet_b200 import check
+    check(ctx.lib.cn_gemm_set_tuning(ctx.h, nt, splits, 0))
+    try:
+        _split_k_and_tile_variant(ctx, splits, nt)
+    finally:
+        check(ctx.lib.cn_gemm_set_tuning(ctx.h, 0, 0, 0))
+
+
+def _split_k_and_tile_variant(ctx, splits, nt):
     rng = np.random.default_rng(splits * 10 + nt)
     M, K, N = 128, 2048, 640
     A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
