@@ -486,12 +486,12 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                 // wait for their drain warps) on the same K block: while one tile's accumulator is read out, the MMAs of
                 // the other keep the tensor pipe busy
                 int chain_pos = (NT == 2 && w == 1) ? chain_kb / 2 : 0, ab = 0;
+                bool chain_first = true;   // the next K block opens a chain: it overwrites the accumulator
                 uint32_t aph = 0;
                 // operands of the first K block
                 ok = mbar_wait(afull_bar(0), 0u, abort_flag, p.status, 2u) && mbar_wait(tfull_bar(0), 0u, abort_flag, p.status, 3u);
                 for (int i = 0; i < num_kb && ok; ++i) {
                     const int s = i % Cfg::A_STAGES, t = i % Cfg::TMEM_STAGES;
-                    const bool chain_first = chain_pos == 0;
                     const bool chain_last = chain_pos == chain_kb - 1 || i == num_kb - 1;
                     tc_fence_after();
                     const uint32_t stage = smem_base + Cfg::A_RING + s * Cfg::A_STAGE_BYTES;
@@ -526,9 +526,11 @@ cn_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                     if (chain_last) {
                         tc_commit(accfull_bar(w, ab));
                         chain_pos = 0;
+                        chain_first = true;
                         if (++ab == Cfg::ACC_BUFS) { ab = 0; aph ^= 1u; }
                     } else {
                         ++chain_pos;
+                        chain_first = false;
                     }
                     tc_commit(aempty_bar(s));   // activation stage may be refilled once these MMAs retire
                     tc_commit(tempty_bar(t));   // and the TMEM operand stage rewritten

@@ -159,6 +159,64 @@ def run_nccl():
             want = (want + oracle.decompress(ctx.codebook, oracle.compress(ctx.codebook, grads[r], p), p)).astype(np.float32)
         torch.cuda.synchronize()
         assert np.array_equal(g.cpu().numpy(), want), fixed
+    # the packed exchange (several tensors, one gather, one decode-and-sum pass) == one exchange per tensor
+    segs = [30001, 0, 40000]
+    gp = torch.from_numpy(grads[rank].copy()).cuda()
+    cn.check(ctx.lib.cn_grad_sync_8bit_multi(ctx.h, gp.data_ptr(), (ctypes.c_int64 * 3)(*segs), 3, 0.0, ctx.stream_ptr()))
+    gs = torch.from_numpy(grads[rank].copy()).cuda()
+    o = 0
+    for sz in segs:
+        cn.check(ctx.lib.cn_grad_sync_8bit(ctx.h, gs[o:].data_ptr(), sz, 0.0, ctx.stream_ptr()))
+        o += sz
+    torch.cuda.synchronize()
+    assert torch.equal(gp, gs)
+    # TdotMPI with a sharded B: the row-major batch as a transposed operand, through the fused gather
+    M, K, N = 128, 2048, 2048 + 8 * world
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    W = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    s0, c0 = ctx.shard_cols(N, rank, world)
+    dW = ctx.colmajor(np.ascontiguousarray(W[:, s0:s0 + c0]))
+    want = ctx.dotmpi(ctx.colmajor(A), dW, N)
+    rm = torch.from_numpy(A).cuda()
+    got = ctx.sym_empty(M, N)
+    epi = cn.Epilogue(None, 0, 0, None)
+    cn.check(ctx.lib.cn_tdotmpi_f32(ctx.h, M, K, N, rm.data_ptr(), K, dW.data_ptr(), got.data_ptr(), ctypes.byref(epi), _lib.GEMM_3XTF32, 0,
+                                    ctx.stream_ptr()))
+    ctx.gemm_check()
+    assert torch.equal(got, want)
+    # batch allocator with the sharded upload: every rank holds the data set and uploads 1/G of each batch's rows; the
+    # blocks are exchanged over NVLink; every rank then sees every batch whole (tests/batchAllocator_test.cu:40-114 form)
+    rows, cols_x, B = 1000, 36, 128
+    X = np.arange(rows * cols_x, dtype=np.float32).reshape(rows, cols_x)
+    y = np.arange(rows, dtype=np.float32).reshape(rows, 1) + 0.5
+    hX, hy = torch.from_numpy(X).pin_memory(), torch.from_numpy(y).pin_memory()
+    for flags in (_lib.BATCH_SHARDED_UPLOAD, _lib.BATCH_SHARDED_UPLOAD | _lib.BATCH_NO_COL_MAJOR):
+        bh = ctypes.c_void_p()
+        cn.check(ctx.lib.cn_batch_create_ex(ctx.h, hX.data_ptr(), hy.data_ptr(), rows, cols_x, 1, B, 0, flags, ctypes.byref(bh)))
+        ora = oracle.BatchOracle(rows, B, False)
+        px, py, n, prm = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_int64(), ctypes.c_void_p()
+        cn.check(ctx.lib.cn_batch_current(bh, ctypes.byref(px), ctypes.byref(py), ctypes.byref(n)))
+        start, cnt = ora.current
+        rt = ctypes.CDLL("libcudart.so.12")
+        for step in range(2 * ora.total + 2):
+            cn.check(ctx.lib.cn_batch_copy_next_async(bh))
+            cn.check(ctx.lib.cn_batch_current_row_major(bh, ctypes.byref(prm), ctypes.byref(n)))
+            torch.cuda.synchronize()
+            assert n.value == cnt
+            buf = torch.empty((cnt, cols_x), device="cuda")
+            assert rt.cudaMemcpy(ctypes.c_void_p(buf.data_ptr()), prm, ctypes.c_size_t(cnt * cols_x * 4), 3) == 0
+            assert np.array_equal(buf.cpu().numpy(), X[start:start + cnt]), (flags, step)
+            if not (flags & _lib.BATCH_NO_COL_MAJOR):
+                cm = torch.empty((cols_x, cnt), device="cuda")
+                assert rt.cudaMemcpy(ctypes.c_void_p(cm.data_ptr()), px, ctypes.c_size_t(cnt * cols_x * 4), 3) == 0
+                assert np.array_equal(cm.cpu().numpy().T, X[start:start + cnt])
+            cn.check(ctx.lib.cn_batch_swap(bh, ctx.stream_ptr(), ctypes.byref(px), ctypes.byref(py), ctypes.byref(n)))
+            start, cnt = ora.advance()
+        ctx.gemm_check()
+        torch.cuda.synchronize()
+        dist.barrier()
+        ctx.lib.cn_batch_destroy(bh)
+        dist.barrier()
     # scalar gather and all-reduce
     v = torch.zeros(world, device="cuda")
     v[rank] = rank + 1.5

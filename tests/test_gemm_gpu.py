@@ -55,6 +55,33 @@ def test_tensor_core_gemm_vs_fp64(ctx, M, K, N, mode):
     assert err < (TOL_3XTF32 if mode == _lib.GEMM_3XTF32 else TOL_TF32), err
 
 
+@pytest.mark.parametrize("M,K,N", [(128, 100000, 1024), (128, 100000, 5000), (128, 40000, 2500), (128, 100000, 2304)])
+@pytest.mark.parametrize("mode", [_lib.GEMM_3XTF32, _lib.GEMM_TF32])
+def test_long_inner_dimension_vs_fp64_on_sampled_columns(ctx, M, K, N, mode):
+    """The regime of the README benchmark (source/test.cu, README.md:22-32): K = 100000 and the per-rank shapes of its two
+    layers at 8 ranks.  Inputs as there (batch uniform [0,1), weights uniform +-4*sqrt(6/(in+out))); the accumulation runs
+    over 3125 K blocks, i.e. hundreds of TMEM chains and several K splits.  Checked on sampled columns (both ends, tile
+    edges, random) against an fp64 host product."""
+    g = torch.Generator(device="cuda")
+    g.manual_seed(K + N)
+    lim = 4.0 * np.sqrt(6.0 / (K + 8 * N))
+    A = torch.rand((K, M), device="cuda", generator=g)                          # column-major M x K
+    W = (torch.rand((N, K), device="cuda", generator=g) * 2 - 1) * lim         # column-major K x N
+    C = ctx.gemm(A, W, mode=mode)
+    ctx.gemm_check()
+    assert ctx.gemm_last_path() == ("tcgen05_3xtf32" if mode == _lib.GEMM_3XTF32 else "tcgen05_tf32")
+    rng = np.random.default_rng(N)
+    cols = np.unique(np.concatenate([[0, 1, 127, 128, 129, 255, 256, 257, N - 2, N - 1], rng.integers(0, N, 40)]))
+    ci = torch.from_numpy(cols).cuda()
+    ref = A.T.double().cpu().numpy() @ W[ci].double().cpu().numpy().T          # (M, ncols) in fp64 on the host
+    got = C[ci].double().cpu().numpy().T
+    err = float(np.abs(got - ref).max() / float(C.abs().max()))
+    assert err < (TOL_3XTF32 if mode == _lib.GEMM_3XTF32 else TOL_TF32), err
+    # the same launch twice gives the same bits (split-K partials are added in split order)
+    C2 = ctx.gemm(A, W, mode=mode)
+    assert torch.equal(C, C2)
+
+
 @pytest.mark.parametrize("transA,transB", [(True, False), (False, True), (True, True)])
 @pytest.mark.parametrize("M,K,N", [(128, 1200, 1200), (784, 128, 1200), (200, 96, 333 * 4), (128, 4096, 1024)])
 def test_transposed_operands_on_the_tensor_path(ctx, transA, transB, M, K, N):

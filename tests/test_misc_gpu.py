@@ -79,12 +79,20 @@ def _copy_from_device_pointer(ptr, count):
     return out
 
 
-def _batch_epochs(ctx, rows, cols_x, cols_y, B, skip_last=False, epochs=2):
+def _batch_epochs(ctx, rows, cols_x, cols_y, B, skip_last=False, epochs=2, flags=0, pinned=False):
     X = np.arange(rows * cols_x, dtype=np.float32).reshape(rows, cols_x)
     y = np.arange(rows * cols_y, dtype=np.float32).reshape(rows, cols_y) + 0.5
     hX, hy = torch.from_numpy(X), torch.from_numpy(y)
+    if pinned:
+        hX, hy = hX.pin_memory(), hy.pin_memory()
     h = ctypes.c_void_p()
-    cn.check(ctx.lib.cn_batch_create(ctx.h, hX.data_ptr(), hy.data_ptr(), rows, cols_x, cols_y, B, int(skip_last), ctypes.byref(h)))
+    if flags:
+        cn.check(ctx.lib.cn_batch_create_ex(ctx.h, hX.data_ptr(), hy.data_ptr(), rows, cols_x, cols_y, B, int(skip_last), flags, ctypes.byref(h)))
+    else:
+        cn.check(ctx.lib.cn_batch_create(ctx.h, hX.data_ptr(), hy.data_ptr(), rows, cols_x, cols_y, B, int(skip_last), ctypes.byref(h)))
+    keep_rm = bool(flags & (_lib.BATCH_KEEP_ROW_MAJOR | _lib.BATCH_NO_COL_MAJOR))
+    prm, nrm = ctypes.c_void_p(), ctypes.c_int64()
+    prev_rm = None
     ora = oracle.BatchOracle(rows, B, skip_last)
     assert ctx.lib.cn_batch_total_batches(h) == ora.total
     px, py, n = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_int64()
@@ -95,12 +103,23 @@ def _batch_epochs(ctx, rows, cols_x, cols_y, B, skip_last=False, epochs=2):
         assert n.value == cnt
         # current batch on the device is column-major n x cols
         torch.cuda.synchronize()
-        bx = _copy_from_device_pointer(px, cols_x * n.value).reshape(cols_x, n.value)
+        if flags & _lib.BATCH_NO_COL_MAJOR:
+            assert not px.value
+        else:
+            bx = _copy_from_device_pointer(px, cols_x * n.value).reshape(cols_x, n.value)
+            assert np.array_equal(bx.cpu().numpy().T, X[start:start + cnt])
+            total += float(bx.double().sum())
         by = _copy_from_device_pointer(py, cols_y * n.value).reshape(cols_y, n.value)
-        assert np.array_equal(bx.cpu().numpy().T, X[start:start + cnt])
         assert np.array_equal(by.cpu().numpy().T, y[start:start + cnt])
-        total += float(bx.double().sum())
         cn.check(ctx.lib.cn_batch_copy_next_async(h))
+        if keep_rm:
+            # the row-major copy of the CURRENT batch must survive the copy of the next one that was just queued
+            cn.check(ctx.lib.cn_batch_current_row_major(h, ctypes.byref(prm), ctypes.byref(nrm)))
+            torch.cuda.synchronize()
+            assert nrm.value == cnt and prm.value != prev_rm
+            rm = _copy_from_device_pointer(prm, cols_x * cnt).reshape(cnt, cols_x)
+            assert np.array_equal(rm.cpu().numpy(), X[start:start + cnt])
+            prev_rm = prm.value
         cn.check(ctx.lib.cn_batch_swap(h, ctx.stream_ptr(), ctypes.byref(px), ctypes.byref(py), ctypes.byref(n)))
         start, cnt = ora.advance()
     ctx.lib.cn_batch_destroy(h)
@@ -115,6 +134,50 @@ def test_batch_allocator_epochs_with_partial_last_batch(ctx):
 def test_batch_allocator_exact_multiple_and_skip_last(ctx):
     _batch_epochs(ctx, rows=512, cols_x=8, cols_y=2, B=128)
     _batch_epochs(ctx, rows=1000, cols_x=5, cols_y=1, B=128, skip_last=True)
+
+
+@pytest.mark.parametrize("flags", [_lib.BATCH_KEEP_ROW_MAJOR, _lib.BATCH_NO_COL_MAJOR, _lib.BATCH_SHARDED_UPLOAD])
+@pytest.mark.parametrize("pinned", [False, True])
+def test_batch_allocator_options(ctx, flags, pinned):
+    """cn_batch_create_ex: the row-major copy of the current batch stays valid (two buffers alternate), X is not
+    transposed when that is switched off, and the sharded upload is the plain one on a single rank."""
+    _batch_epochs(ctx, rows=1000, cols_x=20, cols_y=1, B=128, flags=flags, pinned=pinned)
+    h = ctypes.c_void_p()
+    x = torch.zeros(256, 4)
+    assert ctx.lib.cn_batch_create_ex(ctx.h, x.data_ptr(), x.data_ptr(), 256, 4, 4, 128, 0, 64, ctypes.byref(h)) == _lib.CN_ERR_ARG
+
+
+def test_row_major_batch_feeds_the_product_as_a_transposed_operand(ctx):
+    """The batch as the host holds it (row-major M x K) is the transposed operand of TdotMPI (source/clusterNet.cpp:510):
+    the product equals the one computed from the column-major copy, bit for bit, also for K that is not a multiple of 4
+    and for a leading dimension above K."""
+    rng = np.random.default_rng(9)
+    for (M, K, N, pad) in [(128, 4096, 512, 0), (128, 1000, 384, 0), (100, 1002, 256, 0), (64, 512, 256, 8), (7, 33, 64, 1)]:
+        A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+        W = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+        dW = ctx.colmajor(W)
+        want = ctx.gemm(ctx.colmajor(A), dW)
+        lda = K + pad
+        rm = torch.zeros((M, lda), device="cuda")
+        rm[:, :K] = torch.from_numpy(A).cuda()
+        got = ctx.empty(M, N)
+        epi = cn.Epilogue(None, 0, 0, None)
+        cn.check(ctx.lib.cn_tdotmpi_f32(ctx.h, M, K, N, rm.data_ptr(), lda, dW.data_ptr(), got.data_ptr(), ctypes.byref(epi),
+                                        _lib.GEMM_3XTF32, 0, ctx.stream_ptr()))
+        ctx.gemm_check()
+        assert torch.equal(got, want), (M, K, N, pad)
+        ref = oracle.gemm_f64(A, W)
+        assert np.abs(ctx.to_numpy(got) - ref).max() / np.abs(ref).max() < 1e-5
+
+
+def test_packed_gradient_exchange_is_a_no_op_on_one_rank(ctx):
+    g = torch.randn(1000, device="cuda")
+    keep = g.clone()
+    seg = (ctypes.c_int64 * 3)(300, 0, 700)
+    cn.check(ctx.lib.cn_grad_sync_8bit_multi(ctx.h, g.data_ptr(), seg, 3, 0.0, ctx.stream_ptr()))
+    assert torch.equal(g, keep)
+    seg = (ctypes.c_int64 * 1)(-1)
+    assert ctx.lib.cn_grad_sync_8bit_multi(ctx.h, g.data_ptr(), seg, 1, 0.0, ctx.stream_ptr()) == _lib.CN_ERR_ARG
 
 
 def test_batch_size_larger_than_data_is_rejected(ctx):
