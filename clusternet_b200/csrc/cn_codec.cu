@@ -15,13 +15,31 @@
 // Whenever that construction is not available (precision zero, non-finite or outside 2^-100..2^100, or a
 // codebook so dense that two boundaries share a bucket) the kernel takes the generic path: IEEE divide
 // per element, then a 7-step search of the 127 thresholds.  Both paths give identical codes.
+//
+// Streaming.  For 16-byte aligned buffers the compressor (cn_compress_ring_kernel) stages its input through a
+// shared-memory ring filled by bulk asynchronous copies (cp.async.bulk global -> shared, completion on mbarriers):
+// one elected thread keeps six 32 KB tiles per SM in flight from the first microsecond, independently of what the
+// 1024 coding threads are doing, so the depth of the prefetch does not cost registers and the table build overlaps the
+// first loads.  The coding threads read the staged tile with conflict-free 16-byte shared loads.
+//
+// Launch overlap.  All codec kernels are launched with programmatic stream serialisation: each kernel lets its
+// successor start as soon as it is resident (griddepcontrol.launch_dependents), does everything that needs no global
+// memory (barrier set-up, and the table build when the scale came from the host) and only then waits for the
+// predecessor to finish (griddepcontrol.wait) - before its first access to global memory.  In a series of codec
+// calls the launch latency, the CTA start-up and the table build of call i+1 then overlap the tail of call i.
 #include <math.h>
+#include <string.h>
 #include "cn_internal.h"
 
 #define CODEC_THREADS 1024
 #define ABSMAX_THREADS 512
 #define LUT_SHIFT 16
 #define LUT_MAX 2816
+
+// Programmatic dependent launch: "my successor in the stream may start" / "my predecessor has finished and its writes are
+// visible".  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void cdc_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void cdc_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // The small per-codebook tables travel as kernel parameters (constant bank): read from global memory they would be a
 // cold DRAM miss on the critical path of every launch's table build.
@@ -114,6 +132,8 @@ cn_compress_kernel(const float *__restrict__ A, float precision_arg, const float
 {
     __shared__ CodecTables t;
     const int tid = threadIdx.x;
+    cdc_pdl_launch_dependents();
+    cdc_pdl_wait();
     const float p = PRECISION_ON_DEVICE ? *d_precision : precision_arg;
     const uint32_t pb = __float_as_uint(p);
     const uint32_t psign4 = (pb >> 31) * 0x80808080u;
@@ -249,6 +269,329 @@ cn_compress_kernel(const float *__restrict__ A, float precision_arg, const float
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------- ring compressor
+#define RING_THREADS 512                    // two CTAs per SM
+#define RING_TILE 8192                      // elements per tile: 32 KB of input, four 16-byte groups per thread
+#define RING_STAGES 3                       // per CTA: 6 tiles = 192 KB in flight per SM
+#define RING_GROUPS_PER_THREAD (RING_TILE / 4 / RING_THREADS)
+#define RING_WAIT_LIMIT (4000000000LL)      // clock cycles (~2 s)
+
+__device__ __forceinline__ uint32_t cdc_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cdc_mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void cdc_mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cdc_mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t cdc_mbar_try(uint32_t bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done;
+}
+// Bounded wait: false when the limit ran out (the caller stops streaming and reports through *status).
+__device__ __forceinline__ bool cdc_mbar_wait(uint32_t bar, uint32_t parity, unsigned int *status)
+{
+    if (cdc_mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; ++it) {
+        if (cdc_mbar_try(bar, parity)) return true;
+        if ((it & 255u) == 0u && clock64() - t0 > RING_WAIT_LIMIT) {
+            if (status) atomicMax(status, 12u);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void cdc_bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// Per-launch tables of the ring compressor.  The magnitudes are looked up in a shifted and clamped domain,
+//     c = clamp(|x| bits + delta - lo, 0, hi - lo),
+// with delta (< 65536) chosen so that the boundary of the top level (code 127) falls exactly on the start of a bucket
+// (the top level then owns whole buckets and never shares one with its close neighbour), lo = start of a bucket that
+// lies entirely below the first boundary and hi = start of the top level's bucket.  The clamp is one instruction
+// (min.relu.s32).  One 4-byte entry per bucket of 65536 consecutive c: bits 31..16 = low 16 bits of the boundary inside
+// the bucket (0 = none: every c of the bucket counts as "at or above"), bits 15..8 = code at and above the boundary,
+// bits 7..0 = code below it; c is compared as (c << 16 | 0xffff) >= entry.
+// Two resources bound the stream next to HBM: the integer pipe (64 lanes per SM and clock against 128 for fp32) and the
+// shared-memory pipe (the table reads of a warp hit random banks: ~4 wavefronts per read).  Hence 4-byte entries, and
+// a per-element sequence of: and, add, min.relu, shift, address, shared load, multiply-add (the compare key, on the
+// fp32/imad pipe), compare, predicated shift.
+struct RingTables {
+    uint32_t lut[LUT_MAX];
+    uint32_t X[128];        // boundaries in |x| space (bit patterns); [126] = top level, [127] = pad
+    uint32_t T[128];        // thresholds in |x/precision| space (generic path)
+    uint32_t lc[128];       // level codes
+    uint32_t kadd;          // delta - lo (mod 2^32)
+    int32_t span;           // hi - lo
+    int nb, bad;
+};
+
+// Boundaries found on the host for a host-side scale (same IEEE arithmetic), or left to the kernel (device scale).
+struct RingConst {
+    uint32_t thr[128];
+    uint32_t lc[128];
+    uint32_t X[128];
+    int x_valid;            // X holds the boundaries for this launch's precision
+};
+
+__device__ __forceinline__ uint32_t ring_generic(float x, float p, const RingTables &t)
+{
+    float a = __fdiv_rn(x, p);
+    if (a != a) return 1u;
+    const bool neg = a < 0.0f;
+    const uint32_t ab = __float_as_uint(a) & 0x7fffffffu;
+    const uint32_t c = t.lc[count_le(t.T, ab)];
+    return (neg && c != 254u) ? (c | 0x80u) : c;
+}
+
+// code of one magnitude (low byte of the result; the bytes above are not meaningful): finite or infinite input
+__device__ __forceinline__ uint32_t ring_lookup(uint32_t xbits, uint32_t kadd, int32_t span, uint32_t lut_addr)
+{
+    const int32_t w = (int32_t)((xbits & 0x7fffffffu) + kadd);
+    int32_t c;
+    asm("min.relu.s32 %0, %1, %2;" : "=r"(c) : "r"(w), "r"(span));
+    uint32_t bucket, e, key;
+    asm("shr.u32 %0, %1, 16;" : "=r"(bucket) : "r"(c));             // kept apart from the scaling below: index * 4 + base is an addressing mode
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(e) : "r"(bucket * 4u + lut_addr));
+    asm("mad.lo.u32 %0, %1, 65536, 65535;" : "=r"(key) : "r"(c));   // (c << 16) | 0xffff
+    asm("{\n\t.reg .pred p;\n\tsetp.ge.u32 p, %1, %0;\n\t@p shr.u32 %0, %0, 8;\n\t}" : "+r"(e) : "r"(key));
+    return e;
+}
+
+__device__ __forceinline__ uint32_t ring_code(uint32_t xb, uint32_t pb, uint32_t kadd, int32_t span, uint32_t lut_addr)
+{
+    if ((xb & 0x7fffffffu) > 0x7f800000u) return 1u;      // NaN: the reference's search ends on index 1, sign clear
+    return (ring_lookup(xb, kadd, span, lut_addr) & 0xffu) | (((xb ^ pb) >> 24) & 0x80u);
+}
+
+// four codes for one 16-byte group.  A NaN anywhere in the group (rare) sends it through the per-element form; the test
+// is a floating-point sum (x != x for the sum: NaN inputs, and +inf with -inf, which the per-element form codes
+// correctly as well), which keeps it off the integer pipe.
+__device__ __forceinline__ uint32_t ring_code4(const float4 q, uint32_t pb, uint32_t psign4, uint32_t kadd, int32_t span, uint32_t lut_addr)
+{
+    const uint32_t x0 = __float_as_uint(q.x), x1 = __float_as_uint(q.y), x2 = __float_as_uint(q.z), x3 = __float_as_uint(q.w);
+    const float sum = (q.x + q.y) + (q.z + q.w);
+    if (sum != sum)
+        return pack4(ring_code(x0, pb, kadd, span, lut_addr), ring_code(x1, pb, kadd, span, lut_addr),
+                     ring_code(x2, pb, kadd, span, lut_addr), ring_code(x3, pb, kadd, span, lut_addr));
+    const uint32_t c0 = ring_lookup(x0, kadd, span, lut_addr), c1 = ring_lookup(x1, kadd, span, lut_addr);
+    const uint32_t c2 = ring_lookup(x2, kadd, span, lut_addr), c3 = ring_lookup(x3, kadd, span, lut_addr);
+    // top bytes of x0..x3 -> one word; flip by the sign of precision; keep bit 7 of each byte (code 254 has it set already)
+    const uint32_t tops = __byte_perm(__byte_perm(x0, x1, 0x0073), __byte_perm(x2, x3, 0x0073), 0x5410);
+    return pack4(c0, c1, c2, c3) | ((tops ^ psign4) & 0x80808080u);
+}
+
+// Shift, clamp range and bucket table from the 127 boundaries in t.X (all threads of the CTA; ends with a barrier).
+__device__ __forceinline__ void ring_build_tables(RingTables &t, int tid, bool usable)
+{
+    __shared__ uint32_t s_delta, s_lo;
+    __shared__ int s_base;
+    if (tid < 32) {
+        bool bad = !usable;
+        for (int k = 0; k < 4; ++k) {
+            const int idx = tid + 32 * k;
+            if (idx < CN_NUM_THR && t.X[idx] >= 0x7f800000u) bad = true;   // unpinned (0xfffffffe) or not finite
+        }
+        bad = __any_sync(0xffffffffu, bad);
+        if (tid == 0) {
+            const uint32_t xtop = t.X[CN_NUM_THR - 1];
+            const uint32_t delta = ((xtop + 0xffffu) & 0xffff0000u) - xtop;
+            const uint32_t hi = xtop + delta;
+            const int base = (int)((t.X[0] + delta) >> 16) - 1;       // bucket 0 lies entirely below the first boundary
+            const int nb = (int)(hi >> 16) - base + 1;
+            const uint32_t lo = (uint32_t)base << 16;
+            s_delta = delta;
+            s_lo = lo;
+            s_base = base;
+            t.kadd = delta - lo;
+            t.span = (int32_t)(hi - lo);
+            t.nb = nb;
+            t.bad = (bad || base < 1 || nb > LUT_MAX || nb < 3) ? 1 : 0;
+        }
+    }
+    __syncthreads();
+    if (!t.bad) {
+        const int base = s_base, nb = t.nb;
+        const uint32_t delta = s_delta, lo = s_lo;
+        for (int b = tid; b < nb; b += RING_THREADS) {
+            const uint32_t kbv = (uint32_t)(b + base);
+            // first boundary (of 0..126) whose shifted bucket is >= this one
+            int first = 0;
+#pragma unroll
+            for (int step2 = 64; step2 > 0; step2 >>= 1)
+                if (first + step2 - 1 < CN_NUM_THR && ((t.X[first + step2 - 1] + delta) >> 16) < kbv) first += step2;
+            uint32_t e;
+            if (first < CN_NUM_THR && ((t.X[first] + delta) >> 16) == kbv) {
+                e = ((t.X[first] + delta) << 16) | (t.lc[first + 1] << 8) | t.lc[first];
+                if (first + 1 < CN_NUM_THR && ((t.X[first + 1] + delta) >> 16) == kbv) atomicOr(&t.bad, 1);   // two boundaries in one bucket
+            } else {
+                e = (t.lc[first] << 8) | t.lc[first];
+            }
+            t.lut[b] = e;
+        }
+    }
+    __syncthreads();
+}
+
+// Work split: every CTA codes the same number of tiles (tiles_per_cta) of the same size (tile_groups 16-byte groups,
+// at most RING_TILE / 4), chosen on the host so that grid * tiles_per_cta tiles cover the tensor with less than one
+// group of slack per tile; tile j goes to CTA j % grid.  The last tiles may be short or empty.
+template <bool PRECISION_ON_DEVICE>
+__global__ void __launch_bounds__(RING_THREADS, 2)
+cn_compress_ring_kernel(const float *__restrict__ A, float precision_arg, const float *__restrict__ d_precision,
+                        int64_t n, uint8_t *__restrict__ out, const __grid_constant__ RingConst rc, unsigned int *status,
+                        int tile_groups, int tiles_per_cta)
+{
+    extern __shared__ __align__(128) uint8_t ring_smem[];
+    __shared__ RingTables t;
+    __shared__ __align__(8) uint64_t bars[2 * RING_STAGES];
+    const int tid = threadIdx.x;
+    const uint32_t ring_base = (cdc_smem_u32(ring_smem) + 127u) & ~127u;
+    const uint8_t *ring_gen = ring_smem + (ring_base - cdc_smem_u32(ring_smem));
+    auto full_bar = [&](int s) { return cdc_smem_u32(&bars[s]); };
+    auto empty_bar = [&](int s) { return cdc_smem_u32(&bars[RING_STAGES + s]); };
+
+    if (tid == 0) {
+        for (int s = 0; s < RING_STAGES; ++s) { cdc_mbar_init(full_bar(s), 1); cdc_mbar_init(empty_bar(s), RING_THREADS / 32); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    cdc_pdl_launch_dependents();
+    if (tid < 128) {
+        t.T[tid] = rc.thr[tid];
+        t.lc[tid] = rc.lc[tid];
+        if (!PRECISION_ON_DEVICE) t.X[tid] = rc.X[tid];
+    }
+    const int64_t groups_total = n >> 2;                    // 16-byte groups of the tensor
+    // 16-byte groups in tile j (0 for tiles past the end)
+    auto tile_count = [&](int64_t j) {
+        const int64_t left = groups_total - j * tile_groups;
+        return (int)(left < 0 ? 0 : (left < tile_groups ? left : tile_groups));
+    };
+    __syncthreads();   // barriers initialised, constant tables in shared memory
+
+    // ---- everything below may touch global memory: the predecessor in the stream must have finished
+    cdc_pdl_wait();
+    if (tid == 0) {    // fill the ring before anything else: the first loads are in flight while the tables are built
+        for (int i = 0; i < RING_STAGES && i < tiles_per_cta; ++i) {
+            const int64_t j = blockIdx.x + (int64_t)i * gridDim.x;
+            const uint32_t bytes = (uint32_t)tile_count(j) * 16u;
+            if (bytes) {
+                cdc_mbar_expect_tx(full_bar(i), bytes);
+                cdc_bulk_load(ring_base + (uint32_t)i * (RING_TILE * 4), A + j * tile_groups * 4, bytes, full_bar(i));
+            }
+        }
+    }
+    const float p = PRECISION_ON_DEVICE ? *d_precision : precision_arg;
+    const uint32_t pb = __float_as_uint(p);
+    const uint32_t psign4 = (pb >> 31) * 0x80808080u;
+    const float ap = fabsf(p);
+    // 2^-100 <= |p| <= 2^100 keeps every boundary T*|p| a normal number; NaN fails both tests
+    const bool p_ok = (ap >= 7.8886090522101181e-31f) && (ap <= 1.2676506002282294e30f);
+    if (!PRECISION_ON_DEVICE) {
+        ring_build_tables(t, tid, rc.x_valid && p_ok);   // boundaries came with the launch (found on the host)
+    } else {
+        if (tid < 128) {
+            // smallest |x| with fl(|x|/|p|) >= T for each of the 127 thresholds (see cn_compress_kernel)
+            uint32_t xb = 0xffffffffu;
+            bool good = true;
+            if (tid < CN_NUM_THR && p_ok) {
+                const float T = __uint_as_float(rc.thr[tid]);
+                xb = __float_as_uint(__fmul_rn(T, ap));
+                int down = 0;
+                for (; down < 6; ++down) {
+                    if (xb > 0u && __fdiv_rn(__uint_as_float(xb - 1u), ap) >= T) --xb; else break;
+                }
+                good = down < 6;
+                if (down == 0) {
+                    int up = 0;
+                    for (; up < 6; ++up) {
+                        if (__fdiv_rn(__uint_as_float(xb), ap) < T) ++xb; else break;
+                    }
+                    good = up < 6;
+                }
+            }
+            t.X[tid] = good ? xb : 0xfffffffeu;
+        }
+        __syncthreads();
+        ring_build_tables(t, tid, p_ok);
+    }
+    const bool fast = t.bad == 0;
+    const uint32_t kadd = t.kadd;
+    const int32_t span = t.span;
+    const uint32_t lut_addr = cdc_smem_u32(t.lut);
+
+    uint32_t *out4 = reinterpret_cast<uint32_t *>(out);
+    bool ok = true;
+    for (int i = 0; i < tiles_per_cta && ok; ++i) {
+        const int s = i % RING_STAGES;
+        const uint32_t ph = (uint32_t)(i / RING_STAGES) & 1u;
+        if (tid == 0 && i >= 1 && i - 1 + RING_STAGES < tiles_per_cta) {
+            // refill the stage that every warp finished in the previous iteration
+            const int ps = (i - 1) % RING_STAGES;
+            const uint32_t pph = (uint32_t)((i - 1) / RING_STAGES) & 1u;
+            const int64_t j = blockIdx.x + (int64_t)(i - 1 + RING_STAGES) * gridDim.x;
+            const uint32_t bytes = (uint32_t)tile_count(j) * 16u;
+            if (bytes && cdc_mbar_wait(empty_bar(ps), pph, status)) {
+                cdc_mbar_expect_tx(full_bar(ps), bytes);
+                cdc_bulk_load(ring_base + (uint32_t)ps * (RING_TILE * 4), A + j * tile_groups * 4, bytes, full_bar(ps));
+            }
+        }
+        const int64_t j = blockIdx.x + (int64_t)i * gridDim.x;
+        const int groups = tile_count(j);
+        if (groups == 0) break;                                // tiles past the end of the tensor: nothing was loaded
+        ok = cdc_mbar_wait(full_bar(s), ph, status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const float4 *src = reinterpret_cast<const float4 *>(ring_gen + (size_t)s * (RING_TILE * 4));
+        uint32_t *dst = out4 + j * tile_groups;
+        if (groups == RING_TILE / 4 && fast) {
+            // whole tile, table path: all loads first, then the lookups of the four groups interleave
+            float4 q[RING_GROUPS_PER_THREAD];
+#pragma unroll
+            for (int u = 0; u < RING_GROUPS_PER_THREAD; ++u) q[u] = src[tid + u * RING_THREADS];
+#pragma unroll
+            for (int u = 0; u < RING_GROUPS_PER_THREAD; ++u) __stcs(dst + tid + u * RING_THREADS, ring_code4(q[u], pb, psign4, kadd, span, lut_addr));
+        } else {
+#pragma unroll 1
+            for (int g = tid; g < groups; g += RING_THREADS) {
+                const float4 q = src[g];
+                __stcs(dst + g, fast ? ring_code4(q, pb, psign4, kadd, span, lut_addr)
+                                     : pack4(ring_generic(q.x, p, t), ring_generic(q.y, p, t), ring_generic(q.z, p, t), ring_generic(q.w, p, t)));
+            }
+        }
+        __syncwarp();
+        if ((tid & 31) == 0) cdc_mbar_arrive(empty_bar(s));
+    }
+    if (!ok && tid == 0) {
+        // a wait ran out: give the copies that are still in flight a bounded chance to land before the CTA exits
+        for (int s = 0; s < RING_STAGES; ++s) {
+            const long long t0 = clock64();
+            while (!cdc_mbar_try(full_bar(s), 0u) && !cdc_mbar_try(full_bar(s), 1u) && clock64() - t0 < 20000000LL) {}
+        }
+    }
+    // the last n % 4 elements
+    const int64_t n4 = groups_total << 2;
+    if (blockIdx.x == 0 && tid < (int)(n - n4)) {
+        const float x = A[n4 + tid];
+        out[n4 + tid] = (uint8_t)(fast ? ring_code(__float_as_uint(x), pb, kadd, span, lut_addr) : ring_generic(x, p, t));
+    }
+}
+
 // kDecompression_8bit (source/clusterKernels.cu:1135-1160): 256-entry table built in the reference's
 // statement order, then out[i] = table[code].
 template <bool PRECISION_ON_DEVICE>
@@ -258,6 +601,8 @@ cn_decompress_kernel(const uint8_t *__restrict__ codes, float precision_arg, con
 {
     __shared__ float lut[256];
     const int tid = threadIdx.x;
+    cdc_pdl_launch_dependents();
+    if (PRECISION_ON_DEVICE) cdc_pdl_wait();   // the scale is in global memory; a host scale lets the table precede the wait
     const float p = PRECISION_ON_DEVICE ? *d_precision : precision_arg;
     if (tid < 256) {
         float v = 0.0f;
@@ -270,6 +615,7 @@ cn_decompress_kernel(const uint8_t *__restrict__ codes, float precision_arg, con
         }
         lut[tid] = v;
     }
+    if (!PRECISION_ON_DEVICE) cdc_pdl_wait();
     __syncthreads();
     const int64_t nvec = vector_ok ? (n >> 2) : 0;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -327,6 +673,8 @@ cn_absmax_kernel(const float *__restrict__ A, int64_t n, float *__restrict__ out
     __shared__ float warp_max[ABSMAX_THREADS / 32];
     __shared__ bool is_last;
     const int tid = threadIdx.x;
+    cdc_pdl_launch_dependents();
+    cdc_pdl_wait();
     float m = -1.0f;   // the reference seeds thrust::reduce with -1.0f (source/basicOps.cu:1079)
     const int64_t nvec = vector_ok ? (n >> 2) : 0;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -389,6 +737,68 @@ static int codec_grid(const cn_context *ctx, int64_t n, int threads, int per_thr
     return (int)(need < cap ? need : cap);
 }
 
+// Launch with programmatic stream serialisation: the kernel may become resident while its predecessor in the stream is
+// still running; it synchronises with it through griddepcontrol.wait.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t s, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+// The 127 boundaries in |x| space for a host-side scale: the smallest fp32 |x| with fl(|x| / |p|) >= T_j, found with the
+// same IEEE single-precision products and quotients the kernel uses for a device-side scale (this file is compiled
+// without fast-math or contraction).  Kept per context for the last scale seen.
+static bool host_boundaries(cn_context *ctx, float precision, uint32_t X[128])
+{
+    uint32_t pbits;
+    memcpy(&pbits, &precision, 4);
+    if (ctx->codec_cache_valid && ctx->codec_cache_pbits == pbits) {
+        memcpy(X, ctx->codec_cache_X, sizeof(ctx->codec_cache_X));
+        return ctx->codec_cache_ok;
+    }
+    const float ap = fabsf(precision);
+    bool ok = (ap >= 7.8886090522101181e-31f) && (ap <= 1.2676506002282294e30f);
+    for (int j = 0; j < 128; ++j) X[j] = 0xffffffffu;
+    for (int j = 0; j < CN_NUM_THR && ok; ++j) {
+        float T;
+        memcpy(&T, &ctx->h_thr[j], 4);
+        volatile float prod = T * ap;
+        float pf = prod;
+        uint32_t xb;
+        memcpy(&xb, &pf, 4);
+        auto quot = [&](uint32_t bits) { float v; memcpy(&v, &bits, 4); volatile float q = v / ap; return (float)q; };
+        int down = 0;
+        for (; down < 6; ++down) {
+            if (xb > 0u && quot(xb - 1u) >= T) --xb; else break;
+        }
+        bool good = down < 6;
+        if (down == 0) {
+            int up = 0;
+            for (; up < 6; ++up) {
+                if (quot(xb) < T) ++xb; else break;
+            }
+            good = up < 6;
+        }
+        if (!good) ok = false;
+        X[j] = xb;
+    }
+    ctx->codec_cache_valid = true;
+    ctx->codec_cache_pbits = pbits;
+    ctx->codec_cache_ok = ok;
+    memcpy(ctx->codec_cache_X, X, sizeof(ctx->codec_cache_X));
+    return ok;
+}
+
 static int compress_impl(cn_context *ctx, const float *d_A, float precision, const float *d_precision, int64_t n,
                          uint8_t *d_codes, void *stream)
 {
@@ -396,15 +806,48 @@ static int compress_impl(cn_context *ctx, const float *d_A, float precision, con
     CN_REQUIRE(n >= 0, CN_ERR_ARG, "cn_compress_8bit: negative size");
     if (n == 0) return CN_OK;
     CN_REQUIRE(d_A && d_codes, CN_ERR_ARG, "cn_compress_8bit: null buffer");
-    int vector_ok = ((uintptr_t)d_A % 16 == 0) && ((uintptr_t)d_codes % 4 == 0);
+    cudaStream_t s = cn_stream(stream);
+    if (((uintptr_t)d_A % 16 == 0) && ((uintptr_t)d_codes % 4 == 0) && n >= 4) {
+        // aligned buffers: the ring compressor
+        static bool attr_set[64] = {};   // per device: the attribute belongs to the device's copy of the function
+        const size_t smem = (size_t)RING_STAGES * RING_TILE * 4 + 128;
+        if (ctx->device < 0 || ctx->device >= 64 || !attr_set[ctx->device]) {
+            CN_CUDA(cudaFuncSetAttribute(cn_compress_ring_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            CN_CUDA(cudaFuncSetAttribute(cn_compress_ring_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            if (ctx->device >= 0 && ctx->device < 64) attr_set[ctx->device] = true;
+        }
+        unsigned int *d_status = nullptr;
+        int st = cn_status_block(ctx, &d_status);
+        if (st != CN_OK) return st;
+        RingConst rc;
+        for (int i = 0; i < 128; ++i) { rc.thr[i] = ctx->h_thr[i]; rc.lc[i] = ctx->h_level_codes[i]; rc.X[i] = 0xffffffffu; }
+        rc.x_valid = 0;
+        if (!d_precision) rc.x_valid = host_boundaries(ctx, precision, rc.X) ? 1 : 0;
+        // every CTA gets the same number of equally sized tiles (at most RING_TILE elements each)
+        const int64_t groups = n >> 2, max_groups = RING_TILE / 4;
+        const int64_t min_tiles = (groups + max_groups - 1) / max_groups;
+        const int64_t max_grid = 2 * (int64_t)ctx->sm_count;   // two resident CTAs per SM
+        const int grid = (int)(min_tiles < max_grid ? min_tiles : max_grid);
+        const int64_t tpc64 = (min_tiles + grid - 1) / grid;
+        CN_REQUIRE(tpc64 < (1LL << 30), CN_ERR_UNSUPPORTED, "cn_compress_8bit: tensor too large");
+        const int tiles_per_cta = (int)tpc64;
+        const int tile_groups = (int)((groups + (int64_t)grid * tiles_per_cta - 1) / ((int64_t)grid * tiles_per_cta));
+        if (d_precision)
+            CN_CUDA(launch_pdl(cn_compress_ring_kernel<true>, grid, RING_THREADS, smem, s, d_A, 0.f, d_precision, n, d_codes, rc, d_status,
+                               tile_groups, tiles_per_cta));
+        else
+            CN_CUDA(launch_pdl(cn_compress_ring_kernel<false>, grid, RING_THREADS, smem, s, d_A, precision, (const float *)nullptr, n, d_codes, rc,
+                               d_status, tile_groups, tiles_per_cta));
+        cn_count_launch();
+        return CN_OK;
+    }
     int grid = codec_grid(ctx, n, CODEC_THREADS, 4, 1);
     CodecConst cc;
     for (int i = 0; i < 128; ++i) { cc.thr[i] = ctx->h_thr[i]; cc.lc[i] = ctx->h_level_codes[i]; }
     if (d_precision)
-        cn_compress_kernel<true><<<grid, CODEC_THREADS, 0, cn_stream(stream)>>>(d_A, 0.f, d_precision, n, d_codes, cc, vector_ok);
+        CN_CUDA(launch_pdl(cn_compress_kernel<true>, grid, CODEC_THREADS, 0, s, d_A, 0.f, d_precision, n, d_codes, cc, 0));
     else
-        cn_compress_kernel<false><<<grid, CODEC_THREADS, 0, cn_stream(stream)>>>(d_A, precision, nullptr, n, d_codes, cc, vector_ok);
-    CN_CUDA(cudaGetLastError());
+        CN_CUDA(launch_pdl(cn_compress_kernel<false>, grid, CODEC_THREADS, 0, s, d_A, precision, (const float *)nullptr, n, d_codes, cc, 0));
     cn_count_launch();
     return CN_OK;
 }
@@ -432,10 +875,9 @@ static int decompress_impl(cn_context *ctx, const uint8_t *d_codes, float precis
     DecodeConst dc;
     for (int i = 0; i < 128; ++i) dc.tbl[i] = ctx->h_tbl[i];
     if (d_precision)
-        cn_decompress_kernel<true><<<grid, CODEC_THREADS, 0, cn_stream(stream)>>>(d_codes, 0.f, d_precision, n, d_out, dc, vector_ok);
+        CN_CUDA(launch_pdl(cn_decompress_kernel<true>, grid, CODEC_THREADS, 0, cn_stream(stream), d_codes, 0.f, d_precision, n, d_out, dc, vector_ok));
     else
-        cn_decompress_kernel<false><<<grid, CODEC_THREADS, 0, cn_stream(stream)>>>(d_codes, precision, nullptr, n, d_out, dc, vector_ok);
-    CN_CUDA(cudaGetLastError());
+        CN_CUDA(launch_pdl(cn_decompress_kernel<false>, grid, CODEC_THREADS, 0, cn_stream(stream), d_codes, precision, (const float *)nullptr, n, d_out, dc, vector_ok));
     cn_count_launch();
     return CN_OK;
 }
@@ -460,8 +902,7 @@ extern "C" int cn_absmax_f32(cn_context *ctx, const float *d_A, int64_t n, float
     // four), eight per SM stream best on large ones (1 GiB: 6737 GB/s vs 6332)
     int grid = codec_grid(ctx, n, ABSMAX_THREADS, 16, n < (1LL << 27) ? 2 : 8);
     if (grid > CN_MAX_PARTIALS) grid = CN_MAX_PARTIALS;
-    cn_absmax_kernel<true><<<grid, ABSMAX_THREADS, 0, cn_stream(stream)>>>(d_A, n, d_out, ctx->d_partials, ctx->d_ticket, vector_ok);
-    CN_CUDA(cudaGetLastError());
+    CN_CUDA(launch_pdl(cn_absmax_kernel<true>, grid, ABSMAX_THREADS, 0, cn_stream(stream), d_A, n, d_out, ctx->d_partials, ctx->d_ticket, vector_ok));
     cn_count_launch();
     return CN_OK;
 }

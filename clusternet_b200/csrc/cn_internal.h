@@ -49,6 +49,10 @@ struct cn_context {
     float h_tbl[128];
     uint32_t h_thr[128];
     uint8_t h_level_codes[128];
+    // boundaries of the compressor's levels in |x| space for the last host-side scale (cn_compress_8bit), see cn_codec.cu
+    bool codec_cache_valid = false, codec_cache_ok = false;
+    uint32_t codec_cache_pbits = 0;
+    uint32_t codec_cache_X[128];
     // reduction scratch: per-CTA partial maxima + a ticket counter that the last CTA resets
     float *d_partials = nullptr;
     unsigned int *d_ticket = nullptr;
