@@ -183,7 +183,8 @@ def codec_bench(ctx, torch, peaks):
     """compress / decompress / absmax GB/s: config 2 (4096^2, six rotating buffer sets so that no launch finds its
     input in L2) and a 1 GiB tensor."""
     out = {}
-    for label, n, sets, iters in (("config2_4096x4096", 4096 * 4096, 6, 30), ("1GiB", 1 << 28, 2, 6)):
+    for label, n, sets, iters in (("config2_4096x4096", 4096 * 4096, 6, 30), ("1GiB", 1 << 28, 2, 6),
+                                  ("config4_gradients_2392800", 2392800, 8, 40)):
         xs = [torch.randn(n, device="cuda") * 0.1 for _ in range(sets)]
         codes = [torch.empty(n, dtype=torch.uint8, device="cuda") for _ in range(sets)]
         outs = [torch.empty(n, device="cuda") for _ in range(sets)]
@@ -197,10 +198,15 @@ def codec_bench(ctx, torch, peaks):
             # from device memory (no host synchronisation); 9 algorithmic bytes per element (4 + 4 read, 1 written)
             ctx.absmax(xs[i], out=scale)
             ctx.compress(xs[i], scale, out=codes[i])
+
+        def fused(i):
+            # the same as one cooperative launch (cn_absmax_compress_8bit): reduce, grid barrier, code
+            ctx.absmax_compress(xs[i], scale=scale, out=codes[i])
         for name, fn, bytes_per in (("compress", lambda i: ctx.compress(xs[i], p, out=codes[i]), 5),
                                     ("decompress", lambda i: ctx.decompress(codes[i], p, out=outs[i]), 5),
                                     ("absmax", lambda i: ctx.absmax(xs[i], out=pm), 4),
-                                    ("absmax_then_compress", pipeline, 9)):
+                                    ("absmax_then_compress", pipeline, 9),
+                                    ("absmax_compress_one_launch", fused, 9)):
             for i in range(sets):
                 fn(i)
             torch.cuda.synchronize()
@@ -306,12 +312,12 @@ def train_step_bench(ctx, cn, _lib, torch, dist, world, rank, steps=30):
     n0 = lib.cn_kernel_launches()
     ms_eager = timed(one_step)
     launches = (lib.cn_kernel_launches() - n0) / steps
-    # the same step recorded once in a CUDA graph and replayed (the dropout seed advances on the device)
-    ms = ms_eager
-    graph_ms = None
+    # the same step recorded once in a CUDA graph and replayed (the dropout seed advances on the device; with several
+    # ranks the all-gather of the gradient exchange is part of the recording)
+    graph_ms, g = None, None
     try:
-        if world > 1:
-            raise RuntimeError("not attempted with more than one rank (collectives inside a capture)")
+        if world > 1 and os.environ.get("CN_BENCH_GRAPH_MULTI", "1") != "1":
+            raise RuntimeError("switched off for more than one rank (CN_BENCH_GRAPH_MULTI=0)")
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -319,18 +325,29 @@ def train_step_bench(ctx, cn, _lib, torch, dist, world, rank, steps=30):
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        with torch.cuda.graph(g, capture_error_mode="thread_local"):
             one_step()
+    except Exception as exc:   # capture is an optimisation of the harness, not of the library
+        graph_ms, g = f"no graph: {exc}"[:120], None
+    captured = g is not None
+    if world > 1:
+        # every rank replays, or none does (a rank that replays alone would wait in the all-gather)
+        t = torch.tensor([1 if captured else 0], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        if captured and not bool(t.item()):
+            graph_ms = "no graph: another rank could not capture"
+        captured = bool(t.item())
+    if captured:
         for _ in range(3):
             g.replay()
         graph_ms = timed(g.replay)
-        ms = min(ms, graph_ms)
-    except Exception as exc:   # capture is an optimisation of the harness, not of the library
-        graph_ms = f"no graph: {exc}"[:120]
     if world > 1:
-        t = torch.tensor([ms_eager], dtype=torch.float64, device="cuda")
+        t = torch.tensor([ms_eager, graph_ms if captured else 0.0], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = ms_eager = float(t.item())
+        ms_eager = float(t[0].item())
+        if captured:
+            graph_ms = float(t[1].item())
+    ms = min(ms_eager, graph_ms) if captured else ms_eager
     ctx.gemm_check()
     return {"workload": "config 4: MLP 784-1200-1200-10, batch 128 per GPU, 8-bit gradient exchange, RMSprop", "ms_per_step": ms,
             "ms_per_step_eager": ms_eager, "ms_per_step_cuda_graph": graph_ms,
@@ -880,7 +897,7 @@ def multi_rank_checks(ctx, cn, _lib, torch, dist, world, rank):
     dist.barrier()
     exact = [k for k in res if k.endswith("_exact")]
     res["ok"] = bool(all(res[k] for k in exact) and res["uneven_shards_vs_fp64"] <= 1e-5 and res["dottmpi_vs_fp64"] <= 1e-5
-                     and res["uneven_shards_vs_unsharded"] <= 2e-6)
+                     and res["uneven_shards_vs_unsharded"] <= 5e-6)   # sharded and unsharded launches split K differently
     return res
 
 

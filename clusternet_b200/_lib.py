@@ -53,6 +53,7 @@ _SIGNATURES = {
     "cn_absmax_f32_noalloc": (c_int, [c_void_p, c_int64, c_void_p, c_void_p]),
     "cn_compress_8bit": (c_int, [c_void_p, c_void_p, c_float, c_int64, c_void_p, c_void_p]),
     "cn_compress_8bit_dp": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "cn_absmax_compress_8bit": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     "cn_decompress_8bit": (c_int, [c_void_p, c_void_p, c_float, c_int64, c_void_p, c_void_p]),
     "cn_decompress_8bit_dp": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "cn_to_col_major": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),

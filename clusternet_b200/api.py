@@ -144,6 +144,13 @@ class Context:
             check(self.lib.cn_compress_8bit(self.h, _ptr(a), float(precision), a.numel(), _ptr(out), self.stream_ptr()))
         return out
 
+    def absmax_compress(self, a, scale=None, out=None):
+        """scale = max |a|; codes = compress(a, scale) in one launch; returns (codes, scale tensor)."""
+        out = out if out is not None else torch.empty(a.shape, dtype=torch.uint8, device=self.device)
+        scale = scale if scale is not None else torch.empty(1, dtype=torch.float32, device=self.device)
+        check(self.lib.cn_absmax_compress_8bit(self.h, _ptr(a), a.numel(), _ptr(scale), _ptr(out), self.stream_ptr()))
+        return out, scale
+
     def decompress(self, codes, precision, out=None):
         out = out if out is not None else torch.empty(codes.shape, dtype=torch.float32, device=self.device)
         if isinstance(precision, torch.Tensor):

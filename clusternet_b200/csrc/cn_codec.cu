@@ -275,6 +275,7 @@ cn_compress_kernel(const float *__restrict__ A, float precision_arg, const float
 #define RING_TILE 8192                      // elements per tile: 32 KB of input, four 16-byte groups per thread
 #define RING_STAGES 3                       // per CTA: 6 tiles = 192 KB in flight per SM
 #define RING_GROUPS_PER_THREAD (RING_TILE / 4 / RING_THREADS)
+#define CN_FUSED_ABSMAX_MAX_N (4LL << 20)   // above this size cn_absmax_compress_8bit issues two launches
 #define RING_WAIT_LIMIT (4000000000LL)      // clock cycles (~2 s)
 
 __device__ __forceinline__ uint32_t cdc_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -448,18 +449,49 @@ __device__ __forceinline__ void ring_build_tables(RingTables &t, int tid, bool u
     __syncthreads();
 }
 
+// Grid-wide barrier of a cooperative launch (all CTAs resident): every CTA adds one to a counter that only ever grows
+// and waits, with a clock limit, until it has reached `target` (the host keeps the running total).  A wait that runs out
+// records status 13 and lets the CTA go on, so the kernel always ends; its output is then undefined.
+__device__ __forceinline__ void cdc_grid_barrier(unsigned long long *counter, unsigned long long target, unsigned int *status)
+{
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(counter, 1ULL);
+        const long long t0 = clock64();
+        for (;;) {
+            unsigned long long seen;
+            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(counter) : "memory");
+            if (seen >= target) break;
+            if (clock64() - t0 > RING_WAIT_LIMIT) { if (status) atomicMax(status, 13u); break; }
+            __nanosleep(40);
+        }
+        __threadfence();
+    }
+    __syncthreads();
+}
+
+enum { RING_SCALE_HOST = 0, RING_SCALE_DEVICE = 1, RING_SCALE_ABSMAX = 2 };
+
 // Work split: every CTA codes the same number of tiles (tiles_per_cta) of the same size (tile_groups 16-byte groups,
 // at most RING_TILE / 4), chosen on the host so that grid * tiles_per_cta tiles cover the tensor with less than one
-// group of slack per tile; tile j goes to CTA j % grid.  The last tiles may be short or empty.
-template <bool PRECISION_ON_DEVICE>
+// group of slack per tile; tile j goes to CTA j % grid.  The last tiles may be short or missing.
+//
+// SCALE = RING_SCALE_ABSMAX is the fused form of "scale = absmax(A); codes = compress(A, scale)" (cooperative launch):
+// pass 1 reduces |A| over the CTA's own tiles with plain loads that leave the lines in L2, a grid barrier publishes the
+// per-CTA maxima, every CTA folds them, and pass 2 codes the CTA's tiles in reverse order - most recently read first -
+// so that a tensor that fits the L2 is read from HBM once.  d_precision then receives the scale.
+template <int SCALE>
 __global__ void __launch_bounds__(RING_THREADS, 2)
-cn_compress_ring_kernel(const float *__restrict__ A, float precision_arg, const float *__restrict__ d_precision,
+cn_compress_ring_kernel(const float *__restrict__ A, float precision_arg, float *__restrict__ d_precision,
                         int64_t n, uint8_t *__restrict__ out, const __grid_constant__ RingConst rc, unsigned int *status,
-                        int tile_groups, int tiles_per_cta)
+                        int tile_groups, int tiles_per_cta, float *__restrict__ partials, unsigned long long *barrier_counter,
+                        unsigned long long barrier_target)
 {
     extern __shared__ __align__(128) uint8_t ring_smem[];
     __shared__ RingTables t;
     __shared__ __align__(8) uint64_t bars[2 * RING_STAGES];
+    __shared__ float s_red[RING_THREADS / 32];
     const int tid = threadIdx.x;
     const uint32_t ring_base = (cdc_smem_u32(ring_smem) + 127u) & ~127u;
     const uint8_t *ring_gen = ring_smem + (ring_base - cdc_smem_u32(ring_smem));
@@ -474,35 +506,89 @@ cn_compress_ring_kernel(const float *__restrict__ A, float precision_arg, const 
     if (tid < 128) {
         t.T[tid] = rc.thr[tid];
         t.lc[tid] = rc.lc[tid];
-        if (!PRECISION_ON_DEVICE) t.X[tid] = rc.X[tid];
+        if (SCALE == RING_SCALE_HOST) t.X[tid] = rc.X[tid];
     }
     const int64_t groups_total = n >> 2;                    // 16-byte groups of the tensor
-    // 16-byte groups in tile j (0 for tiles past the end)
+    // tiles of this CTA that hold data: tile (blockIdx.x + k * gridDim.x), k = 0 .. my_tiles - 1
+    int my_tiles = 0;
+    {
+        const int64_t tiles_total = (groups_total + tile_groups - 1) / tile_groups;
+        if ((int64_t)blockIdx.x < tiles_total) {
+            const int64_t mine = (tiles_total - blockIdx.x + gridDim.x - 1) / gridDim.x;
+            my_tiles = (int)(mine < tiles_per_cta ? mine : tiles_per_cta);
+        }
+    }
+    // the i-th tile this CTA codes (pass 2 of the fused form walks its tiles backwards) and its size in 16-byte groups
+    auto tile_of = [&](int i) { return (int64_t)blockIdx.x + (int64_t)(SCALE == RING_SCALE_ABSMAX ? my_tiles - 1 - i : i) * gridDim.x; };
     auto tile_count = [&](int64_t j) {
         const int64_t left = groups_total - j * tile_groups;
-        return (int)(left < 0 ? 0 : (left < tile_groups ? left : tile_groups));
+        return (int)(left < tile_groups ? left : tile_groups);
     };
     __syncthreads();   // barriers initialised, constant tables in shared memory
 
     // ---- everything below may touch global memory: the predecessor in the stream must have finished
     cdc_pdl_wait();
+    float p = precision_arg;
+    if (SCALE == RING_SCALE_ABSMAX) {
+        // pass 1: maximum of |A| over this CTA's tiles (and, in CTA 0, the last n % 4 elements)
+        float m = -1.0f;   // seed of the reference's reduction (source/basicOps.cu:1079)
+        const float4 *A4 = reinterpret_cast<const float4 *>(A);
+        for (int k = 0; k < my_tiles; ++k) {
+            const int64_t j = (int64_t)blockIdx.x + (int64_t)k * gridDim.x;
+            const int groups = tile_count(j);
+            const float4 *src = A4 + j * tile_groups;
+            float4 q[RING_GROUPS_PER_THREAD];
+#pragma unroll
+            for (int u = 0; u < RING_GROUPS_PER_THREAD; ++u)
+                q[u] = (tid + u * RING_THREADS < groups) ? src[tid + u * RING_THREADS] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < RING_GROUPS_PER_THREAD; ++u)
+                if (tid + u * RING_THREADS < groups)
+                    m = fmaxf(m, fmaxf(fmaxf(fabsf(q[u].x), fabsf(q[u].y)), fmaxf(fabsf(q[u].z), fabsf(q[u].w))));
+        }
+        if (blockIdx.x == 0 && tid < (int)(n - (groups_total << 2))) m = fmaxf(m, fabsf(A[(groups_total << 2) + tid]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if ((tid & 31) == 0) s_red[tid >> 5] = m;
+        __syncthreads();
+        if (tid < 32) {
+            m = tid < RING_THREADS / 32 ? s_red[tid] : -1.0f;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            if (tid == 0) partials[blockIdx.x] = m;
+        }
+        cdc_grid_barrier(barrier_counter, barrier_target, status);
+    }
     if (tid == 0) {    // fill the ring before anything else: the first loads are in flight while the tables are built
-        for (int i = 0; i < RING_STAGES && i < tiles_per_cta; ++i) {
-            const int64_t j = blockIdx.x + (int64_t)i * gridDim.x;
+        for (int i = 0; i < RING_STAGES && i < my_tiles; ++i) {
+            const int64_t j = tile_of(i);
             const uint32_t bytes = (uint32_t)tile_count(j) * 16u;
-            if (bytes) {
-                cdc_mbar_expect_tx(full_bar(i), bytes);
-                cdc_bulk_load(ring_base + (uint32_t)i * (RING_TILE * 4), A + j * tile_groups * 4, bytes, full_bar(i));
-            }
+            cdc_mbar_expect_tx(full_bar(i), bytes);
+            cdc_bulk_load(ring_base + (uint32_t)i * (RING_TILE * 4), A + j * tile_groups * 4, bytes, full_bar(i));
         }
     }
-    const float p = PRECISION_ON_DEVICE ? *d_precision : precision_arg;
+    if (SCALE == RING_SCALE_DEVICE) p = *d_precision;
+    if (SCALE == RING_SCALE_ABSMAX) {
+        // every CTA folds the per-CTA maxima (the same values in the same order everywhere)
+        float m = -1.0f;
+        for (int i = tid; i < (int)gridDim.x; i += RING_THREADS) m = fmaxf(m, __ldcg(partials + i));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        __syncthreads();   // s_red was read above
+        if ((tid & 31) == 0) s_red[tid >> 5] = m;
+        __syncthreads();
+        m = s_red[0];
+#pragma unroll
+        for (int w = 1; w < RING_THREADS / 32; ++w) m = fmaxf(m, s_red[w]);
+        p = m;
+        if (blockIdx.x == 0 && tid == 0) *d_precision = p;
+    }
     const uint32_t pb = __float_as_uint(p);
     const uint32_t psign4 = (pb >> 31) * 0x80808080u;
     const float ap = fabsf(p);
     // 2^-100 <= |p| <= 2^100 keeps every boundary T*|p| a normal number; NaN fails both tests
     const bool p_ok = (ap >= 7.8886090522101181e-31f) && (ap <= 1.2676506002282294e30f);
-    if (!PRECISION_ON_DEVICE) {
+    if (SCALE == RING_SCALE_HOST) {
         ring_build_tables(t, tid, rc.x_valid && p_ok);   // boundaries came with the launch (found on the host)
     } else {
         if (tid < 128) {
@@ -537,41 +623,41 @@ cn_compress_ring_kernel(const float *__restrict__ A, float precision_arg, const 
 
     uint32_t *out4 = reinterpret_cast<uint32_t *>(out);
     bool ok = true;
-    for (int i = 0; i < tiles_per_cta && ok; ++i) {
+    for (int i = 0; i < my_tiles && ok; ++i) {
         const int s = i % RING_STAGES;
         const uint32_t ph = (uint32_t)(i / RING_STAGES) & 1u;
-        if (tid == 0 && i >= 1 && i - 1 + RING_STAGES < tiles_per_cta) {
+        if (tid == 0 && i >= 1 && i - 1 + RING_STAGES < my_tiles) {
             // refill the stage that every warp finished in the previous iteration
             const int ps = (i - 1) % RING_STAGES;
             const uint32_t pph = (uint32_t)((i - 1) / RING_STAGES) & 1u;
-            const int64_t j = blockIdx.x + (int64_t)(i - 1 + RING_STAGES) * gridDim.x;
+            const int64_t j = tile_of(i - 1 + RING_STAGES);
             const uint32_t bytes = (uint32_t)tile_count(j) * 16u;
-            if (bytes && cdc_mbar_wait(empty_bar(ps), pph, status)) {
+            if (cdc_mbar_wait(empty_bar(ps), pph, status)) {
                 cdc_mbar_expect_tx(full_bar(ps), bytes);
                 cdc_bulk_load(ring_base + (uint32_t)ps * (RING_TILE * 4), A + j * tile_groups * 4, bytes, full_bar(ps));
             }
         }
-        const int64_t j = blockIdx.x + (int64_t)i * gridDim.x;
+        const int64_t j = tile_of(i);
         const int groups = tile_count(j);
-        if (groups == 0) break;                                // tiles past the end of the tensor: nothing was loaded
         ok = cdc_mbar_wait(full_bar(s), ph, status);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         const float4 *src = reinterpret_cast<const float4 *>(ring_gen + (size_t)s * (RING_TILE * 4));
         uint32_t *dst = out4 + j * tile_groups;
-        if (groups == RING_TILE / 4 && fast) {
-            // whole tile, table path: all loads first, then the lookups of the four groups interleave
+        if (fast) {
+            // table path: all loads of the thread first, then the lookups of its (up to) four groups interleave
             float4 q[RING_GROUPS_PER_THREAD];
 #pragma unroll
-            for (int u = 0; u < RING_GROUPS_PER_THREAD; ++u) q[u] = src[tid + u * RING_THREADS];
+            for (int u = 0; u < RING_GROUPS_PER_THREAD; ++u)
+                if (tid + u * RING_THREADS < groups) q[u] = src[tid + u * RING_THREADS];
 #pragma unroll
-            for (int u = 0; u < RING_GROUPS_PER_THREAD; ++u) __stcs(dst + tid + u * RING_THREADS, ring_code4(q[u], pb, psign4, kadd, span, lut_addr));
+            for (int u = 0; u < RING_GROUPS_PER_THREAD; ++u)
+                if (tid + u * RING_THREADS < groups) __stcs(dst + tid + u * RING_THREADS, ring_code4(q[u], pb, psign4, kadd, span, lut_addr));
         } else {
 #pragma unroll 1
             for (int g = tid; g < groups; g += RING_THREADS) {
                 const float4 q = src[g];
-                __stcs(dst + g, fast ? ring_code4(q, pb, psign4, kadd, span, lut_addr)
-                                     : pack4(ring_generic(q.x, p, t), ring_generic(q.y, p, t), ring_generic(q.z, p, t), ring_generic(q.w, p, t)));
+                __stcs(dst + g, pack4(ring_generic(q.x, p, t), ring_generic(q.y, p, t), ring_generic(q.z, p, t), ring_generic(q.w, p, t)));
             }
         }
         __syncwarp();
@@ -729,6 +815,122 @@ cn_absmax_kernel(const float *__restrict__ A, int64_t n, float *__restrict__ out
     }
 }
 
+// absmax through the same bulk-copy ring as the compressor (16-byte aligned input): the elected thread keeps three 32 KB
+// tiles per CTA (two CTAs per SM) in flight, so the bytes in flight do not depend on how many loads each thread can
+// hold in registers - at a few tens of MiB, where every microsecond of ramp shows, this is what keeps HBM busy.
+// Same partial-maximum + last-ticket fold as cn_absmax_kernel; work split as in cn_compress_ring_kernel.
+__global__ void __launch_bounds__(RING_THREADS, 2)
+cn_absmax_ring_kernel(const float *__restrict__ A, int64_t n, float *__restrict__ out, float *__restrict__ partials,
+                      unsigned int *__restrict__ ticket, unsigned int *status, int tile_groups, int tiles_per_cta)
+{
+    extern __shared__ __align__(128) uint8_t ring_smem[];
+    __shared__ __align__(8) uint64_t bars[2 * RING_STAGES];
+    __shared__ float warp_max[RING_THREADS / 32];
+    __shared__ bool is_last;
+    const int tid = threadIdx.x;
+    const uint32_t ring_base = (cdc_smem_u32(ring_smem) + 127u) & ~127u;
+    const uint8_t *ring_gen = ring_smem + (ring_base - cdc_smem_u32(ring_smem));
+    auto full_bar = [&](int s) { return cdc_smem_u32(&bars[s]); };
+    auto empty_bar = [&](int s) { return cdc_smem_u32(&bars[RING_STAGES + s]); };
+    if (tid == 0) {
+        for (int s = 0; s < RING_STAGES; ++s) { cdc_mbar_init(full_bar(s), 1); cdc_mbar_init(empty_bar(s), RING_THREADS / 32); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    cdc_pdl_launch_dependents();
+    const int64_t groups_total = n >> 2;
+    int my_tiles = 0;
+    {
+        const int64_t tiles_total = (groups_total + tile_groups - 1) / tile_groups;
+        if ((int64_t)blockIdx.x < tiles_total) {
+            const int64_t mine = (tiles_total - blockIdx.x + gridDim.x - 1) / gridDim.x;
+            my_tiles = (int)(mine < tiles_per_cta ? mine : tiles_per_cta);
+        }
+    }
+    auto tile_count = [&](int64_t j) {
+        const int64_t left = groups_total - j * tile_groups;
+        return (int)(left < tile_groups ? left : tile_groups);
+    };
+    __syncthreads();
+    cdc_pdl_wait();
+    if (tid == 0) {
+        for (int i = 0; i < RING_STAGES && i < my_tiles; ++i) {
+            const int64_t j = blockIdx.x + (int64_t)i * gridDim.x;
+            const uint32_t bytes = (uint32_t)tile_count(j) * 16u;
+            cdc_mbar_expect_tx(full_bar(i), bytes);
+            cdc_bulk_load(ring_base + (uint32_t)i * (RING_TILE * 4), A + j * tile_groups * 4, bytes, full_bar(i));
+        }
+    }
+    float m = -1.0f;   // the reference seeds thrust::reduce with -1.0f (source/basicOps.cu:1079)
+    bool ok = true;
+    for (int i = 0; i < my_tiles && ok; ++i) {
+        const int s = i % RING_STAGES;
+        const uint32_t ph = (uint32_t)(i / RING_STAGES) & 1u;
+        if (tid == 0 && i >= 1 && i - 1 + RING_STAGES < my_tiles) {
+            const int ps = (i - 1) % RING_STAGES;
+            const uint32_t pph = (uint32_t)((i - 1) / RING_STAGES) & 1u;
+            const int64_t j = blockIdx.x + (int64_t)(i - 1 + RING_STAGES) * gridDim.x;
+            const uint32_t bytes = (uint32_t)tile_count(j) * 16u;
+            if (cdc_mbar_wait(empty_bar(ps), pph, status)) {
+                cdc_mbar_expect_tx(full_bar(ps), bytes);
+                cdc_bulk_load(ring_base + (uint32_t)ps * (RING_TILE * 4), A + j * tile_groups * 4, bytes, full_bar(ps));
+            }
+        }
+        const int64_t j = blockIdx.x + (int64_t)i * gridDim.x;
+        const int groups = tile_count(j);
+        ok = cdc_mbar_wait(full_bar(s), ph, status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const float4 *src = reinterpret_cast<const float4 *>(ring_gen + (size_t)s * (RING_TILE * 4));
+#pragma unroll
+        for (int u = 0; u < RING_GROUPS_PER_THREAD; ++u) {
+            if (tid + u * RING_THREADS < groups) {
+                const float4 q = src[tid + u * RING_THREADS];
+                m = fmaxf(m, fmaxf(fmaxf(fabsf(q.x), fabsf(q.y)), fmaxf(fabsf(q.z), fabsf(q.w))));
+            }
+        }
+        __syncwarp();
+        if ((tid & 31) == 0) cdc_mbar_arrive(empty_bar(s));
+    }
+    if (!ok && tid == 0) {
+        for (int s = 0; s < RING_STAGES; ++s) {
+            const long long t0 = clock64();
+            while (!cdc_mbar_try(full_bar(s), 0u) && !cdc_mbar_try(full_bar(s), 1u) && clock64() - t0 < 20000000LL) {}
+        }
+    }
+    if (blockIdx.x == 0 && tid < (int)(n - (groups_total << 2))) m = fmaxf(m, fabsf(A[(groups_total << 2) + tid]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((tid & 31) == 0) warp_max[tid >> 5] = m;
+    __syncthreads();
+    if (tid < 32) {
+        m = tid < RING_THREADS / 32 ? warp_max[tid] : -1.0f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (tid == 0) {
+            partials[blockIdx.x] = m;
+            __threadfence();
+            const unsigned int prev = atomicAdd(ticket, 1u);
+            is_last = (prev == gridDim.x - 1);
+        }
+    }
+    __syncthreads();
+    if (is_last) {
+        __threadfence();
+        float r = -1.0f;
+        for (int i = tid; i < (int)gridDim.x; i += RING_THREADS) r = fmaxf(r, __ldcg(partials + i));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) r = fmaxf(r, __shfl_xor_sync(0xffffffffu, r, o));
+        __syncthreads();
+        if ((tid & 31) == 0) warp_max[tid >> 5] = r;
+        __syncthreads();
+        if (tid == 0) {
+            for (int w = 1; w < RING_THREADS / 32; ++w) r = fmaxf(r, warp_max[w]);
+            *out = r;
+            *ticket = 0u;
+        }
+    }
+}
+
 static int codec_grid(const cn_context *ctx, int64_t n, int threads, int per_thread, int ctas_per_sm)
 {
     int64_t need = (n + (int64_t)threads * per_thread - 1) / ((int64_t)threads * per_thread);
@@ -799,22 +1001,37 @@ static bool host_boundaries(cn_context *ctx, float precision, uint32_t X[128])
     return ok;
 }
 
-static int compress_impl(cn_context *ctx, const float *d_A, float precision, const float *d_precision, int64_t n,
+// scale_mode: RING_SCALE_HOST (precision), RING_SCALE_DEVICE (d_precision read) or RING_SCALE_ABSMAX (d_precision written)
+static int compress_impl(cn_context *ctx, const float *d_A, float precision, float *d_precision, int scale_mode, int64_t n,
                          uint8_t *d_codes, void *stream)
 {
     CN_REQUIRE(ctx, CN_ERR_ARG, "cn_compress_8bit: null context");
     CN_REQUIRE(n >= 0, CN_ERR_ARG, "cn_compress_8bit: negative size");
+    cudaStream_t s = cn_stream(stream);
+    const bool ring_ok = ((uintptr_t)d_A % 16 == 0) && ((uintptr_t)d_codes % 4 == 0) && n >= 4;
+    // The single cooperative launch pays off while the pair of launches is bound by launch latency; from a few million
+    // elements on, two pipelined launches are faster (measured on a B200: 13.7 vs 21.6 us at 2.4 M elements, 39.2 vs 33.6 us at
+    // 16.8 M: the second pass is bound by the integer pipe, not by HBM, so reading it from L2 gains nothing).
+    if (scale_mode == RING_SCALE_ABSMAX && (!ring_ok || n > CN_FUSED_ABSMAX_MAX_N)) {
+        // also for buffers the ring kernel does not take (unaligned, tiny, empty): the two-call form
+        int st = cn_absmax_f32(ctx, d_A, n, d_precision, stream);
+        if (st != CN_OK || n == 0) return st;
+        return compress_impl(ctx, d_A, 0.f, d_precision, RING_SCALE_DEVICE, n, d_codes, stream);
+    }
     if (n == 0) return CN_OK;
     CN_REQUIRE(d_A && d_codes, CN_ERR_ARG, "cn_compress_8bit: null buffer");
-    cudaStream_t s = cn_stream(stream);
-    if (((uintptr_t)d_A % 16 == 0) && ((uintptr_t)d_codes % 4 == 0) && n >= 4) {
-        // aligned buffers: the ring compressor
+    if (ring_ok) {
         static bool attr_set[64] = {};   // per device: the attribute belongs to the device's copy of the function
+        static int occupancy[64] = {};
         const size_t smem = (size_t)RING_STAGES * RING_TILE * 4 + 128;
-        if (ctx->device < 0 || ctx->device >= 64 || !attr_set[ctx->device]) {
-            CN_CUDA(cudaFuncSetAttribute(cn_compress_ring_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            CN_CUDA(cudaFuncSetAttribute(cn_compress_ring_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            if (ctx->device >= 0 && ctx->device < 64) attr_set[ctx->device] = true;
+        const int dev = ctx->device;
+        if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+            CN_CUDA(cudaFuncSetAttribute(cn_compress_ring_kernel<RING_SCALE_HOST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            CN_CUDA(cudaFuncSetAttribute(cn_compress_ring_kernel<RING_SCALE_DEVICE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            CN_CUDA(cudaFuncSetAttribute(cn_compress_ring_kernel<RING_SCALE_ABSMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            int occ = 0;
+            CN_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, cn_compress_ring_kernel<RING_SCALE_ABSMAX>, RING_THREADS, smem));
+            if (dev >= 0 && dev < 64) { attr_set[dev] = true; occupancy[dev] = occ; }
         }
         unsigned int *d_status = nullptr;
         int st = cn_status_block(ctx, &d_status);
@@ -822,30 +1039,54 @@ static int compress_impl(cn_context *ctx, const float *d_A, float precision, con
         RingConst rc;
         for (int i = 0; i < 128; ++i) { rc.thr[i] = ctx->h_thr[i]; rc.lc[i] = ctx->h_level_codes[i]; rc.X[i] = 0xffffffffu; }
         rc.x_valid = 0;
-        if (!d_precision) rc.x_valid = host_boundaries(ctx, precision, rc.X) ? 1 : 0;
+        if (scale_mode == RING_SCALE_HOST) rc.x_valid = host_boundaries(ctx, precision, rc.X) ? 1 : 0;
         // every CTA gets the same number of equally sized tiles (at most RING_TILE elements each)
         const int64_t groups = n >> 2, max_groups = RING_TILE / 4;
         const int64_t min_tiles = (groups + max_groups - 1) / max_groups;
-        const int64_t max_grid = 2 * (int64_t)ctx->sm_count;   // two resident CTAs per SM
-        const int grid = (int)(min_tiles < max_grid ? min_tiles : max_grid);
+        int ctas_per_sm = 2;
+        if (scale_mode == RING_SCALE_ABSMAX) {   // cooperative launch: all CTAs must be resident at once
+            const int occ = (dev >= 0 && dev < 64) ? occupancy[dev] : 1;
+            CN_REQUIRE(occ >= 1, CN_ERR_UNSUPPORTED, "cn_absmax_compress_8bit: the kernel does not fit this device");
+            if (occ < ctas_per_sm) ctas_per_sm = occ;
+        }
+        const int64_t max_grid = (int64_t)ctas_per_sm * ctx->sm_count;
+        int grid = (int)(min_tiles < max_grid ? min_tiles : max_grid);
+        if (grid > CN_MAX_PARTIALS) grid = CN_MAX_PARTIALS;
         const int64_t tpc64 = (min_tiles + grid - 1) / grid;
         CN_REQUIRE(tpc64 < (1LL << 30), CN_ERR_UNSUPPORTED, "cn_compress_8bit: tensor too large");
         const int tiles_per_cta = (int)tpc64;
         const int tile_groups = (int)((groups + (int64_t)grid * tiles_per_cta - 1) / ((int64_t)grid * tiles_per_cta));
-        if (d_precision)
-            CN_CUDA(launch_pdl(cn_compress_ring_kernel<true>, grid, RING_THREADS, smem, s, d_A, 0.f, d_precision, n, d_codes, rc, d_status,
-                               tile_groups, tiles_per_cta));
-        else
-            CN_CUDA(launch_pdl(cn_compress_ring_kernel<false>, grid, RING_THREADS, smem, s, d_A, precision, (const float *)nullptr, n, d_codes, rc,
-                               d_status, tile_groups, tiles_per_cta));
+        unsigned long long *counter = reinterpret_cast<unsigned long long *>(ctx->d_ticket + 4);   // bytes 16..23 of the ticket block
+        if (scale_mode == RING_SCALE_ABSMAX) {
+            const unsigned long long target = ctx->grid_barrier_total + (unsigned long long)grid;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)grid);
+            cfg.blockDim = dim3(RING_THREADS);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = s;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeCooperative;
+            attr[0].val.cooperative = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            CN_CUDA(cudaLaunchKernelEx(&cfg, cn_compress_ring_kernel<RING_SCALE_ABSMAX>, d_A, 0.f, d_precision, n, d_codes, rc, d_status, tile_groups,
+                                       tiles_per_cta, ctx->d_partials, counter, target));
+            ctx->grid_barrier_total = target;   // only a launch that was accepted moves the counter
+        } else if (scale_mode == RING_SCALE_DEVICE) {
+            CN_CUDA(launch_pdl(cn_compress_ring_kernel<RING_SCALE_DEVICE>, grid, RING_THREADS, smem, s, d_A, 0.f, d_precision, n, d_codes, rc, d_status,
+                               tile_groups, tiles_per_cta, (float *)nullptr, (unsigned long long *)nullptr, 0ULL));
+        } else {
+            CN_CUDA(launch_pdl(cn_compress_ring_kernel<RING_SCALE_HOST>, grid, RING_THREADS, smem, s, d_A, precision, (float *)nullptr, n, d_codes, rc,
+                               d_status, tile_groups, tiles_per_cta, (float *)nullptr, (unsigned long long *)nullptr, 0ULL));
+        }
         cn_count_launch();
         return CN_OK;
     }
     int grid = codec_grid(ctx, n, CODEC_THREADS, 4, 1);
     CodecConst cc;
     for (int i = 0; i < 128; ++i) { cc.thr[i] = ctx->h_thr[i]; cc.lc[i] = ctx->h_level_codes[i]; }
-    if (d_precision)
-        CN_CUDA(launch_pdl(cn_compress_kernel<true>, grid, CODEC_THREADS, 0, s, d_A, 0.f, d_precision, n, d_codes, cc, 0));
+    if (scale_mode == RING_SCALE_DEVICE)
+        CN_CUDA(launch_pdl(cn_compress_kernel<true>, grid, CODEC_THREADS, 0, s, d_A, 0.f, (const float *)d_precision, n, d_codes, cc, 0));
     else
         CN_CUDA(launch_pdl(cn_compress_kernel<false>, grid, CODEC_THREADS, 0, s, d_A, precision, (const float *)nullptr, n, d_codes, cc, 0));
     cn_count_launch();
@@ -854,13 +1095,20 @@ static int compress_impl(cn_context *ctx, const float *d_A, float precision, con
 
 extern "C" int cn_compress_8bit(cn_context *ctx, const float *d_A, float precision, int64_t n, uint8_t *d_codes, void *stream)
 {
-    return compress_impl(ctx, d_A, precision, nullptr, n, d_codes, stream);
+    return compress_impl(ctx, d_A, precision, nullptr, RING_SCALE_HOST, n, d_codes, stream);
 }
 
 extern "C" int cn_compress_8bit_dp(cn_context *ctx, const float *d_A, const float *d_precision, int64_t n, uint8_t *d_codes, void *stream)
 {
     CN_REQUIRE(d_precision, CN_ERR_ARG, "cn_compress_8bit_dp: null precision pointer");
-    return compress_impl(ctx, d_A, 0.f, d_precision, n, d_codes, stream);
+    return compress_impl(ctx, d_A, 0.f, const_cast<float *>(d_precision), RING_SCALE_DEVICE, n, d_codes, stream);
+}
+
+extern "C" int cn_absmax_compress_8bit(cn_context *ctx, const float *d_A, int64_t n, float *d_scale_out, uint8_t *d_codes, void *stream)
+{
+    CN_REQUIRE(ctx && d_scale_out, CN_ERR_ARG, "cn_absmax_compress_8bit: null argument");
+    CN_REQUIRE(n >= 0 && (n == 0 || (d_A && d_codes)), CN_ERR_ARG, "cn_absmax_compress_8bit: bad input");
+    return compress_impl(ctx, d_A, 0.f, d_scale_out, RING_SCALE_ABSMAX, n, d_codes, stream);
 }
 
 static int decompress_impl(cn_context *ctx, const uint8_t *d_codes, float precision, const float *d_precision, int64_t n,
@@ -898,6 +1146,27 @@ extern "C" int cn_absmax_f32(cn_context *ctx, const float *d_A, int64_t n, float
     CN_REQUIRE(ctx && d_out, CN_ERR_ARG, "cn_absmax_f32: null argument");
     CN_REQUIRE(n >= 0 && (n == 0 || d_A), CN_ERR_ARG, "cn_absmax_f32: bad input");
     int vector_ok = ((uintptr_t)d_A % 16 == 0);
+    if (vector_ok && n >= (1LL << 16) && n < (1LL << 27)) {
+        // mid-sized tensors: the ring kernel (see there); small ones are launch-bound, large ones stream best below
+        static bool attr_set[64] = {};
+        const size_t smem = (size_t)RING_STAGES * RING_TILE * 4 + 128;
+        if (ctx->device < 0 || ctx->device >= 64 || !attr_set[ctx->device]) {
+            CN_CUDA(cudaFuncSetAttribute(cn_absmax_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            if (ctx->device >= 0 && ctx->device < 64) attr_set[ctx->device] = true;
+        }
+        unsigned int *d_status = nullptr;
+        int st = cn_status_block(ctx, &d_status);
+        if (st != CN_OK) return st;
+        const int64_t groups = n >> 2, max_groups = RING_TILE / 4;
+        const int64_t min_tiles = (groups + max_groups - 1) / max_groups, max_grid = 2 * (int64_t)ctx->sm_count;
+        const int grid = (int)(min_tiles < max_grid ? min_tiles : max_grid);
+        const int tiles_per_cta = (int)((min_tiles + grid - 1) / grid);
+        const int tile_groups = (int)((groups + (int64_t)grid * tiles_per_cta - 1) / ((int64_t)grid * tiles_per_cta));
+        CN_CUDA(launch_pdl(cn_absmax_ring_kernel, grid, RING_THREADS, smem, cn_stream(stream), d_A, n, d_out, ctx->d_partials, ctx->d_ticket,
+                           d_status, tile_groups, tiles_per_cta));
+        cn_count_launch();
+        return CN_OK;
+    }
     // measured: two CTAs per SM keep the last-ticket tail short on tensors of tens of MiB (64 MiB: 16.4 us vs 18.6 us with
     // four), eight per SM stream best on large ones (1 GiB: 6737 GB/s vs 6332)
     int grid = codec_grid(ctx, n, ABSMAX_THREADS, 16, n < (1LL << 27) ? 2 : 8);

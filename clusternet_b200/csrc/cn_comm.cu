@@ -503,8 +503,7 @@ static int dotmpi_impl(cn_context *ctx, int transA, int64_t M, int64_t K, int64_
     if (st != CN_OK) return st;
     uint8_t *codes = (uint8_t *)buf;
     float *scales = ctx->comm->d_scales;
-    if ((st = cn_absmax_f32(ctx, slice, M * cnt, scales + rank, stream)) != CN_OK) return st;
-    if ((st = cn_compress_8bit_dp(ctx, slice, scales + rank, M * cnt, codes + (size_t)M * start, stream)) != CN_OK) return st;
+    if ((st = cn_absmax_compress_8bit(ctx, slice, M * cnt, scales + rank, codes + (size_t)M * start, stream)) != CN_OK) return st;
     if ((st = cn_allgather_scalar_f32(ctx, scales, stream)) != CN_OK) return st;
     if ((st = cn_allgather_cols_u8(ctx, codes, M, n_total, stream)) != CN_OK) return st;
     for (int r = 0; r < G; ++r) {
@@ -653,8 +652,7 @@ extern "C" int cn_dotmpi_to_coded_f32(cn_context *ctx, int64_t M, int64_t K, int
     out->cols = n_total;
     int st = cn_gemm_f32(ctx, 0, 0, M, cnt, K, d_A, M, d_Wshard, K, out->own_fp32, M, &local, mode, stream);
     if (st != CN_OK) return st;
-    if ((st = cn_absmax_f32(ctx, out->own_fp32, M * cnt, out->scales + rank, stream)) != CN_OK) return st;
-    if ((st = cn_compress_8bit_dp(ctx, out->own_fp32, out->scales + rank, M * cnt, out->codes + (size_t)M * start, stream)) != CN_OK) return st;
+    if ((st = cn_absmax_compress_8bit(ctx, out->own_fp32, M * cnt, out->scales + rank, out->codes + (size_t)M * start, stream)) != CN_OK) return st;
     if (G == 1) return CN_OK;
     if ((st = cn_allgather_scalar_f32(ctx, out->scales, stream)) != CN_OK) return st;
     return cn_allgather_cols_u8(ctx, out->codes, M, n_total, stream);

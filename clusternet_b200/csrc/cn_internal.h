@@ -55,7 +55,8 @@ struct cn_context {
     uint32_t codec_cache_X[128];
     // reduction scratch: per-CTA partial maxima + a ticket counter that the last CTA resets
     float *d_partials = nullptr;
-    unsigned int *d_ticket = nullptr;
+    unsigned int *d_ticket = nullptr;   // 64 bytes: word 0 = absmax ticket, bytes 16..23 = grid-barrier counter of the fused compressor
+    unsigned long long grid_barrier_total = 0;   // value that counter reaches after the launches queued so far
     // GEMM
     cn_gemm_workspace *gemm = nullptr;
     const char *gemm_last_path = "";

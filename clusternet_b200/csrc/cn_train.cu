@@ -253,10 +253,10 @@ extern "C" int cn_grad_sync_8bit(cn_context *ctx, float *d_grad, int64_t n, floa
     // scale: this rank's absmax (gathered with the codes), or the caller's fixed value on every rank
     if (fixed_precision > 0.0f) {
         if ((st = cn_fill_f32(ctx, scales, G, fixed_precision, stream)) != CN_OK) return st;
+        if ((st = cn_compress_8bit_dp(ctx, d_grad, scales + rank, n, codes + (size_t)rank * n, stream)) != CN_OK) return st;
     } else {
-        if ((st = cn_absmax_f32(ctx, d_grad, n, scales + rank, stream)) != CN_OK) return st;
+        if ((st = cn_absmax_compress_8bit(ctx, d_grad, n, scales + rank, codes + (size_t)rank * n, stream)) != CN_OK) return st;
     }
-    if ((st = cn_compress_8bit_dp(ctx, d_grad, scales + rank, n, codes + (size_t)rank * n, stream)) != CN_OK) return st;
     if ((st = cn_comm_gather_codes(ctx, codes, n, fixed_precision > 0.0f ? nullptr : scales, stream)) != CN_OK) return st;
     int64_t blocks = (n + 511) / 512, cap = (int64_t)ctx->sm_count * 4;
     cn_decode_sum_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 512, (size_t)G * 256 * sizeof(float), cn_stream(stream)>>>(
@@ -306,9 +306,12 @@ extern "C" int cn_grad_sync_8bit_multi(cn_context *ctx, float *d_grad, const int
     int64_t off = 0;
     for (int s = 0; s < num_segments; ++s) {
         const int64_t sz = segment_sizes[s];
-        if (fixed_precision > 0.0f) st = cn_fill_f32(ctx, my_scales + s, 1, fixed_precision, stream);
-        else st = cn_absmax_f32(ctx, d_grad + off, sz, my_scales + s, stream);
-        if (st == CN_OK && sz > 0) st = cn_compress_8bit_dp(ctx, d_grad + off, my_scales + s, sz, mine + off, stream);
+        if (fixed_precision > 0.0f) {
+            st = cn_fill_f32(ctx, my_scales + s, 1, fixed_precision, stream);
+            if (st == CN_OK && sz > 0) st = cn_compress_8bit_dp(ctx, d_grad + off, my_scales + s, sz, mine + off, stream);
+        } else {
+            st = cn_absmax_compress_8bit(ctx, d_grad + off, sz, my_scales + s, mine + off, stream);   // one launch per tensor
+        }
         if (st != CN_OK) return st;
         off += sz;
         sp.seg_end[s] = off;

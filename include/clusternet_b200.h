@@ -107,6 +107,16 @@ int cn_compress_8bit(cn_context *ctx, const float *d_A, float precision, int64_t
  * absmax -> compress chain needs no host synchronisation. */
 int cn_compress_8bit_dp(cn_context *ctx, const float *d_A, const float *d_precision, int64_t n, uint8_t *d_codes, void *stream);
 
+/* scale = max |A|, then compression_8bit(A, scale) - the pair of calls the reference makes when the scale is not known
+ * beforehand (source/test.cu:1964-1968,2108-2109: max(abs(A)) followed by compression_8bit).  Up to 4 Mi elements it is ONE
+ * cooperative kernel launch: pass 1 reduces, a bounded grid-wide barrier publishes the maximum, pass 2 codes the tensor
+ * out of L2; larger tensors, for which launch latency no longer matters, take two pipelined launches.
+ * d_scale_out (device) receives the scale; the codes equal
+ * cn_absmax_f32 + cn_compress_8bit_dp bit for bit.  Uses context scratch: calls on one context must be serialised on
+ * one stream.  A barrier wait that runs out (it cannot unless the GPU is shared with a kernel that blocks half of it)
+ * is reported by cn_gemm_check_status as CN_ERR_TIMEOUT. */
+int cn_absmax_compress_8bit(cn_context *ctx, const float *d_A, int64_t n, float *d_scale_out, uint8_t *d_codes, void *stream);
+
 /* decompression_8bit: replaces ::decompression_8bit (source/basicOps.cu:1172-1176) and
  * kDecompression_8bit (source/clusterKernels.cu:1135-1160), including its committed decoding of the
  * special codes (126, 127, 254 -> +precision; 255 -> -precision). */

@@ -83,6 +83,27 @@ def test_compress_config2_full_size(ctx):
     assert torch.equal(codes, codes2)
 
 
+@pytest.mark.parametrize("n", [0, 1, 3, 4, 5, 2047, 8192, 100003, 1 << 20, (4 << 20) - 1, 4096 * 4096 + 2])
+def test_fused_absmax_compress_equals_the_two_calls(ctx, n):
+    """cn_absmax_compress_8bit (one cooperative launch: reduce, grid barrier, code) gives the scale and the codes of
+    cn_absmax_f32 followed by cn_compress_8bit_dp, on consecutive calls (the barrier counter only ever grows) and for a
+    buffer that is not 16-byte aligned (two-call fallback)."""
+    rng = np.random.default_rng(n + 1)
+    for rep in range(3):
+        x = torch.from_numpy((rng.standard_normal(n + 1) * rng.uniform(1e-3, 30)).astype(np.float32)).cuda()
+        a = x[:n] if rep < 2 else x[1:n + 1]
+        pm = ctx.absmax(a)
+        want = ctx.compress(a, pm)
+        got, scale = ctx.absmax_compress(a)
+        torch.cuda.synchronize()
+        ctx.gemm_check()
+        assert scale.item() == pm.item()
+        assert torch.equal(got, want), (n, rep)
+    if n:
+        p = float(pm.item())
+        assert np.array_equal(got.cpu().numpy(), oracle.compress(ctx.codebook, a.cpu().numpy(), p))
+
+
 def test_unaligned_buffers_take_scalar_path(ctx):
     rng = np.random.default_rng(7)
     x = (rng.standard_normal(10007) * 0.3).astype(np.float32)
