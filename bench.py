@@ -472,6 +472,14 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def rest(seconds=1.5):
+        """Every timed region starts from the same state: the GPUs idle for a moment first.  The products are bound by the
+        1 kW power limit, so a region that follows seconds of load would otherwise be measured at lower clocks than the
+        first one and the regions could not be compared with each other."""
+        barrier()
+        time.sleep(seconds)
+        barrier()
+
     def max_over_ranks(ms):
         if world == 1:
             return ms
@@ -536,9 +544,11 @@ def main():
                 **({"note": "8-bit exchange: the peers' blocks of layer 1 carry the codec's quantisation error by design"} if lossy else {})}
 
     upload(0)
+    two_layers()          # first call: scratch buffers are allocated here, not inside a timed region
+    ctx.gemm_check()
+    rest()
     for _ in range(args.warmup):
         two_layers()
-    ctx.gemm_check()
 
     # ---- timed region 1: resident inputs
     sampler = ClockSampler(local_rank)
@@ -575,6 +585,7 @@ def main():
     if not args.no_extras and coded is None:
         oname = "tf32" if args.mode == "3xtf32" else "3xtf32"
         omode = _lib.GEMM_TF32 if oname == "tf32" else _lib.GEMM_3XTF32
+        rest()
         for _ in range(2):
             two_layers(gemm_mode=omode)
         cn.check(lib.cn_gemm_profile_enable(ctx.h, 1))
@@ -640,20 +651,29 @@ def main():
 
     e2e_batches = []
 
-    def e2e_step():
-        cn.check(lib.cn_batch_copy_next_async(bh))                     # upload of the NEXT batch (side stream, all ranks)
+    def e2e_step(upload_next=True, download_result=True):
+        if upload_next:
+            cn.check(lib.cn_batch_copy_next_async(bh))                 # upload of the NEXT batch (side stream, all ranks)
         if use_rm:
             cn.check(lib.cn_batch_current_row_major(bh, ctypes.byref(px), ctypes.byref(pn)))
         else:
             cn.check(lib.cn_batch_current(bh, ctypes.byref(px), ctypes.byref(py), ctypes.byref(pn)))
         two_layers(px.value, row_major=use_rm)
-        download_overlapped()
-        cn.check(lib.cn_batch_swap(bh, sp, ctypes.byref(px), ctypes.byref(py), ctypes.byref(pn)))
-        e2e_batches.append(len(e2e_batches) % 2)                       # the allocator walks batch 0, 1, 0, 1, ...
+        if download_result:
+            download_overlapped()
+        if upload_next:
+            cn.check(lib.cn_batch_swap(bh, sp, ctypes.byref(px), ctypes.byref(py), ctypes.byref(pn)))
+            e2e_batches.append(len(e2e_batches) % 2)                   # the allocator walks batch 0, 1, 0, 1, ...
 
-    for _ in range(2):
+    rest()
+    for _ in range(args.warmup):
         e2e_step()
+    sampler2 = ClockSampler(local_rank)
+    if rank == 0:
+        sampler2.start()
+        time.sleep(0.25)
     barrier()
+    t_wall2 = time.time()
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2.record()
     for _ in range(args.steps):
@@ -662,8 +682,35 @@ def main():
         torch.cuda.current_stream().wait_event(ev_drained)   # the last step's result must be on the host inside the timed region
     e3.record()
     barrier()
+    t_wall3 = time.time()
     ms_e2e = max_over_ranks(e2.elapsed_time(e3))
+    clocks_e2e = sampler2.stop(t_wall2, t_wall3) if rank == 0 else None
     ctx.gemm_check()
+    e2e_diag = None
+    if os.environ.get("CN_BENCH_E2E_DIAG") == "1":
+        # where the end-to-end step spends its time beyond the two products: the same loop without the download, without
+        # the upload of the next batch, and without either (analysis aid; not part of any reported figure)
+        e2e_diag = {}
+        for name, up, down in (("full", True, True), ("no_download", True, False), ("no_upload", False, True), ("products_only", False, False)):
+            rest()
+            for _ in range(3):
+                e2e_step(up, down)
+            barrier()
+            d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            d0.record()
+            for _ in range(10):
+                e2e_step(up, down)
+            if rank == 0:
+                torch.cuda.current_stream().wait_event(ev_drained)
+            d1.record()
+            barrier()
+            e2e_diag[name] = max_over_ranks(d0.elapsed_time(d1)) / 10
+        e2e_step(True, True)          # a last full step, so that the host result and the record of its batch agree again
+        if rank == 0:
+            torch.cuda.current_stream().wait_event(ev_drained)
+        barrier()
+        if rank == 0:
+            print(f"bench.py: e2e diagnosis (ms per step): {e2e_diag}", file=sys.stderr, flush=True)
     lib.cn_batch_destroy(bh)
     barrier()
     # the end-to-end result, as it arrived on the host, against the resident path on the batch that step used: the two
@@ -708,12 +755,13 @@ def main():
         "config": {"workload": ("README dotMPI two-layer skinny GEMM: " if headline else "REDUCED (profiling) two-layer skinny GEMM: ") +
                                f"128x{K1} . {K1}x{N1} . {N1}x{N2}, W column-sharded",
                    "gemm_mode": args.mode, "exchange": args.exchange, "gather": ("fused peer stores" if fused else ("nccl" if world > 1 else "none")), "parallelism": f"tp{world} (columns of W)",
+                   "timed_regions": "each starts after 1.5 s of idle GPUs and its own warm-up steps (the products are power-limited)",
                    "l2": f"inputs larger than L2 ({4e-9 * (K1 * N1 + N1 * N2):.1f} GB of weights stream once per step)", "flops_per_step": FLOPS_STEP},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": M * K1 * 4,
                 "h2d_bytes_per_step_per_rank": M * K1 * 4 // world, "d2h_bytes_per_step": M * N2 * 4, "result_checksum": checksum,
                 "upload": (f"each of the {world} ranks uploads 1/{world} of the batch rows over its own PCIe link, blocks exchanged over NVLink" if world > 1
                            else "one rank, whole batch") + ("; row-major batch read as a transposed operand" if use_rm else ""),
-                "host_result_equals_resident_path_bitwise": e2e_match, "accuracy_of_that_batch": acc_e2e, "ok": e2e_ok},
+                "host_result_equals_resident_path_bitwise": e2e_match, "accuracy_of_that_batch": acc_e2e, "ok": e2e_ok, "clocks": clocks_e2e},
         "accuracy": acc_main,
         "gpu_launches": int(launches),
         "clocks": clocks,
