@@ -383,7 +383,8 @@ __device__ __forceinline__ uint32_t ring_code(uint32_t xb, uint32_t pb, uint32_t
 // four codes for one 16-byte group.  A NaN anywhere in the group (rare) sends it through the per-element form; the test
 // is a floating-point sum (x != x for the sum: NaN inputs, and +inf with -inf, which the per-element form codes
 // correctly as well), which keeps it off the integer pipe.
-__device__ __forceinline__ uint32_t ring_code4(const float4 q, uint32_t pb, uint32_t psign4, uint32_t kadd, int32_t span, uint32_t lut_addr)
+template <bool NEGP>
+__device__ __forceinline__ uint32_t ring_code4(const float4 q, uint32_t pb, uint32_t kadd, int32_t span, uint32_t lut_addr)
 {
     const uint32_t x0 = __float_as_uint(q.x), x1 = __float_as_uint(q.y), x2 = __float_as_uint(q.z), x3 = __float_as_uint(q.w);
     const float sum = (q.x + q.y) + (q.z + q.w);
@@ -392,9 +393,11 @@ __device__ __forceinline__ uint32_t ring_code4(const float4 q, uint32_t pb, uint
                      ring_code(x2, pb, kadd, span, lut_addr), ring_code(x3, pb, kadd, span, lut_addr));
     const uint32_t c0 = ring_lookup(x0, kadd, span, lut_addr), c1 = ring_lookup(x1, kadd, span, lut_addr);
     const uint32_t c2 = ring_lookup(x2, kadd, span, lut_addr), c3 = ring_lookup(x3, kadd, span, lut_addr);
-    // top bytes of x0..x3 -> one word; flip by the sign of precision; keep bit 7 of each byte (code 254 has it set already)
+    // top bytes of x0..x3 -> one word; keep bit 7 of each byte, flipped when precision is negative (code 254 has the bit set
+    // already); one three-input logic operation either way
     const uint32_t tops = __byte_perm(__byte_perm(x0, x1, 0x0073), __byte_perm(x2, x3, 0x0073), 0x5410);
-    return pack4(c0, c1, c2, c3) | ((tops ^ psign4) & 0x80808080u);
+    const uint32_t codes = pack4(c0, c1, c2, c3);
+    return NEGP ? (codes | (~tops & 0x80808080u)) : (codes | (tops & 0x80808080u));
 }
 
 // Shift, clamp range and bucket table from the 127 boundaries in t.X (all threads of the CTA; ends with a barrier).
@@ -584,7 +587,6 @@ cn_compress_ring_kernel(const float *__restrict__ A, float precision_arg, float 
         if (blockIdx.x == 0 && tid == 0) *d_precision = p;
     }
     const uint32_t pb = __float_as_uint(p);
-    const uint32_t psign4 = (pb >> 31) * 0x80808080u;
     const float ap = fabsf(p);
     // 2^-100 <= |p| <= 2^100 keeps every boundary T*|p| a normal number; NaN fails both tests
     const bool p_ok = (ap >= 7.8886090522101181e-31f) && (ap <= 1.2676506002282294e30f);
@@ -645,14 +647,29 @@ cn_compress_ring_kernel(const float *__restrict__ A, float precision_arg, float 
         const float4 *src = reinterpret_cast<const float4 *>(ring_gen + (size_t)s * (RING_TILE * 4));
         uint32_t *dst = out4 + j * tile_groups;
         if (fast) {
-            // table path: all loads of the thread first, then the lookups of its (up to) four groups interleave
+            // table path: all loads of the thread first, then the lookups of its (up to) four groups interleave.  Whole
+            // tiles (the common case: the host prefers them) need no per-thread bounds
             float4 q[RING_GROUPS_PER_THREAD];
+            if (groups == RING_TILE / 4) {
 #pragma unroll
-            for (int u = 0; u < RING_GROUPS_PER_THREAD; ++u)
-                if (tid + u * RING_THREADS < groups) q[u] = src[tid + u * RING_THREADS];
+                for (int u = 0; u < RING_GROUPS_PER_THREAD; ++u) q[u] = src[tid + u * RING_THREADS];
+                if (pb >> 31) {
 #pragma unroll
-            for (int u = 0; u < RING_GROUPS_PER_THREAD; ++u)
-                if (tid + u * RING_THREADS < groups) __stcs(dst + tid + u * RING_THREADS, ring_code4(q[u], pb, psign4, kadd, span, lut_addr));
+                    for (int u = 0; u < RING_GROUPS_PER_THREAD; ++u) __stcs(dst + tid + u * RING_THREADS, ring_code4<true>(q[u], pb, kadd, span, lut_addr));
+                } else {
+#pragma unroll
+                    for (int u = 0; u < RING_GROUPS_PER_THREAD; ++u) __stcs(dst + tid + u * RING_THREADS, ring_code4<false>(q[u], pb, kadd, span, lut_addr));
+                }
+            } else {
+#pragma unroll
+                for (int u = 0; u < RING_GROUPS_PER_THREAD; ++u)
+                    if (tid + u * RING_THREADS < groups) q[u] = src[tid + u * RING_THREADS];
+#pragma unroll
+                for (int u = 0; u < RING_GROUPS_PER_THREAD; ++u)
+                    if (tid + u * RING_THREADS < groups)
+                        __stcs(dst + tid + u * RING_THREADS, (pb >> 31) ? ring_code4<true>(q[u], pb, kadd, span, lut_addr)
+                                                                        : ring_code4<false>(q[u], pb, kadd, span, lut_addr));
+            }
         } else {
 #pragma unroll 1
             for (int g = tid; g < groups; g += RING_THREADS) {
@@ -1055,7 +1072,10 @@ static int compress_impl(cn_context *ctx, const float *d_A, float precision, flo
         const int64_t tpc64 = (min_tiles + grid - 1) / grid;
         CN_REQUIRE(tpc64 < (1LL << 30), CN_ERR_UNSUPPORTED, "cn_compress_8bit: tensor too large");
         const int tiles_per_cta = (int)tpc64;
-        const int tile_groups = (int)((groups + (int64_t)grid * tiles_per_cta - 1) / ((int64_t)grid * tiles_per_cta));
+        int tile_groups = (int)((groups + (int64_t)grid * tiles_per_cta - 1) / ((int64_t)grid * tiles_per_cta));
+        // whole tiles save the per-thread bounds tests: take them when the busiest CTA gets at most 2 % more work than with
+        // the exactly balanced size
+        if ((int64_t)tiles_per_cta * max_groups * 100 <= (int64_t)tiles_per_cta * tile_groups * 102) tile_groups = (int)max_groups;
         unsigned long long *counter = reinterpret_cast<unsigned long long *>(ctx->d_ticket + 4);   // bytes 16..23 of the ticket block
         if (scale_mode == RING_SCALE_ABSMAX) {
             const unsigned long long target = ctx->grid_barrier_total + (unsigned long long)grid;
@@ -1161,7 +1181,8 @@ extern "C" int cn_absmax_f32(cn_context *ctx, const float *d_A, int64_t n, float
         const int64_t min_tiles = (groups + max_groups - 1) / max_groups, max_grid = 2 * (int64_t)ctx->sm_count;
         const int grid = (int)(min_tiles < max_grid ? min_tiles : max_grid);
         const int tiles_per_cta = (int)((min_tiles + grid - 1) / grid);
-        const int tile_groups = (int)((groups + (int64_t)grid * tiles_per_cta - 1) / ((int64_t)grid * tiles_per_cta));
+        int tile_groups = (int)((groups + (int64_t)grid * tiles_per_cta - 1) / ((int64_t)grid * tiles_per_cta));
+        if (max_groups * 100 <= (int64_t)tile_groups * 102) tile_groups = (int)max_groups;   // whole tiles when nearly balanced anyway
         CN_CUDA(launch_pdl(cn_absmax_ring_kernel, grid, RING_THREADS, smem, cn_stream(stream), d_A, n, d_out, ctx->d_partials, ctx->d_ticket,
                            d_status, tile_groups, tiles_per_cta));
         cn_count_launch();
