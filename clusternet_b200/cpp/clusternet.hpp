@@ -376,30 +376,46 @@ private:
     std::shared_ptr<class BatchAllocator> batches_;
     uint64_t seed_ = 0, offset_ = 0, same_seed_ = 12345, same_offset_ = 0;
 
+    // The file carries the 128-byte NCCL id followed by a launch tag ($CN_NCCL_ID_NONCE, else $MASTER_PORT, else the
+    // launcher's process id, which the ranks of one launch share).  A file left behind by an earlier launch carries
+    // another tag and is ignored; rank 0 removes the file once every rank has joined (ncclCommInitRank returns only then).
+    static void launch_tag(char tag[32])
+    {
+        memset(tag, 0, 32);
+        const char *t = getenv("CN_NCCL_ID_NONCE");
+        if (!t) t = getenv("MASTER_PORT");
+        if (t) snprintf(tag, 32, "%s", t);
+        else snprintf(tag, 32, "ppid%ld", (long)getppid());
+    }
+
     void init_comm_from_file()
     {
         const char *path = getenv("CN_NCCL_ID_FILE");
         if (!path) throw "ClusterNet: WORLD_SIZE > 1 needs CN_NCCL_ID_FILE (a file path shared by the ranks)";
         unsigned char id[128];
+        char tag[32];
+        launch_tag(tag);
         if (MYRANK == 0) {
             cn_detail::check(cn_comm_get_unique_id(id));
             const std::string tmp = std::string(path) + ".tmp";
             FILE *f = fopen(tmp.c_str(), "wb");
-            if (!f || fwrite(id, 1, 128, f) != 128 || fclose(f) != 0) throw "ClusterNet: cannot write CN_NCCL_ID_FILE";
+            if (!f || fwrite(id, 1, 128, f) != 128 || fwrite(tag, 1, 32, f) != 32 || fclose(f) != 0) throw "ClusterNet: cannot write CN_NCCL_ID_FILE";
             if (rename(tmp.c_str(), path) != 0) throw "ClusterNet: cannot publish CN_NCCL_ID_FILE";
         } else {
             bool got = false;
             for (int tries = 0; tries < 1200 && !got; ++tries) {   // up to two minutes
                 FILE *f = fopen(path, "rb");
                 if (f) {
-                    got = fread(id, 1, 128, f) == 128;
+                    char seen[32];
+                    got = fread(id, 1, 128, f) == 128 && fread(seen, 1, 32, f) == 32 && memcmp(seen, tag, 32) == 0;
                     fclose(f);
                 }
                 if (!got) usleep(100000);
             }
-            if (!got) throw "ClusterNet: rank 0 never published CN_NCCL_ID_FILE";
+            if (!got) throw "ClusterNet: rank 0 never published CN_NCCL_ID_FILE for this launch";
         }
         cn_detail::check(cn_comm_init_rank(ctx_.get(), id, MYRANK, MPI_SIZE));
+        if (MYRANK == 0) remove(path);
     }
 
     uint64_t next_offset(int64_t n)

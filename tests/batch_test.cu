@@ -2,8 +2,10 @@
 // facade: arange data sets of 10000 x 784 (+ 10000 x 1 labels) and 70000 x 784 (+ 70000 x 10), 20 % held out, so that
 // every element of every batch equals a running counter; two epochs; short last batches; the counters must end at
 // 6 272 000 / 8 000 / 7 840 000 / 10 000 and 43 904 000 / 560 000 / 54 880 000 / 700 000.  One allocator serves its
-// own process (5-argument init), the other is in Distributed_weights mode: with several processes only rank 0's data
-// are used and every batch reaches the other GPUs by broadcast.
+// own process (5-argument init), the other is in Distributed_weights mode, once in each of its two forms: only rank 0's
+// data are used and every batch reaches the other GPUs by broadcast; or every process holds the data set (as the
+// processes of the reference's own test do), uploads its share of the rows of each batch and the GPUs exchange the
+// blocks (EVERY_RANK_HOLDS_DATA).
 // Runs as one process, or one per GPU with RANK / WORLD_SIZE / LOCAL_RANK / CN_NCCL_ID_FILE / CN_CODEBOOK set.
 #include <stdio.h>
 
@@ -56,14 +58,17 @@ int main(int argc, char **argv)
         ClusterNet gpus = ClusterNet(argc, argv, 12345);
         struct Case { int64_t rows, cols_y, batch, cv_batch, train_total, train_total_y, all_total, all_total_y; };
         const Case cases[2] = {{10000, 1, 128, 256, 6272000, 8000, 7840000, 10000}, {70000, 10, 128, 512, 43904000, 560000, 54880000, 700000}};
-        for (const Case &c : cases) {
-            // every rank builds the data for its own allocator; the distributed one only looks at rank 0's copy
+        for (int form = 0; form < 4; ++form) {
+            const Case &c = cases[form & 1];
+            const bool every_rank_holds = form >= 2;
+            // every rank builds the data for its own allocator; the broadcasting form only looks at rank 0's copy
             Matrix *m1 = to_host(arange(c.rows, 784)), *m2 = to_host(arange(c.rows, c.cols_y));
             Matrix *junk1 = empty_cpu(1, 1), *junk2 = empty_cpu(1, 1);
-            const bool other = gpus.MYRANK != 0;
+            const bool other = gpus.MYRANK != 0 && !every_rank_holds;
             BatchAllocator b = BatchAllocator();
             b.init(m1, m2, 0.20f, c.batch, c.cv_batch);
             BatchAllocator b_dist = BatchAllocator();
+            b_dist.EVERY_RANK_HOLDS_DATA = every_rank_holds;
             b_dist.init(other ? junk1 : m1, other ? junk2 : m2, 0.2f, c.batch, c.cv_batch, &gpus, Distributed_weights);
             const int64_t train = c.rows * 8 / 10, held = c.rows - train;
             CHECK(b.TRAIN_SET_ROWS == train && b_dist.TRAIN_SET_ROWS == train && b_dist.CV_SET_ROWS == held);
