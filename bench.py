@@ -264,36 +264,52 @@ def train_step_bench(ctx, cn, _lib, torch, dist, world, rank, steps=30):
     act = [X] + [ctx.empty(B, sizes[i + 1]) for i in range(3)]
     out = [ctx.empty(B, s) for s in sizes]
     err = [None] + [ctx.empty(B, sizes[i + 1]) for i in range(3)]
-    tmat = ctx.empty(B, 10)
     d_seed = torch.tensor([1000 + rank], dtype=torch.int64, device="cuda")     # dropout seed in device memory
+
+    comm_stream = torch.cuda.Stream()            # the gradient exchange and the weight update run beside the backward pass
+    ev_grad = [torch.cuda.Event() for _ in range(3)]
+    ev_err = [torch.cuda.Event() for _ in range(3)]
+    ev_updated = torch.cuda.Event()
+    seg1 = [(ctypes.c_int64 * 1)(numel[l]) for l in range(3)]
+
+    def exchange_and_update(l):
+        """Layer l's gradient: 8-bit exchange, then RMSprop on its weights - on the side stream, as soon as the gradient GEMM
+        has finished (the reference starts its sends right after backward_grads, source/Layer.cpp:332-390).  The update
+        waits for the backward product that still reads the old weights of this layer."""
+        main_s = torch.cuda.current_stream()
+        ev_grad[l].record(main_s)
+        comm_stream.wait_event(ev_grad[l])
+        if l > 0:
+            comm_stream.wait_event(ev_err[l])
+        cs = ctypes.c_void_p(comm_stream.cuda_stream)
+        cn.check(lib.cn_grad_sync_8bit_multi(h, grad[l].data_ptr(), seg1[l], 1, 0.0, cs))
+        cn.check(lib.cn_rmsprop_update(h, rms_p[offs[l]:].data_ptr(), grad[l].data_ptr(), W[l].data_ptr(), 0.9, 0.006, numel[l], cs))
 
     def one_step():
         sp = ctx.stream_ptr()                                                    # the capture stream while recording
-        # the previous step's gradients: one exchange and one update over the packed buffers (first step: all zero)
-        cn.check(lib.cn_grad_sync_8bit_multi(h, grad_p.data_ptr(), seg, 3, 0.0, sp))
-        cn.check(lib.cn_rmsprop_update(h, rms_p.data_ptr(), grad_p.data_ptr(), Wp.data_ptr(), 0.9, 0.006, total, sp))
+        main_s = torch.cuda.current_stream()
         # forward: fused dot+bias+activation, dropout
         cn.check(lib.cn_dropout_dp(h, act[0].data_ptr(), out[0].data_ptr(), act[0].numel(), drops[0], d_seed.data_ptr(), 0, sp))
         for l in range(3):
             last = l == 2
             ctx.gemm(out[l], W[l], out=(out[l + 1] if last else act[l + 1]), bias=bias[l],
                      activation=_lib.ACT_LINEAR if last else _lib.ACT_RELU)
-            if last:
-                cn.check(lib.cn_softmax(h, out[3].data_ptr(), out[3].data_ptr(), B, 10, sp))
-            else:
+            if not last:
                 cn.check(lib.cn_dropout_dp(h, act[l + 1].data_ptr(), out[l + 1].data_ptr(), act[l + 1].numel(), drops[l + 1], d_seed.data_ptr(),
                                            1 << (20 + l), sp))
-        # backward errors
-        cn.check(lib.cn_create_t_matrix(h, y.data_ptr(), tmat.data_ptr(), B, 10, sp))
-        cn.check(lib.cn_sub(h, out[3].data_ptr(), tmat.data_ptr(), err[3].data_ptr(), err[3].numel(), sp))
-        for l in (2, 1):
-            cn.check(lib.cn_activation_gradient(h, act[l].data_ptr(), _lib.ACT_RELU, out[l].data_ptr(), out[l].numel(), sp))
-            ctx.gemm(err[l + 1], W[l], out=err[l], transB=True)
-            cn.check(lib.cn_mul(h, err[l].data_ptr(), out[l].data_ptr(), err[l].data_ptr(), err[l].numel(), sp))
-        # gradients
-        for l in range(3):
+        # output layer: softmax and error softmax - onehot(y) in one pass
+        cn.check(lib.cn_softmax_error(h, out[3].data_ptr(), y.data_ptr(), out[3].data_ptr(), err[3].data_ptr(), B, 10, sp))
+        # backward, last layer first; each layer's gradient goes to the exchange as soon as it exists
+        for l in (2, 1, 0):
             ctx.gemm(act[l], err[l + 1], out=grad[l], transA=True)
+            if l > 0:
+                ctx.gemm(err[l + 1], W[l], out=err[l], transB=True)              # reads the old W[l]
+                ev_err[l].record(main_s)
+                cn.check(lib.cn_mul_activation_gradient(h, err[l].data_ptr(), act[l].data_ptr(), _lib.ACT_RELU, None, err[l].data_ptr(), err[l].numel(), sp))
+            exchange_and_update(l)
         cn.check(lib.cn_seed_advance(h, d_seed.data_ptr(), sp))
+        ev_updated.record(comm_stream)
+        main_s.wait_event(ev_updated)                                            # the next forward pass needs the new weights
 
     def timed(fn):
         torch.cuda.synchronize()

@@ -112,6 +112,8 @@ _SIGNATURES = {
     "cn_max_f32": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "cn_nesterov_update": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int64, c_float, c_int64, c_void_p]),
     "cn_activation_gradient": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p]),
+    "cn_mul_activation_gradient": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_void_p]),
+    "cn_softmax_error": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "cn_rmsprop_update": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_int64, c_void_p]),
     "cn_grad_sync_8bit": (c_int, [c_void_p, c_void_p, c_int64, c_float, c_void_p]),
     "cn_grad_sync_8bit_multi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),

@@ -25,6 +25,47 @@ __global__ void cn_softmax_kernel(const float *__restrict__ A, float *__restrict
     }
 }
 
+// softmax of each row (as cn_softmax_kernel) and, in the same pass, the output layer's error softmax - onehot(label):
+// the three launches softmax / create_t_matrix / sub of the reference's step (source/Layer.cpp:163-165,318-322) in one.
+__global__ void cn_softmax_error_kernel(const float *__restrict__ A, const float *__restrict__ labels, float *__restrict__ prob,
+                                        float *__restrict__ err, int64_t rows, int64_t cols)
+{
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; row < rows; row += stride) {
+        float mx = -FLT_MAX;
+        for (int64_t i = 0; i < cols; ++i) {
+            const float v = A[i * rows + row];
+            if (v > mx) mx = v;
+        }
+        float sum = 0.0f;
+        for (int64_t i = 0; i < cols; ++i) sum += __expf(A[i * rows + row] - mx);
+        const int64_t hot = (int64_t)(int)labels[row];
+        for (int64_t i = 0; i < cols; ++i) {
+            const float pr = __expf(A[i * rows + row] - mx) / sum;
+            prob[i * rows + row] = pr;
+            err[i * rows + row] = pr - (i == hot ? 1.0f : 0.0f);
+        }
+    }
+}
+
+// err_out = err_in * f'(activation), and optionally grad_out = f'(activation) (the reference writes the derivative into
+// the layer's `out` matrix and multiplies in a second kernel, source/Layer.cpp:323-329)
+template <int ACT>
+__global__ void cn_mul_grad_kernel(const float *__restrict__ err_in, const float *__restrict__ act, float *__restrict__ grad_out,
+                                   float *__restrict__ err_out, int64_t n)
+{
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float a = act[i];
+        float g;
+        if (ACT == CN_ACT_RELU) g = a > 0.0f ? 1.0f : 0.0f;
+        else if (ACT == CN_ACT_LOGISTIC) g = a * (1.0f - a);
+        else g = (a > 0.0f && a < 1.0f) ? 1.0f : 0.0f;
+        if (grad_out) grad_out[i] = g;
+        err_out[i] = err_in[i] * g;
+    }
+}
+
 // out = one-hot(labels): zero fill and scatter in one pass over the output
 __global__ void cn_t_matrix_kernel(const float *__restrict__ labels, float *__restrict__ out, int64_t rows, int64_t n)
 {
@@ -171,6 +212,19 @@ extern "C" int cn_softmax(cn_context *ctx, const float *d_A, float *d_out, int64
     return CN_OK;
 }
 
+extern "C" int cn_softmax_error(cn_context *ctx, const float *d_A, const float *d_labels, float *d_softmax_out, float *d_error_out,
+                                int64_t rows, int64_t cols, void *stream)
+{
+    CN_REQUIRE(ctx && rows >= 0 && cols >= 0 && (rows * cols == 0 || (d_A && d_labels && d_softmax_out && d_error_out)), CN_ERR_ARG,
+               "cn_softmax_error: bad argument");
+    if (rows * cols == 0) return CN_OK;
+    cn_softmax_error_kernel<<<(unsigned)((rows + 127) / 128 < 1024 ? (rows + 127) / 128 : 1024), 128, 0, cn_stream(stream)>>>(
+        d_A, d_labels, d_softmax_out, d_error_out, rows, cols);
+    CN_CUDA(cudaGetLastError());
+    cn_count_launch();
+    return CN_OK;
+}
+
 extern "C" int cn_create_t_matrix(cn_context *ctx, const float *d_labels, float *d_out, int64_t rows, int64_t cols, void *stream)
 {
     CN_REQUIRE(ctx && rows >= 0 && cols >= 0 && (rows * cols == 0 || (d_labels && d_out)), CN_ERR_ARG, "cn_create_t_matrix: bad argument");
@@ -222,6 +276,25 @@ extern "C" int cn_activation_gradient(cn_context *ctx, const float *d_activation
     }
     cn_set_error("cn_activation_gradient: no derivative for activation %d (the reference throws 'Unknown unit')", activation);
     return CN_ERR_ARG;
+}
+
+extern "C" int cn_mul_activation_gradient(cn_context *ctx, const float *d_error_in, const float *d_activation, int activation,
+                                          float *d_gradient_out, float *d_error_out, int64_t n, void *stream)
+{
+    CN_REQUIRE(ctx && n >= 0 && (n == 0 || (d_error_in && d_activation && d_error_out)), CN_ERR_ARG, "cn_mul_activation_gradient: bad argument");
+    if (n == 0) return CN_OK;
+    const int grid = ew_grid(ctx, n);
+    switch (activation) {
+        case CN_ACT_RELU: cn_mul_grad_kernel<CN_ACT_RELU><<<grid, 256, 0, cn_stream(stream)>>>(d_error_in, d_activation, d_gradient_out, d_error_out, n); break;
+        case CN_ACT_LOGISTIC: cn_mul_grad_kernel<CN_ACT_LOGISTIC><<<grid, 256, 0, cn_stream(stream)>>>(d_error_in, d_activation, d_gradient_out, d_error_out, n); break;
+        case CN_ACT_DOUBLE_RELU: cn_mul_grad_kernel<CN_ACT_DOUBLE_RELU><<<grid, 256, 0, cn_stream(stream)>>>(d_error_in, d_activation, d_gradient_out, d_error_out, n); break;
+        default:
+            cn_set_error("cn_mul_activation_gradient: no derivative for activation %d (the reference throws 'Unknown unit')", activation);
+            return CN_ERR_ARG;
+    }
+    CN_CUDA(cudaGetLastError());
+    cn_count_launch();
+    return CN_OK;
 }
 
 extern "C" int cn_rmsprop_update(cn_context *ctx, float *d_rms, const float *d_grad, float *d_w, float rms_multiplier, float learning_rate,

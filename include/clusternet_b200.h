@@ -343,6 +343,16 @@ int cn_nesterov_update(cn_context *ctx, const float *d_grad, float *d_w, float *
 /* derivative of the unit from its activation (Layer::activation_gradient, source/Layer.cpp:180-200): ReLU x>0?1:0
  * (kRectifiedLinear_Derivative :813-821), logistic a(1-a), double ReLU 0<a<1?1:0. */
 int cn_activation_gradient(cn_context *ctx, const float *d_activation, int activation, float *d_out, int64_t n, void *stream);
+/* The same derivative multiplied into an error matrix in one pass: error_out = error_in * f'(activation); when
+ * d_gradient_out is not NULL it also receives f'(activation) (the reference stores it in the layer's `out` matrix and
+ * multiplies with a second kernel, source/Layer.cpp:323-329).  Bit-identical to cn_activation_gradient + cn_mul. */
+int cn_mul_activation_gradient(cn_context *ctx, const float *d_error_in, const float *d_activation, int activation,
+                               float *d_gradient_out, float *d_error_out, int64_t n, void *stream);
+/* Output layer in one pass: softmax over the columns of each row (as cn_softmax) and error = softmax - onehot(label)
+ * (softmax, create_t_matrix and sub of the reference's step, source/Layer.cpp:163-165,318-322).  d_softmax_out may be
+ * d_A.  Bit-identical to the three calls. */
+int cn_softmax_error(cn_context *ctx, const float *d_A, const float *d_labels, float *d_softmax_out, float *d_error_out,
+                     int64_t rows, int64_t cols, void *stream);
 /* RMSprop_with_weight_update (kRMSprop_with_weight_update, :1306-1325): RMS = m RMS + (1-m) g^2; w -= lr g / (sqrt(RMS)+1e-8). */
 int cn_rmsprop_update(cn_context *ctx, float *d_rms, const float *d_grad, float *d_w, float rms_multiplier, float learning_rate,
                       int64_t n, void *stream);

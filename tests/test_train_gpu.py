@@ -30,6 +30,13 @@ def test_softmax_and_t_matrix(ctx):
         t.fill_(7.0)
         cn.check(ctx.lib.cn_create_t_matrix(ctx.h, torch.from_numpy(labels).cuda().data_ptr(), t.data_ptr(), rows, cols, ctx.stream_ptr()))
         assert np.array_equal(ctx.to_numpy(t), oracle.t_matrix(labels, cols))
+        # the fused output layer (softmax + one-hot + sub in one pass) gives the same bits as the three calls
+        want_err = ctx.empty(rows, cols)
+        cn.check(ctx.lib.cn_sub(ctx.h, out.data_ptr(), t.data_ptr(), want_err.data_ptr(), rows * cols, ctx.stream_ptr()))
+        prob, err = ctx.empty(rows, cols), ctx.empty(rows, cols)
+        cn.check(ctx.lib.cn_softmax_error(ctx.h, d.data_ptr(), torch.from_numpy(labels).cuda().data_ptr(), prob.data_ptr(), err.data_ptr(),
+                                          rows, cols, ctx.stream_ptr()))
+        assert torch.equal(prob, out) and torch.equal(err, want_err)
 
 
 def test_elementwise_and_activation_gradients(ctx):
@@ -48,7 +55,15 @@ def test_elementwise_and_activation_gradients(ctx):
                       (_lib.ACT_DOUBLE_RELU, ((a > 0) & (a < 1)).astype(np.float32))]:
         cn.check(ctx.lib.cn_activation_gradient(ctx.h, da.data_ptr(), act, out.data_ptr(), a.size, sp))
         assert np.array_equal(out.cpu().numpy(), want)
+        # error * f'(activation) in one pass == the two calls
+        prod, g2, fused = torch.empty_like(da), torch.empty_like(da), torch.empty_like(da)
+        cn.check(ctx.lib.cn_mul(ctx.h, db.data_ptr(), out.data_ptr(), prod.data_ptr(), a.size, sp))
+        cn.check(ctx.lib.cn_mul_activation_gradient(ctx.h, db.data_ptr(), da.data_ptr(), act, g2.data_ptr(), fused.data_ptr(), a.size, sp))
+        assert torch.equal(fused, prod) and torch.equal(g2, out)
+        cn.check(ctx.lib.cn_mul_activation_gradient(ctx.h, db.data_ptr(), da.data_ptr(), act, None, fused.data_ptr(), a.size, sp))
+        assert torch.equal(fused, prod)
     assert ctx.lib.cn_activation_gradient(ctx.h, da.data_ptr(), _lib.ACT_LINEAR, out.data_ptr(), a.size, sp) == _lib.CN_ERR_ARG
+    assert ctx.lib.cn_mul_activation_gradient(ctx.h, db.data_ptr(), da.data_ptr(), _lib.ACT_LINEAR, None, out.data_ptr(), a.size, sp) == _lib.CN_ERR_ARG
 
 
 def test_abs_div_square_scalar_add_and_seeded_max(ctx):
