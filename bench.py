@@ -200,13 +200,14 @@ def codec_bench(ctx, torch, peaks):
             ctx.compress(xs[i], scale, out=codes[i])
 
         def fused(i):
-            # the same as one cooperative launch (cn_absmax_compress_8bit): reduce, grid barrier, code
+            # the same through cn_absmax_compress_8bit: one cooperative launch up to 4 Mi elements, above that absmax and a
+            # compressor that loads its first tiles while absmax drains
             ctx.absmax_compress(xs[i], scale=scale, out=codes[i])
         for name, fn, bytes_per in (("compress", lambda i: ctx.compress(xs[i], p, out=codes[i]), 5),
                                     ("decompress", lambda i: ctx.decompress(codes[i], p, out=outs[i]), 5),
                                     ("absmax", lambda i: ctx.absmax(xs[i], out=pm), 4),
                                     ("absmax_then_compress", pipeline, 9),
-                                    ("absmax_compress_one_launch", fused, 9)):
+                                    ("absmax_compress_entry_point", fused, 9)):
             for i in range(sets):
                 fn(i)
             torch.cuda.synchronize()

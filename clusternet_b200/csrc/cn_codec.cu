@@ -489,7 +489,7 @@ __global__ void __launch_bounds__(RING_THREADS, 2)
 cn_compress_ring_kernel(const float *__restrict__ A, float precision_arg, float *__restrict__ d_precision,
                         int64_t n, uint8_t *__restrict__ out, const __grid_constant__ RingConst rc, unsigned int *status,
                         int tile_groups, int tiles_per_cta, float *__restrict__ partials, unsigned long long *barrier_counter,
-                        unsigned long long barrier_target)
+                        unsigned long long barrier_target, int input_ready_before_predecessor)
 {
     extern __shared__ __align__(128) uint8_t ring_smem[];
     __shared__ RingTables t;
@@ -529,6 +529,18 @@ cn_compress_ring_kernel(const float *__restrict__ A, float precision_arg, float 
     };
     __syncthreads();   // barriers initialised, constant tables in shared memory
 
+    // input_ready_before_predecessor: the launch directly before this one in the stream is this library's absmax of the
+    // same tensor (cn_absmax_compress_8bit): it does not write A, and it released this kernel only after everything
+    // before it had finished, so A may be loaded already - the ring fills while absmax drains.  Only the scale needs the wait.
+    auto fill_ring = [&]() {
+        for (int i = 0; i < RING_STAGES && i < my_tiles; ++i) {
+            const int64_t j = tile_of(i);
+            const uint32_t bytes = (uint32_t)tile_count(j) * 16u;
+            cdc_mbar_expect_tx(full_bar(i), bytes);
+            cdc_bulk_load(ring_base + (uint32_t)i * (RING_TILE * 4), A + j * tile_groups * 4, bytes, full_bar(i));
+        }
+    };
+    if (SCALE == RING_SCALE_DEVICE && input_ready_before_predecessor && tid == 0) fill_ring();
     // ---- everything below may touch global memory: the predecessor in the stream must have finished
     cdc_pdl_wait();
     float p = precision_arg;
@@ -562,14 +574,8 @@ cn_compress_ring_kernel(const float *__restrict__ A, float precision_arg, float 
         }
         cdc_grid_barrier(barrier_counter, barrier_target, status);
     }
-    if (tid == 0) {    // fill the ring before anything else: the first loads are in flight while the tables are built
-        for (int i = 0; i < RING_STAGES && i < my_tiles; ++i) {
-            const int64_t j = tile_of(i);
-            const uint32_t bytes = (uint32_t)tile_count(j) * 16u;
-            cdc_mbar_expect_tx(full_bar(i), bytes);
-            cdc_bulk_load(ring_base + (uint32_t)i * (RING_TILE * 4), A + j * tile_groups * 4, bytes, full_bar(i));
-        }
-    }
+    // fill the ring before anything else: the first loads are in flight while the tables are built
+    if (tid == 0 && !(SCALE == RING_SCALE_DEVICE && input_ready_before_predecessor)) fill_ring();
     if (SCALE == RING_SCALE_DEVICE) p = *d_precision;
     if (SCALE == RING_SCALE_ABSMAX) {
         // every CTA folds the per-CTA maxima (the same values in the same order everywhere)
@@ -776,8 +782,10 @@ cn_absmax_kernel(const float *__restrict__ A, int64_t n, float *__restrict__ out
     __shared__ float warp_max[ABSMAX_THREADS / 32];
     __shared__ bool is_last;
     const int tid = threadIdx.x;
-    cdc_pdl_launch_dependents();
+    // wait first, then release the successor: a kernel that follows absmax in the stream may then rely on everything
+    // before absmax having finished (cn_absmax_compress_8bit's compressor starts loading A before its own wait)
     cdc_pdl_wait();
+    cdc_pdl_launch_dependents();
     float m = -1.0f;   // the reference seeds thrust::reduce with -1.0f (source/basicOps.cu:1079)
     const int64_t nvec = vector_ok ? (n >> 2) : 0;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -853,7 +861,6 @@ cn_absmax_ring_kernel(const float *__restrict__ A, int64_t n, float *__restrict_
         for (int s = 0; s < RING_STAGES; ++s) { cdc_mbar_init(full_bar(s), 1); cdc_mbar_init(empty_bar(s), RING_THREADS / 32); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    cdc_pdl_launch_dependents();
     const int64_t groups_total = n >> 2;
     int my_tiles = 0;
     {
@@ -869,6 +876,7 @@ cn_absmax_ring_kernel(const float *__restrict__ A, int64_t n, float *__restrict_
     };
     __syncthreads();
     cdc_pdl_wait();
+    cdc_pdl_launch_dependents();   // after the wait: see cn_absmax_kernel
     if (tid == 0) {
         for (int i = 0; i < RING_STAGES && i < my_tiles; ++i) {
             const int64_t j = blockIdx.x + (int64_t)i * gridDim.x;
@@ -1020,7 +1028,7 @@ static bool host_boundaries(cn_context *ctx, float precision, uint32_t X[128])
 
 // scale_mode: RING_SCALE_HOST (precision), RING_SCALE_DEVICE (d_precision read) or RING_SCALE_ABSMAX (d_precision written)
 static int compress_impl(cn_context *ctx, const float *d_A, float precision, float *d_precision, int scale_mode, int64_t n,
-                         uint8_t *d_codes, void *stream)
+                         uint8_t *d_codes, void *stream, int after_own_absmax = 0)
 {
     CN_REQUIRE(ctx, CN_ERR_ARG, "cn_compress_8bit: null context");
     CN_REQUIRE(n >= 0, CN_ERR_ARG, "cn_compress_8bit: negative size");
@@ -1033,7 +1041,7 @@ static int compress_impl(cn_context *ctx, const float *d_A, float precision, flo
         // also for buffers the ring kernel does not take (unaligned, tiny, empty): the two-call form
         int st = cn_absmax_f32(ctx, d_A, n, d_precision, stream);
         if (st != CN_OK || n == 0) return st;
-        return compress_impl(ctx, d_A, 0.f, d_precision, RING_SCALE_DEVICE, n, d_codes, stream);
+        return compress_impl(ctx, d_A, 0.f, d_precision, RING_SCALE_DEVICE, n, d_codes, stream, 1);
     }
     if (n == 0) return CN_OK;
     CN_REQUIRE(d_A && d_codes, CN_ERR_ARG, "cn_compress_8bit: null buffer");
@@ -1090,14 +1098,14 @@ static int compress_impl(cn_context *ctx, const float *d_A, float precision, flo
             cfg.attrs = attr;
             cfg.numAttrs = 1;
             CN_CUDA(cudaLaunchKernelEx(&cfg, cn_compress_ring_kernel<RING_SCALE_ABSMAX>, d_A, 0.f, d_precision, n, d_codes, rc, d_status, tile_groups,
-                                       tiles_per_cta, ctx->d_partials, counter, target));
+                                       tiles_per_cta, ctx->d_partials, counter, target, 0));
             ctx->grid_barrier_total = target;   // only a launch that was accepted moves the counter
         } else if (scale_mode == RING_SCALE_DEVICE) {
             CN_CUDA(launch_pdl(cn_compress_ring_kernel<RING_SCALE_DEVICE>, grid, RING_THREADS, smem, s, d_A, 0.f, d_precision, n, d_codes, rc, d_status,
-                               tile_groups, tiles_per_cta, (float *)nullptr, (unsigned long long *)nullptr, 0ULL));
+                               tile_groups, tiles_per_cta, (float *)nullptr, (unsigned long long *)nullptr, 0ULL, after_own_absmax));
         } else {
             CN_CUDA(launch_pdl(cn_compress_ring_kernel<RING_SCALE_HOST>, grid, RING_THREADS, smem, s, d_A, precision, (float *)nullptr, n, d_codes, rc,
-                               d_status, tile_groups, tiles_per_cta, (float *)nullptr, (unsigned long long *)nullptr, 0ULL));
+                               d_status, tile_groups, tiles_per_cta, (float *)nullptr, (unsigned long long *)nullptr, 0ULL, 0));
         }
         cn_count_launch();
         return CN_OK;

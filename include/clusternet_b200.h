@@ -9,6 +9,12 @@
  *
  * Each declaration cites the reference interface (file:line, relative to the reference tree) whose
  * job it takes over.
+ *
+ * Threading and streams.  One context per host thread.  Calls on one context must be serialised on ONE stream: the
+ * scratch buffers the kernels use (activation planes and split-K partials of the products, exchange codes, partial
+ * maxima) belong to the context, and the first call that needs a larger buffer grows it with a device synchronisation -
+ * make that call before a stream capture.  The codec / gradient-exchange entry points and the product entry points use
+ * disjoint scratch, so one stream for each is allowed.
  */
 #ifndef CLUSTERNET_B200_H
 #define CLUSTERNET_B200_H
