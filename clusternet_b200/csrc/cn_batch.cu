@@ -113,6 +113,10 @@ extern "C" int cn_batch_create_ex(cn_context *ctx, const float *h_X, const float
     b->total_batches = (rows + batch_size - 1) / batch_size;
     const size_t bx = (size_t)batch_size * cols_X * sizeof(float), by = (size_t)batch_size * cols_y * sizeof(float);
     cudaError_t e;
+    // The copy streams get the highest priority: their work is a few copies and, with the sharded upload, two one-warp flag
+    // kernels, which must not queue behind the thousands of CTAs of a product that runs on the compute stream meanwhile.
+    int prio_low = 0, prio_high = 0;
+    cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high);
     {   // the reference keeps the whole data set in pinned memory (empty_pinned); if the caller did the same, the
         // batch rows (contiguous in the row-major set) are copied straight from it
         cudaPointerAttributes ax, ay;
@@ -127,8 +131,8 @@ extern "C" int cn_batch_create_ex(cn_context *ctx, const float *h_X, const float
         (e = cudaMalloc(&b->dn_y, by)) != cudaSuccess ||
         (!(flags & CN_BATCH_NO_COL_MAJOR) && (e = cudaMalloc(&b->dc_X, bx)) != cudaSuccess) ||
         (e = cudaMalloc(&b->dc_y, by)) != cudaSuccess ||
-        (e = cudaStreamCreateWithFlags(&b->s_X, cudaStreamNonBlocking)) != cudaSuccess ||
-        (e = cudaStreamCreateWithFlags(&b->s_y, cudaStreamNonBlocking)) != cudaSuccess ||
+        (e = cudaStreamCreateWithPriority(&b->s_X, cudaStreamNonBlocking, prio_high)) != cudaSuccess ||
+        (e = cudaStreamCreateWithPriority(&b->s_y, cudaStreamNonBlocking, prio_high)) != cudaSuccess ||
         (e = cudaEventCreateWithFlags(&b->e_X, cudaEventDisableTiming)) != cudaSuccess ||
         (e = cudaEventCreateWithFlags(&b->e_y, cudaEventDisableTiming)) != cudaSuccess ||
         (e = cudaEventCreateWithFlags(&b->e_consumed, cudaEventDisableTiming)) != cudaSuccess) {
