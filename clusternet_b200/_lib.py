@@ -77,6 +77,10 @@ _SIGNATURES = {
     "cn_seed_advance": (c_int, [c_void_p, c_void_p, c_void_p]),
     "cn_comm_get_unique_id": (c_int, [c_void_p]),
     "cn_comm_init_rank": (c_int, [c_void_p, c_void_p, c_int, c_int]),
+    "cn_comm_init_all": (c_int, [ctypes.POINTER(c_void_p), c_int]),
+    "cn_group_start": (c_int, []),
+    "cn_group_end": (c_int, []),
+    "cn_context_make_current": (c_int, [c_void_p]),
     "cn_comm_sync": (c_int, [c_void_p, c_void_p, c_int]),
     "cn_comm_destroy": (c_int, [c_void_p]),
     "cn_comm_rank": (c_int, [c_void_p]),

@@ -21,6 +21,7 @@ struct NcclApi {
     void *handle = nullptr;
     ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommInitAll)(ncclComm_t *, int, const int *) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*Broadcast)(const void *, void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
@@ -45,6 +46,7 @@ static int nccl_load()
     CN_REQUIRE(g_nccl.field, CN_ERR_NCCL, "libnccl.so.2 has no symbol %s", name)
     CN_SYM(GetUniqueId, "ncclGetUniqueId");
     CN_SYM(CommInitRank, "ncclCommInitRank");
+    CN_SYM(CommInitAll, "ncclCommInitAll");
     CN_SYM(CommDestroy, "ncclCommDestroy");
     CN_SYM(Broadcast, "ncclBroadcast");
     CN_SYM(AllGather, "ncclAllGather");
@@ -89,6 +91,7 @@ struct cn_comm_state {
     unsigned int epoch = 0;
     int next_flag_slot = 2;   // slots 0 and 1 frame the fused gather; the batch allocators reserve theirs from here
     bool aborted = false;   // cn_comm_sync gave up on a collective: only cn_comm_destroy is accepted from here on
+    bool in_process = false;   // made by cn_comm_init_all: the peers are contexts of this process (no CUDA IPC between them)
 };
 
 // Refuses work on a communicator that cn_comm_sync has aborted; a context without communicator passes (single rank).
@@ -107,6 +110,9 @@ static void sym_release(cn_comm_state *c, cn_sym_buf &b)
 void cn_comm_state_free(cn_context *ctx)
 {
     if (!ctx->comm) return;
+    int prev = -1;
+    cudaGetDevice(&prev);
+    cudaSetDevice(ctx->device);   // several contexts may live in one process (cn_comm_init_all)
     cudaDeviceSynchronize();
     for (auto &b : ctx->comm->sym) sym_release(ctx->comm, b);
     cudaFree(ctx->comm->d_peer_flags);
@@ -114,6 +120,7 @@ void cn_comm_state_free(cn_context *ctx)
     cudaFree(ctx->comm->d_scales);
     delete ctx->comm;
     ctx->comm = nullptr;
+    if (prev >= 0) cudaSetDevice(prev);
 }
 
 extern "C" int cn_comm_get_unique_id(void *id128)
@@ -154,6 +161,74 @@ extern "C" int cn_comm_init_rank(cn_context *ctx, const void *id128, int rank, i
         return cn_cuda_fail(e, "cn_comm_init_rank");
     }
     ctx->comm = c;
+    return CN_OK;
+}
+
+// Single-process form (ncclCommInitAll): contexts of this process, one per device, become ranks 0 .. n-1 of one
+// communicator.  Each rank is then driven by its own host thread, or one thread drives all of them and brackets the
+// per-rank calls of one collective with cn_group_start / cn_group_end.
+extern "C" int cn_comm_init_all(cn_context **ctxs, int n)
+{
+    CN_REQUIRE(ctxs && n >= 1 && n <= CN_MAX_PEERS + 1, CN_ERR_ARG, "cn_comm_init_all: 1 .. %d contexts", CN_MAX_PEERS + 1);
+    std::vector<int> devs(n);
+    for (int i = 0; i < n; ++i) {
+        CN_REQUIRE(ctxs[i] && !ctxs[i]->comm, CN_ERR_ARG, "cn_comm_init_all: context %d is null or already has a communicator", i);
+        devs[i] = ctxs[i]->device;
+        for (int j = 0; j < i; ++j) CN_REQUIRE(devs[j] != devs[i], CN_ERR_ARG, "cn_comm_init_all: two contexts on device %d", devs[i]);
+    }
+    int st = nccl_load();
+    if (st != CN_OK) return st;
+    int prev = 0;
+    CN_CUDA(cudaGetDevice(&prev));
+    std::vector<ncclComm_t> comms(n, nullptr);
+    ncclResult_t r = g_nccl.CommInitAll(comms.data(), n, devs.data());
+    if (r != ncclSuccess) {
+        cn_set_error("NCCL error %d (%s) in ncclCommInitAll", (int)r, g_nccl.GetErrorString(r));
+        cudaSetDevice(prev);
+        return CN_ERR_NCCL;
+    }
+    for (int i = 0; i < n; ++i) {
+        cn_comm_state *c = new cn_comm_state();
+        c->comm = comms[i];
+        c->rank = i;
+        c->nranks = n;
+        c->in_process = true;
+        cudaError_t e = cudaSetDevice(devs[i]);
+        if (e == cudaSuccess) e = cudaMalloc(&c->d_scales, sizeof(float) * (size_t)n);
+        if (e != cudaSuccess) {
+            delete c;
+            for (int j = 0; j < n; ++j) {
+                if (j < i) cn_comm_state_free(ctxs[j]); else g_nccl.CommDestroy(comms[j]);
+            }
+            cudaSetDevice(prev);
+            return cn_cuda_fail(e, "cn_comm_init_all");
+        }
+        ctxs[i]->comm = c;
+    }
+    CN_CUDA(cudaSetDevice(prev));
+    return CN_OK;
+}
+
+extern "C" int cn_group_start(void)
+{
+    int st = nccl_load();
+    if (st != CN_OK) return st;
+    CN_NCCL(g_nccl.GroupStart());
+    return CN_OK;
+}
+
+extern "C" int cn_group_end(void)
+{
+    int st = nccl_load();
+    if (st != CN_OK) return st;
+    CN_NCCL(g_nccl.GroupEnd());
+    return CN_OK;
+}
+
+extern "C" int cn_context_make_current(const cn_context *ctx)
+{
+    CN_REQUIRE(ctx, CN_ERR_ARG, "cn_context_make_current: null context");
+    CN_CUDA(cudaSetDevice(ctx->device));
     return CN_OK;
 }
 
@@ -349,6 +424,9 @@ extern "C" int cn_sym_alloc(cn_context *ctx, size_t bytes, void **ptr)
     }
     cn_comm_state *c = ctx->comm;
     CN_REQUIRE(c->nranks - 1 <= CN_MAX_PEERS, CN_ERR_UNSUPPORTED, "cn_sym_alloc: at most %d ranks", CN_MAX_PEERS + 1);
+    CN_REQUIRE(!c->in_process, CN_ERR_UNSUPPORTED,
+               "cn_sym_alloc: symmetric buffers are CUDA-IPC mappings between processes; a communicator made by cn_comm_init_all gathers with NCCL "
+               "(pass an ordinary buffer)");
     int st;
     if (!c->flags) {   // first use: the flag words, zeroed, and the device table of their peer addresses
         // Everything is built in locals and published (c->flags, c->d_peer_flags) only after every step, the closing

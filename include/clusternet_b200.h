@@ -245,6 +245,20 @@ int cn_seed_advance(cn_context *ctx, uint64_t *d_seed, void *stream);
  * ------------------------------------------------------------------------------------------- */
 int cn_comm_get_unique_id(void *id128);
 int cn_comm_init_rank(cn_context *ctx, const void *id128, int rank, int nranks);
+/* Single-process form of the bootstrap (several GPUs driven from one process): the n contexts, each on its own device,
+ * become ranks 0 .. n-1 of one communicator (ncclCommInitAll).  Either every rank is then driven by its own host thread
+ * (each thread makes its context's device current once: cn_context_make_current), and every entry point works as with
+ * one process per GPU; or one thread drives all ranks and brackets the per-rank calls of one collective with
+ * cn_group_start / cn_group_end (making each context current before its call) - that form covers the entry points that
+ * end in a single collective (cn_bcast_f32, cn_allgather_*, cn_allreduce_sum_f32, cn_dotmpi_f32 / cn_tdotmpi_f32 with
+ * exchange = 0, cn_dottmpi_f32), not the 8-bit exchanges, which launch kernels after their gather.  Symmetric buffers
+ * (cn_sym_alloc, CN_BATCH_SHARDED_UPLOAD) need one process per GPU.  The reference's own bootstrap is one process per
+ * GPU (source/clusterNet.cpp:148-183); its single-process "PCIe" mode (source/clusterNet.cpp:1137-1370) keeps arrays of
+ * per-device matrices instead. */
+int cn_comm_init_all(cn_context **ctxs, int n);
+int cn_group_start(void);
+int cn_group_end(void);
+int cn_context_make_current(const cn_context *ctx);
 /* Host-side wait with a limit, for loops in which a peer may have died: returns CN_OK when everything queued on
  * `stream` has finished; on an asynchronous NCCL error (CN_ERR_NCCL) or after timeout_ms with the stream still busy
  * (CN_ERR_TIMEOUT) it aborts the communicator so that the collectives in flight end; afterwards every collective call

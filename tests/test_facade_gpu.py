@@ -71,3 +71,15 @@ def test_reference_style_program_one_process_per_gpu(built_lib, tmp_path, progra
     outs = _run_ranks(exe, tmp_path, min(n, 4))
     report = "\n".join(f"[rank {r}: exit {code}] {out[-1500:]}" for r, (code, out) in enumerate(outs))
     assert all(code == 0 and "All tests passed" in out for code, out in outs), report
+
+
+def test_several_gpus_in_one_process(built_lib, tmp_path):
+    """cn_comm_init_all: ranks as contexts of one process, driven by one thread each and by a single thread with
+    cn_group_start / cn_group_end (tests/initall_test.cu)."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    exe = _build(tmp_path, "initall_test")
+    r = subprocess.run([exe, os.path.join(ROOT, "tests", "golden", "codebook_126.f32")], capture_output=True, text=True, timeout=300,
+                       env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    assert r.returncode == 0 and "All tests passed" in r.stdout, r.stdout[-3000:] + r.stderr[-2000:]
