@@ -641,6 +641,8 @@ def main():
     # ---- timed region 2: end to end from host memory through the C ABI (see the module docstring)
     use_rm = coded is None
     bflags = _lib.BATCH_SHARDED_UPLOAD | (_lib.BATCH_NO_COL_MAJOR if use_rm else 0)
+    if os.environ.get("CN_BENCH_PUSH_BY_KERNEL") == "1":
+        bflags |= _lib.BATCH_PUSH_BY_KERNEL
     bh = ctypes.c_void_p()
     cn.check(lib.cn_batch_create_ex(ctx.h, h_set.data_ptr(), h_lab.data_ptr(), 2 * M, K1, 1, M, 0, bflags, ctypes.byref(bh)))
     px, py, pn = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_int64()
@@ -715,13 +717,29 @@ def main():
             barrier()
             d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             d0.record()
+            h0 = time.perf_counter()
             for _ in range(10):
                 e2e_step(up, down)
+            host_ms = (time.perf_counter() - h0) * 100.0          # time the host needs to ISSUE one step (no synchronisation)
             if rank == 0:
                 torch.cuda.current_stream().wait_event(ev_drained)
             d1.record()
             barrier()
             e2e_diag[name] = max_over_ranks(d0.elapsed_time(d1)) / 10
+            e2e_diag[name + "_host_issue"] = max_over_ranks(host_ms)
+        # phases of the sharded upload on the copy stream (max over ranks, mean of 6 steps)
+        if world > 1:
+            ph = (ctypes.c_float * 4)()
+            cn.check(lib.cn_batch_profile(bh, 1, ph))
+            acc4 = np.zeros(4)
+            for _ in range(7):
+                e2e_step(True, True)
+                cn.check(lib.cn_batch_profile(bh, 1, ph))
+                acc4 += np.array(list(ph))
+            cn.check(lib.cn_batch_profile(bh, 0, ph))
+            t4 = torch.tensor(acc4 / 7, dtype=torch.float64, device="cuda")
+            dist.all_reduce(t4, op=dist.ReduceOp.MAX)
+            e2e_diag["upload_phases_ms(wait_free,h2d,push,wait_arrived)"] = [round(float(v), 4) for v in t4.tolist()]
         e2e_step(True, True)          # a last full step, so that the host result and the record of its batch agree again
         if rank == 0:
             torch.cuda.current_stream().wait_event(ev_drained)

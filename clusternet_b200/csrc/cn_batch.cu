@@ -45,10 +45,38 @@ struct cn_batch {
     int G = 1, rank = 0, slot = 0;
     unsigned int epoch = 0;
     float *peer_rm[2][8] = {};                // peer addresses of rm[0], rm[1]
+    // optional timing of the copy stream's phases (cn_batch_profile): start, after the "buffer free" exchange, after the
+    // host-to-device copy, after the push to the peers, after the "arrived" exchange
+    bool profile = false;
+    cudaEvent_t e_prof[5] = {};
     float *dc_X = nullptr, *dc_y = nullptr;   // device, current batch, column-major
     cudaStream_t s_X = nullptr, s_y = nullptr;
     cudaEvent_t e_X = nullptr, e_y = nullptr, e_consumed = nullptr;
 };
+
+// Sharded upload: this rank's block of the batch, already in its own buffer, goes to the same place in every peer's
+// buffer with 16-byte stores to the peers' mapped memory (a warp writes 512 contiguous bytes per destination): one
+// launch instead of one copy call per peer, chosen with CN_BATCH_PUSH_BY_KERNEL.  The default is the copy engines, which
+// need no SM: beside a product whose CTAs fill the register files this kernel only runs in the gaps between launches.
+// Plain stores, no multicast.
+struct PushParams {
+    float *dst[8];
+    int ndst;
+};
+__global__ void __launch_bounds__(512)
+cn_push_block_kernel(const float *__restrict__ src, int64_t n, const PushParams pp)
+{
+    const int64_t n4 = n >> 2, stride = (int64_t)gridDim.x * blockDim.x;
+    const float4 *s4 = reinterpret_cast<const float4 *>(src);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const float4 v = s4[i];
+#pragma unroll 1
+        for (int d = 0; d < pp.ndst; ++d) reinterpret_cast<float4 *>(pp.dst[d])[i] = v;
+    }
+    if (blockIdx.x == 0)
+        for (int64_t i = (n4 << 2) + threadIdx.x; i < n; i += blockDim.x)
+            for (int d = 0; d < pp.ndst; ++d) pp.dst[d][i] = src[i];
+}
 
 static int64_t rows_of_batch(const cn_batch *b, int64_t idx)
 {
@@ -77,6 +105,7 @@ extern "C" int cn_batch_destroy(cn_batch *b)
     if (b->e_X) cudaEventDestroy(b->e_X);
     if (b->e_y) cudaEventDestroy(b->e_y);
     if (b->e_consumed) cudaEventDestroy(b->e_consumed);
+    for (cudaEvent_t e : b->e_prof) if (e) cudaEventDestroy(e);
     delete b;
     return CN_OK;
 }
@@ -91,7 +120,7 @@ extern "C" int cn_batch_create_ex(cn_context *ctx, const float *h_X, const float
                                   int64_t batch_size, int skip_last_batch, int flags, cn_batch **out)
 {
     CN_REQUIRE(ctx && h_X && h_y && out, CN_ERR_ARG, "cn_batch_create: null argument");
-    CN_REQUIRE((flags & ~(CN_BATCH_KEEP_ROW_MAJOR | CN_BATCH_NO_COL_MAJOR | CN_BATCH_SHARDED_UPLOAD)) == 0, CN_ERR_ARG,
+    CN_REQUIRE((flags & ~(CN_BATCH_KEEP_ROW_MAJOR | CN_BATCH_NO_COL_MAJOR | CN_BATCH_SHARDED_UPLOAD | CN_BATCH_PUSH_BY_KERNEL)) == 0, CN_ERR_ARG,
                "cn_batch_create_ex: unknown flag bits 0x%x", flags);
     if (flags & CN_BATCH_NO_COL_MAJOR) flags |= CN_BATCH_KEEP_ROW_MAJOR;
     const int G = cn_comm_size(ctx);
@@ -213,6 +242,25 @@ extern "C" int cn_batch_current_row_major(const cn_batch *b, float **d_X_row_maj
     return CN_OK;
 }
 
+// Timing of the last sharded upload's phases on the copy stream, in milliseconds: [0] wait for the peers' "buffer free"
+// flags, [1] host-to-device copy of the own block, [2] push to the peers, [3] wait for the peers' "arrived" flags.
+// enable != 0 switches the recording on for the following copies; the call then returns the last recorded copy (zeros
+// when there is none yet) after waiting for it.
+extern "C" int cn_batch_profile(cn_batch *b, int enable, float *ms4)
+{
+    CN_REQUIRE(b, CN_ERR_ARG, "cn_batch_profile: null handle");
+    if (ms4) ms4[0] = ms4[1] = ms4[2] = ms4[3] = 0.0f;
+    if (b->profile && b->copy_pending && (b->flags & CN_BATCH_SHARDED_UPLOAD) && ms4 && b->epoch > 0) {
+        if (cudaEventSynchronize(b->e_prof[4]) == cudaSuccess)
+            for (int i = 0; i < 4; ++i) cudaEventElapsedTime(&ms4[i], b->e_prof[i], b->e_prof[i + 1]);
+        cudaGetLastError();
+    }
+    if (enable && !b->e_prof[0])
+        for (cudaEvent_t &e : b->e_prof) CN_CUDA(cudaEventCreate(&e));
+    b->profile = enable != 0;
+    return CN_OK;
+}
+
 extern "C" int cn_batch_copy_next_async(cn_batch *b)
 {
     CN_REQUIRE(b, CN_ERR_ARG, "cn_batch_copy_next_async: null handle");
@@ -245,14 +293,31 @@ extern "C" int cn_batch_copy_next_async(cn_batch *b)
         //     each rank says so only after its own e_consumed (waited for above); (2) own block over this rank's PCIe
         //     link; (3) the block into every peer's buffer over NVLink; (4) "my block has arrived everywhere"
         const unsigned int epoch = ++b->epoch;
+        if (b->profile) CN_CUDA(cudaEventRecord(b->e_prof[0], b->s_X));
         int st = cn_comm_flag_barrier(b->ctx, b->slot, epoch, b->s_X);
         if (st != CN_OK) return st;
+        if (b->profile) CN_CUDA(cudaEventRecord(b->e_prof[1], b->s_X));
         if (bytes_X) CN_CUDA(cudaMemcpyAsync(b->dn_X + off_X, src_X + off_X, bytes_X, cudaMemcpyHostToDevice, b->s_X));
-        for (int p = 1; p < b->G && bytes_X; ++p) {
-            const int peer = (b->rank + p) % b->G;   // staggered so that the ranks do not all write to the same GPU at once
-            CN_CUDA(cudaMemcpyAsync(b->peer_rm[b->fill][peer] + off_X, b->dn_X + off_X, bytes_X, cudaMemcpyDeviceToDevice, b->s_X));
+        if (b->profile) CN_CUDA(cudaEventRecord(b->e_prof[2], b->s_X));
+        if (bytes_X) {
+            const bool aligned = (off_X % 4 == 0) && ((uintptr_t)b->dn_X % 16 == 0);   // 16-byte stores need it; buffers are 256-byte aligned
+            if (aligned && (b->flags & CN_BATCH_PUSH_BY_KERNEL)) {
+                PushParams pp;
+                pp.ndst = 0;
+                for (int p = 1; p < b->G; ++p) pp.dst[pp.ndst++] = b->peer_rm[b->fill][(b->rank + p) % b->G] + off_X;   // staggered by rank
+                cn_push_block_kernel<<<32, 512, 0, b->s_X>>>(b->dn_X + off_X, (int64_t)(bytes_X / sizeof(float)), pp);
+                CN_CUDA(cudaGetLastError());
+                cn_count_launch();
+            } else {
+                for (int p = 1; p < b->G; ++p) {
+                    const int peer = (b->rank + p) % b->G;
+                    CN_CUDA(cudaMemcpyAsync(b->peer_rm[b->fill][peer] + off_X, b->dn_X + off_X, bytes_X, cudaMemcpyDeviceToDevice, b->s_X));
+                }
+            }
         }
+        if (b->profile) CN_CUDA(cudaEventRecord(b->e_prof[3], b->s_X));
         if ((st = cn_comm_flag_barrier(b->ctx, b->slot + 1, epoch, b->s_X)) != CN_OK) return st;
+        if (b->profile) CN_CUDA(cudaEventRecord(b->e_prof[4], b->s_X));
     } else {
         CN_CUDA(cudaMemcpyAsync(b->dn_X, src_X, (size_t)r * b->cols_X * sizeof(float), cudaMemcpyHostToDevice, b->s_X));
     }

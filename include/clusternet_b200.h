@@ -413,14 +413,22 @@ int cn_batch_create(cn_context *ctx, const float *h_X, const float *h_y, int64_t
  *       source/batchAllocator.cpp:411-440).  Rank r uploads only its block of floor(batch/G) rows (last rank: plus the
  *       remainder) over its own PCIe link and writes that block into every peer's buffer over NVLink; two bounded
  *       cross-GPU flag exchanges on the copy stream order the writes (a peer that never takes part surfaces as
- *       CN_ERR_TIMEOUT from cn_gemm_check_status).  Ignored with one rank. */
+ *       CN_ERR_TIMEOUT from cn_gemm_check_status).  Ignored with one rank.
+ *   CN_BATCH_PUSH_BY_KERNEL  with CN_BATCH_SHARDED_UPLOAD: the block goes to the peers through one kernel's stores
+ *       instead of one copy-engine transfer per peer (fewer host calls per step; needs SM time beside the product). */
 #define CN_BATCH_KEEP_ROW_MAJOR 1
 #define CN_BATCH_NO_COL_MAJOR 2
 #define CN_BATCH_SHARDED_UPLOAD 4
+#define CN_BATCH_PUSH_BY_KERNEL 8
 int cn_batch_create_ex(cn_context *ctx, const float *h_X, const float *h_y, int64_t rows, int64_t cols_X, int64_t cols_y,
                        int64_t batch_size, int skip_last_batch, int flags, cn_batch **out);
 /* Row-major device copy (batch_rows x cols_X, leading dimension cols_X) of the current batch; needs CN_BATCH_KEEP_ROW_MAJOR. */
 int cn_batch_current_row_major(const cn_batch *b, float **d_X_row_major, int64_t *batch_rows);
+/* Measurement aid for the sharded upload (takes the place of the reference's tick/tock around its batch copies):
+ * enable != 0 makes the following cn_batch_copy_next_async calls record CUDA events on the copy stream; ms4 receives the
+ * phases of the last recorded copy in milliseconds: waiting for the peers' "buffer free" flags, the host-to-device copy of
+ * the own block, the push to the peers, waiting for the peers' "arrived" flags. */
+int cn_batch_profile(cn_batch *b, int enable, float *ms4);
 int cn_batch_destroy(cn_batch *b);
 int64_t cn_batch_total_batches(const cn_batch *b);
 /* The batch that is current now (after cn_batch_create: the first batch, as BatchAllocator::init leaves it). */
