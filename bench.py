@@ -643,6 +643,8 @@ def main():
     bflags = _lib.BATCH_SHARDED_UPLOAD | (_lib.BATCH_NO_COL_MAJOR if use_rm else 0)
     if os.environ.get("CN_BENCH_PUSH_BY_KERNEL") == "1":
         bflags |= _lib.BATCH_PUSH_BY_KERNEL
+    if world > 1 and os.environ.get("CN_BENCH_LOOKAHEAD", "1") == "1":
+        bflags |= _lib.BATCH_LOOKAHEAD       # two uploads in flight: one upload's chain of waits may outlast a short step
     bh = ctypes.c_void_p()
     cn.check(lib.cn_batch_create_ex(ctx.h, h_set.data_ptr(), h_lab.data_ptr(), 2 * M, K1, 1, M, 0, bflags, ctypes.byref(bh)))
     px, py, pn = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_int64()

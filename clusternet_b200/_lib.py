@@ -17,7 +17,7 @@ c_uint64 = ctypes.c_uint64
 CN_OK, CN_ERR_ARG, CN_ERR_SHAPE, CN_ERR_CUDA, CN_ERR_NCCL, CN_ERR_TIMEOUT, CN_ERR_UNSUPPORTED, CN_ERR_NOMEM = range(8)
 GEMM_3XTF32, GEMM_TF32, GEMM_FP32_SIMT = 0, 1, 2
 ACT_LINEAR, ACT_RELU, ACT_LOGISTIC, ACT_DOUBLE_RELU = 0, 1, 2, 3
-BATCH_KEEP_ROW_MAJOR, BATCH_NO_COL_MAJOR, BATCH_SHARDED_UPLOAD, BATCH_PUSH_BY_KERNEL = 1, 2, 4, 8
+BATCH_KEEP_ROW_MAJOR, BATCH_NO_COL_MAJOR, BATCH_SHARDED_UPLOAD, BATCH_PUSH_BY_KERNEL, BATCH_LOOKAHEAD = 1, 2, 4, 8, 16
 
 
 class Coded(ctypes.Structure):

@@ -35,23 +35,31 @@ struct cn_batch {
     bool copy_pending = false;
     bool direct = false;         // the data set itself is pinned: copy from it, no staging memcpy
     float *p_X = nullptr, *p_y = nullptr;     // pinned staging
-    float *dn_X = nullptr, *dn_y = nullptr;   // device, next batch, row-major
+    float *dn_y = nullptr;                    // device, next batch's labels, row-major
     // options (cn_batch_create_ex)
     int flags = 0;
-    float *rm[2] = {nullptr, nullptr};        // row-major X buffers that alternate (dn_X points at the one being filled)
-    bool rm_sym = false;                      // rm[] came from cn_sym_alloc
-    int fill = 0;                             // index of the buffer the next copy goes to
+    // Row-major X buffers form a ring: one (plain: transposed into dc_X at the swap), two (the current batch stays valid
+    // while the next one is copied) or three (CN_BATCH_LOOKAHEAD: two copies in flight).  `fill` is where the next copy
+    // goes, `ready` what the next swap takes, `in_flight` how many copies lie between them.
+    int nb = 1, depth = 1;
+    float *xb[3] = {nullptr, nullptr, nullptr};
+    bool xb_sym = false;                      // xb[] came from cn_sym_alloc
+    float *peer_xb[3][8] = {};                // peer addresses of xb[i]
+    cudaEvent_t e_Xb[3] = {};                 // "buffer i holds its batch"
+    int64_t rows_in[3] = {0, 0, 0}, idx_in[3] = {-1, -1, -1};
+    int fill = 0, ready = 0, in_flight = 0;
+    int staged_from = -1;                     // the buffer whose copy last read the staging memory
+    int64_t x_next_idx = 0;                   // batch number of the next X copy to start
     float *cur_rm = nullptr;                  // row-major copy of the current batch
     int G = 1, rank = 0, slot = 0;
     unsigned int epoch = 0;
-    float *peer_rm[2][8] = {};                // peer addresses of rm[0], rm[1]
     // optional timing of the copy stream's phases (cn_batch_profile): start, after the "buffer free" exchange, after the
     // host-to-device copy, after the push to the peers, after the "arrived" exchange
     bool profile = false;
     cudaEvent_t e_prof[5] = {};
     float *dc_X = nullptr, *dc_y = nullptr;   // device, current batch, column-major
     cudaStream_t s_X = nullptr, s_y = nullptr;
-    cudaEvent_t e_X = nullptr, e_y = nullptr, e_consumed = nullptr;
+    cudaEvent_t e_y = nullptr, e_consumed = nullptr;
 };
 
 // Sharded upload: this rank's block of the batch, already in its own buffer, goes to the same place in every peer's
@@ -91,18 +99,14 @@ extern "C" int cn_batch_destroy(cn_batch *b)
     if (b->s_X) cudaStreamSynchronize(b->s_X);
     if (b->s_y) cudaStreamSynchronize(b->s_y);
     cudaFreeHost(b->p_X); cudaFreeHost(b->p_y);
-    if (b->rm[0] || b->rm[1]) {
-        for (int i = 0; i < 2; ++i) {
-            if (!b->rm[i]) continue;
-            if (b->rm_sym) cn_sym_free(b->ctx, b->rm[i]); else cudaFree(b->rm[i]);
-        }
-    } else {
-        cudaFree(b->dn_X);
+    for (int i = 0; i < 3; ++i) {
+        if (!b->xb[i]) continue;
+        if (b->xb_sym) cn_sym_free(b->ctx, b->xb[i]); else cudaFree(b->xb[i]);
     }
     cudaFree(b->dn_y); cudaFree(b->dc_X); cudaFree(b->dc_y);
     if (b->s_X) cudaStreamDestroy(b->s_X);
     if (b->s_y) cudaStreamDestroy(b->s_y);
-    if (b->e_X) cudaEventDestroy(b->e_X);
+    for (cudaEvent_t e : b->e_Xb) if (e) cudaEventDestroy(e);
     if (b->e_y) cudaEventDestroy(b->e_y);
     if (b->e_consumed) cudaEventDestroy(b->e_consumed);
     for (cudaEvent_t e : b->e_prof) if (e) cudaEventDestroy(e);
@@ -120,9 +124,9 @@ extern "C" int cn_batch_create_ex(cn_context *ctx, const float *h_X, const float
                                   int64_t batch_size, int skip_last_batch, int flags, cn_batch **out)
 {
     CN_REQUIRE(ctx && h_X && h_y && out, CN_ERR_ARG, "cn_batch_create: null argument");
-    CN_REQUIRE((flags & ~(CN_BATCH_KEEP_ROW_MAJOR | CN_BATCH_NO_COL_MAJOR | CN_BATCH_SHARDED_UPLOAD | CN_BATCH_PUSH_BY_KERNEL)) == 0, CN_ERR_ARG,
-               "cn_batch_create_ex: unknown flag bits 0x%x", flags);
-    if (flags & CN_BATCH_NO_COL_MAJOR) flags |= CN_BATCH_KEEP_ROW_MAJOR;
+    CN_REQUIRE((flags & ~(CN_BATCH_KEEP_ROW_MAJOR | CN_BATCH_NO_COL_MAJOR | CN_BATCH_SHARDED_UPLOAD | CN_BATCH_PUSH_BY_KERNEL |
+                          CN_BATCH_LOOKAHEAD)) == 0, CN_ERR_ARG, "cn_batch_create_ex: unknown flag bits 0x%x", flags);
+    if (flags & (CN_BATCH_NO_COL_MAJOR | CN_BATCH_LOOKAHEAD)) flags |= CN_BATCH_KEEP_ROW_MAJOR;
     const int G = cn_comm_size(ctx);
     if (G == 1) flags &= ~CN_BATCH_SHARDED_UPLOAD;   // nothing to share the upload with
     if (flags & CN_BATCH_SHARDED_UPLOAD) flags |= CN_BATCH_KEEP_ROW_MAJOR;
@@ -140,6 +144,8 @@ extern "C" int cn_batch_create_ex(cn_context *ctx, const float *h_X, const float
     b->G = G;
     b->rank = cn_comm_rank(ctx);
     b->total_batches = (rows + batch_size - 1) / batch_size;
+    b->nb = (flags & CN_BATCH_LOOKAHEAD) ? 3 : (flags & CN_BATCH_KEEP_ROW_MAJOR) ? 2 : 1;
+    b->depth = (flags & CN_BATCH_LOOKAHEAD) ? 2 : 1;
     const size_t bx = (size_t)batch_size * cols_X * sizeof(float), by = (size_t)batch_size * cols_y * sizeof(float);
     cudaError_t e;
     // The copy streams get the highest priority: their work is a few copies and, with the sharded upload, two one-warp flag
@@ -156,45 +162,44 @@ extern "C" int cn_batch_create_ex(cn_context *ctx, const float *h_X, const float
     }
     if ((!b->direct && (e = cudaHostAlloc(&b->p_X, bx, cudaHostAllocPortable)) != cudaSuccess) ||
         (!b->direct && (e = cudaHostAlloc(&b->p_y, by, cudaHostAllocPortable)) != cudaSuccess) ||
-        (!(flags & CN_BATCH_KEEP_ROW_MAJOR) && (e = cudaMalloc(&b->dn_X, bx)) != cudaSuccess) ||
         (e = cudaMalloc(&b->dn_y, by)) != cudaSuccess ||
         (!(flags & CN_BATCH_NO_COL_MAJOR) && (e = cudaMalloc(&b->dc_X, bx)) != cudaSuccess) ||
         (e = cudaMalloc(&b->dc_y, by)) != cudaSuccess ||
         (e = cudaStreamCreateWithPriority(&b->s_X, cudaStreamNonBlocking, prio_high)) != cudaSuccess ||
         (e = cudaStreamCreateWithPriority(&b->s_y, cudaStreamNonBlocking, prio_high)) != cudaSuccess ||
-        (e = cudaEventCreateWithFlags(&b->e_X, cudaEventDisableTiming)) != cudaSuccess ||
+        (e = cudaEventCreateWithFlags(&b->e_Xb[0], cudaEventDisableTiming)) != cudaSuccess ||
+        (e = cudaEventCreateWithFlags(&b->e_Xb[1], cudaEventDisableTiming)) != cudaSuccess ||
+        (e = cudaEventCreateWithFlags(&b->e_Xb[2], cudaEventDisableTiming)) != cudaSuccess ||
         (e = cudaEventCreateWithFlags(&b->e_y, cudaEventDisableTiming)) != cudaSuccess ||
         (e = cudaEventCreateWithFlags(&b->e_consumed, cudaEventDisableTiming)) != cudaSuccess) {
         cn_batch_destroy(b);
         return cn_cuda_fail(e, "cn_batch_create");
     }
-    if (flags & CN_BATCH_KEEP_ROW_MAJOR) {
-        for (int i = 0; i < 2; ++i) {
-            int st2;
-            if (flags & CN_BATCH_SHARDED_UPLOAD) {
-                void *p = nullptr;
-                st2 = cn_sym_alloc(ctx, bx, &p);   // collective: every rank creates its allocator at the same point
-                b->rm[i] = (float *)p;
-                b->rm_sym = true;
-                void *peers[8] = {};
-                if (st2 == CN_OK && !cn_comm_sym_peers(ctx, p, bx, peers)) {
-                    cn_set_error("cn_batch_create_ex: symmetric buffer not found");
-                    st2 = CN_ERR_CUDA;
-                }
-                for (int r = 0; r < G; ++r) b->peer_rm[i][r] = (float *)peers[r];
-            } else {
-                st2 = cudaMalloc(&b->rm[i], bx) == cudaSuccess ? CN_OK : cn_cuda_fail(cudaGetLastError(), "cn_batch_create_ex");
-            }
-            if (st2 != CN_OK) { cn_batch_destroy(b); return st2; }
-        }
-        b->dn_X = b->rm[0];
+    for (int i = 0; i < b->nb; ++i) {
+        int st2;
         if (flags & CN_BATCH_SHARDED_UPLOAD) {
-            int st2 = cn_comm_flag_slots(ctx, 2, &b->slot);
-            if (st2 != CN_OK) { cn_batch_destroy(b); return st2; }
+            void *p = nullptr;
+            st2 = cn_sym_alloc(ctx, bx, &p);   // collective: every rank creates its allocator at the same point
+            b->xb[i] = (float *)p;
+            b->xb_sym = true;
+            void *peers[8] = {};
+            if (st2 == CN_OK && !cn_comm_sym_peers(ctx, p, bx, peers)) {
+                cn_set_error("cn_batch_create_ex: symmetric buffer not found");
+                st2 = CN_ERR_CUDA;
+            }
+            for (int r = 0; r < G; ++r) b->peer_xb[i][r] = (float *)peers[r];
+        } else {
+            st2 = cudaMalloc(&b->xb[i], bx) == cudaSuccess ? CN_OK : cn_cuda_fail(cudaGetLastError(), "cn_batch_create_ex");
         }
+        if (st2 != CN_OK) { cn_batch_destroy(b); return st2; }
+    }
+    if (flags & CN_BATCH_SHARDED_UPLOAD) {
+        int st2 = cn_comm_flag_slots(ctx, 2, &b->slot);
+        if (st2 != CN_OK) { cn_batch_destroy(b); return st2; }
     }
     // first batch: staged, copied and transposed before returning, as BatchAllocator::init does
     b->next_batch = 0;
+    b->x_next_idx = 0;
     int st = cn_batch_copy_next_async(b);
     float *dx, *dy;
     int64_t r;
@@ -215,10 +220,31 @@ extern "C" int cn_batch_create_ex(cn_context *ctx, const float *h_X, const float
     return CN_OK;
 }
 
+// the batch that follows batch idx: counter and wrap-around exactly as replace_current_batch_with_next
+// (source/batchAllocator.cpp:1036-1052)
+static int64_t batch_after(const cn_batch *b, int64_t idx)
+{
+    int64_t n = idx + 1;
+    if ((n + 1) == b->total_batches && b->skip_last) n = 0;
+    if (n >= b->total_batches) n = 0;
+    return n;
+}
+
 extern "C" int cn_batch_set_skip_last(cn_batch *b, int skip)
 {
     CN_REQUIRE(b, CN_ERR_ARG, "cn_batch_set_skip_last: null handle");
     b->skip_last = skip ? 1 : 0;
+    // X copies already under way were chosen with the old setting: keep those that still lie on the new sequence, forget
+    // the rest (their buffers are simply filled again; the copy stream keeps the order)
+    int64_t expected = b->next_batch;
+    int kept = 0;
+    for (; kept < b->in_flight; ++kept) {
+        if (b->idx_in[(b->ready + kept) % b->nb] != expected) break;
+        expected = batch_after(b, expected);
+    }
+    b->in_flight = kept;
+    b->fill = (b->ready + kept) % b->nb;
+    b->x_next_idx = expected;
     return CN_OK;
 }
 
@@ -250,7 +276,7 @@ extern "C" int cn_batch_profile(cn_batch *b, int enable, float *ms4)
 {
     CN_REQUIRE(b, CN_ERR_ARG, "cn_batch_profile: null handle");
     if (ms4) ms4[0] = ms4[1] = ms4[2] = ms4[3] = 0.0f;
-    if (b->profile && b->copy_pending && (b->flags & CN_BATCH_SHARDED_UPLOAD) && ms4 && b->epoch > 0) {
+    if (b->profile && (b->flags & CN_BATCH_SHARDED_UPLOAD) && ms4 && b->epoch > 0) {
         if (cudaEventSynchronize(b->e_prof[4]) == cudaSuccess)
             for (int i = 0; i < 4; ++i) cudaEventElapsedTime(&ms4[i], b->e_prof[i], b->e_prof[i + 1]);
         cudaGetLastError();
@@ -261,11 +287,13 @@ extern "C" int cn_batch_profile(cn_batch *b, int enable, float *ms4)
     return CN_OK;
 }
 
-extern "C" int cn_batch_copy_next_async(cn_batch *b)
+// Start the copy of batch b->x_next_idx into the ring buffer b->fill.
+static int start_x_copy(cn_batch *b)
 {
-    CN_REQUIRE(b, CN_ERR_ARG, "cn_batch_copy_next_async: null handle");
-    const int64_t idx = b->next_batch, r = rows_of_batch(b, idx);
-    const float *src_X = b->h_X + (size_t)idx * b->batch * b->cols_X, *src_y = b->h_y + (size_t)idx * b->batch * b->cols_y;
+    const int64_t idx = b->x_next_idx, r = rows_of_batch(b, idx);
+    const int buf = b->fill;
+    float *dst = b->xb[buf];
+    const float *src_X = b->h_X + (size_t)idx * b->batch * b->cols_X;
     // rows of the batch this rank uploads itself: all of them, or its block of floor(r / G) rows (last rank: + remainder)
     int64_t row0 = 0, nrows = r;
     if (b->flags & CN_BATCH_SHARDED_UPLOAD) {
@@ -275,43 +303,39 @@ extern "C" int cn_batch_copy_next_async(cn_batch *b)
     }
     const size_t off_X = (size_t)row0 * b->cols_X, bytes_X = (size_t)nrows * b->cols_X * sizeof(float);
     if (!b->direct) {
-        // the staging buffers are free once the previous copy out of them has finished
-        if (b->copy_pending) {
-            CN_CUDA(cudaEventSynchronize(b->e_X));
-            CN_CUDA(cudaEventSynchronize(b->e_y));
-        }
+        // the staging buffer is free once the last copy out of it has finished
+        if (b->staged_from >= 0) CN_CUDA(cudaEventSynchronize(b->e_Xb[b->staged_from]));
         memcpy(b->p_X + off_X, src_X + off_X, bytes_X);
-        memcpy(b->p_y, src_y, (size_t)r * b->cols_y * sizeof(float));
         src_X = b->p_X;
-        src_y = b->p_y;
+        b->staged_from = buf;
     }
-    // do not overwrite the device "next" buffers while the last swap's transposes may still read them
+    // do not overwrite a buffer while the work that read it may still run: its last reader is the batch before the current
+    // one (or, with one buffer, the last swap's transpose), and e_consumed, recorded at the last swap, follows both
     CN_CUDA(cudaStreamWaitEvent(b->s_X, b->e_consumed, 0));
-    CN_CUDA(cudaStreamWaitEvent(b->s_y, b->e_consumed, 0));
     if (b->flags & CN_BATCH_SHARDED_UPLOAD) {
-        // (1) every peer's buffer of this parity must be free: its last reader was the batch before the current one, and
-        //     each rank says so only after its own e_consumed (waited for above); (2) own block over this rank's PCIe
-        //     link; (3) the block into every peer's buffer over NVLink; (4) "my block has arrived everywhere"
+        // (1) every peer's buffer of this index must be free, and each rank says so only after its own e_consumed (waited
+        //     for above); (2) own block over this rank's PCIe link; (3) the block into every peer's buffer over NVLink;
+        //     (4) "my block has arrived everywhere"
         const unsigned int epoch = ++b->epoch;
         if (b->profile) CN_CUDA(cudaEventRecord(b->e_prof[0], b->s_X));
         int st = cn_comm_flag_barrier(b->ctx, b->slot, epoch, b->s_X);
         if (st != CN_OK) return st;
         if (b->profile) CN_CUDA(cudaEventRecord(b->e_prof[1], b->s_X));
-        if (bytes_X) CN_CUDA(cudaMemcpyAsync(b->dn_X + off_X, src_X + off_X, bytes_X, cudaMemcpyHostToDevice, b->s_X));
+        if (bytes_X) CN_CUDA(cudaMemcpyAsync(dst + off_X, src_X + off_X, bytes_X, cudaMemcpyHostToDevice, b->s_X));
         if (b->profile) CN_CUDA(cudaEventRecord(b->e_prof[2], b->s_X));
         if (bytes_X) {
-            const bool aligned = (off_X % 4 == 0) && ((uintptr_t)b->dn_X % 16 == 0);   // 16-byte stores need it; buffers are 256-byte aligned
+            const bool aligned = (off_X % 4 == 0) && ((uintptr_t)dst % 16 == 0);   // 16-byte stores need it; buffers are 256-byte aligned
             if (aligned && (b->flags & CN_BATCH_PUSH_BY_KERNEL)) {
                 PushParams pp;
                 pp.ndst = 0;
-                for (int p = 1; p < b->G; ++p) pp.dst[pp.ndst++] = b->peer_rm[b->fill][(b->rank + p) % b->G] + off_X;   // staggered by rank
-                cn_push_block_kernel<<<32, 512, 0, b->s_X>>>(b->dn_X + off_X, (int64_t)(bytes_X / sizeof(float)), pp);
+                for (int p = 1; p < b->G; ++p) pp.dst[pp.ndst++] = b->peer_xb[buf][(b->rank + p) % b->G] + off_X;   // staggered by rank
+                cn_push_block_kernel<<<32, 512, 0, b->s_X>>>(dst + off_X, (int64_t)(bytes_X / sizeof(float)), pp);
                 CN_CUDA(cudaGetLastError());
                 cn_count_launch();
             } else {
                 for (int p = 1; p < b->G; ++p) {
                     const int peer = (b->rank + p) % b->G;
-                    CN_CUDA(cudaMemcpyAsync(b->peer_rm[b->fill][peer] + off_X, b->dn_X + off_X, bytes_X, cudaMemcpyDeviceToDevice, b->s_X));
+                    CN_CUDA(cudaMemcpyAsync(b->peer_xb[buf][peer] + off_X, dst + off_X, bytes_X, cudaMemcpyDeviceToDevice, b->s_X));
                 }
             }
         }
@@ -319,11 +343,36 @@ extern "C" int cn_batch_copy_next_async(cn_batch *b)
         if ((st = cn_comm_flag_barrier(b->ctx, b->slot + 1, epoch, b->s_X)) != CN_OK) return st;
         if (b->profile) CN_CUDA(cudaEventRecord(b->e_prof[4], b->s_X));
     } else {
-        CN_CUDA(cudaMemcpyAsync(b->dn_X, src_X, (size_t)r * b->cols_X * sizeof(float), cudaMemcpyHostToDevice, b->s_X));
+        CN_CUDA(cudaMemcpyAsync(dst, src_X, (size_t)r * b->cols_X * sizeof(float), cudaMemcpyHostToDevice, b->s_X));
     }
+    CN_CUDA(cudaEventRecord(b->e_Xb[buf], b->s_X));
+    b->rows_in[buf] = r;
+    b->idx_in[buf] = idx;
+    b->fill = (buf + 1) % b->nb;
+    b->in_flight += 1;
+    b->x_next_idx = batch_after(b, idx);
+    return CN_OK;
+}
+
+extern "C" int cn_batch_copy_next_async(cn_batch *b)
+{
+    CN_REQUIRE(b, CN_ERR_ARG, "cn_batch_copy_next_async: null handle");
+    // labels: always one batch ahead
+    const int64_t idx = b->next_batch, r = rows_of_batch(b, idx);
+    const float *src_y = b->h_y + (size_t)idx * b->batch * b->cols_y;
+    if (!b->direct) {
+        CN_CUDA(cudaEventSynchronize(b->e_y));   // the staging buffer is free once the last copy out of it has finished
+        memcpy(b->p_y, src_y, (size_t)r * b->cols_y * sizeof(float));
+        src_y = b->p_y;
+    }
+    CN_CUDA(cudaStreamWaitEvent(b->s_y, b->e_consumed, 0));
     CN_CUDA(cudaMemcpyAsync(b->dn_y, src_y, (size_t)r * b->cols_y * sizeof(float), cudaMemcpyHostToDevice, b->s_y));
-    CN_CUDA(cudaEventRecord(b->e_X, b->s_X));
     CN_CUDA(cudaEventRecord(b->e_y, b->s_y));
+    // X: one copy in flight, or two with CN_BATCH_LOOKAHEAD (the first call then starts two)
+    while (b->in_flight < b->depth) {
+        int st = start_x_copy(b);
+        if (st != CN_OK) return st;
+    }
     b->next_rows = r;
     b->copy_pending = true;
     return CN_OK;
@@ -332,27 +381,26 @@ extern "C" int cn_batch_copy_next_async(cn_batch *b)
 extern "C" int cn_batch_swap(cn_batch *b, void *stream, float **d_X, float **d_y, int64_t *batch_rows)
 {
     CN_REQUIRE(b, CN_ERR_ARG, "cn_batch_swap: null handle");
-    CN_REQUIRE(b->copy_pending, CN_ERR_ARG, "cn_batch_swap: no batch was copied (call cn_batch_copy_next_async first)");
+    CN_REQUIRE(b->copy_pending && b->in_flight > 0, CN_ERR_ARG, "cn_batch_swap: no batch was copied (call cn_batch_copy_next_async first)");
+    const int buf = b->ready;
+    CN_REQUIRE(b->idx_in[buf] == b->next_batch && b->rows_in[buf] == b->next_rows, CN_ERR_ARG,
+               "cn_batch_swap: the copied batch (%lld) is not the next one (%lld)", (long long)b->idx_in[buf], (long long)b->next_batch);
     cudaStream_t s = cn_stream(stream);
-    CN_CUDA(cudaStreamWaitEvent(s, b->e_X, 0));
+    CN_CUDA(cudaStreamWaitEvent(s, b->e_Xb[buf], 0));
     CN_CUDA(cudaStreamWaitEvent(s, b->e_y, 0));
     int st = CN_OK;
-    if (!(b->flags & CN_BATCH_NO_COL_MAJOR)) st = cn_to_col_major(b->ctx, b->dn_X, b->dc_X, b->next_rows, b->cols_X, stream);
+    if (!(b->flags & CN_BATCH_NO_COL_MAJOR)) st = cn_to_col_major(b->ctx, b->xb[buf], b->dc_X, b->next_rows, b->cols_X, stream);
     if (st == CN_OK) st = cn_to_col_major(b->ctx, b->dn_y, b->dc_y, b->next_rows, b->cols_y, stream);
     if (st != CN_OK) return st;
     // everything queued on the compute stream so far - the transposes above and the caller's work on the batch that was
     // current until now - precedes this event; the next copy waits for it before it overwrites a buffer
     CN_CUDA(cudaEventRecord(b->e_consumed, s));
     b->cur_rows = b->next_rows;
-    if (b->flags & CN_BATCH_KEEP_ROW_MAJOR) {   // the filled buffer becomes the current one, the other one is filled next
-        b->cur_rm = b->rm[b->fill];
-        b->fill ^= 1;
-        b->dn_X = b->rm[b->fill];
-    }
-    // counter and wrap-around exactly as replace_current_batch_with_next (source/batchAllocator.cpp:1036-1052)
-    b->next_batch += 1;
-    if ((b->next_batch + 1) == b->total_batches && b->skip_last) b->next_batch = 0;
-    if (b->next_batch >= b->total_batches) b->next_batch = 0;
+    if (b->flags & CN_BATCH_KEEP_ROW_MAJOR) b->cur_rm = b->xb[buf];   // stays valid until the next swap
+    b->ready = (buf + 1) % b->nb;
+    b->in_flight -= 1;
+    b->copy_pending = false;
+    b->next_batch = batch_after(b, b->next_batch);
     if (d_X) *d_X = b->dc_X;
     if (d_y) *d_y = b->dc_y;
     if (batch_rows) *batch_rows = b->cur_rows;

@@ -415,11 +415,16 @@ int cn_batch_create(cn_context *ctx, const float *h_X, const float *h_y, int64_t
  *       cross-GPU flag exchanges on the copy stream order the writes (a peer that never takes part surfaces as
  *       CN_ERR_TIMEOUT from cn_gemm_check_status).  Ignored with one rank.
  *   CN_BATCH_PUSH_BY_KERNEL  with CN_BATCH_SHARDED_UPLOAD: the block goes to the peers through one kernel's stores
- *       instead of one copy-engine transfer per peer (fewer host calls per step; needs SM time beside the product). */
+ *       instead of one copy-engine transfer per peer (fewer host calls per step; needs SM time beside the product).
+ *   CN_BATCH_LOOKAHEAD       two X copies in flight instead of one (three row-major buffers; implies
+ *       CN_BATCH_KEEP_ROW_MAJOR): cn_batch_copy_next_async also starts the copy of the batch AFTER the next one as soon as
+ *       its buffer is free, so a copy has two steps to finish in.  For steps shorter than one upload's latency (many
+ *       ranks, each waiting for every peer's block).  The order of the batches is unchanged. */
 #define CN_BATCH_KEEP_ROW_MAJOR 1
 #define CN_BATCH_NO_COL_MAJOR 2
 #define CN_BATCH_SHARDED_UPLOAD 4
 #define CN_BATCH_PUSH_BY_KERNEL 8
+#define CN_BATCH_LOOKAHEAD 16
 int cn_batch_create_ex(cn_context *ctx, const float *h_X, const float *h_y, int64_t rows, int64_t cols_X, int64_t cols_y,
                        int64_t batch_size, int skip_last_batch, int flags, cn_batch **out);
 /* Row-major device copy (batch_rows x cols_X, leading dimension cols_X) of the current batch; needs CN_BATCH_KEEP_ROW_MAJOR. */

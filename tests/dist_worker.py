@@ -191,7 +191,8 @@ def run_nccl():
     y = np.arange(rows, dtype=np.float32).reshape(rows, 1) + 0.5
     hX, hy = torch.from_numpy(X).pin_memory(), torch.from_numpy(y).pin_memory()
     for flags in (_lib.BATCH_SHARDED_UPLOAD, _lib.BATCH_SHARDED_UPLOAD | _lib.BATCH_NO_COL_MAJOR,
-                  _lib.BATCH_SHARDED_UPLOAD | _lib.BATCH_NO_COL_MAJOR | _lib.BATCH_PUSH_BY_KERNEL):
+                  _lib.BATCH_SHARDED_UPLOAD | _lib.BATCH_NO_COL_MAJOR | _lib.BATCH_PUSH_BY_KERNEL,
+                  _lib.BATCH_SHARDED_UPLOAD | _lib.BATCH_NO_COL_MAJOR | _lib.BATCH_LOOKAHEAD):
         bh = ctypes.c_void_p()
         cn.check(ctx.lib.cn_batch_create_ex(ctx.h, hX.data_ptr(), hy.data_ptr(), rows, cols_x, 1, B, 0, flags, ctypes.byref(bh)))
         ora = oracle.BatchOracle(rows, B, False)

@@ -90,7 +90,7 @@ def _batch_epochs(ctx, rows, cols_x, cols_y, B, skip_last=False, epochs=2, flags
         cn.check(ctx.lib.cn_batch_create_ex(ctx.h, hX.data_ptr(), hy.data_ptr(), rows, cols_x, cols_y, B, int(skip_last), flags, ctypes.byref(h)))
     else:
         cn.check(ctx.lib.cn_batch_create(ctx.h, hX.data_ptr(), hy.data_ptr(), rows, cols_x, cols_y, B, int(skip_last), ctypes.byref(h)))
-    keep_rm = bool(flags & (_lib.BATCH_KEEP_ROW_MAJOR | _lib.BATCH_NO_COL_MAJOR))
+    keep_rm = bool(flags & (_lib.BATCH_KEEP_ROW_MAJOR | _lib.BATCH_NO_COL_MAJOR | _lib.BATCH_LOOKAHEAD))
     prm, nrm = ctypes.c_void_p(), ctypes.c_int64()
     prev_rm = None
     ora = oracle.BatchOracle(rows, B, skip_last)
@@ -136,15 +136,49 @@ def test_batch_allocator_exact_multiple_and_skip_last(ctx):
     _batch_epochs(ctx, rows=1000, cols_x=5, cols_y=1, B=128, skip_last=True)
 
 
-@pytest.mark.parametrize("flags", [_lib.BATCH_KEEP_ROW_MAJOR, _lib.BATCH_NO_COL_MAJOR, _lib.BATCH_SHARDED_UPLOAD])
+@pytest.mark.parametrize("flags", [_lib.BATCH_KEEP_ROW_MAJOR, _lib.BATCH_NO_COL_MAJOR, _lib.BATCH_SHARDED_UPLOAD, _lib.BATCH_LOOKAHEAD,
+                                   _lib.BATCH_LOOKAHEAD | _lib.BATCH_NO_COL_MAJOR])
 @pytest.mark.parametrize("pinned", [False, True])
 def test_batch_allocator_options(ctx, flags, pinned):
     """cn_batch_create_ex: the row-major copy of the current batch stays valid (two buffers alternate), X is not
-    transposed when that is switched off, and the sharded upload is the plain one on a single rank."""
+    transposed when that is switched off, the sharded upload is the plain one on a single rank, and with two copies in
+    flight (three buffers) the batches still come in the reference's order - also when the short last batch is skipped
+    and when the data set holds no more batches than the ring has buffers."""
     _batch_epochs(ctx, rows=1000, cols_x=20, cols_y=1, B=128, flags=flags, pinned=pinned)
+    if flags & _lib.BATCH_LOOKAHEAD:
+        _batch_epochs(ctx, rows=1000, cols_x=6, cols_y=1, B=128, skip_last=True, flags=flags, pinned=pinned)
+        _batch_epochs(ctx, rows=200, cols_x=6, cols_y=1, B=128, flags=flags, pinned=pinned, epochs=4)      # 2 batches
+        _batch_epochs(ctx, rows=300, cols_x=6, cols_y=2, B=128, flags=flags, pinned=pinned, epochs=4)      # 3 batches
     h = ctypes.c_void_p()
     x = torch.zeros(256, 4)
     assert ctx.lib.cn_batch_create_ex(ctx.h, x.data_ptr(), x.data_ptr(), 256, 4, 4, 128, 0, 64, ctypes.byref(h)) == _lib.CN_ERR_ARG
+
+
+@pytest.mark.parametrize("flags", [0, _lib.BATCH_LOOKAHEAD])
+def test_skip_last_switched_while_copies_are_in_flight(ctx, flags):
+    """SKIP_LAST_BATCH is a public member the reference's users flip between epochs (source/batchAllocator.h); a copy that
+    was started under the old setting and no longer lies on the sequence is dropped, not delivered."""
+    rows, cols, B = 1000, 4, 128                       # 8 batches, the last one short
+    X = np.arange(rows * cols, dtype=np.float32).reshape(rows, cols)
+    y = np.arange(rows, dtype=np.float32).reshape(rows, 1)
+    hX, hy = torch.from_numpy(X).pin_memory(), torch.from_numpy(y).pin_memory()
+    h = ctypes.c_void_p()
+    cn.check(ctx.lib.cn_batch_create_ex(ctx.h, hX.data_ptr(), hy.data_ptr(), rows, cols, 1, B, 0, flags | _lib.BATCH_KEEP_ROW_MAJOR, ctypes.byref(h)))
+    px, py, n, prm = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_int64(), ctypes.c_void_p()
+    seen = []
+    for step in range(14):
+        cn.check(ctx.lib.cn_batch_copy_next_async(h))
+        if step == 5:      # current batch is number 5; with two copies in flight, 6 and 7 are under way and 7 must go
+            cn.check(ctx.lib.cn_batch_set_skip_last(h, 1))
+        cn.check(ctx.lib.cn_batch_swap(h, ctx.stream_ptr(), ctypes.byref(px), ctypes.byref(py), ctypes.byref(n)))
+        cn.check(ctx.lib.cn_batch_current_row_major(h, ctypes.byref(prm), ctypes.byref(n)))
+        torch.cuda.synchronize()
+        first = float(_copy_from_device_pointer(prm, cols)[0].item())
+        lab = float(_copy_from_device_pointer(py, 1)[0].item())
+        assert first == lab * cols                     # X and the labels belong to the same batch
+        seen.append(int(lab) // B)
+    assert seen == [1, 2, 3, 4, 5, 6, 0, 1, 2, 3, 4, 5, 6, 0]
+    ctx.lib.cn_batch_destroy(h)
 
 
 def test_row_major_batch_feeds_the_product_as_a_transposed_operand(ctx):
