@@ -244,6 +244,9 @@ def train_step_bench(ctx, cn, _lib, torch, dist, world, rank, steps=30):
     8-bit compressed gradient exchange (per-rank absmax scales gathered with the codes), RMSprop — the call sequence of the
     reference's Layer class (source/Layer.cpp:250-261,314-339,341-471) through the C ABI.  Returns ms per step."""
     lib, h, sp = ctx.lib, ctx.h, ctx.stream_ptr()
+    pushed = world > 1 and os.environ.get("CN_BENCH_PUSH_EXCHANGE", "1") == "1"
+    if world > 1:
+        cn.check(lib.cn_comm_set_push_exchange(h, 1 if pushed else 0))
     B, sizes, drops = 128, [784, 1200, 1200, 10], [0.2, 0.5, 0.5]
     X = ctx.randn(B, sizes[0], seed=100 + rank)
     y = torch.randint(0, 10, (B,), device="cuda").float()
@@ -283,8 +286,7 @@ def train_step_bench(ctx, cn, _lib, torch, dist, world, rank, steps=30):
         if l > 0:
             comm_stream.wait_event(ev_err[l])
         cs = ctypes.c_void_p(comm_stream.cuda_stream)
-        cn.check(lib.cn_grad_sync_8bit_multi(h, grad[l].data_ptr(), seg1[l], 1, 0.0, cs))
-        cn.check(lib.cn_rmsprop_update(h, rms_p[offs[l]:].data_ptr(), grad[l].data_ptr(), W[l].data_ptr(), 0.9, 0.006, numel[l], cs))
+        cn.check(lib.cn_grad_sync_8bit_rmsprop(h, grad[l].data_ptr(), seg1[l], 1, 0.0, rms_p[offs[l]:].data_ptr(), W[l].data_ptr(), 0.9, 0.006, cs))
 
     def one_step():
         sp = ctx.stream_ptr()                                                    # the capture stream while recording
@@ -369,6 +371,7 @@ def train_step_bench(ctx, cn, _lib, torch, dist, world, rank, steps=30):
     return {"workload": "config 4: MLP 784-1200-1200-10, batch 128 per GPU, 8-bit gradient exchange, RMSprop", "ms_per_step": ms,
             "ms_per_step_eager": ms_eager, "ms_per_step_cuda_graph": graph_ms,
             "samples_per_s": 128 * world / (ms * 1e-3), "launches_per_step": launches,
+            "gradient_exchange": ("codes stored into the peers' memory by one kernel" if pushed else "ncclAllGather") if world > 1 else "none (one rank)",
             "flops_per_step_per_gpu": 6.0 * 128 * (784 * 1200 + 1200 * 1200 + 1200 * 10)}
 
 

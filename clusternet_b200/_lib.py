@@ -121,6 +121,8 @@ _SIGNATURES = {
     "cn_rmsprop_update": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_int64, c_void_p]),
     "cn_grad_sync_8bit": (c_int, [c_void_p, c_void_p, c_int64, c_float, c_void_p]),
     "cn_grad_sync_8bit_multi": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
+    "cn_comm_set_push_exchange": (c_int, [c_void_p, c_int]),
+    "cn_grad_sync_8bit_rmsprop": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_float, c_float, c_void_p]),
     "cn_batch_create": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, ctypes.POINTER(c_void_p)]),
     "cn_batch_create_ex": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int, ctypes.POINTER(c_void_p)]),
     "cn_batch_current_row_major": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64)]),

@@ -90,6 +90,15 @@ struct cn_comm_state {
     unsigned int **d_peer_flags = nullptr;   // device copy of peer_flags
     unsigned int epoch = 0;
     int next_flag_slot = 2;   // slots 0 and 1 frame the fused gather; the batch allocators reserve theirs from here
+    // Pushed block exchange (cn_comm_push_area / cn_comm_push_blocks): one symmetric area of nranks blocks; every rank
+    // writes its block into the same place of every peer's area.  The epoch lives in device memory so that a recorded
+    // launch (CUDA graph) can be replayed.
+    uint8_t *xchg = nullptr;
+    size_t xchg_bytes = 0;
+    void *xchg_peer[8] = {};
+    int xchg_slot = -1;                  // two flag slots: "my area may be written", "my block has arrived"
+    unsigned int *d_xchg_state = nullptr;   // [0] epoch of the last finished exchange, [1] ticket
+    int push_exchange = 1;               // cn_comm_set_push_exchange
     bool aborted = false;   // cn_comm_sync gave up on a collective: only cn_comm_destroy is accepted from here on
     bool in_process = false;   // made by cn_comm_init_all: the peers are contexts of this process (no CUDA IPC between them)
 };
@@ -116,6 +125,7 @@ void cn_comm_state_free(cn_context *ctx)
     cudaDeviceSynchronize();
     for (auto &b : ctx->comm->sym) sym_release(ctx->comm, b);
     cudaFree(ctx->comm->d_peer_flags);
+    cudaFree(ctx->comm->d_xchg_state);
     if (ctx->comm->comm && !ctx->comm->aborted && g_nccl.CommDestroy) g_nccl.CommDestroy(ctx->comm->comm);
     cudaFree(ctx->comm->d_scales);
     delete ctx->comm;
@@ -708,6 +718,155 @@ int cn_comm_gather_blocks(cn_context *ctx, uint8_t *d_blocks, size_t block_bytes
     if (!c || c->nranks == 1) return CN_OK;
     CN_COMM_ALIVE(ctx);
     CN_NCCL(g_nccl.AllGather(d_blocks + (size_t)c->rank * block_bytes, d_blocks, block_bytes, ncclUint8, c->comm, cn_stream(stream)));
+    return CN_OK;
+}
+
+// ---- pushed block exchange: an all-gather of one block per rank without a library collective
+//
+// Every rank holds an area of nranks blocks in symmetric memory.  One kernel per exchange: (1) tell the peers "my area
+// may be written" (everything this rank queued before, the decode of the last exchange included, has finished) and wait
+// for theirs; (2) copy the own block to the same place in every peer's area with 16-byte stores over NVLink; (3) the CTA
+// that finishes last tells the peers "my block has arrived" and waits for theirs.  One NVLink hop instead of the nranks-1
+// steps of a ring, and no second launch.  Every wait is clock-bounded (status 10, reported by cn_gemm_check_status as
+// CN_ERR_TIMEOUT); a rank whose first wait ran out does not write into its peers.  The epoch is read from and advanced in
+// device memory, so the launch has the same arguments every time.
+struct XchgPeers {
+    uint8_t *dst[8];
+    int ndst;
+};
+
+__device__ __forceinline__ bool xchg_wait_flags(const unsigned int *local_flags, int slot, int nranks, int my_rank, unsigned int epoch,
+                                                unsigned int *status)
+{
+    // threads 0..nranks-1 each watch one peer's flag
+    bool ok = true;
+    const int r = threadIdx.x;
+    if (r < nranks && r != my_rank) {
+        const volatile unsigned int *f = local_flags + slot * nranks + r;
+        const long long t0 = clock64();
+        while ((int)(*f - epoch) < 0) {
+            if (clock64() - t0 > 6000000000LL) { atomicMax(status, 10u); ok = false; break; }
+            __nanosleep(100);
+        }
+        __threadfence_system();
+    }
+    return __syncthreads_and(ok);
+}
+
+__global__ void __launch_bounds__(512)
+cn_push_exchange_kernel(const uint8_t *__restrict__ src, size_t nbytes, const XchgPeers pp, unsigned int *const *peer_flags,
+                        const unsigned int *local_flags, int nranks, int my_rank, int slot, unsigned int *state, unsigned int *status)
+{
+    __shared__ int s_last;
+    const unsigned int epoch = *reinterpret_cast<volatile unsigned int *>(state) + 1u;   // advanced by the last CTA, after every CTA has read it
+    const int r = threadIdx.x;
+    if (blockIdx.x == 0 && r < nranks && r != my_rank) {
+        __threadfence_system();
+        *reinterpret_cast<volatile unsigned int *>(peer_flags[r] + slot * nranks + my_rank) = epoch;
+    }
+    const bool may_write = xchg_wait_flags(local_flags, slot, nranks, my_rank, epoch, status);
+    if (may_write) {
+        const size_t n16 = nbytes >> 4, stride = (size_t)gridDim.x * blockDim.x;
+        const uint4 *s16 = reinterpret_cast<const uint4 *>(src);
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) {
+            const uint4 v = s16[i];
+#pragma unroll 1
+            for (int d = 0; d < pp.ndst; ++d) reinterpret_cast<uint4 *>(pp.dst[d])[i] = v;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(state + 1, 1u) == gridDim.x - 1) ? 1 : 0;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence_system();
+    if (may_write && r < nranks && r != my_rank)
+        *reinterpret_cast<volatile unsigned int *>(peer_flags[r] + (slot + 1) * nranks + my_rank) = epoch;
+    if (may_write) xchg_wait_flags(local_flags, slot + 1, nranks, my_rank, epoch, status);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        state[1] = 0u;
+        state[0] = epoch;
+        __threadfence();
+    }
+}
+
+extern "C" int cn_comm_set_push_exchange(cn_context *ctx, int on)
+{
+    CN_REQUIRE(ctx && ctx->comm, CN_ERR_ARG, "cn_comm_set_push_exchange: no communicator");
+    ctx->comm->push_exchange = on ? 1 : 0;
+    return CN_OK;
+}
+
+// An area of nranks blocks of block_bytes (a multiple of 16) in symmetric memory, or *blocks = nullptr when this
+// communicator cannot push (one rank, all ranks in one process, switched off).  Collective: every rank calls it with the
+// same size at the same point; the area grows (rarely) by a collective reallocation.
+int cn_comm_push_area(cn_context *ctx, size_t block_bytes, void *stream, uint8_t **blocks)
+{
+    *blocks = nullptr;
+    cn_comm_state *c = ctx->comm;
+    if (!c || c->nranks == 1 || c->in_process || !c->push_exchange || c->nranks - 1 > CN_MAX_PEERS || (block_bytes & 15)) return CN_OK;
+    CN_COMM_ALIVE(ctx);
+    const size_t need = block_bytes * c->nranks;
+    if (need > c->xchg_bytes) {
+        // growing allocates and synchronises, which a stream that is being recorded cannot do: gather with the library
+        // then (every rank sees the same sizes, so every rank decides the same)
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(cn_stream(stream), &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+            cudaGetLastError();
+            return CN_OK;
+        }
+        int st;
+        if (c->xchg) {
+            if ((st = cn_sym_free(ctx, c->xchg)) != CN_OK) return st;
+            c->xchg = nullptr;
+            c->xchg_bytes = 0;
+        }
+        size_t bytes = need + need / 4;                    // head room, so that slightly larger tensors do not reallocate
+        bytes = (bytes + 65535) & ~(size_t)65535;
+        void *p = nullptr;
+        if ((st = cn_sym_alloc(ctx, bytes, &p)) != CN_OK) return st;
+        void *peers[8] = {};
+        if (!cn_comm_sym_peers(ctx, p, bytes, peers)) {
+            cn_set_error("cn_comm_push_area: symmetric buffer not found");
+            return CN_ERR_CUDA;
+        }
+        if (c->xchg_slot < 0 && (st = cn_comm_flag_slots(ctx, 2, &c->xchg_slot)) != CN_OK) return st;
+        if (!c->d_xchg_state) {
+            CN_CUDA(cudaMalloc(&c->d_xchg_state, 256));
+            CN_CUDA(cudaMemset(c->d_xchg_state, 0, 256));
+        }
+        for (int r = 0; r < c->nranks; ++r) c->xchg_peer[r] = peers[r];
+        c->xchg = (uint8_t *)p;
+        c->xchg_bytes = bytes;
+    }
+    *blocks = c->xchg;
+    return CN_OK;
+}
+
+// blocks: the area cn_comm_push_area returned for this block size, block [rank] filled; on return (in stream order) every
+// block is filled.
+int cn_comm_push_blocks(cn_context *ctx, uint8_t *blocks, size_t block_bytes, void *stream)
+{
+    cn_comm_state *c = ctx->comm;
+    CN_REQUIRE(c && blocks && blocks == c->xchg && block_bytes * c->nranks <= c->xchg_bytes && !(block_bytes & 15), CN_ERR_ARG,
+               "cn_comm_push_blocks: not the area of cn_comm_push_area");
+    CN_COMM_ALIVE(ctx);
+    unsigned int *d_status = nullptr;
+    int st = cn_status_block(ctx, &d_status);
+    if (st != CN_OK) return st;
+    XchgPeers pp;
+    pp.ndst = 0;
+    const size_t off = (size_t)c->rank * block_bytes;
+    for (int p = 1; p < c->nranks; ++p) pp.dst[pp.ndst++] = (uint8_t *)c->xchg_peer[(c->rank + p) % c->nranks] + off;   // staggered by rank
+    const size_t n16 = block_bytes >> 4;
+    int grid = (int)((n16 + 4 * 512 - 1) / (4 * 512));   // four 16-byte groups per thread and destination at least
+    if (grid < 1) grid = 1;
+    if (grid > 64) grid = 64;
+    cn_push_exchange_kernel<<<grid, 512, 0, cn_stream(stream)>>>(blocks + off, block_bytes, pp, c->d_peer_flags, c->flags, c->nranks, c->rank,
+                                                                 c->xchg_slot, c->d_xchg_state, d_status);
+    CN_CUDA(cudaGetLastError());
+    cn_count_launch();
     return CN_OK;
 }
 

@@ -115,15 +115,22 @@ __global__ void cn_nesterov_kernel(const float *__restrict__ grad, float *__rest
 
 // kRMSprop_with_weight_update: RMS = m*RMS + (1-m)*g^2 ; w -= lr * g / (sqrt(RMS) + 1e-8).  The reference divides with
 // fdividef and squares with powf(g, 2.0f); both are reproduced as written.
+__device__ __forceinline__ void rmsprop_step(float g, float &rms, float &w, float rms_mult, float rec, float lr)
+{
+    const float r = (rms_mult * rms) + (powf(g, 2.0f) * rec);
+    rms = r;
+    w -= lr * fdividef(g, sqrtf(r) + 1.0e-08f);
+}
+
 __global__ void cn_rmsprop_kernel(float *__restrict__ RMS, const float *__restrict__ grad, float *__restrict__ w, float rms_mult, float lr, int64_t n)
 {
     const float rec = 1.0f - rms_mult;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        const float g = grad[i];
-        const float r = (rms_mult * RMS[i]) + (powf(g, 2.0f) * rec);
+        float r = RMS[i], x = w[i];
+        rmsprop_step(grad[i], r, x, rms_mult, rec, lr);
         RMS[i] = r;
-        w[i] -= lr * fdividef(g, sqrtf(r) + 1.0e-08f);
+        w[i] = x;
     }
 }
 
@@ -164,9 +171,13 @@ struct SegParams {
     int64_t seg_end[CN_SYNC_MAX_SEGMENTS];
 };
 
+// UPDATE: the RMSprop step of cn_rmsprop_kernel on the summed gradient in the same pass (same arithmetic, one launch less).
+// Four elements per thread where the buffers allow 16-byte accesses (vec_ok) and the four lie in one segment.
+template <bool UPDATE>
 __global__ void __launch_bounds__(512)
 cn_decode_sum_multi_kernel(float *__restrict__ grad, const uint8_t *__restrict__ blocks, size_t block_bytes, size_t scales_off,
-                           const float *__restrict__ g_tbl, int64_t n, int nranks, int my_rank, const SegParams sp)
+                           const float *__restrict__ g_tbl, int64_t n, int nranks, int my_rank, const SegParams sp,
+                           float *__restrict__ RMS, float *__restrict__ w, float rms_mult, float lr, int vec_ok)
 {
     extern __shared__ float lut[];   // (segment, rank) x 256
     for (int e = threadIdx.x; e < sp.nseg * nranks * 256; e += blockDim.x) {
@@ -183,8 +194,9 @@ cn_decode_sum_multi_kernel(float *__restrict__ grad, const uint8_t *__restrict__
         lut[e] = v;
     }
     __syncthreads();
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const float rec = 1.0f - rms_mult;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x, tid0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    auto one = [&](int64_t i) {
         int seg = 0;
         while (seg + 1 < sp.nseg && i >= sp.seg_end[seg]) ++seg;
         const float *l = lut + (size_t)seg * nranks * 256;
@@ -192,7 +204,45 @@ cn_decode_sum_multi_kernel(float *__restrict__ grad, const uint8_t *__restrict__
         for (int r = 0; r < nranks; ++r)
             if (r != my_rank) g += l[(r << 8) + blocks[(size_t)r * block_bytes + i]];
         grad[i] = g;
+        if (UPDATE) {
+            float q = RMS[i], x = w[i];
+            rmsprop_step(g, q, x, rms_mult, rec, lr);
+            RMS[i] = q;
+            w[i] = x;
+        }
+    };
+    const int64_t n4 = vec_ok ? (n >> 2) : 0;
+    for (int64_t v = tid0; v < n4; v += stride) {
+        const int64_t i = v << 2;
+        int seg = 0;
+        while (seg + 1 < sp.nseg && i >= sp.seg_end[seg]) ++seg;
+        if (i + 3 >= sp.seg_end[seg] && seg + 1 < sp.nseg) {   // the four straddle a segment boundary
+            for (int k = 0; k < 4; ++k) one(i + k);
+            continue;
+        }
+        const float *l = lut + (size_t)seg * nranks * 256;
+        float4 g = reinterpret_cast<const float4 *>(grad)[v];
+        for (int r = 0; r < nranks; ++r) {
+            if (r == my_rank) continue;
+            const uint32_t c = *reinterpret_cast<const uint32_t *>(blocks + (size_t)r * block_bytes + i);
+            const float *lr_ = l + (r << 8);
+            g.x += lr_[c & 0xffu];
+            g.y += lr_[(c >> 8) & 0xffu];
+            g.z += lr_[(c >> 16) & 0xffu];
+            g.w += lr_[c >> 24];
+        }
+        reinterpret_cast<float4 *>(grad)[v] = g;
+        if (UPDATE) {
+            float4 q = reinterpret_cast<const float4 *>(RMS)[v], x = reinterpret_cast<const float4 *>(w)[v];
+            rmsprop_step(g.x, q.x, x.x, rms_mult, rec, lr);
+            rmsprop_step(g.y, q.y, x.y, rms_mult, rec, lr);
+            rmsprop_step(g.z, q.z, x.z, rms_mult, rec, lr);
+            rmsprop_step(g.w, q.w, x.w, rms_mult, rec, lr);
+            reinterpret_cast<float4 *>(RMS)[v] = q;
+            reinterpret_cast<float4 *>(w)[v] = x;
+        }
     }
+    for (int64_t i = (n4 << 2) + tid0; i < n; i += stride) one(i);
 }
 
 static int ew_grid(const cn_context *ctx, int64_t n)
@@ -340,12 +390,15 @@ extern "C" int cn_grad_sync_8bit(cn_context *ctx, float *d_grad, int64_t n, floa
 }
 
 int cn_comm_gather_blocks(cn_context *ctx, uint8_t *d_blocks, size_t block_bytes, void *stream);
+int cn_comm_push_area(cn_context *ctx, size_t block_bytes, void *stream, uint8_t **blocks);
+int cn_comm_push_blocks(cn_context *ctx, uint8_t *blocks, size_t block_bytes, void *stream);
 
 // Several tensors that lie back to back in one buffer (the gradients of all layers of a step), each coded with its own
 // scale exactly as cn_grad_sync_8bit would code it alone, but exchanged with ONE all-gather and summed in ONE pass.
-extern "C" int cn_grad_sync_8bit_multi(cn_context *ctx, float *d_grad, const int64_t *segment_sizes, int num_segments,
-                                       float fixed_precision, void *stream)
+static int grad_sync_multi_impl(cn_context *ctx, float *d_grad, const int64_t *segment_sizes, int num_segments, float fixed_precision,
+                                float *d_rms, float *d_w, float rms_multiplier, float learning_rate, void *stream)
 {
+    const bool update = d_rms != nullptr;
     CN_REQUIRE(ctx && segment_sizes && num_segments >= 1, CN_ERR_ARG, "cn_grad_sync_8bit_multi: bad argument");
     int rank = 0, G = 1;
     float *unused = nullptr;
@@ -355,8 +408,9 @@ extern "C" int cn_grad_sync_8bit_multi(cn_context *ctx, float *d_grad, const int
         CN_REQUIRE(segment_sizes[s] >= 0, CN_ERR_ARG, "cn_grad_sync_8bit_multi: negative segment size");
         n += segment_sizes[s];
     }
-    if (G == 1 || n == 0) return CN_OK;
+    if (n == 0) return CN_OK;
     CN_REQUIRE(d_grad, CN_ERR_ARG, "cn_grad_sync_8bit_multi: null buffer");
+    if (G == 1) return update ? cn_rmsprop_update(ctx, d_rms, d_grad, d_w, rms_multiplier, learning_rate, n, stream) : CN_OK;
     if (num_segments > CN_SYNC_MAX_SEGMENTS || (size_t)num_segments * G * 1024 > 48 * 1024) {
         // too many tables for one pass: segment by segment
         int64_t off = 0;
@@ -365,14 +419,22 @@ extern "C" int cn_grad_sync_8bit_multi(cn_context *ctx, float *d_grad, const int
             if (st != CN_OK) return st;
             off += segment_sizes[s];
         }
-        return CN_OK;
+        return update ? cn_rmsprop_update(ctx, d_rms, d_grad, d_w, rms_multiplier, learning_rate, n, stream) : CN_OK;
     }
     const size_t scales_off = ((size_t)n + 15) & ~(size_t)15;
     const size_t block_bytes = scales_off + (((size_t)num_segments * sizeof(float) + 15) & ~(size_t)15);
-    void *buf = nullptr;
-    int st = cn_gemm_scratch(ctx, CN_GEMM_SLOT_EXCHANGE, (size_t)G * block_bytes, &buf);
+    // the blocks travel by direct stores into the peers' memory where the communicator can do that (one process per
+    // GPU), else through the library's all-gather
+    uint8_t *blocks = nullptr;
+    int st = cn_comm_push_area(ctx, block_bytes, stream, &blocks);
     if (st != CN_OK) return st;
-    uint8_t *blocks = (uint8_t *)buf, *mine = blocks + (size_t)rank * block_bytes;
+    const bool pushed = blocks != nullptr;
+    if (!pushed) {
+        void *buf = nullptr;
+        if ((st = cn_gemm_scratch(ctx, CN_GEMM_SLOT_EXCHANGE, (size_t)G * block_bytes, &buf)) != CN_OK) return st;
+        blocks = (uint8_t *)buf;
+    }
+    uint8_t *mine = blocks + (size_t)rank * block_bytes;
     float *my_scales = reinterpret_cast<float *>(mine + scales_off);
     SegParams sp;
     sp.nseg = num_segments;
@@ -390,11 +452,37 @@ extern "C" int cn_grad_sync_8bit_multi(cn_context *ctx, float *d_grad, const int
         sp.seg_end[s] = off;
     }
     for (int s = num_segments; s < CN_SYNC_MAX_SEGMENTS; ++s) sp.seg_end[s] = off;
-    if ((st = cn_comm_gather_blocks(ctx, blocks, block_bytes, stream)) != CN_OK) return st;
-    int64_t nblocks = (n + 511) / 512, cap = (int64_t)ctx->sm_count * 4;
-    cn_decode_sum_multi_kernel<<<(unsigned)(nblocks < cap ? nblocks : cap), 512, (size_t)num_segments * G * 256 * sizeof(float), cn_stream(stream)>>>(
-        d_grad, blocks, block_bytes, scales_off, ctx->d_tbl, n, G, rank, sp);
+    st = pushed ? cn_comm_push_blocks(ctx, blocks, block_bytes, stream) : cn_comm_gather_blocks(ctx, blocks, block_bytes, stream);
+    if (st != CN_OK) return st;
+    const int vec_ok = ((uintptr_t)d_grad % 16 == 0) && ((uintptr_t)blocks % 16 == 0) &&
+                       (!update || ((uintptr_t)d_rms % 16 == 0 && (uintptr_t)d_w % 16 == 0));
+    const int64_t work = vec_ok ? (n + 3) / 4 : n;
+    int64_t nblocks = (work + 511) / 512, cap = (int64_t)ctx->sm_count * 4;
+    const unsigned grid = (unsigned)(nblocks < cap ? nblocks : cap);
+    const size_t smem = (size_t)num_segments * G * 256 * sizeof(float);
+    if (update)
+        cn_decode_sum_multi_kernel<true><<<grid, 512, smem, cn_stream(stream)>>>(d_grad, blocks, block_bytes, scales_off, ctx->d_tbl, n, G, rank, sp,
+                                                                                 d_rms, d_w, rms_multiplier, learning_rate, vec_ok);
+    else
+        cn_decode_sum_multi_kernel<false><<<grid, 512, smem, cn_stream(stream)>>>(d_grad, blocks, block_bytes, scales_off, ctx->d_tbl, n, G, rank, sp,
+                                                                                  nullptr, nullptr, 0.f, 0.f, vec_ok);
     CN_CUDA(cudaGetLastError());
     cn_count_launch();
     return CN_OK;
+}
+
+extern "C" int cn_grad_sync_8bit_multi(cn_context *ctx, float *d_grad, const int64_t *segment_sizes, int num_segments,
+                                       float fixed_precision, void *stream)
+{
+    return grad_sync_multi_impl(ctx, d_grad, segment_sizes, num_segments, fixed_precision, nullptr, nullptr, 0.f, 0.f, stream);
+}
+
+// cn_grad_sync_8bit_multi followed by cn_rmsprop_update over the same elements, with the update done in the pass that sums
+// the decoded gradients: the results (gradient, RMS state, weights) are those of the two calls bit for bit.
+extern "C" int cn_grad_sync_8bit_rmsprop(cn_context *ctx, float *d_grad, const int64_t *segment_sizes, int num_segments,
+                                         float fixed_precision, float *d_rms, float *d_w, float rms_multiplier, float learning_rate,
+                                         void *stream)
+{
+    CN_REQUIRE(d_rms && d_w, CN_ERR_ARG, "cn_grad_sync_8bit_rmsprop: null state or weight buffer");
+    return grad_sync_multi_impl(ctx, d_grad, segment_sizes, num_segments, fixed_precision, d_rms, d_w, rms_multiplier, learning_rate, stream);
 }

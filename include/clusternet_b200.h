@@ -389,6 +389,19 @@ int cn_grad_sync_8bit(cn_context *ctx, float *d_grad, int64_t n, float fixed_pre
  * pass per step instead of one per layer (the reference exchanges layer by layer, source/Layer.cpp:341-390). */
 int cn_grad_sync_8bit_multi(cn_context *ctx, float *d_grad, const int64_t *segment_sizes, int num_segments,
                             float fixed_precision, void *stream);
+/* cn_grad_sync_8bit_multi followed by cn_rmsprop_update(d_rms, d_grad, d_w, ...) over the same elements (the reference's
+ * wait_for_synchronization + weight_update pair, source/Layer.cpp:250-261,400-437), with the update done inside the pass
+ * that sums the decoded gradients: one launch and one trip of the gradient through memory less; gradient, RMS state
+ * and weights come out as from the two calls, bit for bit. */
+int cn_grad_sync_8bit_rmsprop(cn_context *ctx, float *d_grad, const int64_t *segment_sizes, int num_segments,
+                              float fixed_precision, float *d_rms, float *d_w, float rms_multiplier, float learning_rate,
+                              void *stream);
+/* How cn_grad_sync_8bit_multi moves its blocks.  on != 0 (the default with one process per GPU): every rank stores its
+ * block straight into every peer's memory (one kernel: "your area may be written" / 16-byte stores over NVLink / "my block
+ * has arrived", every wait bounded and reported by cn_gemm_check_status as CN_ERR_TIMEOUT) - one NVLink hop instead of
+ * the steps of a ring, and no library launch.  on == 0: ncclAllGather.  The results are identical bit for bit.  Call it
+ * on every rank alike.  The reference sends its codes with MPI_Isend / MPI_Recv, rank to rank (source/Layer.cpp:364-390). */
+int cn_comm_set_push_exchange(cn_context *ctx, int on);
 
 /* ---------------------------------------------------------------------------------------------
  * Batch allocator (dense path).  Replaces BatchAllocator::init / init_batch_buffer /

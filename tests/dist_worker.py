@@ -170,6 +170,63 @@ def run_nccl():
         o += sz
     torch.cuda.synchronize()
     assert torch.equal(gp, gs)
+    # ... and the blocks pushed into the peers' memory == the blocks gathered by NCCL, call after call with changing sizes
+    # (the area grows, the flags' epochs advance on the device), also when the launches are replayed from a CUDA graph
+    for segs2 in ([30001, 0, 40000], [7], [70001], [1000, 2000]):
+        tot = sum(segs2)
+        res = []
+        for on in (1, 0):
+            cn.check(ctx.lib.cn_comm_set_push_exchange(ctx.h, on))
+            g2 = torch.from_numpy(grads[rank][:tot].copy()).cuda()
+            n0 = ctx.lib.cn_kernel_launches()
+            cn.check(ctx.lib.cn_grad_sync_8bit_multi(ctx.h, g2.data_ptr(), (ctypes.c_int64 * len(segs2))(*segs2), len(segs2), 0.0, ctx.stream_ptr()))
+            torch.cuda.synchronize()
+            res.append((g2, ctx.lib.cn_kernel_launches() - n0))
+        assert torch.equal(res[0][0], res[1][0]), segs2
+        assert res[0][1] == res[1][1] + 1              # the push is a kernel of this library, the gather is not
+    cn.check(ctx.lib.cn_comm_set_push_exchange(ctx.h, 1))
+    ctx.gemm_check()
+    # the exchange with the RMSprop step inside its summing pass == the exchange, then cn_rmsprop_update (bit for bit),
+    # with segment ends that are no multiples of four and with buffers that are not 16-byte aligned
+    for segs3, shift in (([30001, 0, 40000], 0), ([70001], 0), ([1001, 2003], 1)):
+        tot = sum(segs3)
+        arr = (ctypes.c_int64 * len(segs3))(*segs3)
+        rms0 = np.abs(np.random.default_rng(5).standard_normal(tot + 1)).astype(np.float32)
+        w0 = np.random.default_rng(6).standard_normal(tot + 1).astype(np.float32)
+        outs = []
+        for fused in (True, False):
+            g3 = torch.from_numpy(grads[rank][:tot + 1].copy()).cuda()[shift:shift + tot]
+            r3 = torch.from_numpy(rms0.copy()).cuda()[shift:shift + tot]
+            w3 = torch.from_numpy(w0.copy()).cuda()[shift:shift + tot]
+            if fused:
+                cn.check(ctx.lib.cn_grad_sync_8bit_rmsprop(ctx.h, g3.data_ptr(), arr, len(segs3), 0.0, r3.data_ptr(), w3.data_ptr(), 0.9, 0.006,
+                                                           ctx.stream_ptr()))
+            else:
+                cn.check(ctx.lib.cn_grad_sync_8bit_multi(ctx.h, g3.data_ptr(), arr, len(segs3), 0.0, ctx.stream_ptr()))
+                cn.check(ctx.lib.cn_rmsprop_update(ctx.h, r3.data_ptr(), g3.data_ptr(), w3.data_ptr(), 0.9, 0.006, tot, ctx.stream_ptr()))
+            torch.cuda.synchronize()
+            outs.append((g3.clone(), r3.clone(), w3.clone()))
+        for a, b in zip(outs[0], outs[1]):
+            assert torch.equal(a, b), (segs3, shift)
+    gg = torch.from_numpy(grads[rank][:5000].copy()).cuda()
+    seg1 = (ctypes.c_int64 * 1)(5000)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        cn.check(ctx.lib.cn_grad_sync_8bit_multi(ctx.h, gg.data_ptr(), seg1, 1, 0.0, ctypes.c_void_p(side.cuda_stream)))
+    torch.cuda.synchronize()
+    once = gg.clone()
+    gg.copy_(torch.from_numpy(grads[rank][:5000].copy()).cuda())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+        cn.check(ctx.lib.cn_grad_sync_8bit_multi(ctx.h, gg.data_ptr(), seg1, 1, 0.0, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    for rep in range(3):
+        gg.copy_(torch.from_numpy(grads[rank][:5000].copy()).cuda())
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(gg, once), rep
+    ctx.gemm_check()
     # TdotMPI with a sharded B: the row-major batch as a transposed operand, through the fused gather
     M, K, N = 128, 2048, 2048 + 8 * world
     A = rng.uniform(-1, 1, (M, K)).astype(np.float32)

@@ -1,5 +1,6 @@
 """Data-parallel training step: each elementwise kernel against its numpy restatement, the 8-bit gradient sync at one
 rank, and the facade's Layer chain (forward / backward on the config-4 MLP shape) against an fp64 restatement."""
+import ctypes
 import os
 import subprocess
 
@@ -123,6 +124,15 @@ def test_grad_sync_is_identity_on_one_rank(ctx):
     ref = g.clone()
     cn.check(ctx.lib.cn_grad_sync_8bit(ctx.h, g.data_ptr(), g.numel(), 1.0, ctx.stream_ptr()))
     assert torch.equal(g, ref)
+    # ... and the exchange with the update inside is the plain update there
+    rms, w = torch.rand(10000, device="cuda"), torch.randn(10000, device="cuda")
+    rms2, w2 = rms.clone(), w.clone()
+    seg = (ctypes.c_int64 * 2)(4000, 6000)
+    cn.check(ctx.lib.cn_grad_sync_8bit_rmsprop(ctx.h, g.data_ptr(), seg, 2, 0.0, rms.data_ptr(), w.data_ptr(), 0.9, 0.006, ctx.stream_ptr()))
+    cn.check(ctx.lib.cn_rmsprop_update(ctx.h, rms2.data_ptr(), g.data_ptr(), w2.data_ptr(), 0.9, 0.006, 10000, ctx.stream_ptr()))
+    torch.cuda.synchronize()
+    assert torch.equal(g, ref) and torch.equal(rms, rms2) and torch.equal(w, w2)
+    assert ctx.lib.cn_grad_sync_8bit_rmsprop(ctx.h, g.data_ptr(), seg, 2, 0.0, None, w.data_ptr(), 0.9, 0.006, ctx.stream_ptr()) == _lib.CN_ERR_ARG
 
 
 def test_layer_chain_gradients_and_training(built_lib, tmp_path):
