@@ -403,7 +403,7 @@ __device__ __forceinline__ uint32_t ring_code4(const float4 q, uint32_t pb, uint
 // Shift, clamp range and bucket table from the 127 boundaries in t.X (all threads of the CTA; ends with a barrier).
 __device__ __forceinline__ void ring_build_tables(RingTables &t, int tid, bool usable)
 {
-    __shared__ uint32_t s_delta, s_lo;
+    __shared__ uint32_t s_delta;
     __shared__ int s_base;
     if (tid < 32) {
         bool bad = !usable;
@@ -420,7 +420,6 @@ __device__ __forceinline__ void ring_build_tables(RingTables &t, int tid, bool u
             const int nb = (int)(hi >> 16) - base + 1;
             const uint32_t lo = (uint32_t)base << 16;
             s_delta = delta;
-            s_lo = lo;
             s_base = base;
             t.kadd = delta - lo;
             t.span = (int32_t)(hi - lo);
@@ -431,7 +430,7 @@ __device__ __forceinline__ void ring_build_tables(RingTables &t, int tid, bool u
     __syncthreads();
     if (!t.bad) {
         const int base = s_base, nb = t.nb;
-        const uint32_t delta = s_delta, lo = s_lo;
+        const uint32_t delta = s_delta;
         for (int b = tid; b < nb; b += RING_THREADS) {
             const uint32_t kbv = (uint32_t)(b + base);
             // first boundary (of 0..126) whose shifted bucket is >= this one
@@ -703,6 +702,11 @@ cn_compress_ring_kernel(const float *__restrict__ A, float precision_arg, float 
 
 // kDecompression_8bit (source/clusterKernels.cu:1135-1160): 256-entry table built in the reference's
 // statement order, then out[i] = table[code].
+// vector_ok: 0 = byte by byte; 1 = four codes per load (codes 4-byte, output 16-byte aligned).  When the codes are 16-byte
+// aligned too, cn_decompress16_kernel takes over: a warp reads 512 consecutive codes with one 16-byte load per lane and writes the 2048
+// bytes they decode to with four store instructions of 512 consecutive bytes each - word j of lane l holds float4
+// number 4l + j of the warp's 128, store k of lane l writes number 32k + l, fetched from lane 8k + l/4 by shuffles.
+// Used for large tensors (see decompress_impl).
 template <bool PRECISION_ON_DEVICE>
 __global__ void __launch_bounds__(CODEC_THREADS, 1)
 cn_decompress_kernel(const uint8_t *__restrict__ codes, float precision_arg, const float *__restrict__ d_precision,
@@ -726,12 +730,12 @@ cn_decompress_kernel(const uint8_t *__restrict__ codes, float precision_arg, con
     }
     if (!PRECISION_ON_DEVICE) cdc_pdl_wait();
     __syncthreads();
-    const int64_t nvec = vector_ok ? (n >> 2) : 0;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    int64_t v = (int64_t)blockIdx.x * blockDim.x + tid;
-    const uint32_t *in4 = reinterpret_cast<const uint32_t *>(codes);
     float4 *out4 = reinterpret_cast<float4 *>(out);
 #define CN_DEC4(w) make_float4(lut[(w) & 0xffu], lut[((w) >> 8) & 0xffu], lut[((w) >> 16) & 0xffu], lut[(w) >> 24])
+    const int64_t nvec = vector_ok ? (n >> 2) : 0;
+    int64_t v = (int64_t)blockIdx.x * blockDim.x + tid;
+    const uint32_t *in4 = reinterpret_cast<const uint32_t *>(codes);
     if (v + 3 * stride < nvec) {
         const int64_t step = 4 * stride;
         uint32_t cur[4];
@@ -767,6 +771,51 @@ cn_decompress_kernel(const uint8_t *__restrict__ codes, float precision_arg, con
     }
 #undef CN_DEC4
     for (int64_t i = (nvec << 2) + (int64_t)blockIdx.x * blockDim.x + tid; i < n; i += stride) out[i] = lut[codes[i]];
+}
+
+template <bool PRECISION_ON_DEVICE>
+__global__ void __launch_bounds__(CODEC_THREADS, 2)
+cn_decompress16_kernel(const uint8_t *__restrict__ codes, float precision_arg, const float *__restrict__ d_precision,
+                       int64_t n, float *__restrict__ out, const __grid_constant__ DecodeConst dc)
+{
+    __shared__ float lut[256];
+    const int tid = threadIdx.x;
+    cdc_pdl_launch_dependents();
+    if (PRECISION_ON_DEVICE) cdc_pdl_wait();   // the scale is in global memory; a host scale lets the table precede the wait
+    const float p = PRECISION_ON_DEVICE ? *d_precision : precision_arg;
+    if (tid < 256) {
+        float v = 0.0f;
+        const int i = tid & 127;
+        if (i < CN_CODEBOOK_N) {
+            v = __fmul_rn(dc.tbl[i], p);
+            if (tid >= 128) v = -v;
+        } else {
+            v = (tid == 255) ? -p : p;   // 126, 127, 254 -> +precision; 255 -> -precision
+        }
+        lut[tid] = v;
+    }
+    if (!PRECISION_ON_DEVICE) cdc_pdl_wait();
+    __syncthreads();
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    float4 *out4 = reinterpret_cast<float4 *>(out);
+#define CN_DEC4(w) make_float4(lut[(w) & 0xffu], lut[((w) >> 8) & 0xffu], lut[((w) >> 16) & 0xffu], lut[(w) >> 24])
+    const int64_t n16 = (n >> 4) & ~(int64_t)31;   // whole warps only: the shuffles need all 32 lanes
+    const uint4 *in16 = reinterpret_cast<const uint4 *>(codes);
+    const int lane = tid & 31, j = lane & 3;
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + tid; v < n16; v += stride) {
+        const uint4 w = __ldcs(in16 + v);
+        const int64_t base = (v - lane) << 2;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int src = 8 * k + (lane >> 2);
+            const uint32_t a = __shfl_sync(0xffffffffu, w.x, src), b = __shfl_sync(0xffffffffu, w.y, src),
+                           c = __shfl_sync(0xffffffffu, w.z, src), d = __shfl_sync(0xffffffffu, w.w, src);
+            const uint32_t x = j == 0 ? a : j == 1 ? b : j == 2 ? c : d;
+            __stcs(out4 + base + 32 * k + lane, CN_DEC4(x));
+        }
+    }
+#undef CN_DEC4
+    for (int64_t i = (n16 << 4) + (int64_t)blockIdx.x * blockDim.x + tid; i < n; i += stride) out[i] = lut[codes[i]];
 }
 
 // absmax (ABS) or plain max: one pass; every CTA leaves its partial maximum in the scratch array, the CTA that draws
@@ -1147,9 +1196,21 @@ static int decompress_impl(cn_context *ctx, const uint8_t *d_codes, float precis
     if (n == 0) return CN_OK;
     CN_REQUIRE(d_out && d_codes, CN_ERR_ARG, "cn_decompress_8bit: null buffer");
     int vector_ok = ((uintptr_t)d_out % 16 == 0) && ((uintptr_t)d_codes % 4 == 0);
-    int grid = codec_grid(ctx, n, CODEC_THREADS, 4, 1);   // 1024 threads x 64 registers fill an SM: one resident CTA
+    // Sixteen codes per load for large tensors (2^28 codes: 218 vs 236 us).  Up to tens of MiB the four-codes kernel stays:
+    // in a series of calls its one 1024-thread CTA per SM leaves room for the next launch to become resident early
+    // (programmatic dependent launch), which is worth more there (4096 x 4096: 15.8 vs 16.9 us).
+    if (vector_ok && (uintptr_t)d_codes % 16 == 0 && n >= (1LL << 26)) vector_ok = 2;
+    int grid = codec_grid(ctx, n, CODEC_THREADS, vector_ok == 2 ? 16 : 4, 1);   // one resident CTA per SM
     DecodeConst dc;
     for (int i = 0; i < 128; ++i) dc.tbl[i] = ctx->h_tbl[i];
+    if (vector_ok == 2) {
+        if (d_precision)
+            CN_CUDA(launch_pdl(cn_decompress16_kernel<true>, grid, CODEC_THREADS, 0, cn_stream(stream), d_codes, 0.f, d_precision, n, d_out, dc));
+        else
+            CN_CUDA(launch_pdl(cn_decompress16_kernel<false>, grid, CODEC_THREADS, 0, cn_stream(stream), d_codes, precision, (const float *)nullptr, n, d_out, dc));
+        cn_count_launch();
+        return CN_OK;
+    }
     if (d_precision)
         CN_CUDA(launch_pdl(cn_decompress_kernel<true>, grid, CODEC_THREADS, 0, cn_stream(stream), d_codes, 0.f, d_precision, n, d_out, dc, vector_ok));
     else

@@ -7,6 +7,7 @@ import numpy as np
 import pytest
 import torch
 
+import clusternet_b200 as cn
 from oracle import oracle
 
 pytestmark = pytest.mark.gpu
@@ -132,6 +133,31 @@ def test_decompress_all_codes(ctx, p):
     with np.errstate(all="ignore"):
         want = oracle.decompress(ctx.codebook, codes, p)
     assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("extra", [0, 517])
+def test_decompress_large_tensor_takes_the_sixteen_codes_kernel(ctx, extra):
+    """From 2^26 codes on (16-byte aligned) a warp decodes 512 codes per load and exchanges words by shuffles; every element
+    must still be table[code], the ragged end (no whole warp, no whole 16 bytes) included.  The 256-entry table itself is
+    pinned against the oracle, so a gather through it on the device is the full-size check."""
+    n = (1 << 26) + extra
+    g = torch.Generator(device="cuda").manual_seed(11 + extra)
+    codes = torch.randint(0, 256, (n,), dtype=torch.uint8, device="cuda", generator=g)
+    p = 0.37
+    table = ctx.decompress(torch.arange(256, dtype=torch.uint8, device="cuda"), p)
+    torch.cuda.synchronize()
+    want_tbl = oracle.decompress(ctx.codebook, np.arange(256, dtype=np.uint8), p)
+    assert np.array_equal(table.cpu().numpy().view(np.uint32), want_tbl.view(np.uint32))
+    out = ctx.decompress(codes, p)
+    pd = torch.tensor([p], device="cuda")
+    out_dp = torch.empty_like(out)
+    cn.check(ctx.lib.cn_decompress_8bit_dp(ctx.h, codes.data_ptr(), pd.data_ptr(), n, out_dp.data_ptr(), ctx.stream_ptr()))
+    torch.cuda.synchronize()
+    step = 1 << 24                                  # gather in pieces: the int64 index of the whole tensor would take 512 MiB
+    for lo in range(0, n, step):
+        want = table[codes[lo:lo + step].long()]
+        assert torch.equal(out[lo:lo + step].view(torch.int32), want.view(torch.int32)), lo
+        assert torch.equal(out_dp[lo:lo + step].view(torch.int32), want.view(torch.int32)), lo
 
 
 @pytest.mark.parametrize("n", [0, 1, 5, 1000, 65537, 1 << 22])
