@@ -487,6 +487,37 @@ def main():
             cn.check(lib.cn_dotmpi_f32(ctx.h, M, K1, N1, a_ptr, W1.data_ptr(), out1.data_ptr(), ctypes.byref(no_epi), gm, exchange, sp))
         ctx.dotmpi(out1, W2, N2, out=out2, mode=gm, exchange=exchange)
 
+    # Layer 1's activation planes are made one step ahead on a second stream (cn_gemm_prepare), so that the pass over the
+    # batch overlaps the previous step's products instead of preceding its own: two handles alternate; a handle is refilled
+    # only after the product that read it has finished (ev_read), and a product starts only after its handle is filled
+    # (ev_filled).  Every step still makes one set of planes - for its successor.
+    use_prep = coded is None and os.environ.get("CN_BENCH_PREPARE", "1") == "1"
+    prep, prep_stream, ev_filled, ev_read = [], None, [], []
+    if use_prep:
+        prep_stream = torch.cuda.Stream(priority=-1)   # its CTAs take the SM slots the product leaves free before the product's next wave does
+        for _ in range(2):
+            hnd = ctypes.c_void_p()
+            cn.check(lib.cn_gemm_prepare_create(ctx.h, M, K1, mode, ctypes.byref(hnd)))
+            prep.append(hnd)
+            ev_filled.append(torch.cuda.Event())
+            ev_read.append(torch.cuda.Event())
+
+    def prepare_planes(k, a_ptr=None, row_major=False, after=None):
+        """Fill handle k from the batch at a_ptr on the second stream (after: an event the batch itself depends on)."""
+        prep_stream.wait_event(ev_read[k])
+        if after is not None:
+            prep_stream.wait_event(after)
+        a = ctypes.c_void_p(a_ptr if a_ptr is not None else batch.data_ptr())
+        cn.check(lib.cn_gemm_prepare(ctx.h, prep[k], 1 if row_major else 0, a, K1 if row_major else M, ctypes.c_void_p(prep_stream.cuda_stream)))
+        ev_filled[k].record(prep_stream)
+
+    def two_layers_prepared(k):
+        main_s = torch.cuda.current_stream()
+        main_s.wait_event(ev_filled[k])
+        cn.check(lib.cn_dotmpi_prepared_f32(ctx.h, prep[k], N1, W1.data_ptr(), out1.data_ptr(), ctypes.byref(no_epi), exchange, sp))
+        ev_read[k].record(main_s)
+        ctx.dotmpi(out1, W2, N2, out=out2, mode=mode, exchange=exchange)
+
     def barrier():
         if world > 1:
             dist.barrier()
@@ -567,8 +598,21 @@ def main():
     two_layers()          # first call: scratch buffers are allocated here, not inside a timed region
     ctx.gemm_check()
     rest()
+    step_no = 0
+
+    def resident_step():
+        nonlocal step_no
+        if not use_prep:
+            two_layers()
+            return
+        prepare_planes((step_no + 1) % 2)          # for the next step; overlaps this step's products
+        two_layers_prepared(step_no % 2)
+        step_no += 1
+
+    if use_prep:
+        prepare_planes(0)
     for _ in range(args.warmup):
-        two_layers()
+        resident_step()
 
     # ---- timed region 1: resident inputs
     sampler = ClockSampler(local_rank)
@@ -582,7 +626,7 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        two_layers()
+        resident_step()
     e1.record()
     barrier()
     t_wall1 = time.time()
@@ -675,20 +719,42 @@ def main():
 
     e2e_batches = []
 
+    e2e_prep = use_prep and use_rm
+    e2e_no = 0
+    pnx, pnn = ctypes.c_void_p(), ctypes.c_int64()
+
     def e2e_step(upload_next=True, download_result=True):
+        nonlocal e2e_no
         if upload_next:
             cn.check(lib.cn_batch_copy_next_async(bh))                 # upload of the NEXT batch (side stream, all ranks)
         if use_rm:
             cn.check(lib.cn_batch_current_row_major(bh, ctypes.byref(px), ctypes.byref(pn)))
         else:
             cn.check(lib.cn_batch_current(bh, ctypes.byref(px), ctypes.byref(py), ctypes.byref(pn)))
-        two_layers(px.value, row_major=use_rm)
+        if e2e_prep and upload_next:
+            # the planes of the NEXT batch are made on the second stream as soon as its upload has arrived, beside this
+            # step's products; this step's own planes were made during the step before
+            cn.check(lib.cn_batch_next_row_major(bh, ctypes.c_void_p(prep_stream.cuda_stream), ctypes.byref(pnx), ctypes.byref(pnn)))
+            prepare_planes((e2e_no + 1) % 2, pnx.value, row_major=True)
+            two_layers_prepared(e2e_no % 2)
+            e2e_no += 1
+        else:
+            two_layers(px.value, row_major=use_rm)
         if download_result:
             download_overlapped()
         if upload_next:
             cn.check(lib.cn_batch_swap(bh, sp, ctypes.byref(px), ctypes.byref(py), ctypes.byref(pn)))
             e2e_batches.append(len(e2e_batches) % 2)                   # the allocator walks batch 0, 1, 0, 1, ...
 
+    def e2e_prime():
+        """Planes of the batch that is current now (the steps make them for their successor only)."""
+        if e2e_prep:
+            cn.check(lib.cn_batch_current_row_major(bh, ctypes.byref(px), ctypes.byref(pn)))
+            ev_now = torch.cuda.Event()
+            ev_now.record(torch.cuda.current_stream())
+            prepare_planes(e2e_no % 2, px.value, row_major=True, after=ev_now)
+
+    e2e_prime()
     rest()
     for _ in range(args.warmup):
         e2e_step()
@@ -752,6 +818,9 @@ def main():
         if rank == 0:
             print(f"bench.py: e2e diagnosis (ms per step): {e2e_diag}", file=sys.stderr, flush=True)
     lib.cn_batch_destroy(bh)
+    torch.cuda.synchronize()
+    for hnd in prep:
+        lib.cn_gemm_prepare_destroy(hnd)
     barrier()
     # the end-to-end result, as it arrived on the host, against the resident path on the batch that step used: the two
     # paths differ only in how the batch reaches the product, so they must agree bit for bit; the resident recomputation
@@ -795,6 +864,8 @@ def main():
         "config": {"workload": ("README dotMPI two-layer skinny GEMM: " if headline else "REDUCED (profiling) two-layer skinny GEMM: ") +
                                f"128x{K1} . {K1}x{N1} . {N1}x{N2}, W column-sharded",
                    "gemm_mode": args.mode, "exchange": args.exchange, "gather": ("fused peer stores" if fused else ("nccl" if world > 1 else "none")), "parallelism": f"tp{world} (columns of W)",
+                   "activation_planes": ("layer 1's TF32 hi/lo planes are made one step ahead on a second stream (cn_gemm_prepare): every step makes "
+                                         "the planes of its successor beside its own products" if use_prep else "made inside each product call"),
                    "timed_regions": "each starts after 1.5 s of idle GPUs and its own warm-up steps (the products are power-limited)",
                    "l2": f"inputs larger than L2 ({4e-9 * (K1 * N1 + N1 * N2):.1f} GB of weights stream once per step)", "flops_per_step": FLOPS_STEP},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": M * K1 * 4,

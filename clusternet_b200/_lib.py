@@ -127,6 +127,11 @@ _SIGNATURES = {
     "cn_batch_create_ex": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int, ctypes.POINTER(c_void_p)]),
     "cn_batch_current_row_major": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64)]),
     "cn_batch_profile": (c_int, [c_void_p, c_int, c_void_p]),
+    "cn_batch_next_row_major": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),
+    "cn_gemm_prepare_create": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p]),
+    "cn_gemm_prepare": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p]),
+    "cn_dotmpi_prepared_f32": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "cn_gemm_prepare_destroy": (c_int, [c_void_p]),
     "cn_batch_destroy": (c_int, [c_void_p]),
     "cn_batch_total_batches": (c_int64, [c_void_p]),
     "cn_batch_current": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64)]),

@@ -268,6 +268,18 @@ extern "C" int cn_batch_current_row_major(const cn_batch *b, float **d_X_row_maj
     return CN_OK;
 }
 
+extern "C" int cn_batch_next_row_major(cn_batch *b, void *stream, float **d_X_row_major, int64_t *batch_rows)
+{
+    CN_REQUIRE(b, CN_ERR_ARG, "cn_batch_next_row_major: null handle");
+    CN_REQUIRE(b->flags & CN_BATCH_KEEP_ROW_MAJOR, CN_ERR_ARG, "cn_batch_next_row_major: the allocator was created without CN_BATCH_KEEP_ROW_MAJOR");
+    CN_REQUIRE(b->in_flight > 0, CN_ERR_ARG, "cn_batch_next_row_major: no copy under way (call cn_batch_copy_next_async first)");
+    const int buf = b->ready;
+    CN_CUDA(cudaStreamWaitEvent(cn_stream(stream), b->e_Xb[buf], 0));
+    if (d_X_row_major) *d_X_row_major = b->xb[buf];
+    if (batch_rows) *batch_rows = b->rows_in[buf];
+    return CN_OK;
+}
+
 // Timing of the last sharded upload's phases on the copy stream, in milliseconds: [0] wait for the peers' "buffer free"
 // flags, [1] host-to-device copy of the own block, [2] push to the peers, [3] wait for the peers' "arrived" flags.
 // enable != 0 switches the recording on for the following copies; the call then returns the last recorded copy (zeros

@@ -937,6 +937,69 @@ extern "C" int cn_dotmpi_from_coded_f32(cn_context *ctx, const cn_coded *A, int6
     return cn_dotmpi_f32(ctx, M, K, n_total, Af, d_Wshard, d_C, epi, mode, exchange, stream);
 }
 
+// ---- activation planes made ahead of the product
+extern "C" int cn_gemm_prepare_create(cn_context *ctx, int64_t M, int64_t K, int mode, cn_prepared **out)
+{
+    CN_REQUIRE(ctx && out, CN_ERR_ARG, "cn_gemm_prepare_create: null argument");
+    CN_REQUIRE(M >= 1 && K >= 1, CN_ERR_SHAPE, "cn_gemm_prepare_create: empty operand");
+    CN_REQUIRE(mode == CN_GEMM_3XTF32 || mode == CN_GEMM_TF32, CN_ERR_ARG, "cn_gemm_prepare_create: the planes exist for the tensor-core modes only");
+    *out = nullptr;
+    CN_CUDA(cudaSetDevice(ctx->device));
+    cn_prepared *p = new cn_prepared();
+    p->ctx = ctx;
+    p->M = M;
+    p->K = K;
+    p->Kpad = (K + 31) / 32 * 32;
+    p->mode = mode;
+    const size_t plane = (size_t)M * p->Kpad;
+    cudaError_t e = cudaMalloc(&p->hi, plane * sizeof(float) * (mode == CN_GEMM_3XTF32 ? 2 : 1));
+    if (e != cudaSuccess) {
+        delete p;
+        return cn_cuda_fail(e, "cn_gemm_prepare_create");
+    }
+    p->lo = mode == CN_GEMM_3XTF32 ? p->hi + plane : nullptr;
+    *out = p;
+    return CN_OK;
+}
+
+extern "C" int cn_gemm_prepare_destroy(cn_prepared *p)
+{
+    if (!p) return CN_OK;
+    cudaFree(p->hi);
+    delete p;
+    return CN_OK;
+}
+
+extern "C" int cn_gemm_prepare(cn_context *ctx, cn_prepared *p, int transA, const float *d_A, int64_t lda, void *stream)
+{
+    CN_REQUIRE(ctx && p && d_A && p->ctx == ctx, CN_ERR_ARG, "cn_gemm_prepare: null argument or a handle of another context");
+    CN_REQUIRE(lda >= (transA ? p->K : p->M), CN_ERR_SHAPE, "cn_gemm_prepare: leading dimension smaller than the stored rows");
+    if (!ctx->gemm) ctx->gemm = cn_gemm_workspace_new();
+    int st = cn_gemm_tc_split_activations(ctx, transA, p->M, p->K, d_A, lda, p->hi, p->lo, cn_stream(stream));
+    if (st == CN_OK) p->filled = true;
+    return st;
+}
+
+extern "C" int cn_dotmpi_prepared_f32(cn_context *ctx, const cn_prepared *p, int64_t n_total, const float *d_Wshard, float *d_C,
+                                      const cn_epilogue *epi, int exchange, void *stream)
+{
+    CN_REQUIRE(ctx && p && d_Wshard && d_C && p->ctx == ctx, CN_ERR_ARG, "cn_dotmpi_prepared_f32: null argument or a handle of another context");
+    CN_REQUIRE(p->filled, CN_ERR_ARG, "cn_dotmpi_prepared_f32: cn_gemm_prepare has not run on this handle");
+    CN_REQUIRE(!epi || epi->maxout_level <= 1, CN_ERR_UNSUPPORTED, "cn_dotmpi_prepared_f32: maxout is not available on the sharded product");
+    const int G = ctx->comm ? ctx->comm->nranks : 1, rank = ctx->comm ? ctx->comm->rank : 0;
+    int64_t start, cnt;
+    cn_shard_cols(n_total, rank, G, &start, &cnt);
+    // the planes only feed the tensor-core kernel; every rank must be able to take it (the decision is made from the
+    // shapes and this rank's W pointer, like the fused gather's)
+    CN_REQUIRE(cnt > 0 && cn_gemm_tc_supported(ctx, 0, 0, p->M, cnt, p->K, p->hi, p->M, d_Wshard, p->K, d_C, p->M), CN_ERR_UNSUPPORTED,
+               "cn_dotmpi_prepared_f32: this shard is no shape for the tensor-core kernel (empty, or W not 16-byte aligned)");
+    if (!ctx->gemm) ctx->gemm = cn_gemm_workspace_new();
+    ctx->gemm->prepared = p;   // consumed by the launch inside the call below; the fp32 pointer handed down is a placeholder
+    int st = dotmpi_impl(ctx, 0, p->M, p->K, n_total, p->hi, p->M, d_Wshard, d_C, epi, p->mode, exchange, stream);
+    ctx->gemm->prepared = nullptr;
+    return st;
+}
+
 // ---- diagnostics: the bounded wait on a cross-GPU flag, exercised without a peer.
 // Waits for an epoch that nothing will ever write into this context's own probe word, with a caller-chosen cycle
 // limit; when the limit runs out the kernel records status 10 and returns, exactly like cn_flag_barrier_kernel does

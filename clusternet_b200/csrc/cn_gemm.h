@@ -22,12 +22,23 @@ struct cn_coded_src {
     int nranks = 1, own_rank = 0;
 };
 
+// The K-major TF32 hi / lo planes of an activation operand, made ahead of the product that consumes them
+// (cn_gemm_prepare): the product's own pre-pass is then skipped.  `hi` holds both planes back to back.
+struct cn_prepared {
+    cn_context *ctx = nullptr;
+    float *hi = nullptr, *lo = nullptr;
+    int64_t M = 0, K = 0, Kpad = 0;
+    int mode = 0;
+    bool filled = false;
+};
+
 struct cn_gemm_workspace {
     void *ptr[CN_GEMM_SLOTS] = {nullptr, nullptr, nullptr, nullptr};
     size_t bytes[CN_GEMM_SLOTS] = {0, 0, 0, 0};
     unsigned int *d_status = nullptr;   // word 0: set by a kernel whose bounded wait ran out
     void *encode_fn = nullptr;          // cuTensorMapEncodeTiled, resolved once
     const cn_coded_src *coded_src = nullptr;   // one-shot: see cn_coded_src
+    const cn_prepared *prepared = nullptr;   // one-shot: planes made ahead of the launch (cn_gemm_prepare)
     // test and sweep knobs (0 = automatic choice): W tiles per CTA, K splits, K blocks per accumulation chain.  Seeded once,
     // when the workspace is made, from CN_GEMM_NT / CN_GEMM_SPLITS / CN_GEMM_CHAIN; changed with cn_gemm_set_tuning.
     int force_nt = 0, force_splits = 0, force_chain = 0;
@@ -58,6 +69,9 @@ struct cn_peer_out {
 bool cn_gemm_tc_supported(cn_context *ctx, int transA, int transB, int64_t M, int64_t N, int64_t K,
                           const float *A, int64_t lda, const float *B, int64_t ldb, const float *C, int64_t ldc);
 bool cn_gemm_tc_can_fuse_maxout(int level);
+// the activation pre-pass alone, into caller-owned planes (lo == nullptr in the single-pass mode)
+int cn_gemm_tc_split_activations(cn_context *ctx, int transA, int64_t M, int64_t K, const float *A, int64_t lda, float *hi, float *lo,
+                                 cudaStream_t s);
 int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const float *A, int64_t lda,
                       const float *B, int64_t ldb, float *C, int64_t ldc, const cn_epilogue *epi, int mode, cudaStream_t s,
                       const cn_peer_out *peers = nullptr, int transA = 0, int transB = 0);

@@ -947,6 +947,25 @@ static int launch_cfg(const CUtensorMap &mw, const CUtensorMap &mhi, const CUten
     return CN_OK;
 }
 
+int cn_gemm_tc_split_activations(cn_context *ctx, int transA, int64_t M, int64_t K, const float *A, int64_t lda, float *hi, float *lo,
+                                 cudaStream_t s)
+{
+    (void)ctx;
+    const int64_t Kpad = (K + TC_BK - 1) / TC_BK * TC_BK;
+    const int64_t tiles_k = Kpad / 32, tiles_mm = (M + 31) / 32;
+    CN_REQUIRE(tiles_k * tiles_mm < (1LL << 31), CN_ERR_UNSUPPORTED, "cn_gemm_f32: activation matrix too large for the split pre-pass");
+    if (transA) {
+        const int vec_ok = ((lda & 3) == 0) && ((reinterpret_cast<uintptr_t>(A) & 15u) == 0);
+        dim3 grid((unsigned)((Kpad / 4 + 255) / 256), (unsigned)(M < 65535 ? M : 65535));
+        cn_act_split_t_kernel<<<grid, 256, 0, s>>>(A, lda, M, K, Kpad, hi, lo, vec_ok);
+    } else {
+        cn_act_split_kernel<<<(unsigned)(tiles_k * tiles_mm), 256, 0, s>>>(A, lda, M, K, Kpad, hi, lo, tiles_k);
+    }
+    CN_CUDA(cudaGetLastError());
+    cn_count_launch();
+    return CN_OK;
+}
+
 int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const float *A, int64_t lda, const float *B,
                       int64_t ldb, float *C, int64_t ldc, const cn_epilogue *epi, int mode, cudaStream_t s, const cn_peer_out *peers,
                       int transA, int transB)
@@ -962,30 +981,36 @@ int cn_gemm_tc_launch(cn_context *ctx, int64_t M, int64_t N, int64_t K, const fl
     const bool mode3x = mode == CN_GEMM_3XTF32;
     const int64_t Kpad = (K + TC_BK - 1) / TC_BK * TC_BK;
 
-    // 1. activations -> K-major hi / lo planes
-    void *planes = nullptr;
+    // 1. activations -> K-major hi / lo planes (made here, or ahead of the call by cn_gemm_prepare)
     const size_t plane_elems = (size_t)M * Kpad;
-    st = cn_gemm_scratch(ctx, CN_GEMM_SLOT_ASPLIT, plane_elems * sizeof(float) * (mode3x ? 2 : 1), &planes);
-    if (st != CN_OK) return st;
-    float *hi = (float *)planes, *lo = mode3x ? hi + plane_elems : nullptr;
-    {
-        const int64_t tiles_k = Kpad / 32, tiles_mm = (M + 31) / 32;
-        CN_REQUIRE(tiles_k * tiles_mm < (1LL << 31), CN_ERR_UNSUPPORTED, "cn_gemm_f32: activation matrix too large for the split pre-pass");
+    float *hi = nullptr, *lo = nullptr;
+    if (ws->prepared) {
+        const cn_prepared *pr = ws->prepared;
+        ws->prepared = nullptr;
+        CN_REQUIRE(pr->filled && pr->M == M && pr->K == K && pr->Kpad == Kpad && pr->mode == mode, CN_ERR_SHAPE,
+                   "prepared activations are %lld x %lld for mode %d, the product wants %lld x %lld for mode %d", (long long)pr->M,
+                   (long long)pr->K, pr->mode, (long long)M, (long long)K, mode);
+        hi = pr->hi;
+        lo = mode3x ? pr->lo : nullptr;
+    } else {
+        void *planes = nullptr;
+        st = cn_gemm_scratch(ctx, CN_GEMM_SLOT_ASPLIT, plane_elems * sizeof(float) * (mode3x ? 2 : 1), &planes);
+        if (st != CN_OK) return st;
+        hi = (float *)planes;
+        lo = mode3x ? hi + plane_elems : nullptr;
         if (ws->coded_src) {
+            const int64_t tiles_k = Kpad / 32, tiles_mm = (M + 31) / 32;
+            CN_REQUIRE(tiles_k * tiles_mm < (1LL << 31), CN_ERR_UNSUPPORTED, "cn_gemm_f32: activation matrix too large for the split pre-pass");
             const cn_coded_src *cs = ws->coded_src;
             ws->coded_src = nullptr;
             CN_REQUIRE(!transA && lda == M, CN_ERR_UNSUPPORTED, "coded activations must be untransposed with ld = rows");
             cn_act_split_coded_kernel<<<(unsigned)(tiles_k * tiles_mm), 256, (size_t)cs->nranks * 256 * sizeof(float), s>>>(
                 cs->codes, cs->scales, ctx->d_tbl, cs->own_fp32, cs->own_rank, cs->nranks, M, K, Kpad, hi, lo, tiles_k);
-        } else if (transA) {
-            const int vec_ok = ((lda & 3) == 0) && ((reinterpret_cast<uintptr_t>(A) & 15u) == 0);
-            dim3 grid((unsigned)((Kpad / 4 + 255) / 256), (unsigned)(M < 65535 ? M : 65535));
-            cn_act_split_t_kernel<<<grid, 256, 0, s>>>(A, lda, M, K, Kpad, hi, lo, vec_ok);
-        } else {
-            cn_act_split_kernel<<<(unsigned)(tiles_k * tiles_mm), 256, 0, s>>>(A, lda, M, K, Kpad, hi, lo, tiles_k);
+            CN_CUDA(cudaGetLastError());
+            cn_count_launch();
+        } else if ((st = cn_gemm_tc_split_activations(ctx, transA, M, K, A, lda, hi, lo, s)) != CN_OK) {
+            return st;
         }
-        CN_CUDA(cudaGetLastError());
-        cn_count_launch();
     }
 
     // 2. tiling

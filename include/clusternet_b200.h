@@ -325,6 +325,23 @@ int cn_dotmpi_to_coded_f32(cn_context *ctx, int64_t M, int64_t K, int64_t n_tota
 int cn_dotmpi_from_coded_f32(cn_context *ctx, const cn_coded *A, int64_t n_total, const float *d_Wshard, float *d_C,
                              const cn_epilogue *epi, int mode, int exchange, void *stream);
 
+/* Activation planes made ahead of the product.  The tensor-core kernel reads the activation operand as K-major TF32
+ * hi / lo planes, which every product call otherwise makes first (one pass over A: 12 bytes per element).  Where A is
+ * known before the product can start - the next batch, while the current step still multiplies - the planes can be made
+ * then, on another stream, and the product starts with its first tile:
+ *   cn_gemm_prepare_create  allocates planes for an M x K operand and a mode (CN_GEMM_3XTF32 / CN_GEMM_TF32);
+ *   cn_gemm_prepare         fills them from A (transA = 0: column-major M x K, lda >= M; transA = 1: the row-major batch,
+ *                           K x M column-major, lda >= K, as cn_tdotmpi_f32 takes it) on `stream`;
+ *   cn_dotmpi_prepared_f32  = cn_dotmpi_f32 / cn_tdotmpi_f32 on that operand, bit for bit, without the pre-pass.
+ * The caller orders the streams (an event after cn_gemm_prepare, waited for by the product's stream) and keeps a handle
+ * untouched while a product that reads it may run.  The reference has no counterpart (cuBLAS reads A as it is). */
+typedef struct cn_prepared cn_prepared;
+int cn_gemm_prepare_create(cn_context *ctx, int64_t M, int64_t K, int mode, cn_prepared **out);
+int cn_gemm_prepare(cn_context *ctx, cn_prepared *p, int transA, const float *d_A, int64_t lda, void *stream);
+int cn_dotmpi_prepared_f32(cn_context *ctx, const cn_prepared *p, int64_t n_total, const float *d_Wshard, float *d_C,
+                           const cn_epilogue *epi, int exchange, void *stream);
+int cn_gemm_prepare_destroy(cn_prepared *p);
+
 /* dotTMPI: replaces ClusterNet::dotTMPI (source/clusterNet.cpp:511,628-642,698-727), the backward product through a
  * column-sharded weight: out (M x R) = A (M x n_total) . B^T, where this rank holds the R x cols_local block of the
  * R x n_total matrix B.  Each rank multiplies its column slice of A with its shard (transposed) and the full-size
@@ -447,6 +464,11 @@ int cn_batch_current_row_major(const cn_batch *b, float **d_X_row_major, int64_t
  * phases of the last recorded copy in milliseconds: waiting for the peers' "buffer free" flags, the host-to-device copy of
  * the own block, the push to the peers, waiting for the peers' "arrived" flags. */
 int cn_batch_profile(cn_batch *b, int enable, float *ms4);
+/* The row-major device copy of the NEXT batch (the one the next cn_batch_swap makes current) and its row count, for work
+ * that can start before the swap, e.g. cn_gemm_prepare on another stream: `stream` is made to wait for the batch's copy.
+ * Needs CN_BATCH_KEEP_ROW_MAJOR and a copy under way (cn_batch_copy_next_async).  The buffer stays valid until the swap
+ * after next. */
+int cn_batch_next_row_major(cn_batch *b, void *stream, float **d_X_row_major, int64_t *batch_rows);
 int cn_batch_destroy(cn_batch *b);
 int64_t cn_batch_total_batches(const cn_batch *b);
 /* The batch that is current now (after cn_batch_create: the first batch, as BatchAllocator::init leaves it). */

@@ -241,6 +241,17 @@ def run_nccl():
                                     ctx.stream_ptr()))
     ctx.gemm_check()
     assert torch.equal(got, want)
+    # ... and the same product from planes made ahead of it (cn_gemm_prepare), through the fused gather: bit-identical
+    hp = ctypes.c_void_p()
+    cn.check(ctx.lib.cn_gemm_prepare_create(ctx.h, M, K, _lib.GEMM_3XTF32, ctypes.byref(hp)))
+    cn.check(ctx.lib.cn_gemm_prepare(ctx.h, hp, 1, rm.data_ptr(), K, ctx.stream_ptr()))
+    got_p = ctx.sym_empty(M, N)
+    cn.check(ctx.lib.cn_dotmpi_prepared_f32(ctx.h, hp, N, dW.data_ptr(), got_p.data_ptr(), ctypes.byref(epi), 0, ctx.stream_ptr()))
+    ctx.gemm_check()
+    torch.cuda.synchronize()
+    assert torch.equal(got_p, want)
+    dist.barrier()
+    ctx.lib.cn_gemm_prepare_destroy(hp)
     # batch allocator with the sharded upload: every rank holds the data set and uploads 1/G of each batch's rows; the
     # blocks are exchanged over NVLink; every rank then sees every batch whole (tests/batchAllocator_test.cu:40-114 form)
     rows, cols_x, B = 1000, 36, 128

@@ -1,8 +1,11 @@
 """GEMM parity: the reference's known-answer tests, an fp64 host GEMM as accuracy yardstick, fused epilogues."""
+import ctypes
+
 import numpy as np
 import pytest
 import torch
 
+import clusternet_b200 as cn
 from clusternet_b200 import _lib
 from oracle import oracle
 
@@ -96,6 +99,55 @@ def test_transposed_operands_on_the_tensor_path(ctx, transA, transB, M, K, N):
     assert ctx.gemm_last_path() == "tcgen05_3xtf32"
     ref = np.maximum(oracle.gemm_f64(A, B, transA, transB) + bias, 0)
     assert normwise(ctx.to_numpy(C), ref) < TOL_3XTF32
+
+
+@pytest.mark.parametrize("mode", [_lib.GEMM_3XTF32, _lib.GEMM_TF32])
+@pytest.mark.parametrize("row_major", [False, True])
+@pytest.mark.parametrize("M,K,N", [(128, 4100, 1024), (96, 1000, 2304)])
+def test_planes_made_ahead_give_the_same_product(ctx, mode, row_major, M, K, N):
+    """cn_gemm_prepare + cn_dotmpi_prepared_f32 == cn_dotmpi_f32 / cn_tdotmpi_f32 bit for bit (the product only skips its own
+    pass over the activations), the planes made on another stream and handed over through an event; a handle of another
+    shape or mode is refused."""
+    rng = np.random.default_rng(M + K + N + mode)
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    W = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    bias = torch.from_numpy(rng.uniform(-1, 1, N).astype(np.float32)).cuda()
+    dW = ctx.colmajor(W)
+    a_dev = torch.from_numpy(A).cuda() if row_major else ctx.colmajor(A)      # row-major M x K == column-major K x M
+    epi = cn.Epilogue(bias.data_ptr(), _lib.ACT_RELU, 0, None)
+    want = ctx.empty(M, N)
+    if row_major:
+        cn.check(ctx.lib.cn_tdotmpi_f32(ctx.h, M, K, N, a_dev.data_ptr(), K, dW.data_ptr(), want.data_ptr(), ctypes.byref(epi), mode, 0, ctx.stream_ptr()))
+    else:
+        cn.check(ctx.lib.cn_dotmpi_f32(ctx.h, M, K, N, a_dev.data_ptr(), dW.data_ptr(), want.data_ptr(), ctypes.byref(epi), mode, 0, ctx.stream_ptr()))
+    h = ctypes.c_void_p()
+    cn.check(ctx.lib.cn_gemm_prepare_create(ctx.h, M, K, mode, ctypes.byref(h)))
+    got = ctx.empty(M, N)
+    # not filled yet
+    assert ctx.lib.cn_dotmpi_prepared_f32(ctx.h, h, N, dW.data_ptr(), got.data_ptr(), ctypes.byref(epi), 0, ctx.stream_ptr()) == _lib.CN_ERR_ARG
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    cn.check(ctx.lib.cn_gemm_prepare(ctx.h, h, 1 if row_major else 0, a_dev.data_ptr(), K if row_major else M, ctypes.c_void_p(side.cuda_stream)))
+    ev = torch.cuda.Event()
+    ev.record(side)
+    torch.cuda.current_stream().wait_event(ev)
+    a_cm, scratch_out = ctx.colmajor(A), ctx.empty(M, N)
+    n0 = ctx.lib.cn_kernel_launches()
+    cn.check(ctx.lib.cn_dotmpi_prepared_f32(ctx.h, h, N, dW.data_ptr(), got.data_ptr(), ctypes.byref(epi), 0, ctx.stream_ptr()))
+    n1 = ctx.lib.cn_kernel_launches()
+    cn.check(ctx.lib.cn_dotmpi_f32(ctx.h, M, K, N, a_cm.data_ptr(), dW.data_ptr(), scratch_out.data_ptr(), ctypes.byref(epi), mode, 0, ctx.stream_ptr()))
+    n2 = ctx.lib.cn_kernel_launches()
+    ctx.gemm_check()
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    assert (n1 - n0) == (n2 - n1) - 1               # one launch less: no pass over the activations
+    ref = np.maximum(oracle.gemm_f64(A, W, False, False) + bias.cpu().numpy(), 0)
+    assert normwise(ctx.to_numpy(got), ref) < (TOL_3XTF32 if mode == _lib.GEMM_3XTF32 else TOL_TF32)
+    # a leading dimension below the stored rows, and a mode without planes, are refused
+    assert ctx.lib.cn_gemm_prepare(ctx.h, h, 0, a_cm.data_ptr(), M - 1, ctx.stream_ptr()) == _lib.CN_ERR_SHAPE
+    assert ctx.lib.cn_gemm_prepare_create(ctx.h, M, K, _lib.GEMM_FP32_SIMT, ctypes.byref(ctypes.c_void_p())) == _lib.CN_ERR_ARG
+    torch.cuda.synchronize()
+    ctx.lib.cn_gemm_prepare_destroy(h)
 
 
 def test_config1_dot_bias_relu(ctx):
