@@ -20,6 +20,9 @@
 //                            addresses of a symmetric buffer), framed by two bounded cross-GPU flag exchanges on the
 //                            copy stream ("your buffer may be overwritten" / "my block has arrived").  One link no
 //                            longer carries the whole batch.
+//   CN_BATCH_PUSH_BY_KERNEL  the push of the sharded upload by one kernel's stores instead of the copy engines;
+//   CN_BATCH_LOOKAHEAD       three row-major buffers and two copies in flight: the copy of the batch after next starts
+//                            as soon as its buffer is free, so one copy's chain of waits has two steps to finish in.
 #include <string.h>
 #include "cn_internal.h"
 
