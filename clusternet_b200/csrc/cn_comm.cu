@@ -697,20 +697,6 @@ int cn_comm_info(cn_context *ctx, int *rank, int *nranks, float **d_scales)
     return CN_OK;
 }
 
-// codes_all: nranks blocks of n bytes, block [rank] filled; scales (optional): nranks floats, entry [rank] filled
-int cn_comm_gather_codes(cn_context *ctx, uint8_t *d_codes_all, int64_t n, float *d_scales, void *stream)
-{
-    cn_comm_state *c = ctx->comm;
-    if (!c || c->nranks == 1) return CN_OK;
-    CN_COMM_ALIVE(ctx);
-    CN_NCCL(g_nccl.GroupStart());
-    ncclResult_t r1 = g_nccl.AllGather(d_codes_all + (size_t)c->rank * n, d_codes_all, (size_t)n, ncclUint8, c->comm, cn_stream(stream));
-    ncclResult_t r2 = d_scales ? g_nccl.AllGather(d_scales + c->rank, d_scales, 1, ncclFloat, c->comm, cn_stream(stream)) : ncclSuccess;
-    ncclResult_t r3 = g_nccl.GroupEnd();
-    CN_REQUIRE(r1 == ncclSuccess && r2 == ncclSuccess && r3 == ncclSuccess, CN_ERR_NCCL, "cn_grad_sync_8bit: all-gather failed");
-    return CN_OK;
-}
-
 // blocks: nranks blocks of block_bytes bytes, block [rank] filled
 int cn_comm_gather_blocks(cn_context *ctx, uint8_t *d_blocks, size_t block_bytes, void *stream)
 {

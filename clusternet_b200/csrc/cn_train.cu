@@ -135,35 +135,8 @@ __global__ void cn_rmsprop_kernel(float *__restrict__ RMS, const float *__restri
 }
 
 // grad[i] += sum over peers r != me of decode_r(codes_r[i]); decode tables as kDecompression_8bit builds them, one per
-// rank with that rank's scale; peers are added in rank order (the order of the reference's loop).
-__global__ void __launch_bounds__(512)
-cn_decode_sum_kernel(float *__restrict__ grad, const uint8_t *__restrict__ codes, const float *__restrict__ scales,
-                     const float *__restrict__ g_tbl, int64_t n, int nranks, int my_rank)
-{
-    extern __shared__ float lut[];   // nranks x 256
-    for (int e = threadIdx.x; e < nranks * 256; e += blockDim.x) {
-        const int r = e >> 8, c = e & 255, i = c & 127;
-        const float p = scales[r];
-        float v;
-        if (i < CN_CODEBOOK_N) {
-            v = __fmul_rn(g_tbl[i], p);
-            if (c >= 128) v = -v;
-        } else {
-            v = (c == 255) ? -p : p;
-        }
-        lut[e] = v;
-    }
-    __syncthreads();
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        float g = grad[i];
-        for (int r = 0; r < nranks; ++r)
-            if (r != my_rank) g += lut[(r << 8) + codes[(size_t)r * n + i]];
-        grad[i] = g;
-    }
-}
-
-// The same for a packed buffer of several tensors (segments), each coded with its own scale per rank.  A rank's block of
+// rank with that rank's scale; peers are added in rank order (the order of the reference's loop).  The gradients of
+// several tensors (segments) lie back to back in one buffer, each coded with its own scale per rank.  A rank's block of
 // the gathered buffer is [codes of all segments][one scale per segment]; seg_end[s] is the end offset of segment s.
 #define CN_SYNC_MAX_SEGMENTS 8
 struct SegParams {
@@ -359,35 +332,7 @@ extern "C" int cn_rmsprop_update(cn_context *ctx, float *d_rms, const float *d_g
 }
 
 // comm-side pieces live in cn_comm.cu
-int cn_comm_gather_codes(cn_context *ctx, uint8_t *d_codes_all, int64_t n, float *d_scales, void *stream);
 int cn_comm_info(cn_context *ctx, int *rank, int *nranks, float **d_scales);
-
-extern "C" int cn_grad_sync_8bit(cn_context *ctx, float *d_grad, int64_t n, float fixed_precision, void *stream)
-{
-    CN_REQUIRE(ctx && n >= 0 && (n == 0 || d_grad), CN_ERR_ARG, "cn_grad_sync_8bit: bad argument");
-    int rank = 0, G = 1;
-    float *scales = nullptr;
-    cn_comm_info(ctx, &rank, &G, &scales);
-    if (G == 1 || n == 0) return CN_OK;
-    void *buf = nullptr;
-    int st = cn_gemm_scratch(ctx, CN_GEMM_SLOT_EXCHANGE, (size_t)G * n, &buf);
-    if (st != CN_OK) return st;
-    uint8_t *codes = (uint8_t *)buf;
-    // scale: this rank's absmax (gathered with the codes), or the caller's fixed value on every rank
-    if (fixed_precision > 0.0f) {
-        if ((st = cn_fill_f32(ctx, scales, G, fixed_precision, stream)) != CN_OK) return st;
-        if ((st = cn_compress_8bit_dp(ctx, d_grad, scales + rank, n, codes + (size_t)rank * n, stream)) != CN_OK) return st;
-    } else {
-        if ((st = cn_absmax_compress_8bit(ctx, d_grad, n, scales + rank, codes + (size_t)rank * n, stream)) != CN_OK) return st;
-    }
-    if ((st = cn_comm_gather_codes(ctx, codes, n, fixed_precision > 0.0f ? nullptr : scales, stream)) != CN_OK) return st;
-    int64_t blocks = (n + 511) / 512, cap = (int64_t)ctx->sm_count * 4;
-    cn_decode_sum_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 512, (size_t)G * 256 * sizeof(float), cn_stream(stream)>>>(
-        d_grad, codes, scales, ctx->d_tbl, n, G, rank);
-    CN_CUDA(cudaGetLastError());
-    cn_count_launch();
-    return CN_OK;
-}
 
 int cn_comm_gather_blocks(cn_context *ctx, uint8_t *d_blocks, size_t block_bytes, void *stream);
 int cn_comm_push_area(cn_context *ctx, size_t block_bytes, void *stream, uint8_t **blocks);
@@ -395,6 +340,8 @@ int cn_comm_push_blocks(cn_context *ctx, uint8_t *blocks, size_t block_bytes, vo
 
 // Several tensors that lie back to back in one buffer (the gradients of all layers of a step), each coded with its own
 // scale exactly as cn_grad_sync_8bit would code it alone, but exchanged with ONE all-gather and summed in ONE pass.
+extern "C" int cn_grad_sync_8bit(cn_context *ctx, float *d_grad, int64_t n, float fixed_precision, void *stream);
+
 static int grad_sync_multi_impl(cn_context *ctx, float *d_grad, const int64_t *segment_sizes, int num_segments, float fixed_precision,
                                 float *d_rms, float *d_w, float rms_multiplier, float learning_rate, void *stream)
 {
@@ -469,6 +416,12 @@ static int grad_sync_multi_impl(cn_context *ctx, float *d_grad, const int64_t *s
     CN_CUDA(cudaGetLastError());
     cn_count_launch();
     return CN_OK;
+}
+
+extern "C" int cn_grad_sync_8bit(cn_context *ctx, float *d_grad, int64_t n, float fixed_precision, void *stream)
+{
+    CN_REQUIRE(ctx && n >= 0 && (n == 0 || d_grad), CN_ERR_ARG, "cn_grad_sync_8bit: bad argument");
+    return grad_sync_multi_impl(ctx, d_grad, &n, 1, fixed_precision, nullptr, nullptr, 0.f, 0.f, stream);
 }
 
 extern "C" int cn_grad_sync_8bit_multi(cn_context *ctx, float *d_grad, const int64_t *segment_sizes, int num_segments,
