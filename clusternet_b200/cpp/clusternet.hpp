@@ -514,7 +514,8 @@ private:
         const bool sharded = EVERY_RANK_HOLDS_DATA && method != Single_GPU && nranks > 1;
         bcast_ = method != Single_GPU && nranks > 1 && !sharded;
         root_ = !bcast_ || rank == 0;
-        const int flags = sharded ? CN_BATCH_SHARDED_UPLOAD : 0;
+        // two uploads in flight: with many ranks one upload's exchanges can outlast a short step
+        const int flags = sharded ? (CN_BATCH_SHARDED_UPLOAD | CN_BATCH_LOOKAHEAD) : 0;
         BATCH_SIZE = batch_size;
         BATCH_SIZE_CV = cv_batch_size;
         cn_detail::cuda(cudaMalloc((void **)&d_hdr_, 8 * sizeof(float)));
