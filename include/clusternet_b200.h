@@ -417,7 +417,8 @@ int cn_grad_sync_8bit_rmsprop(cn_context *ctx, float *d_grad, const int64_t *seg
  * block straight into every peer's memory (one kernel: "your area may be written" / 16-byte stores over NVLink / "my block
  * has arrived", every wait bounded and reported by cn_gemm_check_status as CN_ERR_TIMEOUT) - one NVLink hop instead of
  * the steps of a ring, and no library launch.  on == 0: ncclAllGather.  The results are identical bit for bit.  Call it
- * on every rank alike.  The reference sends its codes with MPI_Isend / MPI_Recv, rank to rank (source/Layer.cpp:364-390). */
+ * on every rank alike.  After a CN_ERR_TIMEOUT (a peer never took part) the ranks' exchange counters no longer agree:
+ * re-create the communicator (cn_comm_destroy + cn_comm_init_rank), as after cn_comm_sync gave up on a collective.  The reference sends its codes with MPI_Isend / MPI_Recv, rank to rank (source/Layer.cpp:364-390). */
 int cn_comm_set_push_exchange(cn_context *ctx, int on);
 
 /* ---------------------------------------------------------------------------------------------
