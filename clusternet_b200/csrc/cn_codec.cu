@@ -451,22 +451,30 @@ __device__ __forceinline__ void ring_build_tables(RingTables &t, int tid, bool u
     __syncthreads();
 }
 
-// Grid-wide barrier of a cooperative launch (all CTAs resident): every CTA adds one to a counter that only ever grows
-// and waits, with a clock limit, until it has reached `target` (the host keeps the running total).  A wait that runs out
-// records status 13 and lets the CTA go on, so the kernel always ends; its output is then undefined.
-__device__ __forceinline__ void cdc_grid_barrier(unsigned long long *counter, unsigned long long target, unsigned int *status)
+// Grid-wide barrier of a cooperative launch (all CTAs resident).  Two words in device memory, nothing on the host, so a
+// launch that was recorded in a CUDA graph can be replayed: every CTA reads the generation, adds one to the arrival
+// count, and the CTA that arrives last clears the count and advances the generation, which releases the others.  The wait
+// has a clock limit; a wait that runs out records status 13 and lets the CTA go on, so the kernel always ends (its
+// output is then undefined).  One kernel at a time may use a pair of words (launches of one context are stream-ordered).
+__device__ __forceinline__ void cdc_grid_barrier(unsigned int *arrive, unsigned int *generation, unsigned int *status)
 {
     __syncthreads();
     if (threadIdx.x == 0) {
+        unsigned int gen, seen;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(gen) : "l"(generation) : "memory");
         __threadfence();
-        atomicAdd(counter, 1ULL);
-        const long long t0 = clock64();
-        for (;;) {
-            unsigned long long seen;
-            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(counter) : "memory");
-            if (seen >= target) break;
-            if (clock64() - t0 > RING_WAIT_LIMIT) { if (status) atomicMax(status, 13u); break; }
-            __nanosleep(40);
+        if (atomicAdd(arrive, 1u) == gridDim.x - 1) {
+            *reinterpret_cast<volatile unsigned int *>(arrive) = 0u;
+            __threadfence();
+            atomicAdd(generation, 1u);
+        } else {
+            const long long t0 = clock64();
+            for (;;) {
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(generation) : "memory");
+                if (seen != gen) break;
+                if (clock64() - t0 > RING_WAIT_LIMIT) { if (status) atomicMax(status, 13u); break; }
+                __nanosleep(40);
+            }
         }
         __threadfence();
     }
@@ -487,8 +495,8 @@ template <int SCALE>
 __global__ void __launch_bounds__(RING_THREADS, 2)
 cn_compress_ring_kernel(const float *__restrict__ A, float precision_arg, float *__restrict__ d_precision,
                         int64_t n, uint8_t *__restrict__ out, const __grid_constant__ RingConst rc, unsigned int *status,
-                        int tile_groups, int tiles_per_cta, float *__restrict__ partials, unsigned long long *barrier_counter,
-                        unsigned long long barrier_target, int input_ready_before_predecessor)
+                        int tile_groups, int tiles_per_cta, float *__restrict__ partials, unsigned int *barrier_words,
+                        int input_ready_before_predecessor)
 {
     extern __shared__ __align__(128) uint8_t ring_smem[];
     __shared__ RingTables t;
@@ -571,7 +579,7 @@ cn_compress_ring_kernel(const float *__restrict__ A, float precision_arg, float 
             for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
             if (tid == 0) partials[blockIdx.x] = m;
         }
-        cdc_grid_barrier(barrier_counter, barrier_target, status);
+        cdc_grid_barrier(barrier_words, barrier_words + 1, status);
     }
     // fill the ring before anything else: the first loads are in flight while the tables are built
     if (tid == 0 && !(SCALE == RING_SCALE_DEVICE && input_ready_before_predecessor)) fill_ring();
@@ -1133,9 +1141,8 @@ static int compress_impl(cn_context *ctx, const float *d_A, float precision, flo
         // whole tiles save the per-thread bounds tests: take them when the busiest CTA gets at most 2 % more work than with
         // the exactly balanced size
         if ((int64_t)tiles_per_cta * max_groups * 100 <= (int64_t)tiles_per_cta * tile_groups * 102) tile_groups = (int)max_groups;
-        unsigned long long *counter = reinterpret_cast<unsigned long long *>(ctx->d_ticket + 4);   // bytes 16..23 of the ticket block
+        unsigned int *barrier_words = ctx->d_ticket + 4;   // words 4, 5 of the ticket block: arrival count, generation
         if (scale_mode == RING_SCALE_ABSMAX) {
-            const unsigned long long target = ctx->grid_barrier_total + (unsigned long long)grid;
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((unsigned)grid);
             cfg.blockDim = dim3(RING_THREADS);
@@ -1147,14 +1154,13 @@ static int compress_impl(cn_context *ctx, const float *d_A, float precision, flo
             cfg.attrs = attr;
             cfg.numAttrs = 1;
             CN_CUDA(cudaLaunchKernelEx(&cfg, cn_compress_ring_kernel<RING_SCALE_ABSMAX>, d_A, 0.f, d_precision, n, d_codes, rc, d_status, tile_groups,
-                                       tiles_per_cta, ctx->d_partials, counter, target, 0));
-            ctx->grid_barrier_total = target;   // only a launch that was accepted moves the counter
+                                       tiles_per_cta, ctx->d_partials, barrier_words, 0));
         } else if (scale_mode == RING_SCALE_DEVICE) {
             CN_CUDA(launch_pdl(cn_compress_ring_kernel<RING_SCALE_DEVICE>, grid, RING_THREADS, smem, s, d_A, 0.f, d_precision, n, d_codes, rc, d_status,
-                               tile_groups, tiles_per_cta, (float *)nullptr, (unsigned long long *)nullptr, 0ULL, after_own_absmax));
+                               tile_groups, tiles_per_cta, (float *)nullptr, (unsigned int *)nullptr, after_own_absmax));
         } else {
             CN_CUDA(launch_pdl(cn_compress_ring_kernel<RING_SCALE_HOST>, grid, RING_THREADS, smem, s, d_A, precision, (float *)nullptr, n, d_codes, rc,
-                               d_status, tile_groups, tiles_per_cta, (float *)nullptr, (unsigned long long *)nullptr, 0ULL, 0));
+                               d_status, tile_groups, tiles_per_cta, (float *)nullptr, (unsigned int *)nullptr, 0));
         }
         cn_count_launch();
         return CN_OK;

@@ -55,8 +55,7 @@ struct cn_context {
     uint32_t codec_cache_X[128];
     // reduction scratch: per-CTA partial maxima + a ticket counter that the last CTA resets
     float *d_partials = nullptr;
-    unsigned int *d_ticket = nullptr;   // 64 bytes: word 0 = absmax ticket, bytes 16..23 = grid-barrier counter of the fused compressor
-    unsigned long long grid_barrier_total = 0;   // value that counter reaches after the launches queued so far
+    unsigned int *d_ticket = nullptr;   // 64 bytes: word 0 = absmax ticket, words 4 and 5 = grid barrier of the fused compressor (arrivals, generation)
     // GEMM
     cn_gemm_workspace *gemm = nullptr;
     const char *gemm_last_path = "";

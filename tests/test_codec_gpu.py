@@ -87,8 +87,8 @@ def test_compress_config2_full_size(ctx):
 @pytest.mark.parametrize("n", [0, 1, 3, 4, 5, 2047, 8192, 100003, 1 << 20, (4 << 20) - 1, 4096 * 4096 + 2])
 def test_fused_absmax_compress_equals_the_two_calls(ctx, n):
     """cn_absmax_compress_8bit (one cooperative launch: reduce, grid barrier, code) gives the scale and the codes of
-    cn_absmax_f32 followed by cn_compress_8bit_dp, on consecutive calls (the barrier counter only ever grows) and for a
-    buffer that is not 16-byte aligned (two-call fallback)."""
+    cn_absmax_f32 followed by cn_compress_8bit_dp, on consecutive calls and for a buffer that is not 16-byte aligned
+    (two-call fallback)."""
     rng = np.random.default_rng(n + 1)
     for rep in range(3):
         x = torch.from_numpy((rng.standard_normal(n + 1) * rng.uniform(1e-3, 30)).astype(np.float32)).cuda()
@@ -103,6 +103,38 @@ def test_fused_absmax_compress_equals_the_two_calls(ctx, n):
     if n:
         p = float(pm.item())
         assert np.array_equal(got.cpu().numpy(), oracle.compress(ctx.codebook, a.cpu().numpy(), p))
+
+
+def test_fused_absmax_compress_replays_from_a_cuda_graph(ctx):
+    """The one-launch form keeps its grid barrier's state on the device only, so a recorded launch can be replayed: every
+    replay must wait for ITS maxima.  The data shrink from replay to replay - a barrier that let a CTA through early would
+    fold a stale, larger maximum of the replay before into the scale."""
+    n = 1_000_003 + 1                                     # the one-launch form (at most 4 Mi elements), with a ragged end
+    rng = np.random.default_rng(99)
+    base = torch.from_numpy((rng.standard_normal(n) * 5).astype(np.float32)).cuda()
+    a = base.clone()
+    codes = torch.empty(n, dtype=torch.uint8, device="cuda")
+    scale = torch.zeros(1, device="cuda")
+    cn.check(ctx.lib.cn_absmax_compress_8bit(ctx.h, a.data_ptr(), n, scale.data_ptr(), codes.data_ptr(), ctx.stream_ptr()))   # warm-up
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        cn.check(ctx.lib.cn_absmax_compress_8bit(ctx.h, a.data_ptr(), n, scale.data_ptr(), codes.data_ptr(),
+                                                 ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    for rep, f in enumerate((1.0, 0.5, 0.01, 3.0, 0.001)):
+        a.copy_(base * f)
+        g.replay()
+        torch.cuda.synchronize()
+        pm = ctx.absmax(a)
+        want = ctx.compress(a, pm)
+        torch.cuda.synchronize()
+        assert scale.item() == pm.item(), (rep, f)
+        assert torch.equal(codes, want), (rep, f)
+    # ... and calls outside the graph still work afterwards
+    got, sc = ctx.absmax_compress(a)
+    torch.cuda.synchronize()
+    assert sc.item() == pm.item() and torch.equal(got, want)
+    ctx.gemm_check()
 
 
 def test_unaligned_buffers_take_scalar_path(ctx):
