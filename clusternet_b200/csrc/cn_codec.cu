@@ -708,6 +708,161 @@ cn_compress_ring_kernel(const float *__restrict__ A, float precision_arg, float 
     }
 }
 
+// ---- code and push in one launch (the gradient exchange of small tensors)
+//
+// scale = absmax(A); codes = compress(A, scale) as in the fused form above, but the codes (and the scale) go to this
+// rank's block AND to the same place in every peer's area, framed by the two flag exchanges of the pushed block exchange:
+// CTA 0 tells the peers "my area may be written" when the kernel starts (everything queued before it has finished), every
+// CTA waits (bounded) for the peers' flags after the grid barrier - the first pass hides the round trip - and the CTA that
+// finishes last tells the peers "my block has arrived" and waits for theirs.  Tensors of this size (at most 4 Mi
+// elements) stay in L2 between the passes, so the second pass reads with plain loads.  Stores to the peers are 4-byte
+// words that a warp lays down 128 contiguous bytes at a time; no multicast.
+__device__ __forceinline__ bool push_wait_flags(const unsigned int *local_flags, int slot, int nranks, int my_rank, unsigned int epoch,
+                                                unsigned int *status)
+{
+    bool ok = true;
+    const int r = threadIdx.x;
+    if (r < nranks && r != my_rank) {
+        const volatile unsigned int *f = local_flags + slot * nranks + r;
+        const long long t0 = clock64();
+        while ((int)(*f - epoch) < 0) {
+            if (clock64() - t0 > RING_WAIT_LIMIT) { atomicMax(status, 10u); ok = false; break; }
+            __nanosleep(100);
+        }
+        __threadfence_system();
+    }
+    return __syncthreads_and(ok);
+}
+
+__global__ void __launch_bounds__(RING_THREADS, 2)
+cn_absmax_compress_push_kernel(const float *__restrict__ A, int64_t n, float *__restrict__ scale_out, uint8_t *__restrict__ out,
+                               const __grid_constant__ RingConst rc, unsigned int *status, float *__restrict__ partials,
+                               unsigned int *barrier_words, const __grid_constant__ cn_codec_push cp)
+{
+    __shared__ RingTables t;
+    __shared__ float s_red[RING_THREADS / 32];
+    __shared__ int s_last;
+    const int tid = threadIdx.x;
+    if (tid < 128) {
+        t.T[tid] = rc.thr[tid];
+        t.lc[tid] = rc.lc[tid];
+    }
+    const unsigned int epoch = *reinterpret_cast<volatile unsigned int *>(cp.state) + 1u;   // advanced by the last CTA, at the very end
+    if (blockIdx.x == 0 && tid < cp.nranks && tid != cp.my_rank) {
+        __threadfence_system();
+        *reinterpret_cast<volatile unsigned int *>(cp.peer_flags[tid] + cp.slot * cp.nranks + cp.my_rank) = epoch;
+    }
+    const int64_t groups_total = n >> 2, n4 = groups_total << 2;
+    const int64_t stride = (int64_t)gridDim.x * RING_THREADS, g0 = (int64_t)blockIdx.x * RING_THREADS + tid;
+    const float4 *A4 = reinterpret_cast<const float4 *>(A);
+    // pass 1: maximum of |A|
+    float m = -1.0f;   // seed of the reference's reduction (source/basicOps.cu:1079)
+#pragma unroll 4
+    for (int64_t g = g0; g < groups_total; g += stride) {
+        const float4 q = A4[g];
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(q.x), fabsf(q.y)), fmaxf(fabsf(q.z), fabsf(q.w))));
+    }
+    if (blockIdx.x == 0 && tid < (int)(n - n4)) m = fmaxf(m, fabsf(A[n4 + tid]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((tid & 31) == 0) s_red[tid >> 5] = m;
+    __syncthreads();
+    if (tid < 32) {
+        m = tid < RING_THREADS / 32 ? s_red[tid] : -1.0f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (tid == 0) partials[blockIdx.x] = m;
+    }
+    cdc_grid_barrier(barrier_words, barrier_words + 1, status);
+    // every CTA folds the per-CTA maxima (the same values in the same order everywhere)
+    m = -1.0f;
+    for (int i = tid; i < (int)gridDim.x; i += RING_THREADS) m = fmaxf(m, __ldcg(partials + i));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    __syncthreads();   // s_red was read above
+    if ((tid & 31) == 0) s_red[tid >> 5] = m;
+    __syncthreads();
+    m = s_red[0];
+#pragma unroll
+    for (int w = 1; w < RING_THREADS / 32; ++w) m = fmaxf(m, s_red[w]);
+    const float p = m;
+    const uint32_t pb = __float_as_uint(p);
+    const float ap = fabsf(p);
+    const bool p_ok = (ap >= 7.8886090522101181e-31f) && (ap <= 1.2676506002282294e30f);
+    if (tid < 128) {
+        // smallest |x| with fl(|x|/|p|) >= T for each of the 127 thresholds (see cn_compress_kernel)
+        uint32_t xb = 0xffffffffu;
+        bool good = true;
+        if (tid < CN_NUM_THR && p_ok) {
+            const float T = __uint_as_float(rc.thr[tid]);
+            xb = __float_as_uint(__fmul_rn(T, ap));
+            int down = 0;
+            for (; down < 6; ++down) {
+                if (xb > 0u && __fdiv_rn(__uint_as_float(xb - 1u), ap) >= T) --xb; else break;
+            }
+            good = down < 6;
+            if (down == 0) {
+                int up = 0;
+                for (; up < 6; ++up) {
+                    if (__fdiv_rn(__uint_as_float(xb), ap) < T) ++xb; else break;
+                }
+                good = up < 6;
+            }
+        }
+        t.X[tid] = good ? xb : 0xfffffffeu;
+    }
+    __syncthreads();
+    ring_build_tables(t, tid, p_ok);
+    const bool fast = t.bad == 0;
+    const uint32_t kadd = t.kadd;
+    const int32_t span = t.span;
+    const uint32_t lut_addr = cdc_smem_u32(t.lut);
+    // the peers' areas may be written once every peer has said so
+    const bool may_write = push_wait_flags(cp.local_flags, cp.slot, cp.nranks, cp.my_rank, epoch, status);
+    if (blockIdx.x == 0 && tid == 0) {
+        *scale_out = p;
+        if (may_write)
+            for (int d = 0; d < cp.ndst; ++d) *cp.scale_dst[d] = p;
+    }
+    // pass 2: code; this CTA's groups in reverse order (most recently read first)
+    uint32_t *out4 = reinterpret_cast<uint32_t *>(out);
+    const int ndst = may_write ? cp.ndst : 0;
+    if (g0 < groups_total) {
+        const int64_t last = g0 + (groups_total - 1 - g0) / stride * stride;
+        for (int64_t g = last; g >= g0; g -= stride) {
+            const float4 q = A4[g];
+            uint32_t w;
+            if (fast) w = (pb >> 31) ? ring_code4<true>(q, pb, kadd, span, lut_addr) : ring_code4<false>(q, pb, kadd, span, lut_addr);
+            else w = pack4(ring_generic(q.x, p, t), ring_generic(q.y, p, t), ring_generic(q.z, p, t), ring_generic(q.w, p, t));
+            out4[g] = w;
+#pragma unroll 1
+            for (int d = 0; d < ndst; ++d) reinterpret_cast<uint32_t *>(cp.codes_dst[d])[g] = w;
+        }
+    }
+    if (blockIdx.x == 0 && tid < (int)(n - n4)) {
+        const float x = A[n4 + tid];
+        const uint8_t c = (uint8_t)(fast ? ring_code(__float_as_uint(x), pb, kadd, span, lut_addr) : ring_generic(x, p, t));
+        out[n4 + tid] = c;
+        for (int d = 0; d < ndst; ++d) cp.codes_dst[d][n4 + tid] = c;
+    }
+    // the CTA that finishes last closes the exchange
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) s_last = (atomicAdd(barrier_words, 1u) == gridDim.x - 1) ? 1 : 0;   // the arrival count is zero again after the barrier
+    __syncthreads();
+    if (!s_last) return;
+    if (tid == 0) *reinterpret_cast<volatile unsigned int *>(barrier_words) = 0u;
+    __threadfence_system();
+    if (may_write && tid < cp.nranks && tid != cp.my_rank)
+        *reinterpret_cast<volatile unsigned int *>(cp.peer_flags[tid] + (cp.slot + 1) * cp.nranks + cp.my_rank) = epoch;
+    if (may_write) push_wait_flags(cp.local_flags, cp.slot + 1, cp.nranks, cp.my_rank, epoch, status);
+    __syncthreads();
+    if (tid == 0) {
+        *cp.state = epoch;
+        __threadfence();
+    }
+}
+
 // kDecompression_8bit (source/clusterKernels.cu:1135-1160): 256-entry table built in the reference's
 // statement order, then out[i] = table[code].
 // vector_ok: 0 = byte by byte; 1 = four codes per load (codes 4-byte, output 16-byte aligned).  When the codes are 16-byte
@@ -1173,6 +1328,53 @@ static int compress_impl(cn_context *ctx, const float *d_A, float precision, flo
     else
         CN_CUDA(launch_pdl(cn_compress_kernel<false>, grid, CODEC_THREADS, 0, s, d_A, precision, (const float *)nullptr, n, d_codes, cc, 0));
     cn_count_launch();
+    return CN_OK;
+}
+
+int cn_absmax_compress_push(cn_context *ctx, const float *d_A, int64_t n, float *d_scale_out, uint8_t *d_codes, const cn_codec_push *push,
+                            void *stream, int *done)
+{
+    *done = 0;
+    CN_REQUIRE(ctx && d_scale_out && push, CN_ERR_ARG, "cn_absmax_compress_push: null argument");
+    if (n < 4 || n > CN_FUSED_ABSMAX_MAX_N || (uintptr_t)d_A % 16 != 0 || (uintptr_t)d_codes % 4 != 0) return CN_OK;
+    for (int d = 0; d < push->ndst; ++d)
+        if ((uintptr_t)push->codes_dst[d] % 4 != 0) return CN_OK;
+    static bool have_occ[64] = {};
+    static int occupancy[64] = {};
+    const int dev = ctx->device;
+    int occ = (dev >= 0 && dev < 64 && have_occ[dev]) ? occupancy[dev] : 0;
+    if (occ == 0) {
+        CN_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, cn_absmax_compress_push_kernel, RING_THREADS, 0));
+        if (dev >= 0 && dev < 64) { have_occ[dev] = true; occupancy[dev] = occ; }
+    }
+    if (occ < 1) return CN_OK;
+    unsigned int *d_status = nullptr;
+    int st = cn_status_block(ctx, &d_status);
+    if (st != CN_OK) return st;
+    RingConst rc;
+    for (int i = 0; i < 128; ++i) { rc.thr[i] = ctx->h_thr[i]; rc.lc[i] = ctx->h_level_codes[i]; rc.X[i] = 0xffffffffu; }
+    rc.x_valid = 0;
+    // cooperative launch: all CTAs resident; four 16-byte groups per thread and pass at least
+    const int64_t groups = n >> 2;
+    int64_t grid = (groups + (int64_t)RING_THREADS * 4 - 1) / ((int64_t)RING_THREADS * 4);
+    const int64_t max_grid = (int64_t)(occ < 2 ? occ : 2) * ctx->sm_count;
+    if (grid > max_grid) grid = max_grid;
+    if (grid > CN_MAX_PARTIALS) grid = CN_MAX_PARTIALS;
+    if (grid < 1) grid = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(RING_THREADS);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = cn_stream(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CN_CUDA(cudaLaunchKernelEx(&cfg, cn_absmax_compress_push_kernel, d_A, n, d_scale_out, d_codes, rc, d_status, ctx->d_partials,
+                               ctx->d_ticket + 4, *push));
+    cn_count_launch();
+    *done = 1;
     return CN_OK;
 }
 

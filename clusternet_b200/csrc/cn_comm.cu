@@ -830,6 +830,29 @@ int cn_comm_push_area(cn_context *ctx, size_t block_bytes, void *stream, uint8_t
     return CN_OK;
 }
 
+int cn_comm_push_params(cn_context *ctx, size_t block_bytes, size_t scale_offset, cn_codec_push *out)
+{
+    cn_comm_state *c = ctx->comm;
+    CN_REQUIRE(c && c->xchg && block_bytes * c->nranks <= c->xchg_bytes && c->xchg_slot >= 0 && c->d_xchg_state && c->d_peer_flags, CN_ERR_ARG,
+               "cn_comm_push_params: no exchange area of this size (cn_comm_push_area first)");
+    CN_COMM_ALIVE(ctx);
+    const size_t off = (size_t)c->rank * block_bytes;
+    out->ndst = 0;
+    for (int p = 1; p < c->nranks; ++p) {   // staggered by rank
+        uint8_t *base = (uint8_t *)c->xchg_peer[(c->rank + p) % c->nranks] + off;
+        out->codes_dst[out->ndst] = base;
+        out->scale_dst[out->ndst] = reinterpret_cast<float *>(base + scale_offset);
+        out->ndst += 1;
+    }
+    out->peer_flags = c->d_peer_flags;
+    out->local_flags = c->flags;
+    out->nranks = c->nranks;
+    out->my_rank = c->rank;
+    out->slot = c->xchg_slot;
+    out->state = c->d_xchg_state;
+    return CN_OK;
+}
+
 // blocks: the area cn_comm_push_area returned for this block size, block [rank] filled; on return (in stream order) every
 // block is filled.
 int cn_comm_push_blocks(cn_context *ctx, uint8_t *blocks, size_t block_bytes, void *stream)

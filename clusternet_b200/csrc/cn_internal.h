@@ -80,3 +80,23 @@ int cn_comm_flag_slots(cn_context *ctx, int count, int *first_slot);
 int cn_comm_flag_barrier(cn_context *ctx, int slot, unsigned int epoch, cudaStream_t s);
 
 static inline cudaStream_t cn_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// Pushed block exchange, seen from the codec: where this rank's codes and scale go in every peer's area, and the flags
+// that frame the stores ("your area may be written" = slot, "my block has arrived" = slot + 1; see cn_push_exchange_kernel).
+struct cn_codec_push {
+    uint8_t *codes_dst[7];
+    float *scale_dst[7];
+    int ndst;
+    unsigned int *const *peer_flags;
+    const unsigned int *local_flags;
+    int nranks, my_rank, slot;
+    unsigned int *state;   // [0] epoch of the last finished exchange
+};
+// scale = absmax(A); codes = compress(A, scale), the codes and the scale stored locally AND in every peer's area, the two
+// flag exchanges included: one cooperative launch.  *done = 0 when the tensor is no case for it (too large, unaligned):
+// nothing was launched and the caller takes the separate calls.
+int cn_absmax_compress_push(cn_context *ctx, const float *d_A, int64_t n, float *d_scale_out, uint8_t *d_codes, const cn_codec_push *push,
+                            void *stream, int *done);
+// Fills the destinations for a block of block_bytes whose codes start at the block's first byte and whose scale lies at
+// scale_offset; only valid for the area cn_comm_push_area returned for that block size.
+int cn_comm_push_params(cn_context *ctx, size_t block_bytes, size_t scale_offset, cn_codec_push *out);

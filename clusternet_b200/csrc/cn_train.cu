@@ -386,9 +386,20 @@ static int grad_sync_multi_impl(cn_context *ctx, float *d_grad, const int64_t *s
     SegParams sp;
     sp.nseg = num_segments;
     int64_t off = 0;
+    bool exchanged = false;
+    if (pushed && num_segments == 1 && fixed_precision <= 0.0f) {
+        // one tensor, scale = its absmax: code and push in ONE launch where the tensor is small enough for that form
+        cn_codec_push cp;
+        if ((st = cn_comm_push_params(ctx, block_bytes, scales_off, &cp)) != CN_OK) return st;
+        int done = 0;
+        if ((st = cn_absmax_compress_push(ctx, d_grad, n, my_scales, mine, &cp, stream, &done)) != CN_OK) return st;
+        exchanged = done != 0;
+    }
     for (int s = 0; s < num_segments; ++s) {
         const int64_t sz = segment_sizes[s];
-        if (fixed_precision > 0.0f) {
+        if (exchanged) {
+            // done above
+        } else if (fixed_precision > 0.0f) {
             st = cn_fill_f32(ctx, my_scales + s, 1, fixed_precision, stream);
             if (st == CN_OK && sz > 0) st = cn_compress_8bit_dp(ctx, d_grad + off, my_scales + s, sz, mine + off, stream);
         } else {
@@ -399,8 +410,10 @@ static int grad_sync_multi_impl(cn_context *ctx, float *d_grad, const int64_t *s
         sp.seg_end[s] = off;
     }
     for (int s = num_segments; s < CN_SYNC_MAX_SEGMENTS; ++s) sp.seg_end[s] = off;
-    st = pushed ? cn_comm_push_blocks(ctx, blocks, block_bytes, stream) : cn_comm_gather_blocks(ctx, blocks, block_bytes, stream);
-    if (st != CN_OK) return st;
+    if (!exchanged) {
+        st = pushed ? cn_comm_push_blocks(ctx, blocks, block_bytes, stream) : cn_comm_gather_blocks(ctx, blocks, block_bytes, stream);
+        if (st != CN_OK) return st;
+    }
     const int vec_ok = ((uintptr_t)d_grad % 16 == 0) && ((uintptr_t)blocks % 16 == 0) &&
                        (!update || ((uintptr_t)d_rms % 16 == 0 && (uintptr_t)d_w % 16 == 0));
     const int64_t work = vec_ok ? (n + 3) / 4 : n;

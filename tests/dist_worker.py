@@ -183,7 +183,8 @@ def run_nccl():
             torch.cuda.synchronize()
             res.append((g2, ctx.lib.cn_kernel_launches() - n0))
         assert torch.equal(res[0][0], res[1][0]), segs2
-        assert res[0][1] == res[1][1] + 1              # the push is a kernel of this library, the gather is not
+        # several tensors: the push is one more kernel of this library (the gather is none); one tensor: coded and pushed in ONE launch
+        assert res[0][1] == res[1][1] + (0 if len(segs2) == 1 else 1), segs2
     cn.check(ctx.lib.cn_comm_set_push_exchange(ctx.h, 1))
     ctx.gemm_check()
     # the exchange with the RMSprop step inside its summing pass == the exchange, then cn_rmsprop_update (bit for bit),
@@ -208,24 +209,30 @@ def run_nccl():
             outs.append((g3.clone(), r3.clone(), w3.clone()))
         for a, b in zip(outs[0], outs[1]):
             assert torch.equal(a, b), (segs3, shift)
-    gg = torch.from_numpy(grads[rank][:5000].copy()).cuda()
-    seg1 = (ctypes.c_int64 * 1)(5000)
-    side = torch.cuda.Stream()
-    with torch.cuda.stream(side):
-        cn.check(ctx.lib.cn_grad_sync_8bit_multi(ctx.h, gg.data_ptr(), seg1, 1, 0.0, ctypes.c_void_p(side.cuda_stream)))
+    # one tensor with its own absmax goes through ONE launch that codes and pushes; recorded in a CUDA graph and replayed
+    # on data that change from replay to replay (the exchange's epochs and the kernel's grid barrier live on the device)
+    nrep = 300007
+    src = torch.from_numpy(np.random.default_rng(200 + rank).standard_normal(nrep).astype(np.float32)).cuda()
+    gg = src.clone()
+    seg1 = (ctypes.c_int64 * 1)(nrep)
+    n0 = ctx.lib.cn_kernel_launches()
+    cn.check(ctx.lib.cn_grad_sync_8bit_multi(ctx.h, gg.data_ptr(), seg1, 1, 0.0, ctx.stream_ptr()))
+    assert ctx.lib.cn_kernel_launches() - n0 == 2          # code + push, decode + sum
     torch.cuda.synchronize()
-    once = gg.clone()
-    gg.copy_(torch.from_numpy(grads[rank][:5000].copy()).cuda())
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph, capture_error_mode="thread_local"):
         cn.check(ctx.lib.cn_grad_sync_8bit_multi(ctx.h, gg.data_ptr(), seg1, 1, 0.0, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
-    for rep in range(3):
-        gg.copy_(torch.from_numpy(grads[rank][:5000].copy()).cuda())
+    for rep, f in enumerate((1.0, 0.25, 3.0, 0.01)):
+        want_g = src * f
+        cn.check(ctx.lib.cn_comm_set_push_exchange(ctx.h, 0))
+        cn.check(ctx.lib.cn_grad_sync_8bit_multi(ctx.h, want_g.data_ptr(), seg1, 1, 0.0, ctx.stream_ptr()))      # NCCL gather, call by call
+        cn.check(ctx.lib.cn_comm_set_push_exchange(ctx.h, 1))
+        gg.copy_(src * f)
         torch.cuda.synchronize()
         dist.barrier()
         graph.replay()
         torch.cuda.synchronize()
-        assert torch.equal(gg, once), rep
+        assert torch.equal(gg, want_g), rep
     ctx.gemm_check()
     # TdotMPI with a sharded B: the row-major batch as a transposed operand, through the fused gather
     M, K, N = 128, 2048, 2048 + 8 * world
