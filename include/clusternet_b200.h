@@ -416,7 +416,8 @@ int cn_grad_sync_8bit_rmsprop(cn_context *ctx, float *d_grad, const int64_t *seg
 /* How cn_grad_sync_8bit_multi moves its blocks.  on != 0 (the default with one process per GPU): every rank stores its
  * block straight into every peer's memory (one kernel: "your area may be written" / 16-byte stores over NVLink / "my block
  * has arrived", every wait bounded and reported by cn_gemm_check_status as CN_ERR_TIMEOUT) - one NVLink hop instead of
- * the steps of a ring, and no library launch.  on == 0: ncclAllGather.  The results are identical bit for bit.  Call it
+ * the steps of a ring, and no library launch; a single tensor of up to 4 Mi elements with its own absmax is coded and
+ * pushed by ONE kernel.  on == 0: ncclAllGather.  The results are identical bit for bit.  Call it
  * on every rank alike.  After a CN_ERR_TIMEOUT (a peer never took part) the ranks' exchange counters no longer agree:
  * re-create the communicator (cn_comm_destroy + cn_comm_init_rank), as after cn_comm_sync gave up on a collective.  The reference sends its codes with MPI_Isend / MPI_Recv, rank to rank (source/Layer.cpp:364-390). */
 int cn_comm_set_push_exchange(cn_context *ctx, int on);
