@@ -24,6 +24,23 @@ def test_library_exports_every_declared_symbol(built_lib):
     assert built_lib.cn_status_string(5).decode() == "CN_ERR_TIMEOUT"
 
 
+def test_python_constants_equal_the_header(built_lib):
+    """The ctypes binding repeats the header's status codes and option bits by value: they must not drift apart."""
+    import re
+    text = open(os.path.join(ROOT, "include", "clusternet_b200.h")).read()
+    defines = {m.group(1): int(m.group(2), 0) for m in re.finditer(r"^#define\s+(CN_[A-Z0-9_]+)\s+(\d+|0x[0-9a-fA-F]+)\s*$", text, re.M)}
+    enums = {m.group(1): int(m.group(2)) for m in re.finditer(r"^\s+(CN_[A-Z0-9_]+)\s*=\s*(\d+)\s*,?", text, re.M)}
+    for name in ("KEEP_ROW_MAJOR", "NO_COL_MAJOR", "SHARDED_UPLOAD", "PUSH_BY_KERNEL", "LOOKAHEAD"):
+        assert defines["CN_BATCH_" + name] == getattr(_lib, "BATCH_" + name), name
+    bits = [defines["CN_BATCH_" + n] for n in ("KEEP_ROW_MAJOR", "NO_COL_MAJOR", "SHARDED_UPLOAD", "PUSH_BY_KERNEL", "LOOKAHEAD")]
+    assert len(set(bits)) == 5 and all(b & (b - 1) == 0 for b in bits)        # distinct single bits
+    for name in ("CN_OK", "CN_ERR_ARG", "CN_ERR_SHAPE", "CN_ERR_CUDA", "CN_ERR_NCCL", "CN_ERR_TIMEOUT", "CN_ERR_UNSUPPORTED", "CN_ERR_NOMEM"):
+        assert enums[name] == getattr(_lib, name), name
+        assert built_lib.cn_status_string(enums[name]).decode() == name
+    for name in ("3XTF32", "TF32", "FP32_SIMT"):
+        assert enums.get("CN_GEMM_" + name, defines.get("CN_GEMM_" + name)) == getattr(_lib, "GEMM_" + name), name
+
+
 def test_codebook_loader_reads_raw_and_hdf5_container(built_lib, codebook, tmp_path):
     tbl = np.zeros(126, np.float32)
     raw = os.path.join(ROOT, "tests", "golden", "codebook_126.f32")
